@@ -1,0 +1,134 @@
+// Host-side plumbing behind the C ABI: thread-local error text, device checks,
+// launch counters, and the window -> tile-range / mask-packing helpers that need
+// no GPU.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "att3_abi_internal.h"
+
+namespace att3 {
+
+static thread_local char g_err[512] = "";
+static std::atomic<unsigned long long> g_launches[4];
+
+int set_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int set_cuda_error(cudaError_t e, const char* where) {
+    return set_error(ATT3_ERR_CUDA, "%s: %s", where, cudaGetErrorString(e));
+}
+
+bool require_sm100(const char* who) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        set_error(ATT3_ERR_UNSUPPORTED, "%s: tensor-core path unavailable, no CUDA device (%s)", who,
+                  cudaGetErrorString(e));
+        return false;
+    }
+    int major = 0;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (major != 10) {
+        set_error(ATT3_ERR_UNSUPPORTED,
+                  "%s: tensor-core path unavailable on this device (built for sm_100a, device is sm_%d0)", who,
+                  major);
+        return false;
+    }
+    return true;
+}
+
+int sm_count() {
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != cached_dev) {
+        cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+        cached_dev = dev;
+    }
+    return cached > 0 ? cached : 148;
+}
+
+void count_launch(int which, int n) {
+    if (which >= 0 && which < 4) g_launches[which] += n;
+}
+
+}  // namespace att3
+
+extern "C" const char* att3_last_error(void) { return att3::g_err; }
+
+extern "C" int att3_abi_version(void) { return 1; }
+
+extern "C" unsigned long long att3_launch_count(int which) {
+    return (which >= 0 && which < 4) ? att3::g_launches[which].load() : 0ull;
+}
+
+// Rows and columns a windowed single-gather work item has to visit.  The
+// interval starts on the first visible key rather than on a tile boundary, ends
+// are exclusive, and the column end is rounded up to a multiple of bk counted
+// from the start, so padding never widens the set of visited real keys.
+//   side 0 (query is anchor a): rows and cols are both (a - w, a].
+//   side 1 (a is a key, queries are rows): rows [a, a + w); a row block at j0
+//          needs cols (j0 - w, min(j0 + bj, a + w, N)).
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+static void row_range(int side, int a, int N, int w, int* lo, int* hi) {
+    if (w <= 0) { *lo = 0; *hi = N; return; }
+    int l = side == 0 ? a - w + 1 : a;
+    int h = side == 0 ? a + 1 : a + w;
+    *lo = l < 0 ? 0 : l;
+    *hi = h > N ? N : h;
+}
+
+static void col_range(int side, int a, int j0, int bj, int N, int w, int bk, int* lo, int* hi) {
+    if (w <= 0) { *lo = 0; *hi = ceil_div(N, bk) * bk; return; }
+    int l = side == 0 ? a - w + 1 : j0 - w + 1;
+    int h = side == 0 ? a + 1 : j0 + bj;
+    if (side == 1 && h > a + w) h = a + w;
+    if (l < 0) l = 0;
+    if (h > N) h = N;
+    *lo = l;
+    *hi = l + ceil_div(h - l, bk) * bk;
+}
+
+extern "C" int att3_sg_tile_ranges(int N, int window, int a, int side, int bj, int bk, int* out, int max_out) {
+    if (N <= 0 || a < 0 || a >= N || (side != 0 && side != 1) || bj <= 0 || bk <= 0 || (max_out > 0 && !out))
+        return -1;
+    int lo, hi, n = 0;
+    row_range(side, a, N, window, &lo, &hi);
+    for (int j0 = lo; j0 < hi; j0 += bj, ++n) {
+        if (n < max_out) {
+            int kl, kh;
+            col_range(side, a, j0, bj, N, window, bk, &kl, &kh);
+            out[3 * n] = j0;
+            out[3 * n + 1] = kl;
+            out[3 * n + 2] = kh;
+        }
+    }
+    return n;
+}
+
+extern "C" uint32_t att3_pack_mask32(const uint8_t* row, int lim) {
+    uint32_t bits = 0;
+    if (lim > 32) lim = 32;
+    int t = 0;
+    // Byte loads until the pointer is 4-byte aligned, then whole words that lie
+    // entirely inside [row, row + lim), then the tail.
+    for (; t < lim && ((reinterpret_cast<uintptr_t>(row + t)) & 3u); ++t)
+        if (row[t]) bits |= 1u << t;
+    for (; t + 4 <= lim; t += 4) {
+        uint32_t w;
+        memcpy(&w, row + t, 4);
+        for (int b = 0; b < 4; ++b)
+            if ((w >> (8 * b)) & 0xFFu) bits |= 1u << (t + b);
+    }
+    for (; t < lim; ++t)
+        if (row[t]) bits |= 1u << t;
+    return bits;
+}

@@ -1,0 +1,177 @@
+/*
+ * att3_b200.h -- C ABI of the sm_100a hypergraph-attention (triplet) kernels.
+ *
+ * This is the boundary a host binding (pybind, ctypes, cgo, ...) links against:
+ * plain device pointers, sizes and a stream, int status codes, no torch types.
+ * It replaces the device half of the reference's pybind module
+ * att3ntion._cuda_kernels (cpp/cuda_bindings.cpp:30-233, declarations in
+ * cpp/cuda_bindings.h:57-156).  The caller owns every buffer: the reference
+ * allocates outputs inside its host launchers (cuda/forward.cu:1678-1683); here
+ * the binding allocates and passes them in, so nothing in this library calls
+ * an allocator.
+ *
+ * Conventions
+ *   - All activations are contiguous BF16, laid out [B, H, N, D]; statistics
+ *     m, l are contiguous FP32 [B, H, N].  m is the running maximum of the
+ *     scaled score (ATT3_NEG_INF for a query with no visible pair), l the sum
+ *     of exp(score - m) (0 for such a query), LSE = m + log(l)
+ *     (cpp/cuda_bindings.h:59, cuda/common.cuh:17-24).
+ *   - mask, where accepted, is a contiguous byte array [B, N, N] (non-zero =
+ *     visible) or NULL.  A pair (j, k) is live for anchor a iff mask[b,a,j] and
+ *     mask[b,a,k] (cuda/forward.cu:33-46).
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it
+ *     and no entry point synchronises the host.
+ *   - Every function returns ATT3_OK or an ATT3_ERR_* code; the message of the
+ *     last failure on the calling thread is att3_last_error().
+ *   - Pointers must be device pointers valid on the current device.
+ */
+#ifndef ATT3_B200_H
+#define ATT3_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ATT3_OK 0
+#define ATT3_ERR_INVALID 1     /* bad argument: shape, alignment, null pointer, unsupported value */
+#define ATT3_ERR_CUDA 2        /* a CUDA runtime call failed; message carries cudaGetErrorString */
+#define ATT3_ERR_UNSUPPORTED 3 /* device is not sm_100 or lacks the shared memory the kernel needs */
+#define ATT3_ERR_WORKSPACE 4   /* workspace pointer missing or smaller than *_workspace_bytes() */
+#define ATT3_ERR_TIMEOUT 5     /* a bounded device-side wait ran out (see att3_device_status) */
+
+#define ATT3_NEG_INF (-1e30f)  /* cuda/common.cuh:24 */
+
+/* Message of the last error raised on this thread ("" if none).  Replaces the
+ * TORCH_CHECK exceptions of the reference launchers (cuda/forward.cu:1609-1653). */
+const char* att3_last_error(void);
+
+/* ABI revision; bumped when a signature below changes. */
+int att3_abi_version(void);
+
+/* Every device-side wait in these kernels (on an mbarrier that a tensor-core
+ * commit arrives on) has an iteration limit; a wait that runs out sets a sticky
+ * status word on the device and the kernel leaves through its normal exit, so
+ * the context stays usable.  This call synchronises `stream`, reads and clears
+ * the word of the current device and returns ATT3_OK or ATT3_ERR_TIMEOUT.  The
+ * reference has no counterpart (its kernels have no device-side waits). */
+int att3_device_status(void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Single query gather:  Y[i] = sum_{j,k} softmax_{j,k}(Q_i.R_j.S_k/sqrt(D)) Vr[j] Vs[k]
+ *
+ * One pair of entry points covers both reference operators:
+ *   Hkv == Hq : single_gather_{forward,backward}_cuda
+ *               (cuda/forward.cu:1666-1719, cuda/backward.cu:2248-2353)
+ *   Hkv == 1  : single_gather_shared_{forward,backward}_cuda
+ *               (cuda/forward.cu:1723-1760, cuda/backward.cu:2512-2582)
+ * Q, Y, dY, dQ are [B,Hq,N,D]; R, S, Vr, Vs and their gradients [B,Hkv,N,D].
+ * Hq must be a multiple of Hkv; query head h reads KV head h / (Hq/Hkv).
+ *
+ * window > 0 : equal causal window on both key axes, query i sees keys in
+ *              (i - window, i] (cuda/common.cuh:50-85); 1 <= window <= 128.
+ *              mask (optional) may only remove keys inside the window.
+ * window == 0: every key is a candidate; visibility comes from mask alone
+ *              (NULL = all visible).
+ * D is 64 or 128 and N a multiple of 16, as in single_gather_check
+ * (cuda/forward.cu:1609-1631).
+ *
+ * q_begin: queries with index < q_begin are not computed (their Y/m/l/dQ rows
+ *          are left untouched) but their rows still act as keys.  A rank that
+ *          owns query rows [q_begin, N) of a longer sequence passes the
+ *          (window-1)-row key halo in front of its rows this way.  0 = all.
+ * ------------------------------------------------------------------------- */
+
+/* Scratch bytes att3_sg_backward needs for these sizes (FP32 key-gradient
+ * partials that are reduced over heads and query blocks).  Forward needs none. */
+size_t att3_sg_backward_workspace_bytes(int B, int Hq, int Hkv, int N, int D, int window);
+
+int att3_sg_forward(const void* Q, const void* R, const void* S, const void* Vr, const void* Vs,
+                    const uint8_t* mask, void* Y, float* m, float* l,
+                    int B, int Hq, int Hkv, int N, int D, int window, int q_begin, void* stream);
+
+/* dR, dS, dVr, dVs come back reduced over the query heads of each KV head
+ * ([B,Hkv,N,D], one BF16 rounding after the FP32 sum); rows < q_begin of these
+ * hold the contributions of this call's queries to the halo keys. */
+int att3_sg_backward(const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+                     const void* Vs, const void* Y, const float* m, const float* l, const uint8_t* mask,
+                     void* dQ, void* dR, void* dS, void* dVr, void* dVs,
+                     int B, int Hq, int Hkv, int N, int D, int window, int q_begin,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Three-gather hypergraph attention: forward_cuda / backward_cuda
+ * (cuda/forward.cu:1252-1602, cuda/backward.cu:1716-2232; math in
+ * cpp/torch_reference.cpp:24-57).  All nine inputs are [B,H,N,D] with
+ * D in {16,32,64,128}.  Outputs Y_q, Y_r, Y_s (gathers) and Y_q_, Y_r_, Y_s_
+ * (scatters; written only when scatter != 0, else zero-filled) are BF16
+ * [B,H,N,D]; the six statistics FP32 [B,H,N].  n_valid < N marks trailing
+ * padding rows that are invisible in every role (0 or N: none).  gather_mode 1
+ * computes only the Q-anchored gather; the other outputs are zero-filled and
+ * their statistics set to (m = +1e30, l = 1) as the reference does
+ * (cuda/forward.cu:1455-1459).
+ * ------------------------------------------------------------------------- */
+int att3_hg_forward(const void* Q, const void* R, const void* S,
+                    const void* Vq1, const void* Vq2, const void* Vr1, const void* Vr2,
+                    const void* Vs1, const void* Vs2, const uint8_t* mask,
+                    void* Yq, void* Yr, void* Ys, void* Yq_, void* Yr_, void* Ys_,
+                    float* m_i, float* l_i, float* m_j, float* l_j, float* m_k, float* l_k,
+                    int B, int H, int N, int D, int n_valid, int gather_mode, int scatter, void* stream);
+
+size_t att3_hg_backward_workspace_bytes(int B, int H, int N, int D);
+
+/* Nine gradients (Q,R,S,Vq1,Vq2,Vr1,Vr2,Vs1,Vs2), BF16 [B,H,N,D].  g* are the
+ * cotangents of the six outputs; pass scatter = 0 when the three scatter
+ * cotangents are identically zero (att3ntion/_custom_op.py:73-96). */
+int att3_hg_backward(const void* gYq, const void* gYr, const void* gYs,
+                     const void* gYq_, const void* gYr_, const void* gYs_,
+                     const void* Q, const void* R, const void* S,
+                     const void* Vq1, const void* Vq2, const void* Vr1, const void* Vr2,
+                     const void* Vs1, const void* Vs2,
+                     const float* m_i, const float* l_i, const float* m_j, const float* l_j,
+                     const float* m_k, const float* l_k, const uint8_t* mask,
+                     void* dQ, void* dR, void* dS, void* dVq1, void* dVq2, void* dVr1, void* dVr2,
+                     void* dVs1, void* dVs2,
+                     int B, int H, int N, int D, int n_valid, int gather_mode, int scatter,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Host-side helpers (no GPU needed).
+ * ------------------------------------------------------------------------- */
+
+/* Window -> visited tile ranges, the contract of sg_row_bounds / sg_col_bounds
+ * (cuda/common.cuh:50-85) that the reference exposes as sg_tile_ranges
+ * (cpp/cuda_bindings.cpp:117-132).  side 0: the query is anchor a; side 1: a is
+ * a key and the queries are the rows.  Writes up to max_out (j0, k_lo, k_hi)
+ * triples into out[3*i..] and returns the number of row blocks (or -1 on a bad
+ * argument). */
+int att3_sg_tile_ranges(int N, int window, int a, int side, int bj, int bk, int* out, int max_out);
+
+/* Packs up to 32 mask bytes into one word, bit t = (row[t] != 0); never reads
+ * outside [row, row+lim).  Contract of sg_pack_mask32 (cuda/common.cuh:87-101). */
+uint32_t att3_pack_mask32(const uint8_t* row, int lim);
+
+/* Query-block partition the windowed kernels use: number of CTAs launched and
+ * queries per block for these sizes on a device with `sm_count` SMs. */
+int att3_sg_query_blocks(int B, int Hq, int Hkv, int N, int q_begin, int sm_count, int* block_len);
+
+/* Launch counters, the counterpart of att3_tc::State (cpp/cuda_bindings.h:18-48).
+ * which: 0 single-gather forward, 1 single-gather backward, 2 three-gather
+ * forward, 3 three-gather backward.  Returns kernels launched so far. */
+unsigned long long att3_launch_count(int which);
+
+/* ------------------------------------------------------------------------- *
+ * Self-test of the tensor-core building blocks: multiplies two 128x128 BF16
+ * matrices on one CTA through the operand arrangement `mode` selects and
+ * writes the FP32 product to D.  status_dev receives 1 if a bounded wait ran
+ * out.  Used by the test-suite to pin the descriptor encodings.
+ * ------------------------------------------------------------------------- */
+int att3_umma_selftest(const void* A, const void* B, float* D, int mode, int lbo_a, int sbo_a,
+                       int lbo_b, int sbo_b, int reps, int* status_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ATT3_B200_H */
