@@ -87,16 +87,17 @@ __device__ __forceinline__ void fence_mbar_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
-// Bounded parity wait.  Returns true when the phase completed, false when the
-// iteration limit ran out (about a second of polling at the default limit).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 24)) {
+// Bounded parity wait.  Polls with the non-blocking test_wait so the bound is a
+// plain iteration count (a fraction of a second at the default limit).  Returns
+// true when the phase completed, false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 23)) {
     const uint32_t addr = smem_u32(bar);
     for (uint32_t it = 0; it < limit; ++it) {
         uint32_t done;
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t"
             "}\n"
             : "=r"(done)
