@@ -5,6 +5,7 @@
 
 #include "att3_abi_internal.h"
 #include "sg_ring_fwd.cuh"
+#include "sg_ring_bwd.cuh"
 
 namespace {
 
@@ -116,4 +117,105 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
     const int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 2, 16, &p.block_len);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return D == 64 ? launch_ring_fwd<64>(p, nblk, st) : launch_ring_fwd<128>(p, nblk, st);
+}
+
+// ---------------------------------------------------------------------------
+// Backward
+// ---------------------------------------------------------------------------
+
+// Workspace: FP32 partials of the two gradients of one key side, two parities
+// each; the second pass reuses the space after the first pass's reduction.
+extern "C" size_t att3_sg_backward_workspace_bytes(int B, int Hq, int Hkv, int N, int D, int window) {
+    (void)Hq;
+    if (B <= 0 || Hkv <= 0 || N <= 0 || D <= 0 || window <= 0) return 0;
+    return static_cast<size_t>(4) * B * Hkv * N * D * sizeof(float);
+}
+
+template <int D, bool WITH_DQ>
+static int launch_ring_bwd(const sgring::BwdParams& p, int nblk, cudaStream_t stream) {
+    using L = sgring::BwdSmem<D, WITH_DQ>;
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(sgring::sg_ring_bwd_kernel<D, WITH_DQ>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, L::ALLOC);
+        if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: shared-memory opt-in");
+        configured_dev = dev;
+    }
+    dim3 grid(nblk, p.Hkv, p.B);
+    sgring::sg_ring_bwd_kernel<D, WITH_DQ><<<grid, sgring::BWD_THREADS, L::ALLOC, stream>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: launch");
+    att3::count_launch(1);
+    return ATT3_OK;
+}
+
+static int launch_reduce(const sgring::BwdParams& p, int nblk, int D, void* dK, void* dV, cudaStream_t stream) {
+    sgring::ReduceParams r;
+    r.part_K = p.part_K;
+    r.part_V = p.part_V;
+    r.dK = static_cast<__nv_bfloat16*>(dK);
+    r.dV = static_cast<__nv_bfloat16*>(dV);
+    r.rows = p.B * p.Hkv;
+    r.N = p.N; r.D = D; r.q_begin = p.q_begin; r.block_len = p.block_len; r.nblk = nblk;
+    const size_t total = static_cast<size_t>(r.rows) * p.N * (D / 4);
+    const int threads = 256;
+    const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
+    sgring::sg_bwd_reduce_kernel<<<blocks, threads, 0, stream>>>(r);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: reduce launch");
+    att3::count_launch(1);
+    return ATT3_OK;
+}
+
+extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+                                const void* Vs, const void* Y, const float* m, const float* l,
+                                const uint8_t* mask, void* dQ, void* dR, void* dS, void* dVr, void* dVs, int B,
+                                int Hq, int Hkv, int N, int D, int window, int q_begin, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+    if (int rc = check_shapes("att3_sg_backward", B, Hq, Hkv, N, D, window, q_begin)) return rc;
+    if (!dY || !Q || !R || !S || !Vr || !Vs || !Y || !m || !l || !dQ || !dR || !dS || !dVr || !dVs)
+        return att3::set_error(ATT3_ERR_INVALID, "att3_sg_backward: null tensor pointer");
+    if (!att3::require_sm100("att3_sg_backward")) return ATT3_ERR_UNSUPPORTED;
+    if (window == 0)
+        return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_sg_backward: dense (window = 0) path not built");
+    const size_t need = att3_sg_backward_workspace_bytes(B, Hq, Hkv, N, D, window);
+    if (!workspace || workspace_bytes < need)
+        return att3::set_error(ATT3_ERR_WORKSPACE, "att3_sg_backward: workspace of %zu bytes required, got %zu", need,
+                               workspace_bytes);
+    if (reinterpret_cast<uintptr_t>(workspace) % 16 != 0)
+        return att3::set_error(ATT3_ERR_WORKSPACE, "att3_sg_backward: workspace must be 16-byte aligned");
+
+    sgring::BwdParams p;
+    p.Q = static_cast<const __nv_bfloat16*>(Q);
+    p.dY = static_cast<const __nv_bfloat16*>(dY);
+    p.Y = static_cast<const __nv_bfloat16*>(Y);
+    p.m = m; p.l = l;
+    p.mask = mask;
+    p.dQ = static_cast<__nv_bfloat16*>(dQ);
+    p.part_K = static_cast<float*>(workspace);
+    p.part_V = p.part_K + static_cast<size_t>(2) * B * Hkv * N * D;
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
+    p.scale = 1.0f / sqrtf(static_cast<float>(D));
+    p.status = status_ptr();
+    const int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, sgring::BWD_MIN_BLOCK, &p.block_len);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    // Pass 1: own side (S, Vs) -> dS, dVs, and dQ.
+    p.Ka = static_cast<const __nv_bfloat16*>(R);
+    p.Va = static_cast<const __nv_bfloat16*>(Vr);
+    p.Kb = static_cast<const __nv_bfloat16*>(S);
+    p.Vb = static_cast<const __nv_bfloat16*>(Vs);
+    int rc = D == 64 ? launch_ring_bwd<64, true>(p, nblk, st) : launch_ring_bwd<128, true>(p, nblk, st);
+    if (rc) return rc;
+    if ((rc = launch_reduce(p, nblk, D, dS, dVs, st))) return rc;
+    // Pass 2: sides exchanged -> dR, dVr.
+    p.Ka = static_cast<const __nv_bfloat16*>(S);
+    p.Va = static_cast<const __nv_bfloat16*>(Vs);
+    p.Kb = static_cast<const __nv_bfloat16*>(R);
+    p.Vb = static_cast<const __nv_bfloat16*>(Vr);
+    rc = D == 64 ? launch_ring_bwd<64, false>(p, nblk, st) : launch_ring_bwd<128, false>(p, nblk, st);
+    if (rc) return rc;
+    return launch_reduce(p, nblk, D, dR, dVr, st);
 }
