@@ -1,0 +1,265 @@
+"""Host shim over the C ABI with the surface of the reference's pybind module
+``att3ntion._cuda_kernels`` (cpp/cuda_bindings.cpp:30-233): same function names,
+argument order, return tuples and error behaviour (RuntimeError for rejected
+tensors, ValueError for an unknown config key).  The shim validates tensors,
+allocates the outputs with torch on the inputs' device, and passes raw device
+pointers plus torch's current stream to ``libatt3_b200.so``.  There is no other
+compute path: without the library the import of ``_cabi`` fails.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+
+import torch
+
+from . import _cabi
+from ._cabi import lib
+
+_BF16 = torch.bfloat16
+_state = threading.local()
+_cfg = {k: 0 for k in ("fwd_warps", "fwd_bk", "bwd_a_warps", "bwd_a_bk", "bwd_r_warps", "bwd_r_bk", "bwd_dh")}
+_last = {"sg_fwd": "", "sg_bwd": "", "shared_fwd": "", "shared_bwd": ""}
+_enabled = [True, True]
+_workspaces: dict = {}
+
+
+def _call(fn, *args):
+    status = fn(*args)
+    if status != _cabi.OK:
+        raise RuntimeError(_cabi.last_error())
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """Scratch buffer cached per device and stream; grown, never shrunk."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+# --------------------------------------------------------------------------- checks
+# Messages follow single_gather_check / single_gather_shared_check
+# (cuda/forward.cu:1609-1653) so callers' `pytest.raises(match=...)` keep working.
+
+def _check_single(xs, mask, who="single_gather"):
+    Q = xs[0]
+    if not (isinstance(Q, torch.Tensor) and Q.is_cuda):
+        raise RuntimeError(f"{who}: inputs must be CUDA tensors")
+    if Q.dim() != 4:
+        raise RuntimeError(f"{who}: inputs must be [B,H,N,D]")
+    B, H, N, D = Q.shape
+    if not (B > 0 and H > 0 and N > 0):
+        raise RuntimeError(f"{who}: empty batch/head/sequence")
+    if D not in (64, 128):
+        raise RuntimeError(f"{who}: D must be 64 or 128, got {D}")
+    if N % 16:
+        raise RuntimeError(f"{who}: N must be a multiple of 16, got {N}")
+    for x in xs:
+        if not (x.is_cuda and x.device == Q.device):
+            raise RuntimeError(f"{who}: all inputs must be on one CUDA device")
+        if x.dtype != _BF16:
+            raise RuntimeError(f"{who}: inputs must be bf16")
+        if not x.is_contiguous():
+            raise RuntimeError(f"{who}: inputs must be contiguous")
+        if x.shape != Q.shape:
+            raise RuntimeError(f"{who}: all inputs must share one shape")
+    if mask is not None:
+        if not (mask.is_cuda and mask.device == Q.device):
+            raise RuntimeError(f"{who}: mask must be on the input device")
+        if mask.dtype != torch.bool:
+            raise RuntimeError(f"{who}: mask must be bool")
+        if not mask.is_contiguous():
+            raise RuntimeError(f"{who}: mask must be contiguous")
+        if tuple(mask.shape) != (B, N, N):
+            raise RuntimeError(f"{who}: mask must be [B,N,N]")
+
+
+def _check_shared(Q, kv, mask, window, group, who="single_gather_shared", need_mask=True):
+    if not (isinstance(Q, torch.Tensor) and Q.is_cuda and Q.dim() == 4):
+        raise RuntimeError(f"{who}: Q must be a CUDA [B,Hq,N,D] tensor")
+    B, H, N, D = Q.shape
+    if not (B > 0 and H > 0):
+        raise RuntimeError(f"{who}: empty batch/head dimensions are unsupported")
+    if D != 128:
+        raise RuntimeError(f"{who}: D must be 128 (prototype), got {D}")
+    if not (N > 0 and N % 16 == 0):
+        raise RuntimeError(f"{who}: N must be a positive multiple of 16, got {N}")
+    if window not in (16, 32, 64, 128):
+        raise RuntimeError(f"{who}: window must be 16, 32, 64 or 128, got {window}")
+    if group not in (1, 2, 4):
+        raise RuntimeError(f"{who}: head group must be 1, 2 or 4, got {group}")
+    if H % group:
+        raise RuntimeError(f"{who}: Hq={H} is not divisible by the head group {group}")
+    if not (Q.dtype == _BF16 and Q.is_contiguous()):
+        raise RuntimeError(f"{who}: Q must be contiguous bf16")
+    for x in kv:
+        if not (isinstance(x, torch.Tensor) and x.is_cuda and x.device == Q.device and x.dtype == _BF16
+                and x.is_contiguous()):
+            raise RuntimeError(f"{who}: KV tensors must be contiguous bf16 on Q's device")
+        if tuple(x.shape) != (B, 1, N, D):
+            raise RuntimeError(f"{who}: KV tensors must be [B,1,N,D] (Hkv = 1), got {tuple(x.shape)}")
+    if mask is None and not need_mask:
+        return
+    if not (isinstance(mask, torch.Tensor) and mask.is_cuda and mask.device == Q.device and mask.dtype == torch.bool
+            and mask.is_contiguous() and tuple(mask.shape) == (B, N, N)):
+        raise RuntimeError(f"{who}: mask must be a contiguous bool [B,N,N] on Q's device (the window mask)")
+
+
+def _check_state(Q, tensors, who):
+    """Saved forward state must live on Q's device (cuda/backward.cu:2377-2392)."""
+    for name, t, shape in tensors:
+        if not (isinstance(t, torch.Tensor) and t.is_cuda and t.device == Q.device):
+            raise RuntimeError(f"{who}: {name} must be on Q's device ({Q.device})")
+        if not t.is_contiguous() or tuple(t.shape) != tuple(shape):
+            raise RuntimeError(f"{who}: {name} must be contiguous with shape {tuple(shape)}")
+
+
+# --------------------------------------------------------------------------- raw ops (mask optional)
+
+def sg_forward_raw(Q, R, S, Vr, Vs, mask, window: int, q_begin: int = 0):
+    """Windowed/dense single gather on already-validated BF16 tensors.  mask may be
+    None: with window > 0 the causal window is generated from indices inside the
+    kernel, so no [B,N,N] tensor is ever materialised."""
+    B, Hq, N, D = Q.shape
+    Hkv = R.shape[1]
+    with torch.cuda.device(Q.device):
+        Y = torch.empty_like(Q)
+        m = torch.empty((B, Hq, N), dtype=torch.float32, device=Q.device)
+        l = torch.empty_like(m)
+        _call(lib.att3_sg_forward, Q.data_ptr(), R.data_ptr(), S.data_ptr(), Vr.data_ptr(), Vs.data_ptr(),
+              _ptr(mask), Y.data_ptr(), m.data_ptr(), l.data_ptr(), B, Hq, Hkv, N, D, int(window), int(q_begin),
+              _stream(Q))
+    return Y, m, l
+
+
+def sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, window: int, q_begin: int = 0):
+    B, Hq, N, D = Q.shape
+    Hkv = R.shape[1]
+    with torch.cuda.device(Q.device):
+        dQ = torch.zeros_like(Q) if q_begin else torch.empty_like(Q)
+        dR, dS, dVr, dVs = (torch.empty_like(R) for _ in range(4))
+        nbytes = lib.att3_sg_backward_workspace_bytes(B, Hq, Hkv, N, D, int(window))
+        ws = _workspace(Q.device, nbytes)
+        _call(lib.att3_sg_backward, dY.data_ptr(), Q.data_ptr(), R.data_ptr(), S.data_ptr(), Vr.data_ptr(),
+              Vs.data_ptr(), Y.data_ptr(), m.data_ptr(), l.data_ptr(), _ptr(mask),
+              dQ.data_ptr(), dR.data_ptr(), dS.data_ptr(), dVr.data_ptr(), dVs.data_ptr(),
+              B, Hq, Hkv, N, D, int(window), int(q_begin), ws.data_ptr(), nbytes, _stream(Q))
+    return dQ, dR, dS, dVr, dVs
+
+
+def device_status(device=None) -> None:
+    """Synchronises the current stream and raises if a bounded device-side wait ran out."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _call(lib.att3_device_status, torch.cuda.current_stream(dev).cuda_stream)
+
+
+# --------------------------------------------------------------------------- pybind-compatible surface
+
+def _effective_window(window: int, n: int) -> int:
+    """Window the kernels are told about.  A promise wider than the sequence is
+    plain causal visibility of width n; one wider than the 128 resident keys of
+    the ring schedule cannot be exploited, so the dense schedule runs and the
+    mask alone carries the visibility (window 0)."""
+    win = min(max(int(window), 0), int(n))
+    return win if win <= 128 else 0
+
+
+def single_gather_forward(Q, R, S, Vr, Vs, mask=None, window=0):
+    """(Y bf16 [B,H,N,D], m, l fp32 [B,H,N]); cpp/cuda_bindings.cpp:51-61."""
+    _check_single([Q, R, S, Vr, Vs], mask)
+    if window > 0 and mask is None:
+        raise RuntimeError("single_gather: window metadata needs the mask it describes")
+    win = _effective_window(window, Q.shape[2])
+    out = sg_forward_raw(Q, R, S, Vr, Vs, mask, win)
+    _last["sg_fwd"] = f"D={Q.shape[3]} schedule={'ring' if win else 'dense'} masked={int(mask is not None)} win={win}"
+    return out
+
+
+def single_gather_backward(dY, Q, R, S, Vr, Vs, Y, m, l, mask=None, window=0):
+    """(dQ, dR, dS, dVr, dVs) bf16; cpp/cuda_bindings.cpp:63-73."""
+    _check_single([dY, Q, R, S, Vr, Vs, Y], mask, "single_gather_backward")
+    B, H, N, _ = Q.shape
+    _check_state(Q, [("m", m, (B, H, N)), ("l", l, (B, H, N))], "single_gather_backward")
+    if window > 0 and mask is None:
+        raise RuntimeError("single_gather: window metadata needs the mask it describes")
+    win = _effective_window(window, N)
+    out = sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, win)
+    _last["sg_bwd"] = f"D={Q.shape[3]} schedule={'ring' if win else 'dense'} roles=own(S),own(R) win={win}"
+    return out
+
+
+def single_gather_shared_forward(Q, R, S, Vr, Vs, mask, window=128, fwd_group=1):
+    """Shared-KV forward; cpp/cuda_bindings.cpp:75-79.  fwd_group is accepted for
+    compatibility: one schedule serves every group value."""
+    _check_shared(Q, [R, S, Vr, Vs], mask, window, 1 if fwd_group == 0 else fwd_group)
+    out = sg_forward_raw(Q, R, S, Vr, Vs, mask, window)
+    _last["shared_fwd"] = f"D=128 Hkv=1 fwd_group={fwd_group} win={window} implementation=sm100_ring"
+    return out
+
+
+def single_gather_shared_backward(dY, Q, R, S, Vr, Vs, Y, m, l, mask, window=128, rs_group=1):
+    """Shared-KV backward, KV gradients reduced to [B,1,N,128]; cpp/cuda_bindings.cpp:81-86."""
+    _check_shared(Q, [R, S, Vr, Vs], mask, window, 1 if rs_group == 0 else rs_group, "single_gather_shared_backward")
+    B, H, N, D = Q.shape
+    _check_state(Q, [("dY", dY, Q.shape), ("Y", Y, Q.shape), ("m", m, (B, H, N)), ("l", l, (B, H, N))],
+                 "single_gather_shared_backward")
+    out = sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, window)
+    _last["shared_bwd"] = f"D=128 Hkv=1 rs_group={rs_group} win={window} implementation=sm100_ring"
+    return out
+
+
+def tc_launches():
+    """Launch counters (cpp/cuda_bindings.cpp:31-41)."""
+    c = [int(lib.att3_launch_count(i)) for i in range(4)]
+    return {"forward": c[2], "backward": c[3], "sg_forward": c[0], "sg_backward": c[1],
+            "sg_shared_forward": c[0], "sg_shared_backward": c[1]}
+
+
+def sg_dispatch():
+    """Last schedule chosen per entry point (cpp/cuda_bindings.cpp:42-49)."""
+    return {"forward": _last["sg_fwd"], "backward": _last["sg_bwd"],
+            "shared_forward": _last["shared_fwd"], "shared_backward": _last["shared_bwd"]}
+
+
+def sg_set_config(cfg: dict) -> None:
+    """Tile overrides of the reference kernels (cpp/cuda_bindings.cpp:88-106).  The
+    sm_100a kernels have one tile shape, so values are recorded and otherwise ignored."""
+    for k, v in cfg.items():
+        if k not in _cfg:
+            raise ValueError(f"sg_set_config: unknown key {k}")
+        _cfg[k] = int(v)
+
+
+def sg_get_config() -> dict:
+    return dict(_cfg)
+
+
+def sg_tile_ranges(N, window, a, side, bj, bk):
+    """[(j0, k_lo, k_hi), ...] visited by the work item anchored at `a`
+    (cpp/cuda_bindings.cpp:117-132)."""
+    cap = max(1, (int(N) + int(bj) - 1) // int(bj) + 1)
+    buf = (C.c_int * (3 * cap))()
+    n = lib.att3_sg_tile_ranges(int(N), int(window), int(a), int(side), int(bj), int(bk), buf, cap)
+    if n < 0:
+        raise RuntimeError("sg_tile_ranges: bad argument")
+    return [(buf[3 * i], buf[3 * i + 1], buf[3 * i + 2]) for i in range(n)]
+
+
+def tc_set_enabled(forward: bool, backward: bool):
+    """Returns the previous (forward, backward) gates (cpp/cuda_bindings.cpp:134-141).
+    There is no scalar fallback to switch to; the flags are kept for API parity."""
+    prev = tuple(_enabled)
+    _enabled[0], _enabled[1] = bool(forward), bool(backward)
+    return prev

@@ -21,4 +21,19 @@ int sm_count();
 // Launch counters behind att3_launch_count().
 void count_launch(int which, int n = 1);
 
+// Kernel ids of att3_timing_read().
+enum KernelId { K_SG_FWD = 0, K_SG_BWD = 1, K_SG_REDUCE = 2, K_DENSE_FWD = 3, K_DENSE_BWD = 4, K_HG_AUX = 5, K_COUNT = 6 };
+
+// Brackets one kernel launch with CUDA events on its stream while timing is
+// enabled (att3_timing_enable); a no-op otherwise.
+class TimedLaunch {
+public:
+    TimedLaunch(int kernel_id, cudaStream_t stream);
+    ~TimedLaunch();
+private:
+    int id_;
+    cudaStream_t stream_;
+    cudaEvent_t start_ = nullptr;
+};
+
 }  // namespace att3

@@ -5,6 +5,8 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
+#include <vector>
 
 #include "att3_abi_internal.h"
 
@@ -59,7 +61,54 @@ void count_launch(int which, int n) {
     if (which >= 0 && which < 4) g_launches[which] += n;
 }
 
+// ---- optional per-kernel timing ------------------------------------------------
+struct TimingRec { int id; cudaEvent_t a, b; };
+static std::mutex g_time_mu;
+static std::vector<TimingRec> g_time_recs;
+static std::atomic<int> g_time_on{0};
+
+TimedLaunch::TimedLaunch(int kernel_id, cudaStream_t stream) : id_(kernel_id), stream_(stream) {
+    if (!g_time_on.load(std::memory_order_relaxed)) return;
+    if (cudaEventCreate(&start_) != cudaSuccess) { start_ = nullptr; return; }
+    cudaEventRecord(start_, stream_);
+}
+
+TimedLaunch::~TimedLaunch() {
+    if (!start_) return;
+    cudaEvent_t stop = nullptr;
+    if (cudaEventCreate(&stop) != cudaSuccess) { cudaEventDestroy(start_); return; }
+    cudaEventRecord(stop, stream_);
+    std::lock_guard<std::mutex> lk(g_time_mu);
+    g_time_recs.push_back({id_, start_, stop});
+}
+
 }  // namespace att3
+
+extern "C" int att3_timing_enable(int on) { return att3::g_time_on.exchange(on ? 1 : 0); }
+
+extern "C" int att3_timing_read(int kernel_id, double* total_ms, unsigned long long* launches) {
+    if (kernel_id < 0 || kernel_id >= att3::K_COUNT || !total_ms || !launches)
+        return att3::set_error(ATT3_ERR_INVALID, "att3_timing_read: bad argument");
+    double sum = 0.0;
+    unsigned long long n = 0;
+    std::lock_guard<std::mutex> lk(att3::g_time_mu);
+    auto& recs = att3::g_time_recs;
+    for (size_t i = 0; i < recs.size();) {
+        if (recs[i].id != kernel_id) { ++i; continue; }
+        cudaError_t e = cudaEventSynchronize(recs[i].b);
+        float ms = 0.f;
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, recs[i].a, recs[i].b);
+        cudaEventDestroy(recs[i].a);
+        cudaEventDestroy(recs[i].b);
+        recs.erase(recs.begin() + i);
+        if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_timing_read");
+        sum += ms;
+        ++n;
+    }
+    *total_ms = sum;
+    *launches = n;
+    return ATT3_OK;
+}
 
 extern "C" const char* att3_last_error(void) { return att3::g_err; }
 

@@ -85,6 +85,7 @@ static int launch_ring_fwd(const sgring::FwdParams& p, int nblk, cudaStream_t st
         configured_dev = dev;
     }
     dim3 grid(nblk, p.Hkv, p.B);
+    att3::TimedLaunch timed(att3::K_SG_FWD, stream);
     sgring::sg_ring_fwd_kernel<D><<<grid, sgring::NTHREADS, L::ALLOC, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_forward: launch");
@@ -144,6 +145,7 @@ static int launch_ring_bwd(const sgring::BwdParams& p, int nblk, cudaStream_t st
         configured_dev = dev;
     }
     dim3 grid(nblk, p.Hkv, p.B);
+    att3::TimedLaunch timed(att3::K_SG_BWD, stream);
     sgring::sg_ring_bwd_kernel<D, WITH_DQ><<<grid, sgring::BWD_THREADS, L::ALLOC, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: launch");
@@ -162,6 +164,7 @@ static int launch_reduce(const sgring::BwdParams& p, int nblk, int D, void* dK, 
     const size_t total = static_cast<size_t>(r.rows) * p.N * (D / 4);
     const int threads = 256;
     const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
+    att3::TimedLaunch timed(att3::K_SG_REDUCE, stream);
     sgring::sg_bwd_reduce_kernel<<<blocks, threads, 0, stream>>>(r);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: reduce launch");

@@ -1,0 +1,320 @@
+#!/usr/bin/env python
+"""Benchmark of the shared-KV causal-window hot path (forward + all five gradients).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--window 128]
+
+Workload (BASELINE.json config 4, the one the metric is quoted on): BF16, one
+shared KV head, 8 query heads, D = 128, batch 4, N = 8192, causal window 128;
+Q/R/S/Vr/Vs ~ N(0,1)/sqrt(128) from seed 3, dY ~ N(0,1).  A step is one forward
+plus one backward over that batch.  With N GPUs every rank runs its own batch of
+the same shape (weak scaling over the data-parallel batch axis, no collective on
+the data path); the value is the job's total algorithmic TFLOP/s.
+
+Algorithmic FLOPs per step = 16 * D * T with T = B * Hq * sum_i min(i+1, w)^2
+(forward 4*D*T: score and value contraction; backward 12*D*T: six contractions).
+
+One JSON line is printed by rank 0.  `value` is device time with inputs resident;
+`e2e` times the public API call with pinned host buffers, host<->device copies
+included.  `--impl reference` times the CPU restatement of the reference's naive
+path (oracle/triplet_oracle.py) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+B, HQ, HKV, N, D = 4, 8, 1, 8192, 128
+METRIC = "fwd+bwd TFLOP/s, shared-KV causal w=128 d=128"
+SEED = 3
+
+
+def triplets(batch, heads, n, w):
+    full = max(0, n - w + 1) * w * w
+    ramp = sum(min(i + 1, w) ** 2 for i in range(min(n, w - 1)))
+    return batch * heads * (full + ramp)
+
+
+def measured_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d.get("bf16_tflops", 1590.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = sorted(sm)[len(sm) // 2:]            # the idle samples before/after the region sit in the lower half
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def draw_inputs(window):
+    g = torch.Generator(device="cpu").manual_seed(SEED)
+    s = 1.0 / math.sqrt(D)
+    Q = (torch.randn(B, HQ, N, D, generator=g) * s).to(torch.bfloat16)
+    kv = [(torch.randn(B, HKV, N, D, generator=g) * s).to(torch.bfloat16) for _ in range(4)]
+    dY = torch.randn(B, HQ, N, D, generator=g).to(torch.bfloat16)
+    return Q, kv, dY
+
+
+# --------------------------------------------------------------------------- CPU arm (oracle port)
+
+def cpu_sample(window, queries=4096, batch=1):
+    """fwd+bwd of the banded FP32 restatement on `queries` interior queries of one
+    batch (all 8 heads, full window) with every host thread.  Returns (TFLOP/s, seconds, cores)."""
+    from oracle import triplet_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n = queries + window - 1
+    n += (-n) % 16
+    g = torch.Generator(device="cpu").manual_seed(SEED)
+    s = 1.0 / math.sqrt(D)
+    Q = (torch.randn(batch, HQ, n, D, generator=g) * s).to(torch.bfloat16)
+    kv = [(torch.randn(batch, HKV, n, D, generator=g) * s).to(torch.bfloat16) for _ in range(4)]
+    dY = torch.randn(batch, HQ, n, D, generator=g).to(torch.bfloat16)
+    q_begin = n - queries
+    t0 = time.perf_counter()
+    O.single_gather_banded(Q, *kv, window=window, dY=dY, chunk=32, q_begin=q_begin, dtype=torch.float32)
+    dt = time.perf_counter() - t0
+    flops = 16 * D * batch * HQ * sum(min(i + 1, window) ** 2 for i in range(q_begin, n))
+    return flops / dt / 1e12, dt, cores
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for _ in range(args.warmup):
+        cpu_sample(args.window, queries=256)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        v, dt, cores = cpu_sample(args.window, queries=args.cpu_queries)
+        vals.append(v)
+    total = time.perf_counter() - t0
+    value = statistics.mean(vals)
+    sample = (f"banded FP32 torch restatement, 1 batch x 8 heads x {args.cpu_queries} interior queries "
+              f"(full window {args.window}) per step")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / max(1, args.steps),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"shared-KV B{B} Hq{HQ} Hkv{HKV} N{N} D{D} causal window {args.window}",
+                   "note": "each step is a bounded sample of that workload on the host cores"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def run_ours(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the sm_100a kernels have no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    from att3ntion_b200 import _cabi, _cuda_kernels as ck, single_gather_shared_attention
+    lib = _cabi.lib
+    w = args.window
+    Qh, kvh, dYh = draw_inputs(w)
+    host_in = [t.pin_memory() for t in (Qh, *kvh, dYh)]
+    Q, R, S, Vr, Vs, dY = (t.to(dev, non_blocking=True) for t in host_in)
+    torch.cuda.synchronize()
+    flops_step = 16 * D * triplets(B, HQ, N, w)
+
+    def step():
+        Y, m, l = ck.sg_forward_raw(Q, R, S, Vr, Vs, None, w)
+        return Y, ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, None, w)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    lib.att3_timing_enable(1)
+    for k in range(6):
+        tot, cnt = C.c_double(), C.c_ulonglong()
+        lib.att3_timing_read(k, C.byref(tot), C.byref(cnt))          # drop anything recorded during warm-up
+    launches0 = [lib.att3_launch_count(i) for i in range(4)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    launches = sum(lib.att3_launch_count(i) for i in range(4)) - sum(launches0)
+    ktime = {}
+    for k, name in enumerate(["sg_ring_fwd", "sg_ring_bwd", "sg_bwd_reduce"]):
+        tot, cnt = C.c_double(), C.c_ulonglong()
+        lib.att3_timing_read(k, C.byref(tot), C.byref(cnt))
+        ktime[name] = (tot.value, cnt.value)
+    lib.att3_timing_enable(0)
+    ck.device_status()
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    ms_step = ms / args.steps
+    value = world * flops_step / (ms_step * 1e-3) / 1e12
+
+    # --- end to end through the public API with host buffers (pinned), copies inside the timed region
+    host_out = [torch.empty_like(t).pin_memory() for t in (Qh, Qh, *kvh)]     # Y, dQ, dR, dS, dVr, dVs
+    h2d = sum(t.numel() * t.element_size() for t in host_in)
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def e2e_step():
+        q, r, s, vr, vs, dy = (t.to(dev, non_blocking=True) for t in host_in)
+        leaves = [t.requires_grad_(True) for t in (q, r, s, vr, vs)]
+        y = single_gather_shared_attention(*leaves, None, window=w)
+        y.backward(dy)
+        host_out[0].copy_(y.detach(), non_blocking=True)
+        for dst, leaf in zip(host_out[1:], leaves):
+            dst.copy_(leaf.grad, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    e2e_value = world * flops_step / (e2e_ms / e2e_steps * 1e-3) / 1e12
+
+    if rank == 0:
+        burst, sustained, src = measured_peaks()
+        bwd_ms, bwd_n = ktime["sg_ring_bwd"]
+        # dominant kernel: one backward pass launch produces one key side's gradients (and dQ once),
+        # half of the backward's 12*D*T algorithmic FLOPs
+        flops_launch = 6 * D * triplets(B, HQ, N, w)
+        achieved = flops_launch / (bwd_ms / max(1, bwd_n) * 1e-3) / 1e12 if bwd_n else None
+        roofline = {"bound": "tensor", "kernel": "sg_ring_bwd_kernel<128>", "achieved": achieved, "peak": sustained,
+                    "unit": "TFLOP/s", "frac": (achieved / sustained) if achieved else None,
+                    "peak_source": f"{src} bf16_tflops_sustained (kernel timed inside the step loop)",
+                    "frac_of_burst_peak": (achieved / burst) if achieved else None,
+                    "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(w),
+                    "kernel_ms": {k: (v[0] / v[1] if v[1] else None) for k, v in ktime.items()},
+                    "step_frac_of_sustained_peak": value / world / sustained}
+        cpu_v, cpu_dt, cores = cpu_sample(w, queries=args.cpu_queries) if world == 1 and not args.no_cpu else (None, 0, 0)
+        out = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"shared-KV B{B} Hq{HQ} Hkv{HKV} N{N} D{D} causal window {w}, fwd + 5 gradients",
+                       "per_gpu_batch": B, "parallelism": f"dp{world} over batch, no data-path collective",
+                       "l2": "inputs+outputs 0.5 GB per step exceed the 126 MB L2; no explicit flush",
+                       "flops_per_step": flops_step},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": roofline,
+        }
+        if cpu_v is not None:
+            out["cpu_baseline"] = {"value": cpu_v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                   "sample": f"banded FP32 torch restatement of the naive path, 1 batch x 8 heads x "
+                                             f"{args.cpu_queries} interior queries, {cpu_dt:.1f} s"}
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one sg_ring_bwd_kernel launch at this workload, from the ncu
+# capture summarised under profiles/ (null until measured for a window).
+TRAFFIC_BYTES_PER_LAUNCH = {}
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--window", type=int, default=128, choices=[16, 32, 64, 128])
+    ap.add_argument("--cpu-queries", type=int, default=4096)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -162,6 +162,17 @@ int att3_sg_query_blocks(int B, int Hq, int Hkv, int N, int q_begin, int sm_coun
  * forward, 3 three-gather backward.  Returns kernels launched so far. */
 unsigned long long att3_launch_count(int which);
 
+/* Per-kernel device timing for benchmarks (no counterpart in the reference,
+ * which times whole calls from Python: benchmarks/bench_single_gather.py:965-982).
+ * While enabled, every kernel launch is bracketed by CUDA events on its own
+ * stream.  att3_timing_read waits for the recorded launches of one kernel,
+ * returns their summed duration and count, and forgets them.  kernel_id:
+ * 0 windowed forward, 1 windowed backward pass, 2 key-gradient reduction,
+ * 3 dense forward, 4 dense backward, 5 three-gather helpers.
+ * att3_timing_enable returns the previous setting. */
+int att3_timing_enable(int on);
+int att3_timing_read(int kernel_id, double* total_ms, unsigned long long* launches);
+
 /* ------------------------------------------------------------------------- *
  * Self-test of the tensor-core building blocks: multiplies two 128x128 BF16
  * matrices on one CTA through the operand arrangement `mode` selects and

@@ -1,0 +1,42 @@
+"""Shared fixtures.  Tests marked ``gpu`` need a B200; everything else runs on a
+CPU-only machine (the native library still has to be built: it is cross-compiled
+by nvcc and loads without a GPU)."""
+import os
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+REPO = Path(__file__).resolve().parent.parent
+GOLDEN = REPO / "tests" / "golden"
+if str(REPO) not in sys.path:
+    sys.path.insert(0, str(REPO))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100a)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session", autouse=True)
+def _native_library():
+    """Build the library once per session if it is missing or stale."""
+    from att3ntion_b200 import build
+    build.build()
+
+
+def golden_files(prefix):
+    return sorted(p.name for p in GOLDEN.glob(f"{prefix}*.pt"))
+
+
+def load_golden(name):
+    return torch.load(GOLDEN / name, map_location="cpu", weights_only=False)
