@@ -199,7 +199,9 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    sampler = ClockSampler(local)
+    sampler.__enter__()                      # nvidia-smi needs a moment to start: begin before the warm-up
+    for _ in range(args.warmup if args.profile else max(args.warmup, 3)):
         step()
     barrier()
     lib.att3_timing_enable(1)
@@ -208,13 +210,14 @@ def run_ours(args):
         lib.att3_timing_read(k, C.byref(tot), C.byref(cnt))          # drop anything recorded during warm-up
     launches0 = [lib.att3_launch_count(i) for i in range(4)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
-        barrier()
-        e0.record()
-        for _ in range(args.steps):
-            step()
-        e1.record()
-        barrier()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    sampler.__exit__()
+    clocks = sampler
     ms = e0.elapsed_time(e1)
     launches = sum(lib.att3_launch_count(i) for i in range(4)) - sum(launches0)
     ktime = {}
@@ -230,6 +233,12 @@ def run_ours(args):
         ms = t.item()
     ms_step = ms / args.steps
     value = world * flops_step / (ms_step * 1e-3) / 1e12
+
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "ms_per_step": ms_step, "value": value,
+                              "kernel_ms": {k: (v[0] / v[1] if v[1] else None) for k, v in ktime.items()}}))
+        return
 
     # --- end to end through the public API with host buffers (pinned), copies inside the timed region
     host_out = [torch.empty_like(t).pin_memory() for t in (Qh, Qh, *kvh)]     # Y, dQ, dR, dS, dVr, dVs
@@ -307,13 +316,18 @@ TRAFFIC_BYTES_PER_LAUNCH = {}
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--window", type=int, default=128, choices=[16, 32, 64, 128])
     ap.add_argument("--cpu-queries", type=int, default=4096)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--seq-len", type=int, default=N, help="sequence length (profiling captures use a smaller case)")
+    ap.add_argument("--batch", type=int, default=B)
+    ap.add_argument("--profile", action="store_true",
+                    help="kernel-only run for profiler captures: exact warm-up count, no e2e and no CPU leg")
     a = ap.parse_args()
+    N, B = a.seq_len, a.batch
     if a.impl == "reference":
         run_reference(a)
     else:
