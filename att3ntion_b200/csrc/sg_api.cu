@@ -6,11 +6,23 @@
 #include "att3_abi_internal.h"
 #include "sg_ring_fwd.cuh"
 #include "sg_ring_bwd.cuh"
+#include <cstdlib>
 
 namespace {
 
 // Sticky status word of this translation unit's kernels (bounded-wait failures).
 __device__ int g_sg_status = 0;
+
+// Cycle counters of the pipelined backward (diagnostic; filled when ATT3_TRACE=1).
+__device__ long long g_sg_trace[32];
+
+long long* trace_ptr() {
+    static const bool on = [] { const char* e = getenv("ATT3_TRACE"); return e && e[0] == '1'; }();
+    if (!on) return nullptr;
+    long long* p = nullptr;
+    cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_sg_trace);
+    return p;
+}
 
 int* status_ptr() {
     int* p = nullptr;
@@ -56,6 +68,15 @@ extern "C" int att3_sg_query_blocks(int B, int Hq, int Hkv, int N, int q_begin, 
     const int n = plan_blocks(B, Hkv, N, q_begin, sm_count, 2, 16, &len);
     if (block_len) *block_len = len;
     return n * B * Hkv;
+}
+
+// Diagnostic: copies and clears the 32 cycle counters (not part of the public header).
+extern "C" int att3_debug_trace(long long* out32) {
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(out32, g_sg_trace, sizeof(long long) * 32) != cudaSuccess) return ATT3_ERR_CUDA;
+    long long z[32] = {0};
+    cudaMemcpyToSymbol(g_sg_trace, z, sizeof(z));
+    return ATT3_OK;
 }
 
 extern "C" int att3_device_status(void* stream) {
@@ -134,7 +155,7 @@ extern "C" size_t att3_sg_backward_workspace_bytes(int B, int Hq, int Hkv, int N
 
 template <int D, bool WITH_DQ>
 static int launch_ring_bwd(const sgring::BwdParams& p, int nblk, cudaStream_t stream) {
-    using L = sgring::BwdSmem<D, WITH_DQ>;
+    using L = sgring::PipeSmem<D, WITH_DQ>;
     static thread_local int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -146,7 +167,7 @@ static int launch_ring_bwd(const sgring::BwdParams& p, int nblk, cudaStream_t st
     }
     dim3 grid(nblk, p.Hkv, p.B);
     att3::TimedLaunch timed(att3::K_SG_BWD, stream);
-    sgring::sg_ring_bwd_kernel<D, WITH_DQ><<<grid, sgring::BWD_THREADS, L::ALLOC, stream>>>(p);
+    sgring::sg_ring_bwd_kernel<D, WITH_DQ><<<grid, sgring::PIPE_THREADS, L::ALLOC, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: launch");
     att3::count_launch(1);
@@ -202,6 +223,7 @@ extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, co
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status_ptr();
+    p.trace = trace_ptr();
     const int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, sgring::BWD_MIN_BLOCK, &p.block_len);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 

@@ -1,4 +1,4 @@
-// Windowed single-gather backward for sm_100a ("ring" schedule).
+// Windowed single-gather backward for sm_100a ("ring" schedule, role-specialised and pipelined).
 //
 // With P = softmax over the visible (j,k) pairs of query i, delta_i = dY_i . Y_i,
 // dP[j][k] = sum_d dY_i[d] Vr_j[d] Vs_k[d] and gA = P o (dP - delta_i):
@@ -31,13 +31,36 @@
 //    least 127 queries long, so every partial row has exactly one writer and the
 //    final sum (reduce kernel below) has a fixed order: repeated calls are
 //    bit-identical.
+//
+// Schedule.  A CTA that ran these steps one after the other would spend most of its time at
+// the barrier between CUDA-core and tensor-core phases, so the CTA is split into roles that
+// hand work to each other through mbarriers, and every (query, head) is processed in two
+// 64-column halves a/b that overlap:
+//
+//   H warps (4)  build the Hadamard tiles Qp = Q_i o Ka, Gt = dY_i o Va, one ring
+//                row per thread; rows 0-63 (half a) and 64-127 (half b) are
+//                released separately.
+//   MMA warp (1) one thread issues, in order:
+//                  B_a, B_b : X^T[:,x] = Kb Qp_x^T, dP^T[:,x] = Vb Gt_x^T      (N = 64)
+//                  D_a, D_b : dKb += gA^T[:,x] Qp_x, dVb += P^T[:,x] Gt_x       (K = 64)
+//                  W        : gA^T Ka, for dQ (dQ pass only)
+//   E warps (8)  turn score columns into P^T / gA^T (BF16, back into tensor
+//                memory), flush finished accumulator lanes, and collapse W to dQ.
+//
+// Hand-offs per processed head (all mbarriers, phase = processed-head counter):
+//   H_full[x]  H -> MMA   tile half x written          D_done[x]  MMA -> H  tile half x read
+//   S_full[x]  MMA -> E   score half x in TMEM          P_full[x]  E -> MMA  P^T/gA^T half x stored
+//   W_full     MMA -> E   W in TMEM                     W_free     E -> MMA/H  W and the Kb rows read
+// While E works on half a the tensor pipe computes half b; while the D MMAs of one
+// half run, E finishes the other and H rebuilds the freed half for the next head.
+// Every wait is bounded and also watches a CTA-wide failure flag, so a protocol
+// error ends the kernel with a status code instead of hanging it.
 #pragma once
 
 #include "sg_ring_fwd.cuh"
 
 namespace sgring {
 
-constexpr int BWD_THREADS = 256;
 constexpr int BWD_MIN_BLOCK = 128;   // queries per block >= window so each partial row has one writer
 
 struct BwdParams {
@@ -57,34 +80,97 @@ struct BwdParams {
     int B, Hq, Hkv, N, window, q_begin, block_len;
     float scale;
     int* status;
+    long long* trace;                // optional cycle counters of the pipelined schedule (null: off)
 };
 
+constexpr int PIPE_E_THREADS = 256;
+constexpr int PIPE_H_THREADS = 128;
+// Four full warpgroups: E (2), H (1) and one whose first warp issues the MMAs while the
+// other three only hand their registers to the working roles (setmaxnreg below).
+constexpr int PIPE_THREADS = PIPE_E_THREADS + PIPE_H_THREADS + 128;
+
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+enum PipeBar {
+    PB_H_FULL_A = 0, PB_H_FULL_B, PB_S_FULL_A, PB_S_FULL_B, PB_P_FULL_A, PB_P_FULL_B, PB_D_DONE_A, PB_D_DONE_B,
+    PB_W_FULL, PB_W_FREE, PB_E_SYNC, PB_E_SYNC2, PB_H_SYNC, PB_RING_FREE, PB_COUNT
+};
+
+// One arrival per warp: the lanes' earlier writes are ordered before lane 0's releasing
+// arrive by the warp barrier.  256 per-thread arrivals on one barrier word serialise into
+// more than a thousand cycles per hand-off; eight do not.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+}
+
 template <int D, bool WITH_DQ>
-struct BwdSmem {
+struct PipeSmem {
     static constexpr int TILE = RING * D * 2;
     static constexpr int OFF_KB = 0;
     static constexpr int OFF_VB = TILE;
     static constexpr int OFF_QP = 2 * TILE;
     static constexpr int OFF_G = 3 * TILE;
-    static constexpr int OFF_KA = 4 * TILE;                       // only WITH_DQ
-    static constexpr int OFF_STAGE = (WITH_DQ ? 5 : 4) * TILE;    // 2 stages x {Q, dY, Y} rows
-    static constexpr int OFF_RED = OFF_STAGE + 2 * 3 * D * 2;     // 4 x D floats (dQ partials)
-    static constexpr int OFF_VIS = OFF_RED + 4 * D * 4;
-    static constexpr int OFF_MISC = OFF_VIS + 16;
+    static constexpr int OFF_KA = 4 * TILE;                        // only WITH_DQ
+    static constexpr int OFF_STAGE = (WITH_DQ ? 5 : 4) * TILE;     // 2 stages x {Q, dY} rows
+    static constexpr int OFF_RED = OFF_STAGE + 2 * 2 * D * 2;      // 2 x 4 x D floats (dQ partials)
+    static constexpr int OFF_BARS = OFF_RED + 2 * 4 * D * 4;
+    static constexpr int OFF_MISC = OFF_BARS + PB_COUNT * 8;       // tmem slot (4) + fail flag (4)
     static constexpr int BYTES = OFF_MISC + 16;
     static constexpr int ALLOC = BYTES + 1024;
 };
 
+// Bounded wait that also leaves when another thread has raised the CTA's failure flag.
+__device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volatile int* fail,
+                                          long long* trace = nullptr) {
+    const uint32_t addr = smem_u32(bar);
+    const long long t0 = trace ? clock64() : 0;
+    // try_wait parks the thread in hardware for up to the hinted time instead of spinning on
+    // shared memory (hundreds of pollers would otherwise compete with the operand traffic);
+    // the iteration count still bounds the total wait to about a second.
+    for (uint32_t it = 0; it < (1u << 20); ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) {
+            if (trace) *trace += clock64() - t0;
+            return true;
+        }
+        if ((it & 15u) == 15u && *fail) return false;
+    }
+    *fail = 1;
+    return false;
+}
+
+// Visibility of the 128 ring slots for query i as four ballot words; every warp
+// computes the same words (lane L looks at slots L, 32+L, 64+L, 96+L).
+__device__ __forceinline__ void ring_visibility(const uint8_t* mask_row, int i, int window, int lane, uint32_t (&vw)[4]) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int key = ring_key(i, q * 32 + lane);
+        bool v = key >= 0 && key > i - window;
+        if (v && mask_row) v = mask_row[key] != 0;
+        vw[q] = __ballot_sync(0xFFFFFFFFu, v);
+    }
+}
+
 template <int D, bool WITH_DQ>
-__global__ void __launch_bounds__(BWD_THREADS, 1) sg_ring_bwd_kernel(const BwdParams p) {
-    using L = BwdSmem<D, WITH_DQ>;
-    constexpr int HD = D / 2;            // columns of d owned by one thread in the Hadamard / dQ steps
-    constexpr int HCH = HD / 8;          // 16-byte chunks in that half row
-    constexpr int HW = HD / 2;           // packed words in that half row
+__global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdParams p) {
+    using L = PipeSmem<D, WITH_DQ>;
+    constexpr int CH = D / 8;            // 16-byte chunks per row
+    constexpr int DW = D / 2;            // packed words per row
+    constexpr int HD = D / 2;            // d columns per E thread in the dQ collapse
     constexpr uint32_t TMEM_COLS = 512;
-    // Tensor-memory columns: scores X^T [0,128) (P^T as BF16 in [0,64)), dP^T [128,256)
-    // (gA^T as BF16 in [128,192)), accumulators dKb [256,256+D) and dVb [384,384+D).
-    // W = gA^T Ka (dQ pass) reuses the consumed upper halves [64,128) and [192,256).
     constexpr uint32_t C_XT = 0, C_DP = 128, C_AK = 256, C_AV = 384, C_W0 = 64, C_W1 = 192;
 
     extern __shared__ uint8_t smem_raw[];
@@ -96,27 +182,34 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) sg_ring_bwd_kernel(const BwdPa
     uint8_t* sKa = smem + L::OFF_KA;
     __nv_bfloat16* sStage = reinterpret_cast<__nv_bfloat16*>(smem + L::OFF_STAGE);
     float* sRed = reinterpret_cast<float*>(smem + L::OFF_RED);
-    uint32_t* sVis = reinterpret_cast<uint32_t*>(smem + L::OFF_VIS);
-    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::OFF_MISC);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::OFF_MISC + 8);
-    volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 12);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BARS);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::OFF_MISC);
+    volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 4);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int slot = tid & (RING - 1);   // ring slot = tensor-memory lane owned by this thread
-    const int half = tid >> 7;           // 0/1: which half of d (Hadamard, dQ) and of the score columns
     const int b = blockIdx.z, g = blockIdx.y;
     const int G = p.Hq / p.Hkv;
     const int q0 = p.q_begin + blockIdx.x * p.block_len;
     const int q1 = min(q0 + p.block_len, p.N);
     if (q0 >= q1) return;
-    const int parity = blockIdx.x & 1;
+    const int parity_buf = blockIdx.x & 1;
+    const bool is_e = warp < 8, is_h = warp >= 8 && warp < 12, is_mma = warp == 12;
 
-    if (warp == 0) {
+    (void)is_e;
+    if (is_mma) {
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
     }
     if (tid == 0) {
-        mbar_init(bar, 1);
+        // Arrival counts are in warps: one elected lane arrives for its warp (warp_arrive).
+        mbar_init(&bars[PB_H_FULL_A], 2);   mbar_init(&bars[PB_H_FULL_B], 2);
+        mbar_init(&bars[PB_S_FULL_A], 1);   mbar_init(&bars[PB_S_FULL_B], 1);
+        mbar_init(&bars[PB_P_FULL_A], 8);   mbar_init(&bars[PB_P_FULL_B], 8);
+        mbar_init(&bars[PB_D_DONE_A], 1);   mbar_init(&bars[PB_D_DONE_B], 1);
+        mbar_init(&bars[PB_W_FULL], 1);     mbar_init(&bars[PB_W_FREE], 8);
+        mbar_init(&bars[PB_E_SYNC], 8);     mbar_init(&bars[PB_E_SYNC2], 8);
+        mbar_init(&bars[PB_H_SYNC], 4);
+        mbar_init(&bars[PB_RING_FREE], WITH_DQ ? 9 : 1);
         fence_mbar_init();
         *sFail = 0;
     }
@@ -126,316 +219,460 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) sg_ring_bwd_kernel(const BwdPa
     const __nv_bfloat16* gVa = p.Va + kv_base * D;
     const __nv_bfloat16* gKb = p.Kb + kv_base * D;
     const __nv_bfloat16* gVb = p.Vb + kv_base * D;
-    float* gPartK = p.part_K + (static_cast<size_t>(parity) * p.B * p.Hkv * p.N + kv_base) * D;
-    float* gPartV = p.part_V + (static_cast<size_t>(parity) * p.B * p.Hkv * p.N + kv_base) * D;
+    float* gPartK = p.part_K + (static_cast<size_t>(parity_buf) * p.B * p.Hkv * p.N + kv_base) * D;
+    float* gPartV = p.part_V + (static_cast<size_t>(parity_buf) * p.B * p.Hkv * p.N + kv_base) * D;
+    const uint8_t* mask_b = p.mask ? p.mask + static_cast<size_t>(b) * p.N * p.N : nullptr;
 
-    // This thread's half row of the other side's ring slot, for the Hadamard tiles.
-    uint32_t rKa[HW], rVa[HW];
-    auto load_slot = [&](int key) {
-        const int c0 = half * HCH;
+    const int n_iter = (q1 - q0) * G;
+    auto row_index = [&](int it) {
+        const int i = q0 + it / G, h = g * G + it % G;
+        return (static_cast<size_t>(b) * p.Hq + h) * p.N + i;
+    };
+    const float c2 = p.scale * LOG2E;
+
+    // ------------------------------------------------------------------ H role state
+    const int hslot = tid - PIPE_E_THREADS;          // ring slot of an H thread (0..127)
+    uint32_t rKa[DW], rVa[DW];
+    auto h_load_slot = [&](int key) {
         if (key >= 0) {
             const uint4* ka4 = reinterpret_cast<const uint4*>(gKa + static_cast<size_t>(key) * D);
             const uint4* va4 = reinterpret_cast<const uint4*>(gVa + static_cast<size_t>(key) * D);
             const uint4* kb4 = reinterpret_cast<const uint4*>(gKb + static_cast<size_t>(key) * D);
             const uint4* vb4 = reinterpret_cast<const uint4*>(gVb + static_cast<size_t>(key) * D);
 #pragma unroll
-            for (int c = 0; c < HCH; ++c) {
-                const uint4 a = __ldg(ka4 + c0 + c), v = __ldg(va4 + c0 + c);
+            for (int c = 0; c < CH; ++c) {
+                const uint4 a = __ldg(ka4 + c), v = __ldg(va4 + c);
                 rKa[4 * c] = a.x; rKa[4 * c + 1] = a.y; rKa[4 * c + 2] = a.z; rKa[4 * c + 3] = a.w;
                 rVa[4 * c] = v.x; rVa[4 * c + 1] = v.y; rVa[4 * c + 2] = v.z; rVa[4 * c + 3] = v.w;
-                *reinterpret_cast<uint4*>(sKb + sw128_offset<RING>(slot, c0 + c)) = __ldg(kb4 + c0 + c);
-                *reinterpret_cast<uint4*>(sVb + sw128_offset<RING>(slot, c0 + c)) = __ldg(vb4 + c0 + c);
-                if (WITH_DQ) *reinterpret_cast<uint4*>(sKa + sw128_offset<RING>(slot, c0 + c)) = a;
+                *reinterpret_cast<uint4*>(sKb + sw128_offset<RING>(hslot, c)) = __ldg(kb4 + c);
+                *reinterpret_cast<uint4*>(sVb + sw128_offset<RING>(hslot, c)) = __ldg(vb4 + c);
+                if (WITH_DQ) *reinterpret_cast<uint4*>(sKa + sw128_offset<RING>(hslot, c)) = a;
             }
         } else {
             const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-            for (int c = 0; c < HCH; ++c) {
+            for (int c = 0; c < CH; ++c) {
                 rKa[4 * c] = rKa[4 * c + 1] = rKa[4 * c + 2] = rKa[4 * c + 3] = 0;
                 rVa[4 * c] = rVa[4 * c + 1] = rVa[4 * c + 2] = rVa[4 * c + 3] = 0;
-                *reinterpret_cast<uint4*>(sKb + sw128_offset<RING>(slot, c0 + c)) = z;
-                *reinterpret_cast<uint4*>(sVb + sw128_offset<RING>(slot, c0 + c)) = z;
-                if (WITH_DQ) *reinterpret_cast<uint4*>(sKa + sw128_offset<RING>(slot, c0 + c)) = z;
+                *reinterpret_cast<uint4*>(sKb + sw128_offset<RING>(hslot, c)) = z;
+                *reinterpret_cast<uint4*>(sVb + sw128_offset<RING>(hslot, c)) = z;
+                if (WITH_DQ) *reinterpret_cast<uint4*>(sKa + sw128_offset<RING>(hslot, c)) = z;
             }
         }
     };
-    load_slot(ring_key(q0, slot));
-
-    // Staged rows {Q, dY, Y} of a (query, head): stage s at sStage + s*3*D.
-    const int n_iter = (q1 - q0) * G;
-    auto row_index = [&](int it) {
-        const int i = q0 + it / G, h = g * G + it % G;
-        return (static_cast<size_t>(b) * p.Hq + h) * p.N + i;
-    };
-    auto stage_rows = [&](int it) {       // threads [0, 3*D/8) copy one 16-byte chunk each
-        constexpr int CH = D / 8;
-        if (tid < 3 * CH) {
-            const int which = tid / CH, c = tid % CH;
-            const __nv_bfloat16* src = (which == 0 ? p.Q : which == 1 ? p.dY : p.Y) + row_index(it) * D;
-            const uint32_t dst = smem_u32(sStage + ((it & 1) * 3 + which) * D) + c * 16;
+    auto h_stage = [&](int it) {          // H threads [0, 2*CH): one 16-byte chunk of the Q / dY row each
+        if (hslot < 2 * CH) {
+            const int which = hslot / CH, c = hslot % CH;
+            const __nv_bfloat16* src = (which == 0 ? p.Q : p.dY) + row_index(it) * D;
+            const uint32_t dst = smem_u32(sStage + ((it & 1) * 2 + which) * D) + c * 16;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
                          "l"(reinterpret_cast<const uint4*>(src) + c)
                          : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    stage_rows(0);
-    asm volatile("cp.async.wait_all;" ::: "memory");
-
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tl = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);   // this warp's lane quarter
-
-    // Zero the two persistent accumulators: half 0 clears dKb, half 1 clears dVb.
-    {
-        uint32_t z[32];
-#pragma unroll
-        for (int t = 0; t < 32; ++t) z[t] = 0;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) tmem_st32(tl + (half ? C_AV : C_AK) + c * 32, z);
-        tmem_wait_st();
-    }
-
-    // Copies lane `slot`'s accumulator row to the partial buffers (row `key`) and,
-    // unless this is the final drain, zeroes it.  Runs on the two warps that own
-    // the lane quarter `quarter`; warp-uniform control flow around the collective
-    // tensor-memory accesses.
-    auto flush = [&](int quarter, int only_lane /* -1: all lanes */, int i_ref, bool rezero) {
-        if ((warp & 3) != quarter) return;
-        const uint32_t col = half ? C_AV : C_AK;
-        float* dst_base = half ? gPartV : gPartK;
-        const float mul = half ? 1.0f : p.scale;
-        const int key = ring_key(i_ref, slot);
-        const bool mine = (only_lane < 0 || lane == only_lane) && key >= 0;
-        uint32_t a[32];
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-            tmem_ld32(tl + col + c * 32, a);
-            tmem_wait_ld();
-            if (mine) {
-                float4* dst = reinterpret_cast<float4*>(dst_base + static_cast<size_t>(key) * D + c * 32);
-#pragma unroll
-                for (int t = 0; t < 8; ++t)
-                    dst[t] = make_float4(mul * __uint_as_float(a[4 * t]), mul * __uint_as_float(a[4 * t + 1]),
-                                         mul * __uint_as_float(a[4 * t + 2]), mul * __uint_as_float(a[4 * t + 3]));
-            }
-            if (rezero) {
-                if (only_lane < 0 || lane == only_lane) {
-#pragma unroll
-                    for (int t = 0; t < 32; ++t) a[t] = 0;
-                }
-                tmem_st32(tl + col + c * 32, a);
-            }
-        }
-        if (rezero) tmem_wait_st();
-    };
-
-    const uint32_t idesc_s = make_idesc_bf16(RING, RING, 0, 0);     // score-shaped, both operands K-major
-    const uint32_t idesc_acc = make_idesc_bf16(RING, D, 0, 1);      // A in tensor memory, B MN-major, N = D
-    const uint32_t idesc_w = make_idesc_bf16(RING, 64, 0, 1);       // W halves, N = 64
-    const uint32_t aKb = smem_u32(sKb), aVb = smem_u32(sVb), aQp = smem_u32(sQp), aG = smem_u32(sG),
-                   aKa = smem_u32(sKa);
-    const float c2 = p.scale * LOG2E;
-    uint32_t phase = 0;
-    bool failed = false;
-
-    int it = 0;
-    for (int i = q0; i < q1 && !failed; ++i) {
-        // --- slide the window ---------------------------------------------------
-        if (i > q0) {
-            const int s = i & (RING - 1);
-            flush(s >> 5, s & 31, i - 1, true);      // slot s still maps to key i-128 under query i-1
-            if (slot == s) load_slot(i);
-        }
-        bool my_vis;
-        {
-            const int key = ring_key(i, slot);
-            my_vis = key >= 0 && key > i - p.window;
-            if (my_vis && p.mask) my_vis = p.mask[(static_cast<size_t>(b) * p.N + i) * p.N + key] != 0;
-            const uint32_t w = __ballot_sync(0xFFFFFFFFu, my_vis);
-            if (lane == 0 && warp < 4) sVis[warp] = w;
-        }
+    // Each role first sets its register budget (the CTA starts at 128 per thread: the last
+    // warpgroup gives most of its registers away, the H threads take room for two ring rows,
+    // the E warps keep theirs), does its share of the set-up and then meets the others at
+    // one CTA barrier before the hand-off protocol starts.
+    // Optional cycle accounting of the hand-off waits (one thread per role of CTA 0).
+    const bool tracer = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&
+                        (tid == 0 || tid == PIPE_E_THREADS || tid == PIPE_E_THREADS + PIPE_H_THREADS);
+    const long long t_begin = tracer ? clock64() : 0;
+#define TR(k) (tracer ? p.trace + (k) : nullptr)
+    uint32_t tmem_base = 0;
+    auto cta_start_sync = [&]() {
         tc_fence_before();
         __syncthreads();
         tc_fence_after();
-        const uint32_t vw0 = sVis[0], vw1 = sVis[1], vw2 = sVis[2], vw3 = sVis[3];
-        const int n_vis = __popc(vw0) + __popc(vw1) + __popc(vw2) + __popc(vw3);
-        const bool all_vis = n_vis == RING;
+        tmem_base = *tmem_slot;
+    };
 
-        for (int hh = 0; hh < G && !failed; ++hh, ++it) {
-            const size_t row = row_index(it);
-            if (it + 1 < n_iter) stage_rows(it + 1);
-            const float m_i = __ldg(p.m + row), l_i = __ldg(p.l + row);
-            const __nv_bfloat16* stQ = sStage + (it & 1) * 3 * D;
-            const __nv_bfloat16* stdY = stQ + D;
-            const __nv_bfloat16* stY = stQ + 2 * D;
-
-            if (n_vis == 0 || !(l_i > 0.f)) {
-                // No visible pair: every gradient contribution of this query is zero.
-                if (WITH_DQ && tid < D) p.dQ[row * D + tid] = __float2bfloat16(0.f);
-                asm volatile("cp.async.wait_all;" ::: "memory");
-                __syncthreads();
-                continue;
+    if (is_h) {
+        // ================================================================== H warps
+        reg_inc<184>();
+        h_load_slot(ring_key(q0, hslot));
+        h_stage(0);
+        fence_async_smem();
+        cta_start_sync();
+        const int x = hslot >> 6;                      // tile half this thread's row belongs to
+        uint64_t* bar_full = &bars[x ? PB_H_FULL_B : PB_H_FULL_A];
+        uint64_t* bar_done = &bars[x ? PB_D_DONE_B : PB_D_DONE_A];
+        int n = 0, it = 0, n_query = 0, ring_phase = 0;
+        bool ok = true;
+        float l_next = __ldg(p.l + row_index(0));
+        for (int i = q0; i < q1 && ok; ++i) {
+            if (i > q0) {
+                // Ring slot i mod 128 changes key: every MMA that reads the rings, and in the dQ
+                // pass the E warps' reads of the Kb rows, must have finished with the previous
+                // query.  RING_FREE completes once per query that had work, so every H thread sees
+                // each of its phases in turn (a per-head barrier would be observed here only now
+                // and then, and a one-bit phase parity cannot tell phases two apart).
+                if (n > n_query) {
+                    ok = pipe_wait(&bars[PB_RING_FREE], ring_phase & 1, sFail, TR(16));
+                    ++ring_phase;
+                    if (!ok) break;
+                }
+                if (hslot == (i & (RING - 1))) {
+                    h_load_slot(i);
+                    fence_async_smem();
+                }
             }
-
-            // delta = sum_d dY[d] * Y[d], the same value in every warp
-            float delta = 0.f;
+            n_query = n;
+            uint32_t vw[4];
+            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
+            const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
+            for (int hh = 0; hh < G && ok; ++hh, ++it) {
+                const float l_i = l_next;
+                if (it + 1 < n_iter) l_next = __ldg(p.l + row_index(it + 1));
+                // the staged rows of this iteration have landed; everyone is past the previous build
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                warp_arrive(&bars[PB_H_SYNC], lane);
+                ok = pipe_wait(&bars[PB_H_SYNC], it & 1, sFail, TR(17));
+                if (!ok) break;
+                if (it + 1 < n_iter) h_stage(it + 1);
+                if (!any_vis || !(l_i > 0.f)) continue;
+                if (n > 0) {
+                    ok = pipe_wait(bar_done, (n - 1) & 1, sFail, TR(18));
+                    if (!ok) break;
+                }
+                const uint4* q4 = reinterpret_cast<const uint4*>(sStage + (it & 1) * 2 * D);
+                const uint4* y4 = q4 + CH;
 #pragma unroll
-            for (int t = 0; t < D / 32; ++t)
-                delta += __bfloat162float(stdY[lane + 32 * t]) * __bfloat162float(stY[lane + 32 * t]);
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) delta += __shfl_xor_sync(0xFFFFFFFFu, delta, o);
-            const float lse2 = m_i * LOG2E + __log2f(l_i);
-
-            // --- Hadamard tiles: Qp[j] = Q_i o Ka_j, Gt[j] = dY_i o Va_j (this thread: half a row)
-            {
-                const uint4* q4 = reinterpret_cast<const uint4*>(stQ) + half * HCH;
-                const uint4* y4 = reinterpret_cast<const uint4*>(stdY) + half * HCH;
-#pragma unroll
-                for (int c = 0; c < HCH; ++c) {
+                for (int c = 0; c < CH; ++c) {
                     const uint4 q = q4[c], y = y4[c];
                     uint4 o, gq;
                     o.x = mul_bf16x2(q.x, rKa[4 * c]);      gq.x = mul_bf16x2(y.x, rVa[4 * c]);
                     o.y = mul_bf16x2(q.y, rKa[4 * c + 1]);  gq.y = mul_bf16x2(y.y, rVa[4 * c + 1]);
                     o.z = mul_bf16x2(q.z, rKa[4 * c + 2]);  gq.z = mul_bf16x2(y.z, rVa[4 * c + 2]);
                     o.w = mul_bf16x2(q.w, rKa[4 * c + 3]);  gq.w = mul_bf16x2(y.w, rVa[4 * c + 3]);
-                    *reinterpret_cast<uint4*>(sQp + sw128_offset<RING>(slot, half * HCH + c)) = o;
-                    *reinterpret_cast<uint4*>(sG + sw128_offset<RING>(slot, half * HCH + c)) = gq;
+                    *reinterpret_cast<uint4*>(sQp + sw128_offset<RING>(hslot, c)) = o;
+                    *reinterpret_cast<uint4*>(sG + sw128_offset<RING>(hslot, c)) = gq;
                 }
+                fence_async_smem();
+                warp_arrive(bar_full, lane);
+                ++n;
             }
-            fence_async_smem();
-            tc_fence_before();
-            __syncthreads();                                                   // B1
-            if (tid == 0) {
-                tc_fence_after();
+        }
+    } else if (warp >= 12) {
+        reg_dec<72>();
+        cta_start_sync();
+        if (is_mma) {
+        // ================================================================== MMA warp
+        const uint32_t idesc_s = make_idesc_bf16(RING, 64, 0, 0);       // score halves: N = 64
+        const uint32_t idesc_acc = make_idesc_bf16(RING, D, 0, 1);      // A in TMEM, B MN-major, N = D
+        const uint32_t idesc_w = make_idesc_bf16(RING, 64, 0, 1);
+        // Descriptor bases are built once; a k-step only adds a compile-time constant to the
+        // start-address field (16-byte units).  The single issuing thread runs a dependent
+        // instruction every few cycles, so every instruction spared per MMA shows up directly
+        // in the issue rate: rebuilding descriptors per MMA costs ~100-190 cycles an MMA,
+        // against 32-64 cycles of tensor-pipe time.
+        const uint64_t dKb = make_smem_desc(smem_u32(sKb), 16, 1024, SWIZZLE_128B);           // A, K-major
+        const uint64_t dVb = make_smem_desc(smem_u32(sVb), 16, 1024, SWIZZLE_128B);
+        const uint64_t dQpK = make_smem_desc(smem_u32(sQp), 16, 1024, SWIZZLE_128B);          // B, K-major
+        const uint64_t dGK = make_smem_desc(smem_u32(sG), 16, 1024, SWIZZLE_128B);
+        const uint64_t dQpM = make_smem_desc(smem_u32(sQp), RING * 128, 1024, SWIZZLE_128B);  // B, MN-major
+        const uint64_t dGM = make_smem_desc(smem_u32(sG), RING * 128, 1024, SWIZZLE_128B);
+        const uint64_t dKaM = make_smem_desc(smem_u32(sKa), RING * 128, 1024, SWIZZLE_128B);
+        const uint32_t tXT = tmem_base + C_XT, tDP = tmem_base + C_DP, tAK = tmem_base + C_AK, tAV = tmem_base + C_AV;
+        int n = 0, it = 0, n_query = 0;
+        bool ok = true;
+        float l_next = __ldg(p.l + row_index(0));
+        for (int i = q0; i < q1 && ok; ++i) {
+            uint32_t vw[4];
+            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
+            const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
+            for (int hh = 0; hh < G && ok; ++hh, ++it) {
+                const float l_i = l_next;
+                if (it + 1 < n_iter) l_next = __ldg(p.l + row_index(it + 1));
+                if (!any_vis || !(l_i > 0.f)) continue;
+                {   // whole warp, converged: one elected lane issues each MMA (see umma_ss_warp)
+                    const uint32_t ph = n & 1;
+                    // The score MMAs of this head overwrite the tensor-memory columns that the
+                    // previous head's accumulation (and W) MMAs read their A operand from; a later
+                    // MMA is not held back for an earlier one's operand reads, so wait until the
+                    // previous head's last group has completed.
+                    if (n > 0) ok = pipe_wait(&bars[WITH_DQ ? PB_W_FULL : PB_D_DONE_B], (n - 1) & 1, sFail, TR(0));
+                    // ---- score halves
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * (RING * 128) + (kk & 3) * 32;
-                    umma_ss(tmem_base + C_XT, make_smem_desc(aKb + off, 16, 1024, SWIZZLE_128B),
-                            make_smem_desc(aQp + off, 16, 1024, SWIZZLE_128B), idesc_s, kk > 0);
-                }
+                    for (int x = 0; x < 2; ++x) {
+                        if (!ok) break;
+                        ok = pipe_wait(&bars[x ? PB_H_FULL_B : PB_H_FULL_A], ph, sFail, TR(1 + x));
+                        // half b overwrites the columns that held W of the previous head
+                        if (ok && WITH_DQ && x == 1 && n > 0) ok = pipe_wait(&bars[PB_W_FREE], (n - 1) & 1, sFail, TR(3));
+                        if (!ok) break;
+                        tc_fence_after();
+                        constexpr uint32_t kRowsB = 64 * 128 / 16;     // tile rows 64.. of each d-block, 16-byte units
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * (RING * 128) + (kk & 3) * 32;
-                    umma_ss(tmem_base + C_DP, make_smem_desc(aVb + off, 16, 1024, SWIZZLE_128B),
-                            make_smem_desc(aG + off, 16, 1024, SWIZZLE_128B), idesc_s, kk > 0);
-                }
-                umma_commit(bar);
-                if (!mbar_wait(bar, phase)) *sFail = 1;
-            }
-            phase ^= 1;
-            __syncthreads();                                                   // B2
-            tc_fence_after();
-            if (*sFail) { failed = true; break; }
-
-            // --- P^T and gA^T for this thread's (lane k, 32-column chunk) in two rounds.  Round r
-            //     covers chunks 2r (half 0) and 2r+1 (half 1); their BF16 results land on columns
-            //     that both halves have finished reading, hence the barrier inside the round.
-            const bool single = n_vis == 1;     // one visible key: score gradients are exactly zero
-#pragma unroll 1
-            for (int rd = 0; rd < 2; ++rd) {
-                const int c = 2 * rd + half;
-                uint32_t x[32], dp[32], pk[16], gk[16];
-                tmem_ld32(tl + C_XT + c * 32, x);
-                tmem_ld32(tl + C_DP + c * 32, dp);
-                tmem_wait_ld();
-                const uint32_t cw = my_vis ? (rd == 0 ? (half ? vw1 : vw0) : (half ? vw3 : vw2)) : 0u;
+                        for (int kk = 0; kk < D / 16; ++kk) {
+                            const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
+                            umma_ss_warp(tXT + x * 64, dKb + off, dQpK + (off + x * kRowsB), idesc_s, kk > 0);
+                        }
 #pragma unroll
-                for (int t = 0; t < 32; t += 2) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2, -lse2));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2, -lse2));
-                    if (!all_vis) {
-                        if (!((cw >> t) & 1u)) p0 = 0.f;
-                        if (!((cw >> (t + 1)) & 1u)) p1 = 0.f;
+                        for (int kk = 0; kk < D / 16; ++kk) {
+                            const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
+                            umma_ss_warp(tDP + x * 64, dVb + off, dGK + (off + x * kRowsB), idesc_s, kk > 0);
+                        }
+                        umma_commit_warp(&bars[x ? PB_S_FULL_B : PB_S_FULL_A]);
                     }
-                    float g0 = p0 * (__uint_as_float(dp[t]) - delta);
-                    float g1 = p1 * (__uint_as_float(dp[t + 1]) - delta);
-                    if (single) { g0 = 0.f; g1 = 0.f; }
-                    pk[t >> 1] = pack_bf16x2(p0, p1);
-                    gk[t >> 1] = pack_bf16x2(g0, g1);
+                    // ---- accumulation halves (K = 64 rows of the Hadamard tiles each)
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        if (!ok) break;
+                        ok = pipe_wait(&bars[x ? PB_P_FULL_B : PB_P_FULL_A], ph, sFail, TR(4 + x));
+                        if (!ok) break;
+                        tc_fence_after();
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; ++k4) {
+                            const int kk = x * 4 + k4;
+                            umma_ts_warp(tAK, tDP + kk * 8, dQpM + kk * (2048 / 16), idesc_acc, 1);
+                        }
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; ++k4) {
+                            const int kk = x * 4 + k4;
+                            umma_ts_warp(tAV, tXT + kk * 8, dGM + kk * (2048 / 16), idesc_acc, 1);
+                        }
+                        umma_commit_warp(&bars[x ? PB_D_DONE_B : PB_D_DONE_A]);
+                    }
+                    if (ok && WITH_DQ) {
+#pragma unroll
+                        for (int dh = 0; dh < D / 64; ++dh)
+#pragma unroll
+                            for (int kk = 0; kk < RING / 16; ++kk)
+                                umma_ts_warp(tmem_base + (dh ? C_W1 : C_W0), tDP + kk * 8,
+                                        dKaM + (dh * (RING * 128) + kk * 2048) / 16, idesc_w, kk > 0);
+                        umma_commit_warp(&bars[PB_W_FULL]);
+                    }
                 }
-                tc_fence_before();
-                __syncthreads();
-                tc_fence_after();
-                tmem_st16(tl + C_XT + c * 16, pk);
-                tmem_st16(tl + C_DP + c * 16, gk);
+                ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+                ++n;
             }
+            // every MMA of this query has been issued: signal the ring rows free once they complete
+            if (n > n_query && ok) umma_commit_warp(&bars[PB_RING_FREE]);
+            n_query = n;
+        }
+        // Let the last committed group finish before the tensor memory is released.
+        if (n > 0 && ok) pipe_wait(&bars[WITH_DQ ? PB_W_FULL : PB_D_DONE_B], (n - 1) & 1, sFail);
+        __syncwarp();
+        }
+    } else {
+        // ================================================================== E warps
+        cta_start_sync();
+        const int slot = tid & (RING - 1);               // tensor-memory lane = ring slot
+        const int ch = tid >> 7;                          // which 32-column chunk of each half
+        const uint32_t tl = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        {
+            uint32_t z[32];
+#pragma unroll
+            for (int t = 0; t < 32; ++t) z[t] = 0;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) tmem_st32(tl + (ch ? C_AV : C_AK) + c * 32, z);
             tmem_wait_st();
             tc_fence_before();
-            __syncthreads();                                                   // B3
-            if (tid == 0) {
-                tc_fence_after();
+        }
+        auto flush = [&](int quarter, int only_lane, int i_ref, bool rezero) {
+            if ((warp & 3) != quarter) return;
+            const uint32_t col = ch ? C_AV : C_AK;
+            float* dst_base = ch ? gPartV : gPartK;
+            const float mul = ch ? 1.0f : p.scale;
+            const int key = ring_key(i_ref, slot);
+            const bool mine = (only_lane < 0 || lane == only_lane) && key >= 0;
+            uint32_t a[32];
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                tmem_ld32(tl + col + c * 32, a);
+                tmem_wait_ld();
+                if (mine) {
+                    float4* dst = reinterpret_cast<float4*>(dst_base + static_cast<size_t>(key) * D + c * 32);
 #pragma unroll
-                for (int kk = 0; kk < RING / 16; ++kk)      // dKb += gA^T . Qp
-                    umma_ts(tmem_base + C_AK, tmem_base + C_DP + kk * 8,
-                            make_smem_desc(aQp + kk * 2048, RING * 128, 1024, SWIZZLE_128B), idesc_acc, 1);
-#pragma unroll
-                for (int kk = 0; kk < RING / 16; ++kk)      // dVb += P^T . Gt
-                    umma_ts(tmem_base + C_AV, tmem_base + C_XT + kk * 8,
-                            make_smem_desc(aG + kk * 2048, RING * 128, 1024, SWIZZLE_128B), idesc_acc, 1);
-                if (WITH_DQ) {
-#pragma unroll
-                    for (int dh = 0; dh < D / 64; ++dh)     // W[:, 64 dh ..] = gA^T . Ka
-#pragma unroll
-                        for (int kk = 0; kk < RING / 16; ++kk)
-                            umma_ts(tmem_base + (dh ? C_W1 : C_W0), tmem_base + C_DP + kk * 8,
-                                    make_smem_desc(aKa + dh * (RING * 128) + kk * 2048, RING * 128, 1024,
-                                                   SWIZZLE_128B),
-                                    idesc_w, kk > 0);
+                    for (int t = 0; t < 8; ++t)
+                        dst[t] = make_float4(mul * __uint_as_float(a[4 * t]), mul * __uint_as_float(a[4 * t + 1]),
+                                             mul * __uint_as_float(a[4 * t + 2]), mul * __uint_as_float(a[4 * t + 3]));
                 }
-                umma_commit(bar);
-                if (!mbar_wait(bar, phase)) *sFail = 1;
-            }
-            phase ^= 1;
-            asm volatile("cp.async.wait_all;" ::: "memory");
-            __syncthreads();                                                   // B4
-            tc_fence_after();
-            if (*sFail) { failed = true; break; }
-
-            if (WITH_DQ) {
-                // dQ[d] = scale * sum_k Kb_k[d] * W[k][d]; this thread: lane k, d in its half.
-                // D = 128: half h reads W columns of d-block h.  D = 64: both halves share block 0.
-                const uint32_t wcol = (D == 128) ? (half ? C_W1 : C_W0) : (C_W0 + half * 32);
+                if (rezero) {
+                    if (only_lane < 0 || lane == only_lane) {
 #pragma unroll
-                for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t u[32];
-                    float v[32];
-                    tmem_ld32(tl + wcol + c * 32, u);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const uint4 kb =
-                            *reinterpret_cast<const uint4*>(sKb + sw128_offset<RING>(slot, half * HCH + c * 4 + q));
-                        const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 kf = unpack_bf16x2(w4[e]);
-                            v[q * 8 + 2 * e] = kf.x * __uint_as_float(u[q * 8 + 2 * e]);
-                            v[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[q * 8 + 2 * e + 1]);
-                        }
+                        for (int t = 0; t < 32; ++t) a[t] = 0;
                     }
-                    const float s = warp_transpose_sum(v, lane);
-                    sRed[(warp & 3) * D + half * HD + c * 32 + lane] = s;
+                    tmem_st32(tl + col + c * 32, a);
                 }
+            }
+            if (rezero) {
+                tmem_wait_st();
                 tc_fence_before();
-                __syncthreads();                                               // B5
-                if (tid < D)
-                    p.dQ[row * D + tid] =
-                        __float2bfloat16(p.scale * (sRed[tid] + sRed[D + tid] + sRed[2 * D + tid] + sRed[3 * D + tid]));
+            }
+        };
+        // per-head scalars, fetched one iteration ahead: this lane's slice of dY and Y, and m, l
+        uint2 pre_dy = make_uint2(0, 0), pre_y = make_uint2(0, 0);
+        uint32_t pre_dy2[2] = {0, 0}, pre_y2[2] = {0, 0};
+        float pre_m = 0.f, pre_l = 0.f;
+        auto prefetch = [&](int it) {
+            const size_t row = row_index(it);
+            if (D == 128) {
+                pre_dy = __ldg(reinterpret_cast<const uint2*>(p.dY + row * D) + lane);
+                pre_y = __ldg(reinterpret_cast<const uint2*>(p.Y + row * D) + lane);
+            } else {
+                pre_dy2[0] = __ldg(reinterpret_cast<const uint32_t*>(p.dY + row * D) + lane);
+                pre_y2[0] = __ldg(reinterpret_cast<const uint32_t*>(p.Y + row * D) + lane);
+            }
+            pre_m = __ldg(p.m + row);
+            pre_l = __ldg(p.l + row);
+        };
+        prefetch(0);
+        uint64_t* bar_head = &bars[WITH_DQ ? PB_W_FULL : PB_D_DONE_B];
+        int n = 0, it = 0, n_query = 0;
+        bool ok = true;
+        for (int i = q0; i < q1 && ok; ++i) {
+            if (i > q0) {
+                if (n > 0) {
+                    ok = pipe_wait(bar_head, (n - 1) & 1, sFail, TR(13));
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                const int s = i & (RING - 1);
+                flush(s >> 5, s & 31, i - 1, true);
+            }
+            uint32_t vw[4];
+            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
+            const int n_vis = __popc(vw[0]) + __popc(vw[1]) + __popc(vw[2]) + __popc(vw[3]);
+            const bool all_vis = n_vis == RING;
+            const bool single = n_vis == 1;
+            const bool my_vis = (vw[warp & 3] >> lane) & 1u;
+            for (int hh = 0; hh < G && ok; ++hh, ++it) {
+                const size_t row = row_index(it);
+                // delta = dY . Y and lse (log2 units) of this head from the prefetched slices
+                float delta;
+                if (D == 128) {
+                    const float2 a0 = unpack_bf16x2(pre_dy.x), a1 = unpack_bf16x2(pre_dy.y);
+                    const float2 b0 = unpack_bf16x2(pre_y.x), b1 = unpack_bf16x2(pre_y.y);
+                    delta = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
+                } else {
+                    const float2 a0 = unpack_bf16x2(pre_dy2[0]), b0 = unpack_bf16x2(pre_y2[0]);
+                    delta = a0.x * b0.x + a0.y * b0.y;
+                }
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) delta += __shfl_xor_sync(0xFFFFFFFFu, delta, o);
+                const float m_i = pre_m, l_i = pre_l;
+                if (it + 1 < n_iter) prefetch(it + 1);
+                if (n_vis == 0 || !(l_i > 0.f)) {
+                    if (WITH_DQ && tid < D) p.dQ[row * D + tid] = __float2bfloat16(0.f);
+                    continue;
+                }
+                const float lse2 = m_i * LOG2E + __log2f(l_i);
+                const uint32_t ph = n & 1;
+#pragma unroll 1
+                for (int x = 0; x < 2; ++x) {
+                    ok = pipe_wait(&bars[x ? PB_S_FULL_B : PB_S_FULL_A], ph, sFail, TR(8 + x));
+                    if (!ok) break;
+                    tc_fence_after();
+                    const int c = 2 * x + ch;                      // 32-column chunk of the score tile
+                    uint32_t xr[32], dp[32], pk[16], gk[16];
+                    long long tt = tracer ? clock64() : 0;
+                    tmem_ld32(tl + C_XT + c * 32, xr);
+                    tmem_ld32(tl + C_DP + c * 32, dp);
+                    tmem_wait_ld();
+                    if (tracer) { const long long t2 = clock64(); p.trace[20] += t2 - tt; tt = t2; }
+                    const uint32_t cw = my_vis ? (c == 0 ? vw[0] : c == 1 ? vw[1] : c == 2 ? vw[2] : vw[3]) : 0u;
+#pragma unroll
+                    for (int t = 0; t < 32; t += 2) {
+                        float p0 = fast_exp2(fmaf(__uint_as_float(xr[t]), c2, -lse2));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(xr[t + 1]), c2, -lse2));
+                        if (!all_vis) {
+                            if (!((cw >> t) & 1u)) p0 = 0.f;
+                            if (!((cw >> (t + 1)) & 1u)) p1 = 0.f;
+                        }
+                        float g0 = p0 * (__uint_as_float(dp[t]) - delta);
+                        float g1 = p1 * (__uint_as_float(dp[t + 1]) - delta);
+                        if (single) { g0 = 0.f; g1 = 0.f; }
+                        pk[t >> 1] = pack_bf16x2(p0, p1);
+                        gk[t >> 1] = pack_bf16x2(g0, g1);
+                    }
+                    if (tracer) { const long long t2 = clock64(); p.trace[21] += t2 - tt; tt = t2; }
+                    if (x == 0) {
+                        // The BF16 results of half a land on score columns [0,32) that the ch = 0
+                        // threads read: wait until every E thread has its loads in registers.
+                        tc_fence_before();
+                        warp_arrive(&bars[PB_E_SYNC], lane);
+                        ok = pipe_wait(&bars[PB_E_SYNC], ph, sFail, TR(10));
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
+                    if (tracer) tt = clock64();
+                    tmem_st16(tl + C_XT + c * 16, pk);
+                    tmem_st16(tl + C_DP + c * 16, gk);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    if (tracer) p.trace[22] += clock64() - tt;
+                    warp_arrive(&bars[x ? PB_P_FULL_B : PB_P_FULL_A], lane);
+                }
+                if (!ok) break;
+                if (WITH_DQ) {
+                    ok = pipe_wait(&bars[PB_W_FULL], ph, sFail, TR(11));
+                    if (!ok) break;
+                    tc_fence_after();
+                    const long long te = tracer ? clock64() : 0;
+                    // dQ[d] = scale * sum_k Kb_k[d] * W[k][d]; this thread: lane k, d in its half.
+                    const uint32_t wcol = (D == 128) ? (ch ? C_W1 : C_W0) : (C_W0 + ch * 32);
+                    constexpr int NC = HD / 32;
+                    float* red = sRed + (n & 1) * 4 * D;
+#pragma unroll 1
+                    for (int c = 0; c < NC; ++c) {
+                        uint32_t u[32];
+                        float v[32];
+                        tmem_ld32(tl + wcol + c * 32, u);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint4 kb = *reinterpret_cast<const uint4*>(
+                                sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + q));
+                            const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 kf = unpack_bf16x2(w4[e]);
+                                v[q * 8 + 2 * e] = kf.x * __uint_as_float(u[q * 8 + 2 * e]);
+                                v[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[q * 8 + 2 * e + 1]);
+                            }
+                        }
+                        if (c == NC - 1) {
+                            // W and this thread's Kb row are in registers: the next head may overwrite them
+                            tc_fence_before();
+                            warp_arrive(&bars[PB_W_FREE], lane);
+                        }
+                        const float s = warp_transpose_sum(v, lane);
+                        red[(warp & 3) * D + ch * HD + c * 32 + lane] = s;
+                    }
+                    if (tracer) p.trace[23] += clock64() - te;
+                    warp_arrive(&bars[PB_E_SYNC2], lane);
+                    ok = pipe_wait(&bars[PB_E_SYNC2], ph, sFail, TR(12));
+                    if (!ok) break;
+                    if (tid < D)
+                        p.dQ[row * D + tid] =
+                            __float2bfloat16(p.scale * (red[tid] + red[D + tid] + red[2 * D + tid] + red[3 * D + tid]));
+                }
+                ++n;
+            }
+            // dQ pass: this warp has read the Kb rows of the query's last head (in its epilogue)
+            if (WITH_DQ && ok && n > n_query) warp_arrive(&bars[PB_RING_FREE], lane);
+            n_query = n;
+        }
+        // Drain: every slot still holds a key of (q1 - 129, q1 - 1].
+        if (ok) {
+            if (n > 0) {
+                ok = pipe_wait(bar_head, (n - 1) & 1, sFail);
+                tc_fence_after();
+            }
+            if (ok) {
+#pragma unroll 1
+                for (int quarter = 0; quarter < 4; ++quarter) flush(quarter, -1, q1 - 1, false);
             }
         }
     }
-    // Drain: every slot still holds a key of (q1 - 129, q1 - 1].
-    if (!failed) {
-#pragma unroll 1
-        for (int quarter = 0; quarter < 4; ++quarter) flush(quarter, -1, q1 - 1, false);
-    }
-    if (failed && tid == 0) atomicExch(p.status, 2);
+    if (tracer) p.trace[tid == 0 ? 14 : (tid == PIPE_E_THREADS ? 19 : 6)] += clock64() - t_begin;
+#undef TR
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (*sFail && tid == 0) atomicExch(p.status, 3);
+    if (is_mma) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 // Sums the parity partials of one key side into BF16 outputs.  Row k of batch b,

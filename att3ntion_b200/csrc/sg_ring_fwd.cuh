@@ -176,7 +176,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParam
 
     const uint32_t idesc_x = make_idesc_bf16(RING, RING, 0, 0);
     const uint32_t idesc_u = make_idesc_bf16(RING, D, 0, 1);
-    const uint32_t aQp = smem_u32(sQp), aS = smem_u32(sS), aVs = smem_u32(sVs);
+    // descriptor bases, built once; a k-step adds a constant to the start-address field
+    const uint64_t dQp = make_smem_desc(smem_u32(sQp), 16, 1024, SWIZZLE_128B);           // A, K-major
+    const uint64_t dS = make_smem_desc(smem_u32(sS), 16, 1024, SWIZZLE_128B);             // B, K-major
+    const uint64_t dVsM = make_smem_desc(smem_u32(sVs), RING * 128, 1024, SWIZZLE_128B);  // B, MN-major
     const float c2 = p.scale * LOG2E;
     uint32_t phase = 0;
     bool failed = false;
@@ -234,16 +237,17 @@ __global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParam
             fence_async_smem();
             tc_fence_before();
             __syncthreads();                                           // B1
-            if (tid == 0) {
+            if (warp == 0) {
+                // whole warp, one elected lane issues: operands stay warp-uniform (see umma_ss_warp)
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * (RING * 128) + (kk & 3) * 32;
-                    umma_ss(tmem_base, make_smem_desc(aQp + off, 16, 1024, SWIZZLE_128B),
-                            make_smem_desc(aS + off, 16, 1024, SWIZZLE_128B), idesc_x, kk > 0);
+                    const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
+                    umma_ss_warp(tmem_base, dQp + off, dS + off, idesc_x, kk > 0);
                 }
-                umma_commit(bar);
-                if (!mbar_wait(bar, phase)) *sFail = 1;
+                umma_commit_warp(bar);
+                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
+                __syncwarp();
             }
             phase ^= 1;
             __syncthreads();                                           // B2
@@ -300,14 +304,14 @@ __global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParam
             if (lane == 0) sMpart[warp] = m_w;
             tc_fence_before();
             __syncthreads();                                           // B3
-            if (tid == 0) {
+            if (warp == 0) {
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < RING / 16; ++kk)
-                    umma_ts(tmem_base + 128, tmem_base + kk * 8,
-                            make_smem_desc(aVs + kk * 2048, RING * 128, 1024, SWIZZLE_128B), idesc_u, kk > 0);
-                umma_commit(bar);
-                if (!mbar_wait(bar, phase)) *sFail = 1;
+                    umma_ts_warp(tmem_base + 128, tmem_base + kk * 8, dVsM + kk * (2048 / 16), idesc_u, kk > 0);
+                umma_commit_warp(bar);
+                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
+                __syncwarp();
             }
             phase ^= 1;
             const float M = fmaxf(fmaxf(sMpart[0], sMpart[1]), fmaxf(sMpart[2], sMpart[3]));

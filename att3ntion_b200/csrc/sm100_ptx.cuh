@@ -177,6 +177,50 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         : "memory");
 }
 
+// Whole-warp variants: every lane executes the call with identical (warp-uniform)
+// operands and one elected lane issues the MMA.  Keeping the warp converged lets the
+// compiler hold descriptors and addresses in uniform registers, which is what the
+// instruction takes; issuing from a divergent `lane == 0` branch costs a register-file
+// round trip per operand and limits the issue rate to one MMA per 100-200 cycles.
+__device__ __forceinline__ void umma_ss_warp(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .b32 rx;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync rx|q, 0xFFFFFFFF;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_ts_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .b32 rx;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "elect.sync rx|q, 0xFFFFFFFF;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_warp(uint64_t* bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q;\n\t"
+        ".reg .b32 rx;\n\t"
+        "elect.sync rx|q, 0xFFFFFFFF;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}\n" ::"r"(smem_u32(bar))
+        : "memory");
+}
+
 // Arrives once on `bar` when every MMA issued so far by this thread has
 // completed.  Implies tcgen05.fence::before_thread_sync.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {

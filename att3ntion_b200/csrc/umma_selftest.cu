@@ -21,6 +21,7 @@ struct SelftestParams {
     int mode;
     uint32_t lbo_a, sbo_a, lbo_b, sbo_b;
     int reps;
+    int tight;                    // mode | 16: converged-warp issue with precomputed descriptors
     int* status;
 };
 
@@ -30,6 +31,7 @@ struct SelftestParams {
 // mode 3: D[m][n] = sum_k A[m][k] * B[k][n]   (A in tensor memory, B MN-major)
 // mode 4: D[m][n] = sum_k A[m][k] * B[n][k]   (A in tensor memory, B K-major)
 __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p) {
+    long long t_issue = 0;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // 1024-byte alignment keeps the swizzle phase equal to (row & 7).
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -68,6 +70,9 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
     const uint32_t tmem_a = tmem_base + 128;      // columns [128,192): packed BF16 A operand
     const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
 
+    const int nwidth = (p.mode & 8) ? 64 : T;       // mode | 8: the same product restricted to N = 64 columns
+    p.tight = (p.mode & 16) ? 1 : 0;
+    p.mode &= 7;
     const bool a_in_tmem = (p.mode == 3 || p.mode == 4);
     if (a_in_tmem) {
         // Thread m holds row m of A: 128 BF16 = 64 packed words = columns [0,64) of the A region.
@@ -84,11 +89,33 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
     }
     __syncthreads();
 
-    if (tid == 0) {
+    if (p.tight && warp == 0) {
+        // Rate probe: whole warp converged, descriptor bases precomputed, k-steps unrolled.
+        tc_fence_after();
+        const int b_mn = (p.mode == 1 || p.mode == 3) ? 1 : 0;
+        const uint32_t idesc = make_idesc_bf16(T, nwidth, 0, b_mn);
+        const uint64_t da = make_smem_desc(smem_u32(sA), p.lbo_a, p.sbo_a, SWIZZLE_128B);
+        const uint64_t db = make_smem_desc(smem_u32(sB), p.lbo_b, p.sbo_b, SWIZZLE_128B);
+        const long long t0 = clock64();
+        for (int rep = 0; rep < p.reps; ++rep) {
+#pragma unroll
+            for (int kk = 0; kk < T / 16; ++kk) {
+                const uint32_t koff = ((kk >> 2) * (T * 128) + (kk & 3) * 32) / 16;
+                const uint32_t moff = kk * 2048 / 16;
+                const uint32_t acc = (rep > 0 || kk > 0) ? 1u : 0u;
+                if (a_in_tmem) umma_ts_warp(tmem_d, tmem_a + kk * 8, db + (b_mn ? moff : koff), idesc, acc);
+                else umma_ss_warp(tmem_d, da + koff, db + (b_mn ? moff : koff), idesc, acc);
+            }
+        }
+        const long long t1 = clock64();
+        umma_commit_warp(&mma_bar);
+        if (tid == 0) { p.status[2] = static_cast<int>(t1 - t0); t_issue = t0; }
+    } else if (!p.tight && tid == 0) {
         tc_fence_after();
         const int a_mn = (p.mode == 2) ? 1 : 0;
         const int b_mn = (p.mode == 1 || p.mode == 2 || p.mode == 3) ? 1 : 0;
-        const uint32_t idesc = make_idesc_bf16(T, T, a_mn, b_mn);
+        const uint32_t idesc = make_idesc_bf16(T, nwidth, a_mn, b_mn);
+        t_issue = clock64();
         const uint32_t a_base = smem_u32(sA), b_base = smem_u32(sB);
         for (int rep = 0; rep < p.reps; ++rep) {
 #pragma unroll 1
@@ -107,10 +134,19 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
                 }
             }
         }
+        const long long t_issued = clock64();
         umma_commit(&mma_bar);
+        p.status[2] = static_cast<int>(t_issued - t_issue);              // cycles spent issuing
     }
-    __syncwarp();
-    const bool ok = mbar_wait(&mma_bar, 0);
+    // Only the issuing thread polls; the others park at the CTA barrier so that nothing
+    // competes with the operand traffic while the rate is measured.
+    __shared__ int s_ok;
+    if (tid == 0) {
+        s_ok = mbar_wait(&mma_bar, 0) ? 1 : 0;
+        p.status[1] = static_cast<int>(clock64() - t_issue);             // cycles from first issue to completion
+    }
+    __syncthreads();
+    const bool ok = s_ok != 0;
     tc_fence_after();
     if (!ok) {
         if ((tid & 31) == 0) atomicExch(p.status, 1);
@@ -137,8 +173,8 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
 extern "C" int att3_umma_selftest(const void* A, const void* B, float* D, int mode, int lbo_a, int sbo_a,
                                   int lbo_b, int sbo_b, int reps, int* status_dev, void* stream) {
     if (!A || !B || !D || !status_dev) return att3::set_error(ATT3_ERR_INVALID, "umma_selftest: null pointer");
-    if (mode < 0 || mode > 4 || reps < 1 || reps > 8)
-        return att3::set_error(ATT3_ERR_INVALID, "umma_selftest: mode must be 0..4 and reps 1..8");
+    if ((mode & 7) > 4 || mode < 0 || mode > 31 || ((mode & 16) && (mode & 7) == 2) || reps < 1 || reps > 64)
+        return att3::set_error(ATT3_ERR_INVALID, "umma_selftest: mode must be 0..4 (+8: N = 64, +16: converged-warp issue) and reps 1..64");
     SelftestParams p;
     p.A = static_cast<const __nv_bfloat16*>(A);
     p.B = static_cast<const __nv_bfloat16*>(B);
@@ -146,6 +182,7 @@ extern "C" int att3_umma_selftest(const void* A, const void* B, float* D, int mo
     p.mode = mode;
     p.lbo_a = lbo_a; p.sbo_a = sbo_a; p.lbo_b = lbo_b; p.sbo_b = sbo_b;
     p.reps = reps;
+    p.tight = 0;
     p.status = status_dev;
     const int smem = 2 * TILE_BYTES + 1024;
     cudaError_t e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
