@@ -263,3 +263,83 @@ def tc_set_enabled(forward: bool, backward: bool):
     prev = tuple(_enabled)
     _enabled[0], _enabled[1] = bool(forward), bool(backward)
     return prev
+
+
+# --------------------------------------------------------------------------- three-gather hypergraph attention
+
+_HG_NAMES = ("Q", "R", "S", "Vq_1", "Vq_2", "Vr_1", "Vr_2", "Vs_1", "Vs_2")
+
+
+def _check_hg(tensors, mask, who):
+    Q = tensors[0]
+    if not (isinstance(Q, torch.Tensor) and Q.is_cuda and Q.dim() == 4):
+        raise RuntimeError(f"{who}: inputs must be CUDA [B,H,N,D] tensors")
+    B, H, N, D = Q.shape
+    if D not in (16, 32, 64, 128):
+        raise RuntimeError(f"{who}: head dim must be 16, 32, 64 or 128, got {D}")
+    if N % 16:
+        raise RuntimeError(f"{who}: N must be a multiple of 16, got {N}")
+    for name, t in zip(_HG_NAMES, tensors):
+        if not (t.is_cuda and t.device == Q.device and t.dtype == _BF16 and t.is_contiguous()):
+            raise RuntimeError(f"{who}: {name} must be contiguous bf16 on Q's device")
+        if t.shape != Q.shape:
+            raise RuntimeError(f"{who}: masked/tensor-core path requires equal shapes, {name} is {tuple(t.shape)}")
+    if mask is not None and mask.numel():
+        if not (mask.is_cuda and mask.device == Q.device and mask.dtype == torch.bool and mask.is_contiguous()
+                and tuple(mask.shape) == (B, N, N)):
+            raise RuntimeError(f"{who}: mask must be a contiguous bool [B,N,N] on Q's device")
+        return mask
+    return None
+
+
+def _scatter_in_use(*tensors) -> bool:
+    """True if any of the tensors has a non-zero entry (host sync, as the reference's
+    `scatter_used` gate: cuda/forward.cu:1541-1542)."""
+    return any(bool(t.ne(0).any().item()) for t in tensors)
+
+
+def forward(Q, R, S, Vq_1, Vq_2, Vr_1, Vr_2, Vs_1, Vs_2, dropout_rate=0.0, I_valid=-1, J_valid=-1, K_valid=-1,
+            mask=None, gather_mode=0):
+    """Three anchored gathers (and scatters) of one score cube; returns
+    (Y_q, Y_r, Y_s, Y_q_, Y_r_, Y_s_, m_i, l_i, m_j, l_j, m_k, l_k) as the reference's
+    `forward` (cpp/cuda_bindings.cpp:143-177).  dropout_rate is accepted and unused,
+    as in the reference (cuda/forward.cu:1259)."""
+    ts = [Q, R, S, Vq_1, Vq_2, Vr_1, Vr_2, Vs_1, Vs_2]
+    mask = _check_hg(ts, mask, "forward")
+    B, H, N, D = Q.shape
+    n_valid = int(I_valid) if 0 < int(I_valid) < N else 0
+    scatter = 1 if (gather_mode == 0 and _scatter_in_use(Vq_2, Vr_2, Vs_2)) else 0
+    with torch.cuda.device(Q.device):
+        outs = [torch.empty_like(Q) for _ in range(6)]
+        stats = [torch.empty((B, H, N), dtype=torch.float32, device=Q.device) for _ in range(6)]
+        _call(lib.att3_hg_forward, *[t.data_ptr() for t in ts], _ptr(mask), *[o.data_ptr() for o in outs],
+              *[s.data_ptr() for s in stats], B, H, N, D, n_valid, int(gather_mode), scatter, _stream(Q))
+    return (*outs, *stats)
+
+
+def backward(grad_Y_q, grad_Y_r, grad_Y_s, grad_Y_q_, grad_Y_r_, grad_Y_s_, Q, R, S, Vq_1, Vq_2, Vr_1, Vr_2, Vs_1,
+             Vs_2, m_i, l_i, m_j, l_j, m_k, l_k, dropout_rate=0.0, mask=None, Y_q=None, Y_r=None, Y_s=None):
+    """Nine gradients from the forward's statistics (cpp/cuda_bindings.cpp:179-233).  The
+    gather outputs Y_q, Y_r, Y_s are required: the Jacobian correction is rowsum(dY o Y)."""
+    ts = [Q, R, S, Vq_1, Vq_2, Vr_1, Vr_2, Vs_1, Vs_2]
+    mask = _check_hg(ts, mask, "backward")
+    if Y_q is None or Y_r is None or Y_s is None:
+        raise RuntimeError("backward: tensor-core path unavailable without the forward outputs Y_q, Y_r, Y_s")
+    B, H, N, D = Q.shape
+    gs = [grad_Y_q, grad_Y_r, grad_Y_s, grad_Y_q_, grad_Y_r_, grad_Y_s_]
+    for g in gs + [Y_q, Y_r, Y_s]:
+        if not (g.is_cuda and g.device == Q.device and g.dtype == _BF16 and g.is_contiguous() and g.shape == Q.shape):
+            raise RuntimeError("backward: cotangents and outputs must be contiguous bf16 [B,H,N,D] on Q's device")
+    # gather_mode 1 leaves (m = +1e30, l = 1) in the R/S statistics (cuda/forward.cu:1455-1459)
+    gather_mode = 1 if bool((m_j[0, 0, 0] > 1e29).item()) else 0
+    scatter = 1 if (gather_mode == 0 and _scatter_in_use(grad_Y_q_, grad_Y_r_, grad_Y_s_)) else 0
+    with torch.cuda.device(Q.device):
+        grads = [torch.empty_like(Q) for _ in range(9)]
+        nbytes = lib.att3_hg_backward_workspace_bytes(B, H, N, D)
+        ws = _workspace(Q.device, nbytes)
+        _call(lib.att3_hg_backward, *[g.data_ptr() for g in gs], *[t.data_ptr() for t in ts],
+              Y_q.data_ptr(), Y_r.data_ptr(), Y_s.data_ptr(),
+              m_i.data_ptr(), l_i.data_ptr(), m_j.data_ptr(), l_j.data_ptr(), m_k.data_ptr(), l_k.data_ptr(),
+              _ptr(mask), *[g.data_ptr() for g in grads], B, H, N, D, 0, gather_mode, scatter,
+              ws.data_ptr(), nbytes, _stream(Q))
+    return tuple(grads)

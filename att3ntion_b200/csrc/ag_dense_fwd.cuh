@@ -1,0 +1,337 @@
+// Dense anchored gather, forward, for sm_100a.
+//
+//   Y[a] = sum_{j,k} softmax_{(j,k)}( scale * sum_d A_a[d] Rw_j[d] C_k[d] ) Vrow[j] o Vcol[k]
+//
+// for an "anchor" tensor A and two key-side tensors Rw ("rows") and C ("cols"),
+// every key a candidate, visibility given by a [B,N,N] mask (pair (j,k) is live for
+// anchor a iff mask[b,a,j] and mask[b,a,k]) and by a valid length.  This one
+// operator serves the reference's anchored tensor-core gather with its three role
+// bindings (cuda/forward.cu:108-477 and the role table at its launcher): Y_q uses
+// (A,Rw,C) = (Q,R,S), Y_r = (R,Q,S), Y_s = (S,Q,R); and the un-windowed
+// single_gather_forward (cuda/forward.cu:1666-1719) is the first binding alone.
+//
+// Schedule: a CTA owns a group of anchors of one (batch, head).  It walks the
+// 128x128 (row tile, col tile) grid; the col tile (C, Vcol) is staged once per tile
+// in shared memory in the 128-byte swizzle, the row tile (Rw, Vrow) lives in
+// registers, one row per thread.  For every anchor of the group the tile is
+// processed exactly like one (query, head) of the windowed kernel
+// (sg_ring_fwd.cuh): Hadamard tile -> score MMA -> per-row softmax -> value MMA with
+// P read from tensor memory -> shuffle collapse; the per-tile result is merged into
+// the anchor's running (max, sum, Y) state in shared memory with the usual
+// log-sum-exp rescaling.  Head dims below 64 are zero-padded to 64 in the operand
+// tiles (the padding contributes nothing to either contraction).
+#pragma once
+
+#include "sg_ring_fwd.cuh"
+
+namespace agdense {
+
+using namespace sm100;
+using sgring::warp_transpose_sum;
+using sgring::LOG2E;
+using sgring::NEG_INF_F;
+
+constexpr int TILE = 128;
+constexpr int NTHREADS = 128;
+constexpr int MAX_GROUP = 16;       // anchors per CTA
+
+struct FwdParams {
+    const __nv_bfloat16* A;         // anchor   [B,H,N,D]
+    const __nv_bfloat16* Rw;        // rows     [B,H,N,D]
+    const __nv_bfloat16* C;         // cols     [B,H,N,D]
+    const __nv_bfloat16* Vrow;
+    const __nv_bfloat16* Vcol;
+    const uint8_t* mask;            // [B,N,N] or null; row index = anchor
+    __nv_bfloat16* Y;               // [B,H,N,D]
+    float* m;                       // [B,H,N]
+    float* l;
+    int B, H, N, D, n_valid, group;
+    float scale;
+    int* status;
+};
+
+template <int DP>
+struct FwdSmem {
+    static constexpr int TILE_BYTES = TILE * DP * 2;
+    static constexpr int OFF_C = 0;
+    static constexpr int OFF_VC = TILE_BYTES;
+    static constexpr int OFF_QP = 2 * TILE_BYTES;
+    static constexpr int OFF_STATE = 3 * TILE_BYTES;                       // MAX_GROUP x (DP + 4) floats
+    static constexpr int OFF_RED = OFF_STATE + MAX_GROUP * (DP + 4) * 4;   // 4 x (DP + 4) floats
+    static constexpr int OFF_MPART = OFF_RED + 4 * (DP + 4) * 4;
+    static constexpr int OFF_VIS = OFF_MPART + 16;                         // 4 row words + 4 col words
+    static constexpr int OFF_MISC = OFF_VIS + 32;
+    static constexpr int BYTES = OFF_MISC + 16;
+    static constexpr int ALLOC = BYTES + 1024;
+};
+
+// Loads row `idx` (D valid BF16, zero-padded to DP) of a [N][D] matrix as packed words.
+template <int DP>
+__device__ __forceinline__ void load_row_padded(const __nv_bfloat16* base, int idx, int N, int D, uint32_t (&r)[DP / 2]) {
+#pragma unroll
+    for (int c = 0; c < DP / 8; ++c) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (idx < N && c * 8 < D) v = __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(idx) * D) + c);
+        r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
+    }
+}
+
+template <int DP>
+__global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdParams p) {
+    using L = FwdSmem<DP>;
+    constexpr int CH = DP / 8, DW = DP / 2;
+    constexpr uint32_t TMEM_COLS = 256;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sC = smem + L::OFF_C;
+    uint8_t* sVc = smem + L::OFF_VC;
+    uint8_t* sQp = smem + L::OFF_QP;
+    float* sState = reinterpret_cast<float*>(smem + L::OFF_STATE);
+    float* sRed = reinterpret_cast<float*>(smem + L::OFF_RED);
+    float* sMpart = reinterpret_cast<float*>(smem + L::OFF_MPART);
+    uint32_t* sVis = reinterpret_cast<uint32_t*>(smem + L::OFF_VIS);
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::OFF_MISC);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::OFF_MISC + 8);
+    volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 12);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int a0 = blockIdx.x * p.group;
+    const int a1 = min(a0 + p.group, p.N);
+    if (a0 >= a1) return;
+    const int N = p.N, D = p.D;
+    const int n_keys = (p.n_valid > 0 && p.n_valid < N) ? p.n_valid : N;   // keys at or past this index are padding
+
+    if (warp == 0) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+        *sFail = 0;
+    }
+    // running state per anchor of the group: [0, DP) Y accumulator, [DP] max (raw score units), [DP+1] sum
+    for (int t = tid; t < MAX_GROUP * (DP + 4); t += NTHREADS) sState[t] = 0.f;
+    if (tid < MAX_GROUP) sState[tid * (DP + 4) + DP] = -INFINITY;
+
+    const size_t bh = (static_cast<size_t>(b) * p.H + h) * N;
+    const __nv_bfloat16* gA = p.A + bh * D;
+    const __nv_bfloat16* gRw = p.Rw + bh * D;
+    const __nv_bfloat16* gC = p.C + bh * D;
+    const __nv_bfloat16* gVrow = p.Vrow + bh * D;
+    const __nv_bfloat16* gVcol = p.Vcol + bh * D;
+    const uint8_t* mask_b = p.mask ? p.mask + static_cast<size_t>(b) * N * N : nullptr;
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t tX = tmem_base + lane_field, tU = tmem_base + lane_field + 128;
+    const uint32_t idesc_x = make_idesc_bf16(TILE, TILE, 0, 0);
+    const uint32_t idesc_u = make_idesc_bf16(TILE, DP, 0, 1);
+    const uint64_t dQp = make_smem_desc(smem_u32(sQp), 16, 1024, SWIZZLE_128B);
+    const uint64_t dC = make_smem_desc(smem_u32(sC), 16, 1024, SWIZZLE_128B);
+    const uint64_t dVcM = make_smem_desc(smem_u32(sVc), TILE * 128, 1024, SWIZZLE_128B);
+    const float c2 = p.scale * LOG2E;
+    uint32_t phase = 0;
+    bool failed = false;
+
+    const int n_tiles = (n_keys + TILE - 1) / TILE;
+    for (int jb = 0; jb < n_tiles && !failed; ++jb) {
+        uint32_t rRw[DW], rVr[DW];
+        const int jrow = jb * TILE + tid;
+        load_row_padded<DP>(gRw, jrow, n_keys, D, rRw);
+        load_row_padded<DP>(gVrow, jrow, n_keys, D, rVr);
+        for (int kb = 0; kb < n_tiles && !failed; ++kb) {
+            // stage the col tile; every MMA that read the previous one has been waited for
+            {
+                uint32_t t[DW];
+                const int krow = kb * TILE + tid;
+                load_row_padded<DP>(gC, krow, n_keys, D, t);
+#pragma unroll
+                for (int c = 0; c < CH; ++c)
+                    *reinterpret_cast<uint4*>(sC + sw128_offset<TILE>(tid, c)) =
+                        make_uint4(t[4 * c], t[4 * c + 1], t[4 * c + 2], t[4 * c + 3]);
+                load_row_padded<DP>(gVcol, krow, n_keys, D, t);
+#pragma unroll
+                for (int c = 0; c < CH; ++c)
+                    *reinterpret_cast<uint4*>(sVc + sw128_offset<TILE>(tid, c)) =
+                        make_uint4(t[4 * c], t[4 * c + 1], t[4 * c + 2], t[4 * c + 3]);
+            }
+            fence_async_smem();
+            for (int a = a0; a < a1 && !failed; ++a) {
+                // visibility of this tile's rows and cols from anchor a
+                {
+                    const int krow = kb * TILE + tid;
+                    bool vr = jrow < n_keys, vc = krow < n_keys;
+                    if (mask_b) {
+                        const uint8_t* mrow = mask_b + static_cast<size_t>(a) * N;
+                        if (vr) vr = mrow[jrow] != 0;
+                        if (vc) vc = mrow[krow] != 0;
+                    }
+                    const uint32_t wr = __ballot_sync(0xFFFFFFFFu, vr), wc = __ballot_sync(0xFFFFFFFFu, vc);
+                    if (lane == 0) { sVis[warp] = wr; sVis[4 + warp] = wc; }
+                }
+                __syncthreads();
+                const uint32_t vr_any = sVis[0] | sVis[1] | sVis[2] | sVis[3];
+                const uint32_t vc0 = sVis[4], vc1 = sVis[5], vc2 = sVis[6], vc3 = sVis[7];
+                const bool my_vis = (sVis[warp] >> lane) & 1u;
+                const bool all_cols = (vc0 & vc1 & vc2 & vc3) == 0xFFFFFFFFu;
+                if (vr_any == 0 || (vc0 | vc1 | vc2 | vc3) == 0) {
+                    __syncthreads();          // sVis is rewritten by the next anchor
+                    continue;
+                }
+                // --- Hadamard tile from the anchor row -----------------------------------------
+                {
+                    uint32_t q[DW];
+                    load_row_padded<DP>(gA, a, N, D, q);
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) {
+                        uint4 o;
+                        o.x = mul_bf16x2(q[4 * c], rRw[4 * c]);
+                        o.y = mul_bf16x2(q[4 * c + 1], rRw[4 * c + 1]);
+                        o.z = mul_bf16x2(q[4 * c + 2], rRw[4 * c + 2]);
+                        o.w = mul_bf16x2(q[4 * c + 3], rRw[4 * c + 3]);
+                        *reinterpret_cast<uint4*>(sQp + sw128_offset<TILE>(tid, c)) = o;
+                    }
+                }
+                fence_async_smem();
+                tc_fence_before();
+                __syncthreads();
+                if (warp == 0) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < DP / 16; ++kk) {
+                        const uint32_t off = ((kk >> 2) * (TILE * 128) + (kk & 3) * 32) / 16;
+                        umma_ss_warp(tmem_base, dQp + off, dC + off, idesc_x, kk > 0);
+                    }
+                    umma_commit_warp(bar);
+                    if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
+                    __syncwarp();
+                }
+                phase ^= 1;
+                __syncthreads();
+                tc_fence_after();
+                if (*sFail) { failed = true; break; }
+
+                // --- per-row softmax over the tile's visible columns ------------------------------
+                float m_row = -INFINITY, l_row = 0.f;
+                {
+                    uint32_t x[32];
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        tmem_ld32(tX + c * 32, x);
+                        tmem_wait_ld();
+                        const uint32_t vw = my_vis ? (c == 0 ? vc0 : c == 1 ? vc1 : c == 2 ? vc2 : vc3) : 0u;
+#pragma unroll
+                        for (int t = 0; t < 32; ++t)
+                            if ((vw >> t) & 1u) m_row = fmaxf(m_row, __uint_as_float(x[t]));
+                    }
+                    const bool live = m_row > -INFINITY;
+                    const float mc = (live ? m_row : 0.f) * c2;
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        tmem_ld32(tX + c * 32, x);
+                        tmem_wait_ld();
+                        const uint32_t vw = live ? (c == 0 ? vc0 : c == 1 ? vc1 : c == 2 ? vc2 : vc3) : 0u;
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int t = 0; t < 32; t += 2) {
+                            float e0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2, -mc));
+                            float e1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2, -mc));
+                            if (!all_cols || !live) {
+                                if (!((vw >> t) & 1u)) e0 = 0.f;
+                                if (!((vw >> (t + 1)) & 1u)) e1 = 0.f;
+                            }
+                            l_row += e0 + e1;
+                            pk[t >> 1] = pack_bf16x2(e0, e1);
+                        }
+                        tmem_st16(tX + c * 16, pk);
+                    }
+                }
+                tmem_wait_st();
+                float m_w = m_row;
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) m_w = fmaxf(m_w, __shfl_xor_sync(0xFFFFFFFFu, m_w, o));
+                if (lane == 0) sMpart[warp] = m_w;
+                tc_fence_before();
+                __syncthreads();
+                if (warp == 0) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int kk = 0; kk < TILE / 16; ++kk)
+                        umma_ts_warp(tmem_base + 128, tmem_base + kk * 8, dVcM + kk * (2048 / 16), idesc_u, kk > 0);
+                    umma_commit_warp(bar);
+                    if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
+                    __syncwarp();
+                }
+                phase ^= 1;
+                const float Mt = fmaxf(fmaxf(sMpart[0], sMpart[1]), fmaxf(sMpart[2], sMpart[3]));
+                const float w_row = (m_row > -INFINITY) ? fast_exp2((m_row - Mt) * c2) : 0.f;
+                __syncthreads();
+                tc_fence_after();
+                if (*sFail) { failed = true; break; }
+
+                // --- collapse and merge into the anchor's running state ---------------------------
+                {
+                    uint32_t u[32];
+                    float v[32];
+#pragma unroll
+                    for (int c = 0; c < DP / 32; ++c) {
+                        tmem_ld32(tU + c * 32, u);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int t = 0; t < 32; t += 2) {
+                            const float2 vr = unpack_bf16x2(rVr[c * 16 + (t >> 1)]);
+                            v[t] = w_row * vr.x * __uint_as_float(u[t]);
+                            v[t + 1] = w_row * vr.y * __uint_as_float(u[t + 1]);
+                        }
+                        const float s = warp_transpose_sum(v, lane);
+                        sRed[warp * (DP + 4) + c * 32 + lane] = s;
+                    }
+                    float wl = w_row * l_row;
+#pragma unroll
+                    for (int o = 16; o >= 1; o >>= 1) wl += __shfl_xor_sync(0xFFFFFFFFu, wl, o);
+                    if (lane == 0) sRed[warp * (DP + 4) + DP] = wl;
+                }
+                tc_fence_before();
+                __syncthreads();
+                if (Mt > -INFINITY) {
+                    float* st = sState + (a - a0) * (DP + 4);
+                    const float M_old = st[DP];
+                    const float M_new = fmaxf(M_old, Mt);
+                    const float f_old = (M_old > -INFINITY) ? fast_exp2((M_old - M_new) * c2) : 0.f;
+                    const float f_new = fast_exp2((Mt - M_new) * c2);
+                    float add = 0.f;
+                    if (tid < DP)
+                        add = sRed[tid] + sRed[(DP + 4) + tid] + sRed[2 * (DP + 4) + tid] + sRed[3 * (DP + 4) + tid];
+                    const float Lt = sRed[DP] + sRed[(DP + 4) + DP] + sRed[2 * (DP + 4) + DP] + sRed[3 * (DP + 4) + DP];
+                    const float L_old = st[DP + 1];
+                    __syncthreads();                       // everyone has read the old max and sum
+                    if (tid < DP) st[tid] = st[tid] * f_old + add * f_new;
+                    if (tid == 0) { st[DP] = M_new; st[DP + 1] = L_old * f_old + Lt * f_new; }
+                }
+                __syncthreads();
+            }
+        }
+    }
+    if (!failed) {
+        for (int a = a0; a < a1; ++a) {
+            const float* st = sState + (a - a0) * (DP + 4);
+            const float M = st[DP], Ls = st[DP + 1];
+            const size_t row = bh + a;
+            const bool live = M > -INFINITY && Ls > 0.f;
+            if (tid < D) p.Y[row * D + tid] = __float2bfloat16(live ? st[tid] / Ls : 0.f);
+            if (tid == 0) { p.m[row] = live ? M * p.scale : NEG_INF_F; p.l[row] = live ? Ls : 0.f; }
+        }
+    }
+    if (failed && tid == 0) atomicExch(p.status, 4);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+}  // namespace agdense

@@ -36,4 +36,20 @@ private:
     cudaEvent_t start_ = nullptr;
 };
 
+// ---- dense anchored gather (hg_api.cu), shared with the single-gather entry points ----------
+// Forward of one anchored gather: anchor A, rows (Rw, Vrow), cols (C, Vcol), all [B,H,N,D] BF16.
+int dense_gather_forward(const void* A, const void* Rw, const void* C, const void* Vrow, const void* Vcol,
+                         const uint8_t* mask, void* Y, float* m, float* l, int B, int H, int N, int D, int n_valid,
+                         cudaStream_t st);
+// Backward for one key side: adds d(Kb), d(Vb) into FP32 planes; if dA_part is non-null also
+// accumulates the anchor gradient into one zero-filled partial plane per 128-key tile of the own side.
+int dense_gather_backward_side(const void* A, const void* dY, const void* Y, const float* m, const float* l,
+                               const void* Ka, const void* Va, const void* Kb, const void* Vb, const uint8_t* mask,
+                               float* dKb, float* dVb, float* dA_part, int B, int H, int N, int D, int n_valid,
+                               cudaStream_t st);
+int dense_tiles(int N, int n_valid);
+int add_planes(const float* src, int n_src, size_t plane, float* acc, cudaStream_t st);
+int plane_to_bf16(const float* src, void* out, size_t n, cudaStream_t st);
+int dense_status_read_and_clear(int* out);
+
 }  // namespace att3

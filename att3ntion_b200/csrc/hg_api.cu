@@ -1,20 +1,260 @@
-// C-ABI entry points of the three-gather hypergraph attention.
-#include "att3_abi_internal.h"
+// Dense anchored-gather launchers and the C-ABI entry points of the three-gather
+// hypergraph attention, which is three anchored gathers with permuted roles
+// (forward) and the sum of their gradients (backward).
+#include <algorithm>
+#include <cmath>
 
-extern "C" int att3_hg_forward(const void*, const void*, const void*, const void*, const void*, const void*,
-                               const void*, const void*, const void*, const uint8_t*, void*, void*, void*, void*,
-                               void*, void*, float*, float*, float*, float*, float*, float*, int, int, int, int, int,
-                               int, int, void*) {
-    return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_hg_forward: three-gather path not built");
+#include "att3_abi_internal.h"
+#include "ag_dense_bwd.cuh"
+
+namespace {
+
+__device__ int g_ag_status = 0;
+
+int* ag_status_ptr() {
+    int* p = nullptr;
+    cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_ag_status);
+    return p;
 }
 
-extern "C" size_t att3_hg_backward_workspace_bytes(int, int, int, int) { return 0; }
+template <typename K>
+int opt_in_smem(K kernel, int bytes, const char* who) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, who);
+}
 
-extern "C" int att3_hg_backward(const void*, const void*, const void*, const void*, const void*, const void*,
-                                const void*, const void*, const void*, const void*, const void*, const void*,
-                                const void*, const void*, const void*, const float*, const float*, const float*,
-                                const float*, const float*, const float*, const uint8_t*, void*, void*, void*, void*,
-                                void*, void*, void*, void*, void*, int, int, int, int, int, int, int, void*, size_t,
-                                void*) {
-    return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_hg_backward: three-gather path not built");
+template <int DP>
+int launch_fwd(const agdense::FwdParams& p, cudaStream_t st) {
+    using L = agdense::FwdSmem<DP>;
+    if (int rc = opt_in_smem(agdense::ag_dense_fwd_kernel<DP>, L::ALLOC, "dense gather forward: shared-memory opt-in")) return rc;
+    dim3 grid((p.N + p.group - 1) / p.group, p.H, p.B);
+    att3::TimedLaunch timed(att3::K_DENSE_FWD, st);
+    agdense::ag_dense_fwd_kernel<DP><<<grid, agdense::NTHREADS, L::ALLOC, st>>>(p);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "dense gather forward: launch");
+}
+
+template <int DP, bool WITH_DA>
+int launch_bwd(const agdense::BwdParams& p, int n_tiles, cudaStream_t st) {
+    using L = agdense::BwdSmem<DP, WITH_DA>;
+    if (int rc = opt_in_smem(agdense::ag_dense_bwd_kernel<DP, WITH_DA>, L::ALLOC, "dense gather backward: shared-memory opt-in"))
+        return rc;
+    dim3 grid(n_tiles, p.H, p.B);
+    att3::TimedLaunch timed(att3::K_DENSE_BWD, st);
+    agdense::ag_dense_bwd_kernel<DP, WITH_DA><<<grid, agdense::BWD_THREADS, L::ALLOC, st>>>(p);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "dense gather backward: launch");
+}
+
+int grid_for(size_t n) { return static_cast<int>(std::min<size_t>((n + 255) / 256, 148 * 8)); }
+
+}  // namespace
+
+namespace att3 {
+
+int dense_status_read_and_clear(int* out) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, g_ag_status, sizeof(int));
+    if (e != cudaSuccess) return set_cuda_error(e, "att3_device_status: read");
+    if (*out) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_ag_status, &zero, sizeof(int));
+    }
+    return ATT3_OK;
+}
+
+int dense_tiles(int N, int n_valid) {
+    const int n_keys = (n_valid > 0 && n_valid < N) ? n_valid : N;
+    return (n_keys + agdense::TILE - 1) / agdense::TILE;
+}
+
+int dense_gather_forward(const void* A, const void* Rw, const void* C, const void* Vrow, const void* Vcol,
+                         const uint8_t* mask, void* Y, float* m, float* l, int B, int H, int N, int D, int n_valid,
+                         cudaStream_t st) {
+    agdense::FwdParams p;
+    p.A = static_cast<const __nv_bfloat16*>(A);
+    p.Rw = static_cast<const __nv_bfloat16*>(Rw);
+    p.C = static_cast<const __nv_bfloat16*>(C);
+    p.Vrow = static_cast<const __nv_bfloat16*>(Vrow);
+    p.Vcol = static_cast<const __nv_bfloat16*>(Vcol);
+    p.mask = mask;
+    p.Y = static_cast<__nv_bfloat16*>(Y);
+    p.m = m; p.l = l;
+    p.B = B; p.H = H; p.N = N; p.D = D; p.n_valid = n_valid;
+    p.scale = 1.0f / sqrtf(static_cast<float>(D));
+    p.status = ag_status_ptr();
+    // anchors per CTA: enough CTAs to fill the device twice over, at most 16 anchors each
+    const long ctas_at_16 = static_cast<long>((N + 15) / 16) * H * B;
+    p.group = ctas_at_16 >= 2L * sm_count() ? 16 : (ctas_at_16 * 2 >= 2L * sm_count() ? 8 : 4);
+    return D > 64 ? launch_fwd<128>(p, st) : launch_fwd<64>(p, st);
+}
+
+int dense_gather_backward_side(const void* A, const void* dY, const void* Y, const float* m, const float* l,
+                               const void* Ka, const void* Va, const void* Kb, const void* Vb, const uint8_t* mask,
+                               float* dKb, float* dVb, float* dA_part, int B, int H, int N, int D, int n_valid,
+                               cudaStream_t st) {
+    agdense::BwdParams p;
+    p.A = static_cast<const __nv_bfloat16*>(A);
+    p.dY = static_cast<const __nv_bfloat16*>(dY);
+    p.Y = static_cast<const __nv_bfloat16*>(Y);
+    p.m = m; p.l = l;
+    p.Ka = static_cast<const __nv_bfloat16*>(Ka);
+    p.Va = static_cast<const __nv_bfloat16*>(Va);
+    p.Kb = static_cast<const __nv_bfloat16*>(Kb);
+    p.Vb = static_cast<const __nv_bfloat16*>(Vb);
+    p.mask = mask;
+    p.dKb = dKb; p.dVb = dVb; p.dA_part = dA_part;
+    p.B = B; p.H = H; p.N = N; p.D = D; p.n_valid = n_valid;
+    p.scale = 1.0f / sqrtf(static_cast<float>(D));
+    p.status = ag_status_ptr();
+    const int nt = dense_tiles(N, n_valid);
+    if (dA_part) return D > 64 ? launch_bwd<128, true>(p, nt, st) : launch_bwd<64, true>(p, nt, st);
+    return D > 64 ? launch_bwd<128, false>(p, nt, st) : launch_bwd<64, false>(p, nt, st);
+}
+
+int add_planes(const float* src, int n_src, size_t plane, float* acc, cudaStream_t st) {
+    TimedLaunch timed(K_HG_AUX, st);
+    agdense::ag_add_planes<<<grid_for(plane), 256, 0, st>>>(src, n_src, plane, acc, plane);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ATT3_OK : set_cuda_error(e, "add_planes: launch");
+}
+
+int plane_to_bf16(const float* src, void* out, size_t n, cudaStream_t st) {
+    TimedLaunch timed(K_HG_AUX, st);
+    agdense::ag_sum_planes_to_bf16<<<grid_for(n), 256, 0, st>>>(src, 1, n, static_cast<__nv_bfloat16*>(out), n);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ATT3_OK : set_cuda_error(e, "plane_to_bf16: launch");
+}
+
+}  // namespace att3
+
+// ---------------------------------------------------------------------------------------------
+// Three-gather forward
+// ---------------------------------------------------------------------------------------------
+
+static __global__ void fill_stats_kernel(float* m, float* l, size_t n, float mv, float lv) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        m[i] = mv;
+        l[i] = lv;
+    }
+}
+
+static int check_hg(const char* who, int B, int H, int N, int D) {
+    if (B <= 0 || H <= 0 || N <= 0) return att3::set_error(ATT3_ERR_INVALID, "%s: empty batch/head/sequence", who);
+    if (D != 16 && D != 32 && D != 64 && D != 128)
+        return att3::set_error(ATT3_ERR_INVALID, "%s: head dim must be 16, 32, 64 or 128, got %d", who, D);
+    if (N % 16 != 0) return att3::set_error(ATT3_ERR_INVALID, "%s: N must be a multiple of 16, got %d", who, N);
+    return ATT3_OK;
+}
+
+extern "C" int att3_hg_forward(const void* Q, const void* R, const void* S, const void* Vq1, const void* Vq2,
+                               const void* Vr1, const void* Vr2, const void* Vs1, const void* Vs2,
+                               const uint8_t* mask, void* Yq, void* Yr, void* Ys, void* Yq_, void* Yr_, void* Ys_,
+                               float* m_i, float* l_i, float* m_j, float* l_j, float* m_k, float* l_k, int B, int H,
+                               int N, int D, int n_valid, int gather_mode, int scatter, void* stream) {
+    if (int rc = check_hg("att3_hg_forward", B, H, N, D)) return rc;
+    if (!Q || !R || !S || !Vq1 || !Vr1 || !Vs1 || !Yq || !Yr || !Ys || !Yq_ || !Yr_ || !Ys_ || !m_i || !l_i || !m_j ||
+        !l_j || !m_k || !l_k)
+        return att3::set_error(ATT3_ERR_INVALID, "att3_hg_forward: null tensor pointer");
+    if (gather_mode != 0 && gather_mode != 1)
+        return att3::set_error(ATT3_ERR_INVALID, "att3_hg_forward: gather_mode must be 0 or 1, got %d", gather_mode);
+    if (scatter && gather_mode != 0)
+        return att3::set_error(ATT3_ERR_INVALID, "att3_hg_forward: scatter needs all three gathers (gather_mode 0)");
+    if (scatter && (!Vq2 || !Vr2 || !Vs2))
+        return att3::set_error(ATT3_ERR_INVALID, "att3_hg_forward: scatter needs the second value tensors");
+    if (!att3::require_sm100("att3_hg_forward")) return ATT3_ERR_UNSUPPORTED;
+    if (scatter)
+        return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_hg_forward: scatter outputs unavailable (not built)");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t n = static_cast<size_t>(B) * H * N;
+    const size_t bytes = n * D * 2;
+    // outputs of skipped gathers / scatters read as zero (cuda/forward.cu:1308-1321)
+    cudaMemsetAsync(Yq_, 0, bytes, st);
+    cudaMemsetAsync(Yr_, 0, bytes, st);
+    cudaMemsetAsync(Ys_, 0, bytes, st);
+    int rc = att3::dense_gather_forward(Q, R, S, Vr1, Vs1, mask, Yq, m_i, l_i, B, H, N, D, n_valid, st);
+    if (rc) return rc;
+    att3::count_launch(2);
+    if (gather_mode == 1) {
+        cudaMemsetAsync(Yr, 0, bytes, st);
+        cudaMemsetAsync(Ys, 0, bytes, st);
+        // statistics that make the other two softmax weights vanish (cuda/forward.cu:1455-1459)
+        fill_stats_kernel<<<148, 256, 0, st>>>(m_j, l_j, n, 1e30f, 1.0f);
+        fill_stats_kernel<<<148, 256, 0, st>>>(m_k, l_k, n, 1e30f, 1.0f);
+        return ATT3_OK;
+    }
+    if ((rc = att3::dense_gather_forward(R, Q, S, Vq1, Vs1, mask, Yr, m_j, l_j, B, H, N, D, n_valid, st))) return rc;
+    if ((rc = att3::dense_gather_forward(S, Q, R, Vq1, Vr1, mask, Ys, m_k, l_k, B, H, N, D, n_valid, st))) return rc;
+    att3::count_launch(2, 2);
+    return ATT3_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Three-gather backward
+// ---------------------------------------------------------------------------------------------
+
+// nine FP32 gradient planes + one anchor-gradient partial plane per 128-key tile
+extern "C" size_t att3_hg_backward_workspace_bytes(int B, int H, int N, int D) {
+    if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
+    const size_t plane = static_cast<size_t>(B) * H * N * D * sizeof(float);
+    return plane * (9 + att3::dense_tiles(N, 0));
+}
+
+extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gYs, const void* gYq_,
+                                const void* gYr_, const void* gYs_, const void* Q, const void* R, const void* S,
+                                const void* Vq1, const void* Vq2, const void* Vr1, const void* Vr2, const void* Vs1,
+                                const void* Vs2, const void* Yq, const void* Yr, const void* Ys, const float* m_i,
+                                const float* l_i, const float* m_j, const float* l_j, const float* m_k,
+                                const float* l_k, const uint8_t* mask, void* dQ, void* dR, void* dS, void* dVq1,
+                                void* dVq2, void* dVr1, void* dVr2, void* dVs1, void* dVs2, int B, int H, int N,
+                                int D, int n_valid, int gather_mode, int scatter, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+    (void)gYq_; (void)gYr_; (void)gYs_; (void)Vq2; (void)Vr2; (void)Vs2;
+    if (int rc = check_hg("att3_hg_backward", B, H, N, D)) return rc;
+    if (!gYq || !Q || !R || !S || !Vq1 || !Vr1 || !Vs1 || !Yq || !m_i || !l_i || !dQ || !dR || !dS || !dVq1 || !dVq2 ||
+        !dVr1 || !dVr2 || !dVs1 || !dVs2)
+        return att3::set_error(ATT3_ERR_INVALID, "att3_hg_backward: null tensor pointer");
+    if (gather_mode == 0 && (!gYr || !gYs || !Yr || !Ys || !m_j || !l_j || !m_k || !l_k))
+        return att3::set_error(ATT3_ERR_INVALID, "att3_hg_backward: null tensor pointer (R/S-anchored gathers)");
+    if (!att3::require_sm100("att3_hg_backward")) return ATT3_ERR_UNSUPPORTED;
+    if (scatter)
+        return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_hg_backward: scatter gradients unavailable (not built)");
+    const size_t need = att3_hg_backward_workspace_bytes(B, H, N, D);
+    if (!workspace || workspace_bytes < need)
+        return att3::set_error(ATT3_ERR_WORKSPACE, "att3_hg_backward: workspace of %zu bytes required, got %zu", need,
+                               workspace_bytes);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t plane = static_cast<size_t>(B) * H * N * D;
+    const int nt = att3::dense_tiles(N, n_valid);
+    float* ws = static_cast<float*>(workspace);
+    float *gQ = ws, *gR = ws + plane, *gS = ws + 2 * plane, *gVq1 = ws + 3 * plane, *gVq2 = ws + 4 * plane,
+          *gVr1 = ws + 5 * plane, *gVr2 = ws + 6 * plane, *gVs1 = ws + 7 * plane, *gVs2 = ws + 8 * plane,
+          *part = ws + 9 * plane;
+    cudaMemsetAsync(ws, 0, 9 * plane * sizeof(float), st);
+
+    // One anchored gather: anchor A with statistics (m,l), rows (Kr,Vr), cols (Kc,Vc).
+    auto gather_bwd = [&](const void* A, const void* gY, const void* Y, const float* m, const float* l, const void* Kr,
+                          const void* Vr, const void* Kc, const void* Vc, float* gA, float* gKr, float* gVr, float* gKc,
+                          float* gVc) -> int {
+        cudaMemsetAsync(part, 0, static_cast<size_t>(nt) * plane * sizeof(float), st);
+        int rc = att3::dense_gather_backward_side(A, gY, Y, m, l, Kr, Vr, Kc, Vc, mask, gKc, gVc, part, B, H, N, D,
+                                                  n_valid, st);
+        if (rc) return rc;
+        if ((rc = att3::add_planes(part, nt, plane, gA, st))) return rc;
+        rc = att3::dense_gather_backward_side(A, gY, Y, m, l, Kc, Vc, Kr, Vr, mask, gKr, gVr, nullptr, B, H, N, D,
+                                              n_valid, st);
+        att3::count_launch(3, 3);
+        return rc;
+    };
+    int rc = gather_bwd(Q, gYq, Yq, m_i, l_i, R, Vr1, S, Vs1, gQ, gR, gVr1, gS, gVs1);
+    if (rc) return rc;
+    if (gather_mode == 0) {
+        if ((rc = gather_bwd(R, gYr, Yr, m_j, l_j, Q, Vq1, S, Vs1, gR, gQ, gVq1, gS, gVs1))) return rc;
+        if ((rc = gather_bwd(S, gYs, Ys, m_k, l_k, Q, Vq1, R, Vr1, gS, gQ, gVq1, gR, gVr1))) return rc;
+    }
+    void* outs[9] = {dQ, dR, dS, dVq1, dVq2, dVr1, dVr2, dVs1, dVs2};
+    const float* srcs[9] = {gQ, gR, gS, gVq1, gVq2, gVr1, gVr2, gVs1, gVs2};
+    for (int k = 0; k < 9; ++k)
+        if ((rc = att3::plane_to_bf16(srcs[k], outs[k], plane, st))) return rc;
+    return ATT3_OK;
 }

@@ -82,9 +82,11 @@ extern "C" int att3_debug_trace(long long* out32) {
 extern "C" int att3_device_status(void* stream) {
     cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_device_status: synchronize");
-    int h = 0;
+    int h = 0, h2 = 0;
     e = cudaMemcpyFromSymbol(&h, g_sg_status, sizeof(int));
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_device_status: read");
+    if (int rc = att3::dense_status_read_and_clear(&h2)) return rc;
+    if (h == 0) h = h2;
     if (h != 0) {
         const int zero = 0;
         cudaMemcpyToSymbol(g_sg_status, &zero, sizeof(int));
@@ -121,8 +123,15 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
     if (!Q || !R || !S || !Vr || !Vs || !Y || !m || !l)
         return att3::set_error(ATT3_ERR_INVALID, "att3_sg_forward: null tensor pointer");
     if (!att3::require_sm100("att3_sg_forward")) return ATT3_ERR_UNSUPPORTED;
-    if (window == 0)
-        return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_sg_forward: dense (window = 0) path not built");
+    if (window == 0) {
+        // every key a candidate: the dense anchored gather with (anchor, rows, cols) = (Q, R, S)
+        if (Hkv != Hq)
+            return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_sg_forward: shared KV heads need a window (1..128)");
+        if (q_begin != 0) return att3::set_error(ATT3_ERR_INVALID, "att3_sg_forward: q_begin needs a window");
+        att3::count_launch(0);
+        return att3::dense_gather_forward(Q, R, S, Vr, Vs, mask, Y, m, l, B, Hq, N, D, 0,
+                                          static_cast<cudaStream_t>(stream));
+    }
     sgring::FwdParams p;
     p.Q = static_cast<const __nv_bfloat16*>(Q);
     p.R = static_cast<const __nv_bfloat16*>(R);
@@ -149,7 +158,9 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
 // each; the second pass reuses the space after the first pass's reduction.
 extern "C" size_t att3_sg_backward_workspace_bytes(int B, int Hq, int Hkv, int N, int D, int window) {
     (void)Hq;
-    if (B <= 0 || Hkv <= 0 || N <= 0 || D <= 0 || window <= 0) return 0;
+    if (B <= 0 || Hkv <= 0 || N <= 0 || D <= 0 || window < 0) return 0;
+    if (window == 0)   // dense: five FP32 gradient planes + one anchor-gradient partial plane per 128-key tile
+        return static_cast<size_t>(5 + att3::dense_tiles(N, 0)) * B * Hq * N * D * sizeof(float);
     return static_cast<size_t>(4) * B * Hkv * N * D * sizeof(float);
 }
 
@@ -202,8 +213,9 @@ extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, co
     if (!dY || !Q || !R || !S || !Vr || !Vs || !Y || !m || !l || !dQ || !dR || !dS || !dVr || !dVs)
         return att3::set_error(ATT3_ERR_INVALID, "att3_sg_backward: null tensor pointer");
     if (!att3::require_sm100("att3_sg_backward")) return ATT3_ERR_UNSUPPORTED;
-    if (window == 0)
-        return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_sg_backward: dense (window = 0) path not built");
+    if (window == 0 && Hkv != Hq)
+        return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_sg_backward: shared KV heads need a window (1..128)");
+    if (window == 0 && q_begin != 0) return att3::set_error(ATT3_ERR_INVALID, "att3_sg_backward: q_begin needs a window");
     const size_t need = att3_sg_backward_workspace_bytes(B, Hq, Hkv, N, D, window);
     if (!workspace || workspace_bytes < need)
         return att3::set_error(ATT3_ERR_WORKSPACE, "att3_sg_backward: workspace of %zu bytes required, got %zu", need,
@@ -211,6 +223,26 @@ extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, co
     if (reinterpret_cast<uintptr_t>(workspace) % 16 != 0)
         return att3::set_error(ATT3_ERR_WORKSPACE, "att3_sg_backward: workspace must be 16-byte aligned");
 
+    if (window == 0) {
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        const size_t plane = static_cast<size_t>(B) * Hq * N * D;
+        const int nt = att3::dense_tiles(N, 0);
+        float* ws = static_cast<float*>(workspace);
+        float *gQ = ws, *gR = ws + plane, *gS = ws + 2 * plane, *gVr = ws + 3 * plane, *gVs = ws + 4 * plane,
+              *part = ws + 5 * plane;
+        cudaMemsetAsync(ws, 0, (5 + static_cast<size_t>(nt)) * plane * sizeof(float), st);
+        int rc = att3::dense_gather_backward_side(Q, dY, Y, m, l, R, Vr, S, Vs, mask, gS, gVs, part, B, Hq, N, D, 0, st);
+        if (rc) return rc;
+        if ((rc = att3::add_planes(part, nt, plane, gQ, st))) return rc;
+        if ((rc = att3::dense_gather_backward_side(Q, dY, Y, m, l, S, Vs, R, Vr, mask, gR, gVr, nullptr, B, Hq, N, D, 0, st)))
+            return rc;
+        att3::count_launch(1, 3);
+        void* outs[5] = {dQ, dR, dS, dVr, dVs};
+        const float* srcs[5] = {gQ, gR, gS, gVr, gVs};
+        for (int k = 0; k < 5; ++k)
+            if ((rc = att3::plane_to_bf16(srcs[k], outs[k], plane, st))) return rc;
+        return ATT3_OK;
+    }
     sgring::BwdParams p;
     p.Q = static_cast<const __nv_bfloat16*>(Q);
     p.dY = static_cast<const __nv_bfloat16*>(dY);

@@ -124,12 +124,16 @@ size_t att3_hg_backward_workspace_bytes(int B, int H, int N, int D);
 
 /* Nine gradients (Q,R,S,Vq1,Vq2,Vr1,Vr2,Vs1,Vs2), BF16 [B,H,N,D].  g* are the
  * cotangents of the six outputs; pass scatter = 0 when the three scatter
- * cotangents are identically zero (att3ntion/_custom_op.py:73-96). */
+ * cotangents are identically zero (att3ntion/_custom_op.py:73-96).  Yq, Yr, Ys
+ * are the forward's gather outputs: the softmax Jacobian correction is taken as
+ * rowsum(dY o Y), the reference's tensor-core path (cuda/backward.cu:1835-1837).
+ * With gather_mode 1 only the Q-anchored tensors are read. */
 int att3_hg_backward(const void* gYq, const void* gYr, const void* gYs,
                      const void* gYq_, const void* gYr_, const void* gYs_,
                      const void* Q, const void* R, const void* S,
                      const void* Vq1, const void* Vq2, const void* Vr1, const void* Vr2,
                      const void* Vs1, const void* Vs2,
+                     const void* Yq, const void* Yr, const void* Ys,
                      const float* m_i, const float* l_i, const float* m_j, const float* l_j,
                      const float* m_k, const float* l_k, const uint8_t* mask,
                      void* dQ, void* dR, void* dS, void* dVq1, void* dVq2, void* dVr1, void* dVr2,

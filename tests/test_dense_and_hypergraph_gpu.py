@@ -1,0 +1,194 @@
+"""GPU parity tests of the dense anchored gather: the un-windowed single gather
+(arbitrary masks, any N) and the three-gather HypergraphAttention operator, against the
+golden vectors made from the reference's oracles and against the CPU oracle.
+
+Gates: single gather as in tests/test_single_gather.py:26-30 of the reference; three-gather
+outputs allclose(rtol 5e-2, atol 5e-2 * max(1, max|ref|)), gradients of Q/R/S
+(5e-2, 1e-1 * ...), of the values (2e-2, 2e-2 * ...) as in tests/test_kernel_correctness.py:303-361."""
+import pytest
+import torch
+
+from conftest import golden_files, load_golden
+from oracle import triplet_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+NAMES = ["Q", "R", "S", "Vr", "Vs"]
+GRADS = ["dQ", "dR", "dS", "dVr", "dVs"]
+HG_NAMES = ["Q", "R", "S", "Vq_1", "Vq_2", "Vr_1", "Vr_2", "Vs_1", "Vs_2"]
+
+
+@pytest.fixture(scope="module")
+def ck():
+    from att3ntion_b200 import _cuda_kernels
+    return _cuda_kernels
+
+
+# --------------------------------------------------------------------------- dense single gather
+
+DENSE_SG = [n for n in golden_files("sg_") if "_window" not in n]
+
+
+@pytest.mark.parametrize("name", DENSE_SG)
+def test_dense_single_gather_golden_bridge(name):
+    from att3ntion_b200 import single_gather_attention
+    g = load_golden(name)
+    leaves = {n: g["inputs"][n].cuda().requires_grad_(True) for n in NAMES}
+    mask = None if g["mask"] is None else g["mask"].cuda()
+    Y = single_gather_attention(*[leaves[n] for n in NAMES], mask)
+    Y.backward(g["dY"].cuda())
+    O.check_gate("Y", Y.detach().float().cpu(), g["Y"])
+    dead = torch.isinf(g["lse"])
+    if dead.any():
+        assert Y.detach().cpu()[dead].abs().max().item() == 0.0
+    for gname, n in zip(GRADS, NAMES):
+        O.check_gate(gname, leaves[n].grad.float().cpu(), g[gname])
+
+
+@pytest.mark.parametrize("name", [n for n in DENSE_SG if "N16D" in n or "N128D" in n or "N32D" in n])
+def test_dense_single_gather_golden_lowlevel(ck, name):
+    g = load_golden(name)
+    q = [g["inputs"][n].cuda() for n in NAMES]
+    mask = None if g["mask"] is None else g["mask"].cuda().contiguous()
+    Y, m, l = ck.single_gather_forward(*q, mask)
+    O.check_gate("Y", Y.float().cpu(), g["Y"])
+    O.check_lse(m, l, g["lse"])
+    grads = ck.single_gather_backward(g["dY"].cuda(), *q, Y, m, l, mask)
+    ck.device_status()
+    for gname, t in zip(GRADS, grads):
+        O.check_gate(gname, t.float().cpu(), g[gname])
+    again = ck.single_gather_backward(g["dY"].cuda(), *q, Y, m, l, mask)
+    assert all(torch.equal(a, b) for a, b in zip(grads, again)), "repeated backward must be bit-identical"
+
+
+@pytest.mark.parametrize("N,D", [(144, 64), (272, 128)])
+def test_dense_multi_tile_causal_and_random(ck, N, D):
+    """More than one 128-key tile per side, causal and random masks (the merge across tiles)."""
+    gen = torch.Generator().manual_seed(N)
+    xs = {n: torch.randn(1, 2, N, D, generator=gen).to(torch.bfloat16) for n in NAMES}
+    dY = torch.randn(1, 2, N, D, generator=gen).to(torch.bfloat16)
+    for kind in ("causal", "random"):
+        if kind == "causal":
+            mask = torch.tril(torch.ones(1, N, N, dtype=torch.bool))
+        else:
+            mask = torch.rand(1, N, N, generator=gen) < 0.5
+            mask[:, 3, :] = False
+        ref = O.single_gather_dense(*[xs[n] for n in NAMES], mask=mask, dY=dY)
+        q = [xs[n].cuda() for n in NAMES]
+        mk = mask.cuda().contiguous()
+        Y, m, l = ck.single_gather_forward(*q, mk)
+        grads = ck.single_gather_backward(dY.cuda(), *q, Y, m, l, mk)
+        ck.device_status()
+        O.check_gate("Y", Y.float().cpu(), ref["Y"])
+        O.check_lse(m, l, ref["lse"])
+        for gname, t in zip(GRADS, grads):
+            O.check_gate(gname, t.float().cpu(), ref[gname])
+
+
+# --------------------------------------------------------------------------- three-gather
+
+def hg_close(actual, ref, rtol, atol_scale, what):
+    a, r = actual.double().cpu(), ref.double()
+    atol = atol_scale * max(1.0, r.abs().max().item())
+    bad = (a - r).abs() > atol + rtol * r.abs()
+    assert not bad.any(), f"{what}: {int(bad.sum())} elements off, max err {(a - r).abs().max().item():.4f} (atol {atol:.4f})"
+
+
+def run_hg(ck, g, mask):
+    ins = [g["inputs"][n].cuda() for n in HG_NAMES]
+    # gather-only comparison: the scatter value tensors are zeroed so the scatter outputs vanish
+    for k in (4, 6, 8):
+        ins[k] = torch.zeros_like(ins[k])
+    out = ck.forward(*ins, 0.0, -1, -1, -1, mask, 0)
+    cot = [c.cuda() for c in g["cotangents"][:3]] + [torch.zeros_like(ins[0]) for _ in range(3)]
+    grads = ck.backward(*cot, *ins, *out[6:12], 0.0, mask, out[0], out[1], out[2])
+    ck.device_status()
+    return out, grads
+
+
+@pytest.mark.parametrize("name", [n for n in golden_files("hg_") if "masked" not in n])
+def test_three_gather_unmasked_gathers(ck, name):
+    g = load_golden(name)
+    out, grads = run_hg(ck, g, None)
+    for k, what in enumerate(("Y_q", "Y_r", "Y_s")):
+        hg_close(out[k], g["outputs"][k], 5e-2, 5e-2, what)
+        assert out[3 + k].abs().max().item() == 0.0
+    # gradients of the gather-only objective from the FP64 oracle on the same inputs
+    ins = [g["inputs"][n] for n in HG_NAMES]
+    for k in (4, 6, 8):
+        ins[k] = torch.zeros_like(ins[k])
+    ref = O.hypergraph_grads(ins, list(g["cotangents"][:3]) + [None] * 3, scatter=False)
+    for k, n in enumerate(HG_NAMES):
+        hg_close(grads[k], ref[k], 5e-2, 1e-1 if k < 3 else 2e-2, f"d{n}")
+
+
+@pytest.mark.parametrize("name", golden_files("hg_masked_"))
+def test_three_gather_masked(ck, name):
+    g = load_golden(name)
+    out, grads = run_hg(ck, g, g["mask"].cuda().contiguous())
+    for k, what in enumerate(("Y_q", "Y_r", "Y_s")):
+        hg_close(out[k], g["outputs"][k], 5e-2, 5e-2, what)
+    for k, n in enumerate(HG_NAMES):
+        hg_close(grads[k], g["grads"][k], 5e-2, 1e-1 if k < 3 else 2e-2, f"d{n}")
+    # fully masked anchors: Y = 0 and (m, l) = (-1e30, 0)
+    dead = ~g["mask"].any(-1)                               # [B, N]
+    if dead.any():
+        idx = dead[:, None, :].expand(-1, out[0].shape[1], -1)
+        assert out[0].cpu()[idx].abs().max().item() == 0.0
+        assert (out[6].cpu()[idx] == -1e30).all() and (out[7].cpu()[idx] == 0).all()
+
+
+def test_gather_mode_one_matches_single_gather(ck):
+    g = load_golden("sg_B1H2N16D64_s0_none.pt")
+    x = {n: g["inputs"][n].cuda() for n in NAMES}
+    z = torch.zeros_like(x["Q"])
+    out = ck.forward(x["Q"], x["R"], x["S"], z, z, x["Vr"], z, x["Vs"], z, 0.0, -1, -1, -1, None, 1)
+    O.check_gate("Y", out[0].float().cpu(), g["Y"])
+    assert out[1].abs().max().item() == 0.0 and out[2].abs().max().item() == 0.0
+    assert (out[8] > 1e29).all() and (out[9] == 1).all()      # statistics that null the other softmaxes
+
+
+def test_module_forward_backward_and_compile():
+    """HypergraphAttention end to end (projections by cuBLAS, the op by the kernels), against the
+    module-level FP64 restatement built from the oracle; then the same module under torch.compile."""
+    from att3ntion_b200 import HypergraphAttention
+    torch.manual_seed(0)
+    mod = HypergraphAttention(64, 4).cuda()
+    x = torch.randn(2, 40, 64, device="cuda", requires_grad=True)
+    y = mod(x)
+    y.square().mean().backward()
+    assert torch.isfinite(y).all() and torch.isfinite(x.grad).all()
+
+    xd = x.detach().double().cpu().requires_grad_(True)
+    w = {k: v.detach().double().cpu() for k, v in mod.state_dict().items()}
+    heads = lambda t: t.reshape(2, 40, 4, 16).permute(0, 2, 1, 3)
+    lin = lambda name, bias: xd @ w[f"{name}.weight"].T + (w[f"{name}.bias"] if bias else 0)
+    Q, R, S = heads(lin("Wq", False)), heads(lin("Wr", False)), heads(lin("Ws", False))
+    Vq, Vr, Vs = heads(lin("Wv_q", True)), heads(lin("Wv_r", True)), heads(lin("Wv_s", True))
+    z = torch.zeros_like(Vq)
+    (Yq, Yr, Ys, *_), _ = O.hypergraph_dense(Q, R, S, Vq, z, Vr, z, Vs, z, scatter=False)
+    gelu = lambda t: t * torch.sigmoid(1.702 * t)
+    yr = (gelu(Yq) + gelu(Yr) + gelu(Ys)).permute(0, 2, 1, 3).reshape(2, 40, 64) @ w["Wo.weight"].T + w["Wo.bias"]
+    yr.square().mean().backward()
+    rel = (y.detach().double().cpu() - yr.detach()).norm() / yr.detach().norm()
+    relg = (x.grad.double().cpu() - xd.grad).norm() / xd.grad.norm()
+    assert rel < 0.03 and relg < 0.06, (rel.item(), relg.item())
+
+    compiled = torch.compile(mod)
+    yc = compiled(x.detach())
+    assert torch.allclose(yc, y.detach(), atol=1e-2, rtol=1e-2)
+
+
+def test_module_single_gather_window_route():
+    from att3ntion_b200 import HypergraphAttention
+    torch.manual_seed(1)
+    mod = HypergraphAttention(128, 2, gather_mode=1, window=16).cuda()
+    x = torch.randn(1, 50, 128, device="cuda", requires_grad=True)
+    y = mod(x)
+    y.sum().backward()
+    assert y.shape == (1, 50, 128) and torch.isfinite(y).all() and torch.isfinite(x.grad).all()
+    assert mod.Wv_q is None
+    with pytest.raises(ValueError):
+        HypergraphAttention(64, 4, scatter=True, gather_mode=1)
+    with pytest.raises(ValueError):
+        HypergraphAttention(64, 4, window=8)
