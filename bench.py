@@ -308,6 +308,68 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_rows(args):
+    """Long-sequence workload (BASELINE.json config 5): B1 Hq8 Hkv1 N131072 D128 w128, query rows
+    sharded over the ranks with a 128-row key halo from the left neighbour and the halo key
+    gradients handed back after the backward (two point-to-point messages per step, NCCL).
+    Total work is fixed, so the scaling is strong."""
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from att3ntion_b200 import _cabi, _cuda_kernels as ck
+    from att3ntion_b200._dist import RowShardedGather
+    n, w = args.seq_len if args.seq_len != 8192 else 131072, args.window
+    op = RowShardedGather(n, w)
+    lo, hi = op.plan.lo, op.plan.hi
+    g = torch.Generator(device="cpu").manual_seed(4)
+    s = 1.0 / math.sqrt(D)
+    # every rank draws the full tensors from the same seed and keeps its rows (inputs are row-sharded)
+    def draw(heads, scale):
+        return (torch.randn(1, heads, n, D, generator=g) * scale).to(torch.bfloat16)[:, :, lo:hi].contiguous().to(dev)
+    Q = draw(HQ, s); R = draw(1, s); S = draw(1, s); Vr = draw(1, s); Vs = draw(1, s); dY = draw(HQ, 1.0)
+    flops_step = 16 * D * triplets(1, HQ, n, w)
+
+    def step():
+        y = op.forward(Q, R, S, Vr, Vs)
+        return y, op.backward(dY)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    dist.barrier(); torch.cuda.synchronize()
+    l0 = sum(_cabi.lib.att3_launch_count(i) for i in range(4))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = step()
+    e1.record()
+    dist.barrier(); torch.cuda.synchronize()
+    ck.device_status()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    launches = sum(_cabi.lib.att3_launch_count(i) for i in range(4)) - l0
+    chk = torch.stack([out[0].float().abs().mean(), out[1][0].float().abs().mean(), out[1][1].float().abs().mean()])
+    dist.all_reduce(chk)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "fwd+bwd TFLOP/s, shared-KV causal w=128 d=128, row-sharded long sequence",
+            "value": flops_step / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"shared-KV B1 Hq{HQ} Hkv1 N{n} D{D} causal window {w}, rows sharded over "
+                                   f"{world} GPU(s), 128-row key halo, halo key-gradients handed back",
+                       "shards": op.shards, "flops_per_step": flops_step},
+            "gpu_launches": int(launches), "checksum": [round(v, 6) for v in chk.tolist()],
+        }))
+    dist.destroy_process_group()
+
+
 # DRAM bytes (read + write) of one sg_ring_bwd_kernel launch at this workload, from the ncu
 # capture summarised under profiles/ (null until measured for a window).
 TRAFFIC_BYTES_PER_LAUNCH = {}
@@ -324,11 +386,15 @@ if __name__ == "__main__":
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--seq-len", type=int, default=N, help="sequence length (profiling captures use a smaller case)")
     ap.add_argument("--batch", type=int, default=B)
+    ap.add_argument("--workload", default="batch", choices=["batch", "rows"],
+                    help="batch: config 4, one batch per GPU (default); rows: config 5, one sequence row-sharded")
     ap.add_argument("--profile", action="store_true",
                     help="kernel-only run for profiler captures: exact warm-up count, no e2e and no CPU leg")
     a = ap.parse_args()
     N, B = a.seq_len, a.batch
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload == "rows":
+        run_rows(a)
     else:
         run_ours(a)

@@ -1,0 +1,72 @@
+"""World-size-2 (and 3) gloo runs of the row-sharding host logic on CPU: partitioning,
+halo exchange and the hand-back of halo key gradients.  The compute step is the CPU
+oracle here (the kernels need a GPU); what is under test is att3ntion_b200/_dist.py."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import triplet_oracle as O
+
+NAMES = ["Q", "R", "S", "Vr", "Vs"]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _oracle_fwd(Q, R, S, Vr, Vs, w, qb):
+    r = O.single_gather_banded(Q, R, S, Vr, Vs, window=w, q_begin=qb, chunk=32)
+    return r["Y"], r["m"], r["l"]
+
+
+def _oracle_bwd(dY, Q, R, S, Vr, Vs, Y, m, l, w, qb):
+    r = O.single_gather_banded(Q, R, S, Vr, Vs, window=w, dY=dY, q_begin=qb, chunk=32)
+    return r["dQ"], r["dR"], r["dS"], r["dVr"], r["dVs"]
+
+
+def _worker(rank, world, port, n, window, hkv, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from att3ntion_b200._dist import RowShardedGather, gather_rows
+        g = torch.Generator().manual_seed(4)
+        full = {"Q": torch.randn(1, 4, n, 16, generator=g, dtype=torch.float64)}
+        for k in NAMES[1:]:
+            full[k] = torch.randn(1, hkv, n, 16, generator=g, dtype=torch.float64)
+        dY = torch.randn(1, 4, n, 16, generator=g, dtype=torch.float64)
+        op = RowShardedGather(n, window, compute_fwd=_oracle_fwd, compute_bwd=_oracle_bwd)
+        lo, hi = op.plan.lo, op.plan.hi
+        Y = op.forward(*[full[k][:, :, lo:hi].contiguous() for k in NAMES])
+        grads = op.backward(dY[:, :, lo:hi].contiguous())
+        got = [gather_rows(Y, op.shards)] + [gather_rows(t, op.shards) for t in grads]
+        if rank == 0:
+            ref = O.single_gather_banded(*[full[k] for k in NAMES], window=window, dY=dY, chunk=32)
+            errs = [(a - ref[k]).abs().max().item() for a, k in zip(got, ["Y", "dQ", "dR", "dS", "dVr", "dVs"])]
+            torch.save({"errs": errs, "shards": op.shards}, out)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n,window,hkv", [(2, 400, 128, 1), (2, 272, 33, 4), (3, 300, 64, 1)])
+def test_row_sharding_matches_unsharded(tmp_path, world, n, window, hkv):
+    out = str(tmp_path / "res.pt")
+    mp.spawn(_worker, args=(world, _free_port(), n, window, hkv, out), nprocs=world, join=True)
+    res = torch.load(out)
+    assert max(res["errs"]) < 1e-9, res
+    assert res["shards"][0][0] == 0 and res["shards"][-1][1] == n
+    assert all(lo % 128 == 0 for lo, _ in res["shards"])
+
+
+def test_partition_helpers():
+    from att3ntion_b200._dist import row_shards, shard_batch
+    assert row_shards(131072, 8) == [(i * 16384, (i + 1) * 16384) for i in range(8)]
+    s = row_shards(300, 4)
+    assert s[0] == (0, 128) and s[-1][1] == 300 and sum(hi - lo for lo, hi in s) == 300
+    assert [len(shard_batch(10, 4, r)) for r in range(4)] == [3, 3, 2, 2]
+    assert list(shard_batch(4, 8, 5)) == []
