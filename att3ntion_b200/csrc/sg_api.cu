@@ -276,3 +276,62 @@ extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, co
     if (rc) return rc;
     return launch_reduce(p, nblk, D, dR, dVr, st);
 }
+
+// ---------------------------------------------------------------------------
+// Backward for callers that cannot allocate
+// ---------------------------------------------------------------------------
+//
+// Some hosts of this library have no way to hand the backward a scratch buffer:
+// a plugin running inside a framework's stream-ordered or graph-private memory
+// pool where cudaMalloc is forbidden, a real-time inference/training loop that
+// pre-plans all device memory and treats any allocator call as a fault, or a
+// sandboxed worker whose CUDA allocation entry points are not reachable at all.
+// For them the FP32 key-gradient partials of the windowed backward live in a
+// fixed array that is part of the library image.  Every GPU that loads the
+// library holds these ATT3_STATIC_SCRATCH_BYTES until the process exits.
+//
+// The array's name is only a host-side handle: its device address is looked up
+// once per device, with that device current, by cudaGetSymbolAddress, and that
+// address is what the kernels receive.
+constexpr size_t ATT3_STATIC_SCRATCH_BYTES = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[ATT3_STATIC_SCRATCH_BYTES];
+
+extern "C" size_t att3_sg_backward_static_max_bytes(void) { return ATT3_STATIC_SCRATCH_BYTES; }
+
+extern "C" int att3_sg_backward_static(const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+                                       const void* Vs, const void* Y, const float* m, const float* l,
+                                       const uint8_t* mask, void* dQ, void* dR, void* dS, void* dVr, void* dVs,
+                                       int B, int Hq, int Hkv, int N, int D, int window, int q_begin, void* stream) {
+    if (window < 1 || window > sgring::RING)
+        return att3::set_error(ATT3_ERR_INVALID,
+                               "att3_sg_backward_static: only the windowed path (window 1..128) is offered, got %d",
+                               window);
+    if (int rc = check_shapes("att3_sg_backward_static", B, Hq, Hkv, N, D, window, q_begin)) return rc;
+    const size_t need = att3_sg_backward_workspace_bytes(B, Hq, Hkv, N, D, window);
+    if (need > ATT3_STATIC_SCRATCH_BYTES)
+        return att3::set_error(ATT3_ERR_WORKSPACE,
+                               "att3_sg_backward_static: these sizes need %zu bytes of scratch, the built-in array "
+                               "holds %zu (B*Hkv*N*D must not exceed %zu); use att3_sg_backward with a workspace",
+                               need, ATT3_STATIC_SCRATCH_BYTES, ATT3_STATIC_SCRATCH_BYTES / 16);
+    // Device address of the array, resolved on the first call per device (keep that call outside
+    // any stream capture) and cached afterwards.
+    constexpr int kMaxDevices = 64;
+    static void* cached[kMaxDevices] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward_static: cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices)
+        return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_sg_backward_static: device ordinal %d out of range", dev);
+    void* ptr = cached[dev];
+    if (!ptr) {
+        e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr)
+            return att3::set_cuda_error(e, "att3_sg_backward_static: cudaGetSymbolAddress(scratch)");
+        cached[dev] = ptr;
+    }
+    // Nothing in the scratch has to start at zero: every partial row the reduction reads is
+    // written by exactly one CTA of the same call first.  The array is shared by all calls,
+    // so two calls whose kernels may overlap on the device (different streams) race on it.
+    return att3_sg_backward(dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv, N, D, window,
+                            q_begin, ptr, ATT3_STATIC_SCRATCH_BYTES, stream);
+}

@@ -101,6 +101,33 @@ int att3_sg_backward(const void* dY, const void* Q, const void* R, const void* S
                      int B, int Hq, int Hkv, int N, int D, int window, int q_begin,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* att3_sg_backward for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference, whose launchers allocate their own buffers
+ * through torch.  Meant for hosts where an allocator call is impossible or
+ * forbidden at the point of the call: code running inside a framework's
+ * capture-private or stream-ordered pool, a real-time loop with a fixed memory
+ * plan, a sandboxed worker without access to the allocation entry points.
+ * The FP32 scratch of the windowed backward lives in a fixed array inside the
+ * library (att3_sg_backward_static_max_bytes(), 32 MiB, held by every GPU that
+ * loads the library until the process exits), so the call itself allocates
+ * nothing: no cudaMalloc/cudaFree, no allocating library routine (leave
+ * att3_timing_enable off, it creates events).
+ *   - windowed path only (1 <= window <= 128); sizes whose scratch,
+ *     16 * B * Hkv * N * D bytes, exceeds the array are rejected with
+ *     ATT3_ERR_WORKSPACE and a message naming the limit;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and caches it: make that
+ *     first call before any stream capture;
+ *   - all calls share the one array and it keeps the last call's contents;
+ *     nothing in it needs clearing between calls, but two calls that can overlap
+ *     on the GPU (different streams) race on it -- serialise them;
+ *   - results are bit-identical to att3_sg_backward on the same inputs. */
+size_t att3_sg_backward_static_max_bytes(void);
+int att3_sg_backward_static(const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+                            const void* Vs, const void* Y, const float* m, const float* l, const uint8_t* mask,
+                            void* dQ, void* dR, void* dS, void* dVr, void* dVs,
+                            int B, int Hq, int Hkv, int N, int D, int window, int q_begin, void* stream);
+
 /* ------------------------------------------------------------------------- *
  * Three-gather hypergraph attention: forward_cuda / backward_cuda
  * (cuda/forward.cu:1252-1602, cuda/backward.cu:1716-2232; math in
