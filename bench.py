@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--window 128]
 
-Workload (BASELINE.json config 4, the one the metric is quoted on): BF16, one
+Workload (the shared-KV configuration the headline metric is quoted on): BF16, one
 shared KV head, 8 query heads, D = 128, batch 4, N = 8192, causal window 128;
 Q/R/S/Vr/Vs ~ N(0,1)/sqrt(128) from seed 3, dY ~ N(0,1).  A step is one forward
 plus one backward over that batch.  With N GPUs every rank runs its own batch of
@@ -309,7 +309,7 @@ def run_ours(args):
 
 
 def run_rows(args):
-    """Long-sequence workload (BASELINE.json config 5): B1 Hq8 Hkv1 N131072 D128 w128, query rows
+    """Long-sequence workload: B1 Hq8 Hkv1 N131072 D128 w128, query rows
     sharded over the ranks with a 128-row key halo from the left neighbour and the halo key
     gradients handed back after the backward (two point-to-point messages per step, NCCL).
     Total work is fixed, so the scaling is strong."""
