@@ -95,7 +95,7 @@ template <int N>
 __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 enum PipeBar {
-    PB_H_FULL_A = 0, PB_H_FULL_B, PB_S_FULL_A, PB_S_FULL_B, PB_P_FULL_A, PB_P_FULL_B, PB_D_DONE_A, PB_D_DONE_B,
+    PB_H_FULL = 0, PB_S_XT, PB_S_DP, PB_P_FULL, PB_G_FULL, PB_D_DONE,
     PB_W_FULL, PB_W_FREE, PB_E_SYNC, PB_E_SYNC2, PB_H_SYNC, PB_RING_FREE, PB_COUNT
 };
 
@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     constexpr int DW = D / 2;            // packed words per row
     constexpr int HD = D / 2;            // d columns per E thread in the dQ collapse
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t C_XT = 0, C_DP = 128, C_AK = 256, C_AV = 384, C_W0 = 64, C_W1 = 192;
+    constexpr uint32_t C_XT = 0, C_DP = 128, C_AK = 256, C_AV = 384;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -202,10 +202,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     }
     if (tid == 0) {
         // Arrival counts are in warps: one elected lane arrives for its warp (warp_arrive).
-        mbar_init(&bars[PB_H_FULL_A], 2);   mbar_init(&bars[PB_H_FULL_B], 2);
-        mbar_init(&bars[PB_S_FULL_A], 1);   mbar_init(&bars[PB_S_FULL_B], 1);
-        mbar_init(&bars[PB_P_FULL_A], 8);   mbar_init(&bars[PB_P_FULL_B], 8);
-        mbar_init(&bars[PB_D_DONE_A], 1);   mbar_init(&bars[PB_D_DONE_B], 1);
+        mbar_init(&bars[PB_H_FULL], 4);
+        mbar_init(&bars[PB_S_XT], 1);       mbar_init(&bars[PB_S_DP], 1);
+        mbar_init(&bars[PB_P_FULL], 8);     mbar_init(&bars[PB_G_FULL], 8);
+        mbar_init(&bars[PB_D_DONE], 1);
         mbar_init(&bars[PB_W_FULL], 1);     mbar_init(&bars[PB_W_FREE], 8);
         mbar_init(&bars[PB_E_SYNC], 8);     mbar_init(&bars[PB_E_SYNC2], 8);
         mbar_init(&bars[PB_H_SYNC], 4);
@@ -295,9 +295,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         h_stage(0);
         fence_async_smem();
         cta_start_sync();
-        const int x = hslot >> 6;                      // tile half this thread's row belongs to
-        uint64_t* bar_full = &bars[x ? PB_H_FULL_B : PB_H_FULL_A];
-        uint64_t* bar_done = &bars[x ? PB_D_DONE_B : PB_D_DONE_A];
+        uint64_t* bar_full = &bars[PB_H_FULL];
+        uint64_t* bar_done = &bars[PB_D_DONE];
         int n = 0, it = 0, n_query = 0, ring_phase = 0;
         bool ok = true;
         float l_next = __ldg(p.l + row_index(0));
@@ -359,9 +358,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         cta_start_sync();
         if (is_mma) {
         // ================================================================== MMA warp
-        const uint32_t idesc_s = make_idesc_bf16(RING, 64, 0, 0);       // score halves: N = 64
+        const uint32_t idesc_s = make_idesc_bf16(RING, RING, 0, 0);     // score-shaped, both operands K-major
         const uint32_t idesc_acc = make_idesc_bf16(RING, D, 0, 1);      // A in TMEM, B MN-major, N = D
-        const uint32_t idesc_w = make_idesc_bf16(RING, 64, 0, 1);
         // Descriptor bases are built once; a k-step only adds a compile-time constant to the
         // start-address field (16-byte units).  The single issuing thread runs a dependent
         // instruction every few cycles, so every instruction spared per MMA shows up directly
@@ -388,60 +386,50 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 if (!any_vis || !(l_i > 0.f)) continue;
                 {   // whole warp, converged: one elected lane issues each MMA (see umma_ss_warp)
                     const uint32_t ph = n & 1;
-                    // The score MMAs of this head overwrite the tensor-memory columns that the
-                    // previous head's accumulation (and W) MMAs read their A operand from; a later
-                    // MMA is not held back for an earlier one's operand reads, so wait until the
-                    // previous head's last group has completed.
-                    if (n > 0) ok = pipe_wait(&bars[WITH_DQ ? PB_W_FULL : PB_D_DONE_B], (n - 1) & 1, sFail, TR(0));
-                    // ---- score halves
-#pragma unroll
-                    for (int x = 0; x < 2; ++x) {
-                        if (!ok) break;
-                        ok = pipe_wait(&bars[x ? PB_H_FULL_B : PB_H_FULL_A], ph, sFail, TR(1 + x));
-                        // half b overwrites the columns that held W of the previous head
-                        if (ok && WITH_DQ && x == 1 && n > 0) ok = pipe_wait(&bars[PB_W_FREE], (n - 1) & 1, sFail, TR(3));
-                        if (!ok) break;
+                    // The score MMAs overwrite the tensor-memory columns that the previous head's
+                    // accumulation and W MMAs read their A operand from; a later MMA is not held back
+                    // for an earlier one's operand reads, so wait for the previous head's last group.
+                    if (n > 0) ok = pipe_wait(&bars[WITH_DQ ? PB_W_FULL : PB_D_DONE], (n - 1) & 1, sFail, TR(0));
+                    if (ok) ok = pipe_wait(&bars[PB_H_FULL], ph, sFail, TR(1));
+                    if (ok) {
                         tc_fence_after();
-                        constexpr uint32_t kRowsB = 64 * 128 / 16;     // tile rows 64.. of each d-block, 16-byte units
 #pragma unroll
-                        for (int kk = 0; kk < D / 16; ++kk) {
+                        for (int kk = 0; kk < D / 16; ++kk) {      // X^T = Kb Qp^T
                             const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                            umma_ss_warp(tXT + x * 64, dKb + off, dQpK + (off + x * kRowsB), idesc_s, kk > 0);
+                            umma_ss_warp(tXT, dKb + off, dQpK + off, idesc_s, kk > 0);
                         }
-#pragma unroll
-                        for (int kk = 0; kk < D / 16; ++kk) {
-                            const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                            umma_ss_warp(tDP + x * 64, dVb + off, dGK + (off + x * kRowsB), idesc_s, kk > 0);
-                        }
-                        umma_commit_warp(&bars[x ? PB_S_FULL_B : PB_S_FULL_A]);
+                        umma_commit_warp(&bars[PB_S_XT]);
+                        // dP^T lands on the columns that held W of the previous head
+                        if (WITH_DQ && n > 0) ok = pipe_wait(&bars[PB_W_FREE], (n - 1) & 1, sFail, TR(3));
                     }
-                    // ---- accumulation halves (K = 64 rows of the Hadamard tiles each)
+                    if (ok) {
 #pragma unroll
-                    for (int x = 0; x < 2; ++x) {
-                        if (!ok) break;
-                        ok = pipe_wait(&bars[x ? PB_P_FULL_B : PB_P_FULL_A], ph, sFail, TR(4 + x));
-                        if (!ok) break;
+                        for (int kk = 0; kk < D / 16; ++kk) {      // dP^T = Vb Gt^T
+                            const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
+                            umma_ss_warp(tDP, dVb + off, dGK + off, idesc_s, kk > 0);
+                        }
+                        umma_commit_warp(&bars[PB_S_DP]);
+                        ok = pipe_wait(&bars[PB_P_FULL], ph, sFail, TR(4));
+                    }
+                    if (ok) {
                         tc_fence_after();
 #pragma unroll
-                        for (int k4 = 0; k4 < 4; ++k4) {
-                            const int kk = x * 4 + k4;
-                            umma_ts_warp(tAK, tDP + kk * 8, dQpM + kk * (2048 / 16), idesc_acc, 1);
-                        }
-#pragma unroll
-                        for (int k4 = 0; k4 < 4; ++k4) {
-                            const int kk = x * 4 + k4;
+                        for (int kk = 0; kk < RING / 16; ++kk)    // dVb += P^T Gt
                             umma_ts_warp(tAV, tXT + kk * 8, dGM + kk * (2048 / 16), idesc_acc, 1);
-                        }
-                        umma_commit_warp(&bars[x ? PB_D_DONE_B : PB_D_DONE_A]);
+                        ok = pipe_wait(&bars[PB_G_FULL], ph, sFail, TR(5));
                     }
-                    if (ok && WITH_DQ) {
+                    if (ok) {
+                        tc_fence_after();
 #pragma unroll
-                        for (int dh = 0; dh < D / 64; ++dh)
+                        for (int kk = 0; kk < RING / 16; ++kk)    // dKb += gA^T Qp
+                            umma_ts_warp(tAK, tXT + 64 + kk * 8, dQpM + kk * (2048 / 16), idesc_acc, 1);
+                        umma_commit_warp(&bars[PB_D_DONE]);
+                        if (WITH_DQ) {
 #pragma unroll
-                            for (int kk = 0; kk < RING / 16; ++kk)
-                                umma_ts_warp(tmem_base + (dh ? C_W1 : C_W0), tDP + kk * 8,
-                                        dKaM + (dh * (RING * 128) + kk * 2048) / 16, idesc_w, kk > 0);
-                        umma_commit_warp(&bars[PB_W_FULL]);
+                            for (int kk = 0; kk < RING / 16; ++kk)    // W = gA^T Ka, over the consumed dP^T columns
+                                umma_ts_warp(tDP, tXT + 64 + kk * 8, dKaM + kk * (2048 / 16), idesc_acc, kk > 0);
+                            umma_commit_warp(&bars[PB_W_FULL]);
+                        }
                     }
                 }
                 ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
@@ -452,7 +440,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             n_query = n;
         }
         // Let the last committed group finish before the tensor memory is released.
-        if (n > 0 && ok) pipe_wait(&bars[WITH_DQ ? PB_W_FULL : PB_D_DONE_B], (n - 1) & 1, sFail);
+        if (n > 0 && ok) pipe_wait(&bars[WITH_DQ ? PB_W_FULL : PB_D_DONE], (n - 1) & 1, sFail);
         __syncwarp();
         }
     } else {
@@ -519,7 +507,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             pre_l = __ldg(p.l + row);
         };
         prefetch(0);
-        uint64_t* bar_head = &bars[WITH_DQ ? PB_W_FULL : PB_D_DONE_B];
+        uint64_t* bar_head = &bars[WITH_DQ ? PB_W_FULL : PB_D_DONE];
         int n = 0, it = 0, n_query = 0;
         bool ok = true;
         for (int i = q0; i < q1 && ok; ++i) {
@@ -560,18 +548,18 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 }
                 const float lse2 = m_i * LOG2E + __log2f(l_i);
                 const uint32_t ph = n & 1;
-#pragma unroll 1
-                for (int x = 0; x < 2; ++x) {
-                    ok = pipe_wait(&bars[x ? PB_S_FULL_B : PB_S_FULL_A], ph, sFail, TR(8 + x));
-                    if (!ok) break;
-                    tc_fence_after();
-                    const int c = 2 * x + ch;                      // 32-column chunk of the score tile
-                    uint32_t xr[32], dp[32], pk[16], gk[16];
-                    long long tt = tracer ? clock64() : 0;
+                // ---- phase 1: P^T = exp2(X^T c - lse) for this thread's 64 columns, BF16 into X^T[0,64)
+                uint32_t pk[32];
+                ok = pipe_wait(&bars[PB_S_XT], ph, sFail, TR(8));
+                if (!ok) break;
+                tc_fence_after();
+                long long tt = tracer ? clock64() : 0;
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int c = 2 * ch + cc;                      // 32-column chunk of the score tile
+                    uint32_t xr[32];
                     tmem_ld32(tl + C_XT + c * 32, xr);
-                    tmem_ld32(tl + C_DP + c * 32, dp);
                     tmem_wait_ld();
-                    if (tracer) { const long long t2 = clock64(); p.trace[20] += t2 - tt; tt = t2; }
                     const uint32_t cw = my_vis ? (c == 0 ? vw[0] : c == 1 ? vw[1] : c == 2 ? vw[2] : vw[3]) : 0u;
 #pragma unroll
                     for (int t = 0; t < 32; t += 2) {
@@ -581,30 +569,47 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                             if (!((cw >> t) & 1u)) p0 = 0.f;
                             if (!((cw >> (t + 1)) & 1u)) p1 = 0.f;
                         }
-                        float g0 = p0 * (__uint_as_float(dp[t]) - delta);
-                        float g1 = p1 * (__uint_as_float(dp[t + 1]) - delta);
-                        if (single) { g0 = 0.f; g1 = 0.f; }
-                        pk[t >> 1] = pack_bf16x2(p0, p1);
-                        gk[t >> 1] = pack_bf16x2(g0, g1);
+                        pk[cc * 16 + (t >> 1)] = pack_bf16x2(p0, p1);
                     }
-                    if (tracer) { const long long t2 = clock64(); p.trace[21] += t2 - tt; tt = t2; }
-                    if (x == 0) {
-                        // The BF16 results of half a land on score columns [0,32) that the ch = 0
-                        // threads read: wait until every E thread has its loads in registers.
-                        tc_fence_before();
-                        warp_arrive(&bars[PB_E_SYNC], lane);
-                        ok = pipe_wait(&bars[PB_E_SYNC], ph, sFail, TR(10));
-                        if (!ok) break;
-                        tc_fence_after();
+                }
+                if (tracer) { const long long t2 = clock64(); p.trace[21] += t2 - tt; tt = t2; }
+                // the BF16 results land on score columns that other E threads read: all loads first
+                tc_fence_before();
+                warp_arrive(&bars[PB_E_SYNC], lane);
+                ok = pipe_wait(&bars[PB_E_SYNC], ph, sFail, TR(10));
+                if (!ok) break;
+                tc_fence_after();
+                tmem_st32(tl + C_XT + ch * 32, pk);
+                tmem_wait_st();
+                tc_fence_before();
+                warp_arrive(&bars[PB_P_FULL], lane);
+                // ---- phase 2: gA^T = P^T o (dP^T - delta), BF16 into X^T[64,128)
+                ok = pipe_wait(&bars[PB_S_DP], ph, sFail, TR(9));
+                if (!ok) break;
+                tc_fence_after();
+                if (tracer) tt = clock64();
+                {
+                    uint32_t gk[32];
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        uint32_t dp[32];
+                        tmem_ld32(tl + C_DP + (2 * ch + cc) * 32, dp);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int t = 0; t < 32; t += 2) {
+                            const float2 pp = unpack_bf16x2(pk[cc * 16 + (t >> 1)]);
+                            float g0 = pp.x * (__uint_as_float(dp[t]) - delta);
+                            float g1 = pp.y * (__uint_as_float(dp[t + 1]) - delta);
+                            if (single) { g0 = 0.f; g1 = 0.f; }
+                            gk[cc * 16 + (t >> 1)] = pack_bf16x2(g0, g1);
+                        }
                     }
-                    if (tracer) tt = clock64();
-                    tmem_st16(tl + C_XT + c * 16, pk);
-                    tmem_st16(tl + C_DP + c * 16, gk);
+                    tmem_st32(tl + C_XT + 64 + ch * 32, gk);
                     tmem_wait_st();
                     tc_fence_before();
-                    if (tracer) p.trace[22] += clock64() - tt;
-                    warp_arrive(&bars[x ? PB_P_FULL_B : PB_P_FULL_A], lane);
                 }
+                if (tracer) p.trace[22] += clock64() - tt;
+                warp_arrive(&bars[PB_G_FULL], lane);
                 if (!ok) break;
                 if (WITH_DQ) {
                     ok = pipe_wait(&bars[PB_W_FULL], ph, sFail, TR(11));
@@ -612,7 +617,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     tc_fence_after();
                     const long long te = tracer ? clock64() : 0;
                     // dQ[d] = scale * sum_k Kb_k[d] * W[k][d]; this thread: lane k, d in its half.
-                    const uint32_t wcol = (D == 128) ? (ch ? C_W1 : C_W0) : (C_W0 + ch * 32);
+                    const uint32_t wcol = C_DP + ch * HD;
                     constexpr int NC = HD / 32;
                     float* red = sRed + (n & 1) * 4 * D;
 #pragma unroll 1
