@@ -95,7 +95,7 @@ template <int N>
 __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 enum PipeBar {
-    PB_H_FULL = 0, PB_S_XT, PB_S_DP, PB_P_FULL, PB_G_FULL, PB_D_DONE,
+    PB_H_FULL0 = 0, PB_H_FULL1, PB_S_XT, PB_S_DP, PB_P_FULL, PB_G_FULL, PB_D_DONE0, PB_D_DONE1, PB_V_DONE0, PB_V_DONE1,
     PB_W_FULL, PB_W_FREE, PB_E_SYNC, PB_E_SYNC2, PB_H_SYNC, PB_RING_FREE, PB_COUNT
 };
 
@@ -112,10 +112,13 @@ struct PipeSmem {
     static constexpr int TILE = RING * D * 2;
     static constexpr int OFF_KB = 0;
     static constexpr int OFF_VB = TILE;
-    static constexpr int OFF_QP = 2 * TILE;
-    static constexpr int OFF_G = 3 * TILE;
-    static constexpr int OFF_KA = 4 * TILE;                        // only WITH_DQ
-    static constexpr int OFF_STAGE = (WITH_DQ ? 5 : 4) * TILE;     // 2 stages x {Q, dY} rows
+    // Hadamard tiles: Qp is double-buffered so the H warps build the next head while this one
+    // is consumed; Gt is double-buffered where shared memory allows (the dQ pass also holds Ka).
+    static constexpr int G_BUFS = WITH_DQ ? 1 : 2;
+    static constexpr int OFF_QP = 2 * TILE;                        // 2 buffers
+    static constexpr int OFF_G = 4 * TILE;                         // G_BUFS buffers
+    static constexpr int OFF_KA = 5 * TILE;                        // only WITH_DQ
+    static constexpr int OFF_STAGE = 6 * TILE;                     // 2 stages x {Q, dY} rows
     static constexpr int OFF_RED = OFF_STAGE + 2 * 2 * D * 2;      // 2 x 4 x D floats (dQ partials)
     static constexpr int OFF_BARS = OFF_RED + 2 * 4 * D * 4;
     static constexpr int OFF_MISC = OFF_BARS + PB_COUNT * 8;       // tmem slot (4) + fail flag (4)
@@ -124,13 +127,16 @@ struct PipeSmem {
 };
 
 // Bounded wait that also leaves when another thread has raised the CTA's failure flag.
+// Bounded wait on an mbarrier phase.  try_wait parks the thread in hardware until the phase
+// completes or a system time limit passes.  Measured alternatives on this part, same kernel:
+// all threads spinning on test_wait pulled the SM clock from 1.9 to 1.3 GHz under the power
+// cap (2x the run time); one polling lane per warp with __nanosleep(20) between polls was
+// 2.3x slower still (the sleep is far coarser than its argument).  The iteration count bounds
+// the total wait; the loop also leaves when another thread has raised the CTA's failure flag.
 __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volatile int* fail,
                                           long long* trace = nullptr) {
     const uint32_t addr = smem_u32(bar);
     const long long t0 = trace ? clock64() : 0;
-    // try_wait parks the thread in hardware for up to the hinted time instead of spinning on
-    // shared memory (hundreds of pollers would otherwise compete with the operand traffic);
-    // the iteration count still bounds the total wait to about a second.
     for (uint32_t it = 0; it < (1u << 20); ++it) {
         uint32_t done;
         asm volatile(
@@ -202,10 +208,11 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     }
     if (tid == 0) {
         // Arrival counts are in warps: one elected lane arrives for its warp (warp_arrive).
-        mbar_init(&bars[PB_H_FULL], 4);
+        mbar_init(&bars[PB_H_FULL0], 4);    mbar_init(&bars[PB_H_FULL1], 4);
         mbar_init(&bars[PB_S_XT], 1);       mbar_init(&bars[PB_S_DP], 1);
         mbar_init(&bars[PB_P_FULL], 8);     mbar_init(&bars[PB_G_FULL], 8);
-        mbar_init(&bars[PB_D_DONE], 1);
+        mbar_init(&bars[PB_D_DONE0], 1);    mbar_init(&bars[PB_D_DONE1], 1);
+        mbar_init(&bars[PB_V_DONE0], 1);    mbar_init(&bars[PB_V_DONE1], 1);
         mbar_init(&bars[PB_W_FULL], 1);     mbar_init(&bars[PB_W_FREE], 8);
         mbar_init(&bars[PB_E_SYNC], 8);     mbar_init(&bars[PB_E_SYNC2], 8);
         mbar_init(&bars[PB_H_SYNC], 4);
@@ -295,8 +302,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         h_stage(0);
         fence_async_smem();
         cta_start_sync();
-        uint64_t* bar_full = &bars[PB_H_FULL];
-        uint64_t* bar_done = &bars[PB_D_DONE];
+        constexpr int GB = L::G_BUFS;
         int n = 0, it = 0, n_query = 0, ring_phase = 0;
         bool ok = true;
         float l_next = __ldg(p.l + row_index(0));
@@ -331,10 +337,15 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 if (!ok) break;
                 if (it + 1 < n_iter) h_stage(it + 1);
                 if (!any_vis || !(l_i > 0.f)) continue;
-                if (n > 0) {
-                    ok = pipe_wait(bar_done, (n - 1) & 1, sFail, TR(18));
-                    if (!ok) break;
-                }
+                // Buffer reuse: Qp[n&1] was last read by the dKb MMAs of head n-2, Gt[n%GB] by the dVb
+                // MMAs of head n-GB.  Each per-buffer barrier is waited on at every one of its phases.
+                const int qb = n & 1, gb = n % GB;
+                if (n >= 2) ok = pipe_wait(&bars[PB_D_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, TR(18));
+                if (ok && n >= GB) ok = pipe_wait(&bars[PB_V_DONE0 + gb], ((n / GB) - 1) & 1, sFail, TR(18));
+                if (!ok) break;
+                uint8_t* dQp = sQp + qb * L::TILE;
+                uint8_t* dG = sG + gb * L::TILE;
+                const long long th0 = tracer ? clock64() : 0;
                 const uint4* q4 = reinterpret_cast<const uint4*>(sStage + (it & 1) * 2 * D);
                 const uint4* y4 = q4 + CH;
 #pragma unroll
@@ -345,11 +356,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     o.y = mul_bf16x2(q.y, rKa[4 * c + 1]);  gq.y = mul_bf16x2(y.y, rVa[4 * c + 1]);
                     o.z = mul_bf16x2(q.z, rKa[4 * c + 2]);  gq.z = mul_bf16x2(y.z, rVa[4 * c + 2]);
                     o.w = mul_bf16x2(q.w, rKa[4 * c + 3]);  gq.w = mul_bf16x2(y.w, rVa[4 * c + 3]);
-                    *reinterpret_cast<uint4*>(sQp + sw128_offset<RING>(hslot, c)) = o;
-                    *reinterpret_cast<uint4*>(sG + sw128_offset<RING>(hslot, c)) = gq;
+                    *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c)) = o;
+                    *reinterpret_cast<uint4*>(dG + sw128_offset<RING>(hslot, c)) = gq;
                 }
+                const long long th1 = tracer ? clock64() : 0;
                 fence_async_smem();
-                warp_arrive(bar_full, lane);
+                warp_arrive(&bars[PB_H_FULL0 + qb], lane);
+                if (tracer) { p.trace[24] += th1 - th0; p.trace[25] += clock64() - th1; }
                 ++n;
             }
         }
@@ -389,14 +402,19 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     // The score MMAs overwrite the tensor-memory columns that the previous head's
                     // accumulation and W MMAs read their A operand from; a later MMA is not held back
                     // for an earlier one's operand reads, so wait for the previous head's last group.
-                    if (n > 0) ok = pipe_wait(&bars[WITH_DQ ? PB_W_FULL : PB_D_DONE], (n - 1) & 1, sFail, TR(0));
-                    if (ok) ok = pipe_wait(&bars[PB_H_FULL], ph, sFail, TR(1));
+                    constexpr int GB = L::G_BUFS;
+                    const int qb = n & 1, gb = n % GB;
+                    const uint32_t qoff = qb * (L::TILE / 16), goff = gb * (L::TILE / 16);   // buffer offsets, 16-byte units
+                    if (n > 0)
+                        ok = WITH_DQ ? pipe_wait(&bars[PB_W_FULL], (n - 1) & 1, sFail, TR(0))
+                                     : pipe_wait(&bars[PB_D_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, TR(0));
+                    if (ok) ok = pipe_wait(&bars[PB_H_FULL0 + qb], (n >> 1) & 1, sFail, TR(1));
                     if (ok) {
                         tc_fence_after();
 #pragma unroll
                         for (int kk = 0; kk < D / 16; ++kk) {      // X^T = Kb Qp^T
                             const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                            umma_ss_warp(tXT, dKb + off, dQpK + off, idesc_s, kk > 0);
+                            umma_ss_warp(tXT, dKb + off, dQpK + (off + qoff), idesc_s, kk > 0);
                         }
                         umma_commit_warp(&bars[PB_S_XT]);
                         // dP^T lands on the columns that held W of the previous head
@@ -406,7 +424,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
 #pragma unroll
                         for (int kk = 0; kk < D / 16; ++kk) {      // dP^T = Vb Gt^T
                             const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                            umma_ss_warp(tDP, dVb + off, dGK + off, idesc_s, kk > 0);
+                            umma_ss_warp(tDP, dVb + off, dGK + (off + goff), idesc_s, kk > 0);
                         }
                         umma_commit_warp(&bars[PB_S_DP]);
                         ok = pipe_wait(&bars[PB_P_FULL], ph, sFail, TR(4));
@@ -415,15 +433,16 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                         tc_fence_after();
 #pragma unroll
                         for (int kk = 0; kk < RING / 16; ++kk)    // dVb += P^T Gt
-                            umma_ts_warp(tAV, tXT + kk * 8, dGM + kk * (2048 / 16), idesc_acc, 1);
+                            umma_ts_warp(tAV, tXT + kk * 8, dGM + (kk * (2048 / 16) + goff), idesc_acc, 1);
+                        umma_commit_warp(&bars[PB_V_DONE0 + gb]);
                         ok = pipe_wait(&bars[PB_G_FULL], ph, sFail, TR(5));
                     }
                     if (ok) {
                         tc_fence_after();
 #pragma unroll
                         for (int kk = 0; kk < RING / 16; ++kk)    // dKb += gA^T Qp
-                            umma_ts_warp(tAK, tXT + 64 + kk * 8, dQpM + kk * (2048 / 16), idesc_acc, 1);
-                        umma_commit_warp(&bars[PB_D_DONE]);
+                            umma_ts_warp(tAK, tXT + 64 + kk * 8, dQpM + (kk * (2048 / 16) + qoff), idesc_acc, 1);
+                        umma_commit_warp(&bars[PB_D_DONE0 + qb]);
                         if (WITH_DQ) {
 #pragma unroll
                             for (int kk = 0; kk < RING / 16; ++kk)    // W = gA^T Ka, over the consumed dP^T columns
@@ -440,7 +459,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             n_query = n;
         }
         // Let the last committed group finish before the tensor memory is released.
-        if (n > 0 && ok) pipe_wait(&bars[WITH_DQ ? PB_W_FULL : PB_D_DONE], (n - 1) & 1, sFail);
+        if (n > 0 && ok) {
+            if (WITH_DQ) pipe_wait(&bars[PB_W_FULL], (n - 1) & 1, sFail);
+            else pipe_wait(&bars[PB_D_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail);
+        }
         __syncwarp();
         }
     } else {
@@ -507,13 +529,17 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             pre_l = __ldg(p.l + row);
         };
         prefetch(0);
-        uint64_t* bar_head = &bars[WITH_DQ ? PB_W_FULL : PB_D_DONE];
+        // last MMA group of head k: W (dQ pass, one barrier, phase k) or dKb (per-buffer barrier, phase k/2)
+        auto wait_head_done = [&](int k, long long* tr) {
+            return WITH_DQ ? pipe_wait(&bars[PB_W_FULL], k & 1, sFail, tr)
+                           : pipe_wait(&bars[PB_D_DONE0 + (k & 1)], (k >> 1) & 1, sFail, tr);
+        };
         int n = 0, it = 0, n_query = 0;
         bool ok = true;
         for (int i = q0; i < q1 && ok; ++i) {
             if (i > q0) {
                 if (n > 0) {
-                    ok = pipe_wait(bar_head, (n - 1) & 1, sFail, TR(13));
+                    ok = wait_head_done(n - 1, TR(13));
                     if (!ok) break;
                     tc_fence_after();
                 }
@@ -663,7 +689,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         // Drain: every slot still holds a key of (q1 - 129, q1 - 1].
         if (ok) {
             if (n > 0) {
-                ok = pipe_wait(bar_head, (n - 1) & 1, sFail);
+                ok = wait_head_done(n - 1, nullptr);
                 tc_fence_after();
             }
             if (ok) {
