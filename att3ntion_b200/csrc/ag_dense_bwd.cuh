@@ -225,21 +225,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
             fence_async_smem();
             tc_fence_before();
             __syncthreads();
-            if (warp == 0) {
+            if (tid == 0) {   // one thread issues the unrolled run from precomputed descriptors
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < DP / 16; ++kk) {
                     const uint32_t off = ((kk >> 2) * (TILE * 128) + (kk & 3) * 32) / 16;
-                    umma_ss_warp(tmem_base + C_XT, dKb + off, dQpK + off, idesc_s, kk > 0);
+                    umma_ss(tmem_base + C_XT, dKb + off, dQpK + off, idesc_s, kk > 0);
                 }
 #pragma unroll
                 for (int kk = 0; kk < DP / 16; ++kk) {
                     const uint32_t off = ((kk >> 2) * (TILE * 128) + (kk & 3) * 32) / 16;
-                    umma_ss_warp(tmem_base + C_DP, dVb + off, dGK + off, idesc_s, kk > 0);
+                    umma_ss(tmem_base + C_DP, dVb + off, dGK + off, idesc_s, kk > 0);
                 }
-                umma_commit_warp(bar);
-                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
-                __syncwarp();
+                umma_commit(bar);
+                if (!mbar_wait(bar, phase)) *sFail = 1;
             }
             phase ^= 1;
             __syncthreads();
@@ -280,25 +279,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
             tmem_wait_st();
             tc_fence_before();
             __syncthreads();
-            if (warp == 0) {
+            if (tid == 0) {   // one thread issues the unrolled run from precomputed descriptors
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < TILE / 16; ++kk)
-                    umma_ts_warp(tmem_base + C_AK, tmem_base + C_DP + kk * 8, dQpM + kk * (2048 / 16), idesc_acc, 1);
+                    umma_ts(tmem_base + C_AK, tmem_base + C_DP + kk * 8, dQpM + kk * (2048 / 16), idesc_acc, 1);
 #pragma unroll
                 for (int kk = 0; kk < TILE / 16; ++kk)
-                    umma_ts_warp(tmem_base + C_AV, tmem_base + C_XT + kk * 8, dGM + kk * (2048 / 16), idesc_acc, 1);
+                    umma_ts(tmem_base + C_AV, tmem_base + C_XT + kk * 8, dGM + kk * (2048 / 16), idesc_acc, 1);
                 if (WITH_DA) {
 #pragma unroll
                     for (int dh = 0; dh < DP / 64; ++dh)
 #pragma unroll
                         for (int kk = 0; kk < TILE / 16; ++kk)
-                            umma_ts_warp(tmem_base + (dh ? C_W1 : C_W0), tmem_base + C_DP + kk * 8,
+                            umma_ts(tmem_base + (dh ? C_W1 : C_W0), tmem_base + C_DP + kk * 8,
                                          dKaM + (dh * (TILE * 128) + kk * 2048) / 16, idesc_w, kk > 0);
                 }
-                umma_commit_warp(bar);
-                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
-                __syncwarp();
+                umma_commit(bar);
+                if (!mbar_wait(bar, phase)) *sFail = 1;
             }
             phase ^= 1;
             __syncthreads();

@@ -201,16 +201,15 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                 fence_async_smem();
                 tc_fence_before();
                 __syncthreads();
-                if (warp == 0) {
+                if (tid == 0) {   // one thread issues the unrolled run from precomputed descriptors
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < DP / 16; ++kk) {
                         const uint32_t off = ((kk >> 2) * (TILE * 128) + (kk & 3) * 32) / 16;
-                        umma_ss_warp(tmem_base, dQp + off, dC + off, idesc_x, kk > 0);
+                        umma_ss(tmem_base, dQp + off, dC + off, idesc_x, kk > 0);
                     }
-                    umma_commit_warp(bar);
-                    if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
-                    __syncwarp();
+                    umma_commit(bar);
+                    if (!mbar_wait(bar, phase)) *sFail = 1;
                 }
                 phase ^= 1;
                 __syncthreads();
@@ -259,14 +258,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                 if (lane == 0) sMpart[warp] = m_w;
                 tc_fence_before();
                 __syncthreads();
-                if (warp == 0) {
+                if (tid == 0) {   // one thread issues the unrolled run from precomputed descriptors
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < TILE / 16; ++kk)
-                        umma_ts_warp(tmem_base + 128, tmem_base + kk * 8, dVcM + kk * (2048 / 16), idesc_u, kk > 0);
-                    umma_commit_warp(bar);
-                    if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
-                    __syncwarp();
+                        umma_ts(tmem_base + 128, tmem_base + kk * 8, dVcM + kk * (2048 / 16), idesc_u, kk > 0);
+                    umma_commit(bar);
+                    if (!mbar_wait(bar, phase)) *sFail = 1;
                 }
                 phase ^= 1;
                 const float Mt = fmaxf(fmaxf(sMpart[0], sMpart[1]), fmaxf(sMpart[2], sMpart[3]));

@@ -14,7 +14,7 @@ namespace {
 __device__ int g_sg_status = 0;
 
 // Cycle counters of the pipelined backward (diagnostic; filled when ATT3_TRACE=1).
-__device__ long long g_sg_trace[32];
+__device__ long long g_sg_trace[32 + 384];
 
 long long* trace_ptr() {
     static const bool on = [] { const char* e = getenv("ATT3_TRACE"); return e && e[0] == '1'; }();
@@ -76,6 +76,14 @@ extern "C" int att3_debug_trace(long long* out32) {
     if (cudaMemcpyFromSymbol(out32, g_sg_trace, sizeof(long long) * 32) != cudaSuccess) return ATT3_ERR_CUDA;
     long long z[32] = {0};
     cudaMemcpyToSymbol(g_sg_trace, z, sizeof(z));
+    return ATT3_OK;
+}
+
+// Diagnostic: the hand-off time stamps of six steady-state heads, 32 events each, dQ pass then the other.
+extern "C" int att3_debug_timeline(long long* out384) {
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(out384, g_sg_trace, sizeof(long long) * 384, sizeof(long long) * 32) != cudaSuccess)
+        return ATT3_ERR_CUDA;
     return ATT3_OK;
 }
 

@@ -287,6 +287,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                         (tid == 0 || tid == PIPE_E_THREADS || tid == PIPE_E_THREADS + PIPE_H_THREADS);
     const long long t_begin = tracer ? clock64() : 0;
 #define TR(k) (tracer ? p.trace + (k) : nullptr)
+    // Timeline of six steady-state heads (time stamps of the hand-offs, one thread per role).
+    constexpr int TL_FIRST = 804;
+#define TL(ev)                                                                                          \
+    do {                                                                                                \
+        if (tracer && n >= TL_FIRST && n < TL_FIRST + 6)                                                \
+            p.trace[32 + (WITH_DQ ? 0 : 192) + (n - TL_FIRST) * 32 + (ev)] = clock64();                 \
+    } while (0)
     uint32_t tmem_base = 0;
     auto cta_start_sync = [&]() {
         tc_fence_before();
@@ -335,6 +342,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 warp_arrive(&bars[PB_H_SYNC], lane);
                 ok = pipe_wait(&bars[PB_H_SYNC], it & 1, sFail, TR(17));
                 if (!ok) break;
+                TL(20);
                 if (it + 1 < n_iter) h_stage(it + 1);
                 if (!any_vis || !(l_i > 0.f)) continue;
                 // Buffer reuse: Qp[n&1] was last read by the dKb MMAs of head n-2, Gt[n%GB] by the dVb
@@ -343,6 +351,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 if (n >= 2) ok = pipe_wait(&bars[PB_D_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, TR(18));
                 if (ok && n >= GB) ok = pipe_wait(&bars[PB_V_DONE0 + gb], ((n / GB) - 1) & 1, sFail, TR(18));
                 if (!ok) break;
+                TL(21);
                 uint8_t* dQp = sQp + qb * L::TILE;
                 uint8_t* dG = sG + gb * L::TILE;
                 const long long th0 = tracer ? clock64() : 0;
@@ -363,6 +372,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 fence_async_smem();
                 warp_arrive(&bars[PB_H_FULL0 + qb], lane);
                 if (tracer) { p.trace[24] += th1 - th0; p.trace[25] += clock64() - th1; }
+                TL(22);
                 ++n;
             }
         }
@@ -374,10 +384,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         const uint32_t idesc_s = make_idesc_bf16(RING, RING, 0, 0);     // score-shaped, both operands K-major
         const uint32_t idesc_acc = make_idesc_bf16(RING, D, 0, 1);      // A in TMEM, B MN-major, N = D
         // Descriptor bases are built once; a k-step only adds a compile-time constant to the
-        // start-address field (16-byte units).  The single issuing thread runs a dependent
-        // instruction every few cycles, so every instruction spared per MMA shows up directly
-        // in the issue rate: rebuilding descriptors per MMA costs ~100-190 cycles an MMA,
-        // against 32-64 cycles of tensor-pipe time.
+        // start-address field (16-byte units).  Measured on one CTA (128x128x16 MMAs, 64 cycles
+        // of tensor-pipe time each): one thread issuing an unrolled run with precomputed
+        // descriptors sustains 64 cycles an MMA; electing a lane per MMA costs 102, and
+        // rebuilding descriptors per MMA 140-190.
         const uint64_t dKb = make_smem_desc(smem_u32(sKb), 16, 1024, SWIZZLE_128B);           // A, K-major
         const uint64_t dVb = make_smem_desc(smem_u32(sVb), 16, 1024, SWIZZLE_128B);
         const uint64_t dQpK = make_smem_desc(smem_u32(sQp), 16, 1024, SWIZZLE_128B);          // B, K-major
@@ -397,7 +407,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 const float l_i = l_next;
                 if (it + 1 < n_iter) l_next = __ldg(p.l + row_index(it + 1));
                 if (!any_vis || !(l_i > 0.f)) continue;
-                {   // whole warp, converged: one elected lane issues each MMA (see umma_ss_warp)
+                {   // the warp waits together; lane 0 issues each operand's MMAs back to back and commits them
                     const uint32_t ph = n & 1;
                     // The score MMAs overwrite the tensor-memory columns that the previous head's
                     // accumulation and W MMAs read their A operand from; a later MMA is not held back
@@ -408,54 +418,76 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     if (n > 0)
                         ok = WITH_DQ ? pipe_wait(&bars[PB_W_FULL], (n - 1) & 1, sFail, TR(0))
                                      : pipe_wait(&bars[PB_D_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, TR(0));
+                    TL(0);
                     if (ok) ok = pipe_wait(&bars[PB_H_FULL0 + qb], (n >> 1) & 1, sFail, TR(1));
+                    TL(1);
                     if (ok) {
                         tc_fence_after();
+                        if (lane == 0) {
 #pragma unroll
-                        for (int kk = 0; kk < D / 16; ++kk) {      // X^T = Kb Qp^T
-                            const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                            umma_ss_warp(tXT, dKb + off, dQpK + (off + qoff), idesc_s, kk > 0);
+                            for (int kk = 0; kk < D / 16; ++kk) {      // X^T = Kb Qp^T
+                                const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
+                                umma_ss(tXT, dKb + off, dQpK + (off + qoff), idesc_s, kk > 0);
+                            }
+                            umma_commit(&bars[PB_S_XT]);
                         }
-                        umma_commit_warp(&bars[PB_S_XT]);
+                        __syncwarp();
                         // dP^T lands on the columns that held W of the previous head
+                        TL(2);
                         if (WITH_DQ && n > 0) ok = pipe_wait(&bars[PB_W_FREE], (n - 1) & 1, sFail, TR(3));
+                        TL(3);
                     }
                     if (ok) {
+                        if (lane == 0) {
 #pragma unroll
-                        for (int kk = 0; kk < D / 16; ++kk) {      // dP^T = Vb Gt^T
-                            const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                            umma_ss_warp(tDP, dVb + off, dGK + (off + goff), idesc_s, kk > 0);
+                            for (int kk = 0; kk < D / 16; ++kk) {      // dP^T = Vb Gt^T
+                                const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
+                                umma_ss(tDP, dVb + off, dGK + (off + goff), idesc_s, kk > 0);
+                            }
+                            umma_commit(&bars[PB_S_DP]);
                         }
-                        umma_commit_warp(&bars[PB_S_DP]);
+                        __syncwarp();
+                        TL(4);
                         ok = pipe_wait(&bars[PB_P_FULL], ph, sFail, TR(4));
+                        TL(5);
                     }
                     if (ok) {
                         tc_fence_after();
+                        if (lane == 0) {
 #pragma unroll
-                        for (int kk = 0; kk < RING / 16; ++kk)    // dVb += P^T Gt
-                            umma_ts_warp(tAV, tXT + kk * 8, dGM + (kk * (2048 / 16) + goff), idesc_acc, 1);
-                        umma_commit_warp(&bars[PB_V_DONE0 + gb]);
-                        ok = pipe_wait(&bars[PB_G_FULL], ph, sFail, TR(5));
-                    }
-                    if (ok) {
-                        tc_fence_after();
-#pragma unroll
-                        for (int kk = 0; kk < RING / 16; ++kk)    // dKb += gA^T Qp
-                            umma_ts_warp(tAK, tXT + 64 + kk * 8, dQpM + (kk * (2048 / 16) + qoff), idesc_acc, 1);
-                        umma_commit_warp(&bars[PB_D_DONE0 + qb]);
-                        if (WITH_DQ) {
-#pragma unroll
-                            for (int kk = 0; kk < RING / 16; ++kk)    // W = gA^T Ka, over the consumed dP^T columns
-                                umma_ts_warp(tDP, tXT + 64 + kk * 8, dKaM + kk * (2048 / 16), idesc_acc, kk > 0);
-                            umma_commit_warp(&bars[PB_W_FULL]);
+                            for (int kk = 0; kk < RING / 16; ++kk)    // dVb += P^T Gt
+                                umma_ts(tAV, tXT + kk * 8, dGM + (kk * (2048 / 16) + goff), idesc_acc, 1);
+                            umma_commit(&bars[PB_V_DONE0 + gb]);
                         }
+                        __syncwarp();
+                        TL(6);
+                        ok = pipe_wait(&bars[PB_G_FULL], ph, sFail, TR(5));
+                        TL(7);
+                    }
+                    if (ok) {
+                        tc_fence_after();
+                        if (lane == 0) {
+#pragma unroll
+                            for (int kk = 0; kk < RING / 16; ++kk)    // dKb += gA^T Qp
+                                umma_ts(tAK, tXT + 64 + kk * 8, dQpM + (kk * (2048 / 16) + qoff), idesc_acc, 1);
+                            umma_commit(&bars[PB_D_DONE0 + qb]);
+                            if (WITH_DQ) {
+#pragma unroll
+                                for (int kk = 0; kk < RING / 16; ++kk)    // W = gA^T Ka, over the consumed dP^T columns
+                                    umma_ts(tDP, tXT + 64 + kk * 8, dKaM + kk * (2048 / 16), idesc_acc, kk > 0);
+                                umma_commit(&bars[PB_W_FULL]);
+                            }
+                        }
+                        __syncwarp();
+                        TL(8);
                     }
                 }
                 ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
                 ++n;
             }
             // every MMA of this query has been issued: signal the ring rows free once they complete
-            if (n > n_query && ok) umma_commit_warp(&bars[PB_RING_FREE]);
+            if (n > n_query && ok && lane == 0) umma_commit(&bars[PB_RING_FREE]);
+            __syncwarp();
             n_query = n;
         }
         // Let the last committed group finish before the tensor memory is released.
@@ -576,8 +608,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 const uint32_t ph = n & 1;
                 // ---- phase 1: P^T = exp2(X^T c - lse) for this thread's 64 columns, BF16 into X^T[0,64)
                 uint32_t pk[32];
+                TL(10);
                 ok = pipe_wait(&bars[PB_S_XT], ph, sFail, TR(8));
                 if (!ok) break;
+                TL(11);
                 tc_fence_after();
                 long long tt = tracer ? clock64() : 0;
 #pragma unroll
@@ -601,17 +635,21 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 if (tracer) { const long long t2 = clock64(); p.trace[21] += t2 - tt; tt = t2; }
                 // the BF16 results land on score columns that other E threads read: all loads first
                 tc_fence_before();
+                TL(12);
                 warp_arrive(&bars[PB_E_SYNC], lane);
                 ok = pipe_wait(&bars[PB_E_SYNC], ph, sFail, TR(10));
                 if (!ok) break;
+                TL(13);
                 tc_fence_after();
                 tmem_st32(tl + C_XT + ch * 32, pk);
                 tmem_wait_st();
                 tc_fence_before();
                 warp_arrive(&bars[PB_P_FULL], lane);
+                TL(14);
                 // ---- phase 2: gA^T = P^T o (dP^T - delta), BF16 into X^T[64,128)
                 ok = pipe_wait(&bars[PB_S_DP], ph, sFail, TR(9));
                 if (!ok) break;
+                TL(15);
                 tc_fence_after();
                 if (tracer) tt = clock64();
                 {
@@ -636,10 +674,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 }
                 if (tracer) p.trace[22] += clock64() - tt;
                 warp_arrive(&bars[PB_G_FULL], lane);
+                TL(16);
                 if (!ok) break;
                 if (WITH_DQ) {
                     ok = pipe_wait(&bars[PB_W_FULL], ph, sFail, TR(11));
                     if (!ok) break;
+                    TL(17);
                     tc_fence_after();
                     const long long te = tracer ? clock64() : 0;
                     // dQ[d] = scale * sum_k Kb_k[d] * W[k][d]; this thread: lane k, d in its half.
@@ -673,9 +713,11 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                         red[(warp & 3) * D + ch * HD + c * 32 + lane] = s;
                     }
                     if (tracer) p.trace[23] += clock64() - te;
+                    TL(18);
                     warp_arrive(&bars[PB_E_SYNC2], lane);
                     ok = pipe_wait(&bars[PB_E_SYNC2], ph, sFail, TR(12));
                     if (!ok) break;
+                    TL(19);
                     if (tid < D)
                         p.dQ[row * D + tid] =
                             __float2bfloat16(p.scale * (red[tid] + red[D + tid] + red[2 * D + tid] + red[3 * D + tid]));
@@ -700,6 +742,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     }
     if (tracer) p.trace[tid == 0 ? 14 : (tid == PIPE_E_THREADS ? 19 : 6)] += clock64() - t_begin;
 #undef TR
+#undef TL
     tc_fence_before();
     __syncthreads();
     if (*sFail && tid == 0) atomicExch(p.status, 3);

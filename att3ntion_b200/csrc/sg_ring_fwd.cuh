@@ -238,15 +238,17 @@ __global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParam
             tc_fence_before();
             __syncthreads();                                           // B1
             if (warp == 0) {
-                // whole warp, one elected lane issues: operands stay warp-uniform (see umma_ss_warp)
+                // one thread issues the whole unrolled run from precomputed descriptors and commits it
                 tc_fence_after();
+                if (lane == 0) {
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                    umma_ss_warp(tmem_base, dQp + off, dS + off, idesc_x, kk > 0);
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
+                        umma_ss(tmem_base, dQp + off, dS + off, idesc_x, kk > 0);
+                    }
+                    umma_commit(bar);
+                    if (!mbar_wait(bar, phase)) *sFail = 1;
                 }
-                umma_commit_warp(bar);
-                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
                 __syncwarp();
             }
             phase ^= 1;
@@ -306,11 +308,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParam
             __syncthreads();                                           // B3
             if (warp == 0) {
                 tc_fence_after();
+                if (lane == 0) {
 #pragma unroll
-                for (int kk = 0; kk < RING / 16; ++kk)
-                    umma_ts_warp(tmem_base + 128, tmem_base + kk * 8, dVsM + kk * (2048 / 16), idesc_u, kk > 0);
-                umma_commit_warp(bar);
-                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
+                    for (int kk = 0; kk < RING / 16; ++kk)
+                        umma_ts(tmem_base + 128, tmem_base + kk * 8, dVsM + kk * (2048 / 16), idesc_u, kk > 0);
+                    umma_commit(bar);
+                    if (!mbar_wait(bar, phase)) *sFail = 1;
+                }
                 __syncwarp();
             }
             phase ^= 1;

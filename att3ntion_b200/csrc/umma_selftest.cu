@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
     const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
 
     const int nwidth = (p.mode & 8) ? 64 : T;       // mode | 8: the same product restricted to N = 64 columns
-    p.tight = (p.mode & 16) ? 1 : 0;
+    p.tight = (p.mode >> 4) & 3;                      // 1: elect per MMA, 2: lane-0 thread, 3: elected once
     p.mode &= 7;
     const bool a_in_tmem = (p.mode == 3 || p.mode == 4);
     if (a_in_tmem) {
@@ -89,7 +89,36 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
     }
     __syncthreads();
 
-    if (p.tight && warp == 0) {
+    if (p.tight >= 2 && warp == 0) {
+        // Rate probes for the plain SS product (mode 0): everything but the issue style is a
+        // compile-time constant.  tight 2: one thread (lane 0 branch) issues all MMAs back to
+        // back; tight 3: the lane is elected once and then issues all MMAs.
+        tc_fence_after();
+        const uint32_t idesc = make_idesc_bf16(T, T, 0, 0);
+        const uint64_t da = make_smem_desc(smem_u32(sA), 16, 1024, SWIZZLE_128B);
+        const uint64_t db = make_smem_desc(smem_u32(sB), 16, 1024, SWIZZLE_128B);
+        uint32_t elected = (tid == 0);
+        if (p.tight == 3)
+            asm volatile("{\n\t.reg .pred q;\n\t.reg .b32 rx;\n\telect.sync rx|q, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
+                         : "=r"(elected));
+        long long t0 = 0, t1 = 0;
+        if (elected) {
+            t0 = clock64();
+            for (int rep = 0; rep < p.reps; ++rep) {
+#pragma unroll
+                for (int kk = 0; kk < T / 16; ++kk) {
+                    const uint32_t koff = ((kk >> 2) * (T * 128) + (kk & 3) * 32) / 16;
+                    if (kk == 0) umma_ss(tmem_d, da + koff, db + koff, idesc, rep > 0);
+                    else umma_ss(tmem_d, da + koff, db + koff, idesc, 1u);
+                }
+            }
+            t1 = clock64();
+            umma_commit(&mma_bar);
+            p.status[2] = static_cast<int>(t1 - t0);
+        }
+        __syncwarp();
+        if (tid == 0) t_issue = elected ? t0 : clock64();
+    } else if (p.tight && warp == 0) {
         // Rate probe: whole warp converged, descriptor bases precomputed, k-steps unrolled.
         tc_fence_after();
         const int b_mn = (p.mode == 1 || p.mode == 3) ? 1 : 0;
@@ -173,7 +202,7 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
 extern "C" int att3_umma_selftest(const void* A, const void* B, float* D, int mode, int lbo_a, int sbo_a,
                                   int lbo_b, int sbo_b, int reps, int* status_dev, void* stream) {
     if (!A || !B || !D || !status_dev) return att3::set_error(ATT3_ERR_INVALID, "umma_selftest: null pointer");
-    if ((mode & 7) > 4 || mode < 0 || mode > 31 || ((mode & 16) && (mode & 7) == 2) || reps < 1 || reps > 64)
+    if ((mode & 7) > 4 || mode < 0 || mode > 63 || ((mode & 16) && (mode & 7) == 2) || reps < 1 || reps > 64)
         return att3::set_error(ATT3_ERR_INVALID, "umma_selftest: mode must be 0..4 (+8: N = 64, +16: converged-warp issue) and reps 1..64");
     SelftestParams p;
     p.A = static_cast<const __nv_bfloat16*>(A);
