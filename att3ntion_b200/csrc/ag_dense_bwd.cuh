@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
     volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 12);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t issuer = elect_one();     // one lane per warp; warp 0 predicates its MMAs on it
     const int slot = tid & (TILE - 1);
     const int half = tid >> 7;
     const int b = blockIdx.z, h = blockIdx.y, kb = blockIdx.x;
@@ -225,20 +226,20 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
             fence_async_smem();
             tc_fence_before();
             __syncthreads();
-            if (tid == 0) {   // one thread issues the unrolled run from precomputed descriptors
+            if (warp == 0) {   // converged warp, MMAs and commit predicated on its elected lane
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < DP / 16; ++kk) {
                     const uint32_t off = ((kk >> 2) * (TILE * 128) + (kk & 3) * 32) / 16;
-                    umma_ss(tmem_base + C_XT, dKb + off, dQpK + off, idesc_s, kk > 0);
+                    umma_ss_pred(tmem_base + C_XT, dKb + off, dQpK + off, idesc_s, kk > 0, issuer);
                 }
 #pragma unroll
                 for (int kk = 0; kk < DP / 16; ++kk) {
                     const uint32_t off = ((kk >> 2) * (TILE * 128) + (kk & 3) * 32) / 16;
-                    umma_ss(tmem_base + C_DP, dVb + off, dGK + off, idesc_s, kk > 0);
+                    umma_ss_pred(tmem_base + C_DP, dVb + off, dGK + off, idesc_s, kk > 0, issuer);
                 }
-                umma_commit(bar);
-                if (!mbar_wait(bar, phase)) *sFail = 1;
+                umma_commit_pred(bar, issuer);
+                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
             }
             phase ^= 1;
             __syncthreads();
@@ -279,24 +280,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
             tmem_wait_st();
             tc_fence_before();
             __syncthreads();
-            if (tid == 0) {   // one thread issues the unrolled run from precomputed descriptors
+            if (warp == 0) {   // converged warp, MMAs and commit predicated on its elected lane
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < TILE / 16; ++kk)
-                    umma_ts(tmem_base + C_AK, tmem_base + C_DP + kk * 8, dQpM + kk * (2048 / 16), idesc_acc, 1);
+                    umma_ts_pred(tmem_base + C_AK, tmem_base + C_DP + kk * 8, dQpM + kk * (2048 / 16), idesc_acc, 1, issuer);
 #pragma unroll
                 for (int kk = 0; kk < TILE / 16; ++kk)
-                    umma_ts(tmem_base + C_AV, tmem_base + C_XT + kk * 8, dGM + kk * (2048 / 16), idesc_acc, 1);
+                    umma_ts_pred(tmem_base + C_AV, tmem_base + C_XT + kk * 8, dGM + kk * (2048 / 16), idesc_acc, 1, issuer);
                 if (WITH_DA) {
 #pragma unroll
                     for (int dh = 0; dh < DP / 64; ++dh)
 #pragma unroll
                         for (int kk = 0; kk < TILE / 16; ++kk)
-                            umma_ts(tmem_base + (dh ? C_W1 : C_W0), tmem_base + C_DP + kk * 8,
-                                         dKaM + (dh * (TILE * 128) + kk * 2048) / 16, idesc_w, kk > 0);
+                            umma_ts_pred(tmem_base + (dh ? C_W1 : C_W0), tmem_base + C_DP + kk * 8,
+                                         dKaM + (dh * (TILE * 128) + kk * 2048) / 16, idesc_w, kk > 0, issuer);
                 }
-                umma_commit(bar);
-                if (!mbar_wait(bar, phase)) *sFail = 1;
+                umma_commit_pred(bar, issuer);
+                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
             }
             phase ^= 1;
             __syncthreads();

@@ -96,6 +96,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
     volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 12);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t issuer = elect_one();     // one lane per warp; warp 0 predicates its MMAs on it
     const int b = blockIdx.z, h = blockIdx.y;
     const int a0 = blockIdx.x * p.group;
     const int a1 = min(a0 + p.group, p.N);
@@ -201,15 +202,15 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                 fence_async_smem();
                 tc_fence_before();
                 __syncthreads();
-                if (tid == 0) {   // one thread issues the unrolled run from precomputed descriptors
+                if (warp == 0) {   // converged warp, MMAs and commit predicated on its elected lane
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < DP / 16; ++kk) {
                         const uint32_t off = ((kk >> 2) * (TILE * 128) + (kk & 3) * 32) / 16;
-                        umma_ss(tmem_base, dQp + off, dC + off, idesc_x, kk > 0);
+                        umma_ss_pred(tmem_base, dQp + off, dC + off, idesc_x, kk > 0, issuer);
                     }
-                    umma_commit(bar);
-                    if (!mbar_wait(bar, phase)) *sFail = 1;
+                    umma_commit_pred(bar, issuer);
+                    if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
                 }
                 phase ^= 1;
                 __syncthreads();
@@ -258,13 +259,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                 if (lane == 0) sMpart[warp] = m_w;
                 tc_fence_before();
                 __syncthreads();
-                if (tid == 0) {   // one thread issues the unrolled run from precomputed descriptors
+                if (warp == 0) {   // converged warp, MMAs and commit predicated on its elected lane
                     tc_fence_after();
 #pragma unroll
                     for (int kk = 0; kk < TILE / 16; ++kk)
-                        umma_ts(tmem_base + 128, tmem_base + kk * 8, dVcM + kk * (2048 / 16), idesc_u, kk > 0);
-                    umma_commit(bar);
-                    if (!mbar_wait(bar, phase)) *sFail = 1;
+                        umma_ts_pred(tmem_base + 128, tmem_base + kk * 8, dVcM + kk * (2048 / 16), idesc_u, kk > 0, issuer);
+                    umma_commit_pred(bar, issuer);
+                    if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
                 }
                 phase ^= 1;
                 const float Mt = fmaxf(fmaxf(sMpart[0], sMpart[1]), fmaxf(sMpart[2], sMpart[3]));

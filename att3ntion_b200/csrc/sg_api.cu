@@ -14,11 +14,15 @@ namespace {
 __device__ int g_sg_status = 0;
 
 // Cycle counters of the pipelined backward (diagnostic; filled when ATT3_TRACE=1).
-__device__ long long g_sg_trace[32 + 384];
+__device__ long long g_sg_trace[32 + 384 + 640];
+
+int trace_mode() {
+    static const int mode = [] { const char* e = getenv("ATT3_TRACE"); return e ? atoi(e) : 0; }();
+    return mode;
+}
 
 long long* trace_ptr() {
-    static const bool on = [] { const char* e = getenv("ATT3_TRACE"); return e && e[0] == '1'; }();
-    if (!on) return nullptr;
+    if (trace_mode() <= 0) return nullptr;
     long long* p = nullptr;
     cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_sg_trace);
     return p;
@@ -83,6 +87,14 @@ extern "C" int att3_debug_trace(long long* out32) {
 extern "C" int att3_debug_timeline(long long* out384) {
     cudaDeviceSynchronize();
     if (cudaMemcpyFromSymbol(out384, g_sg_trace, sizeof(long long) * 384, sizeof(long long) * 32) != cudaSuccess)
+        return ATT3_ERR_CUDA;
+    return ATT3_OK;
+}
+
+// Diagnostic: per-CTA (cycles, SM id) pairs of the two backward launches, 160 CTAs each.
+extern "C" int att3_debug_cta_cycles(long long* out640) {
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(out640, g_sg_trace, sizeof(long long) * 640, sizeof(long long) * (32 + 384)) != cudaSuccess)
         return ATT3_ERR_CUDA;
     return ATT3_OK;
 }
@@ -264,6 +276,7 @@ extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, co
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status_ptr();
     p.trace = trace_ptr();
+    p.trace_mode = trace_mode();
     const int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, sgring::BWD_MIN_BLOCK, &p.block_len);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 

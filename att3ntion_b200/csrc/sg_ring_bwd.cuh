@@ -19,41 +19,48 @@
 //  * Per (query, head), with the "own" side called (Kb, Vb) and the other (Ka, Va):
 //      X^T  = Kb (Q_i o Ka)^T,  dP^T = Vb (dY_i o Va)^T        two 128x128xD MMAs
 //      thread (k, column half) forms P^T = exp2(X^T c - lse) and gA^T in registers
-//      and stores both to tensor memory as BF16 over the consumed score columns
+//      and stores both to tensor memory as BF16 over the score columns it has consumed itself
 //      dKb += gA^T (Q_i o Ka),  dVb += P^T (dY_i o Va)          A from tensor memory,
 //                                                              B = the Hadamard tiles (MN-major)
 //      dQ pass only:  W = gA^T Ka, then dQ_i = scale * sum_k Kb_k o W_k by warp shuffles.
 //    The forward statistics (m, l) make P purely elementwise, so no row reduction
 //    is needed here.
 //  * When query i reuses slot i mod 128 the lane holding key i-128 is final for
-//    this CTA: it is copied to an FP32 partial buffer and zeroed.  Neighbouring
+//    this CTA: it is copied to an FP32 partial buffer and zeroed (by the H warp of that lane quarter).  Neighbouring
 //    query blocks write partial buffers of opposite parity and blocks are at
 //    least 127 queries long, so every partial row has exactly one writer and the
 //    final sum (reduce kernel below) has a fixed order: repeated calls are
 //    bit-identical.
 //
-// Schedule.  A CTA that ran these steps one after the other would spend most of its time at
-// the barrier between CUDA-core and tensor-core phases, so the CTA is split into roles that
-// hand work to each other through mbarriers, and every (query, head) is processed in two
-// 64-column halves a/b that overlap:
+// Schedule.  Tensor memory holds the two accumulators (2 x 128 columns) and two 128-column
+// regions R0, R1 for everything transient, so only one head's P^T/gA^T can be live at a time;
+// what overlaps is the next head's score product and exponentials with this head's
+// accumulation.  Head n uses A(n) = R[n & 1] for X^T -> P^T, gA^T and B(n) = R[~n & 1] for
+// dP^T (then W in the dQ pass), so the regions swap roles every head:
 //
-//   H warps (4)  build the Hadamard tiles Qp = Q_i o Ka, Gt = dY_i o Va, one ring
-//                row per thread; rows 0-63 (half a) and 64-127 (half b) are
-//                released separately.
-//   MMA warp (1) one thread issues, in order:
-//                  B_a, B_b : X^T[:,x] = Kb Qp_x^T, dP^T[:,x] = Vb Gt_x^T      (N = 64)
-//                  D_a, D_b : dKb += gA^T[:,x] Qp_x, dVb += P^T[:,x] Gt_x       (K = 64)
-//                  W        : gA^T Ka, for dQ (dQ pass only)
-//   E warps (8)  turn score columns into P^T / gA^T (BF16, back into tensor
-//                memory), flush finished accumulator lanes, and collapse W to dQ.
+//   H warps (4)  build the Hadamard tiles Qp = Q_i o Ka, Gt = dY_i o Va (one ring row per
+//                thread, double-buffered), replace the ring row of the key that leaves the
+//                window (its rows are prefetched a query ahead), and flush + zero the
+//                accumulator lane of that key.
+//   MMA warp (1) one thread issues, for head n:
+//                  X^T(n) -> A(n)      as soon as B(n-1) has been read by the E warps
+//                  dKb += gA^T(n-1) Qp (kept back until here when there is no dQ to form)
+//                  dP^T(n) -> B(n)     once head n-1's accumulation has read A(n-1) = B(n)
+//                  dVb += P^T(n) Gt
+//                  dQ pass: W(n) = gA^T(n) Ka -> B(n), then dKb += gA^T(n) Qp
+//   E warps (8)  thread (lane k, column half c): P^T = exp2(X^T c2 - lse) for its 64 columns,
+//                stored as BF16 over the first 32 of them; gA^T = P^T o (dP^T - delta) over
+//                the other 32 (so no E thread writes columns another one still reads);
+//                dQ pass: collapse W to dQ.
 //
-// Hand-offs per processed head (all mbarriers, phase = processed-head counter):
-//   H_full[x]  H -> MMA   tile half x written          D_done[x]  MMA -> H  tile half x read
-//   S_full[x]  MMA -> E   score half x in TMEM          P_full[x]  E -> MMA  P^T/gA^T half x stored
-//   W_full     MMA -> E   W in TMEM                     W_free     E -> MMA/H  W and the Kb rows read
-// While E works on half a the tensor pipe computes half b; while the D MMAs of one
-// half run, E finishes the other and H rebuilds the freed half for the next head.
-// Every wait is bounded and also watches a CTA-wide failure flag, so a protocol
+// Hand-offs (mbarriers; phase = processed-head counter unless noted):
+//   Qp_full[b], Gt_full[b]  H -> MMA  tile buffer b written   D_done[b]  MMA -> H,MMA  dKb MMAs of buffer b done
+//   S_xt,S_dp  MMA -> E   X^T / dP^T in tensor memory    P_full,G_full  E -> MMA  P^T / gA^T stored
+//   B_free     E -> MMA   B(n) read (dP^T, or W)         V_done[b]  MMA -> H   dVb MMAs of Gt buffer b done
+//   W_full     MMA -> E   W in tensor memory             Ring_free  MMA(+E) -> H  per query: ring rows read
+//   Flush_done H -> MMA   per query: lane flushed        Flush_seen MMA -> H   per query: that was observed
+// A waiter observes every phase of a barrier it waits on (a one-bit parity cannot tell phases
+// two apart).  Every wait is bounded and also watches a CTA-wide failure flag, so a protocol
 // error ends the kernel with a status code instead of hanging it.
 #pragma once
 
@@ -81,6 +88,7 @@ struct BwdParams {
     float scale;
     int* status;
     long long* trace;                // optional cycle counters of the pipelined schedule (null: off)
+    int trace_mode;                  // 1: summed wait cycles per hand-off, 2: time stamps of six steady-state heads
 };
 
 constexpr int PIPE_E_THREADS = 256;
@@ -95,8 +103,8 @@ template <int N>
 __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
 enum PipeBar {
-    PB_H_FULL0 = 0, PB_H_FULL1, PB_S_XT, PB_S_DP, PB_P_FULL, PB_G_FULL, PB_D_DONE0, PB_D_DONE1, PB_V_DONE0, PB_V_DONE1,
-    PB_W_FULL, PB_W_FREE, PB_E_SYNC, PB_E_SYNC2, PB_H_SYNC, PB_RING_FREE, PB_COUNT
+    PB_QP_FULL0 = 0, PB_QP_FULL1, PB_GT_FULL0, PB_GT_FULL1, PB_S_XT, PB_S_DP, PB_P_FULL, PB_G_FULL, PB_D_DONE0, PB_D_DONE1, PB_V_DONE0, PB_V_DONE1,
+    PB_W_FULL, PB_B_FREE, PB_E_SYNC2, PB_H_SYNC, PB_RING_FREE, PB_FLUSH_DONE, PB_ACC_DONE, PB_COUNT
 };
 
 // One arrival per warp: the lanes' earlier writes are ordered before lane 0's releasing
@@ -119,7 +127,9 @@ struct PipeSmem {
     static constexpr int OFF_G = 4 * TILE;                         // G_BUFS buffers
     static constexpr int OFF_KA = 5 * TILE;                        // only WITH_DQ
     static constexpr int OFF_STAGE = 6 * TILE;                     // 2 stages x {Q, dY} rows
-    static constexpr int OFF_RED = OFF_STAGE + 2 * 2 * D * 2;      // 2 x 4 x D floats (dQ partials)
+    static constexpr int NEXT_BYTES = 4 * D * 2;                   // rows Ka, Va, Kb, Vb of the key that enters next
+    static constexpr int OFF_NEXT = OFF_STAGE + 2 * 2 * D * 2;     // 2 buffers (query parity)
+    static constexpr int OFF_RED = OFF_NEXT + 2 * NEXT_BYTES;      // 2 x 4 x D floats (dQ partials)
     static constexpr int OFF_BARS = OFF_RED + 2 * 4 * D * 4;
     static constexpr int OFF_MISC = OFF_BARS + PB_COUNT * 8;       // tmem slot (4) + fail flag (4)
     static constexpr int BYTES = OFF_MISC + 16;
@@ -133,20 +143,21 @@ struct PipeSmem {
 // cap (2x the run time); one polling lane per warp with __nanosleep(20) between polls was
 // 2.3x slower still (the sleep is far coarser than its argument).  The iteration count bounds
 // the total wait; the loop also leaves when another thread has raised the CTA's failure flag.
+constexpr uint32_t PIPE_WAIT_HINT_NS = 20000;   // suspend-time hint: a parked thread issues nothing until the phase flips
 __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volatile int* fail,
                                           long long* trace = nullptr) {
     const uint32_t addr = smem_u32(bar);
     const long long t0 = trace ? clock64() : 0;
-    for (uint32_t it = 0; it < (1u << 20); ++it) {
+    for (uint32_t it = 0; it < (1u << 18); ++it) {
         uint32_t done;
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t"
             "}\n"
             : "=r"(done)
-            : "r"(addr), "r"(parity)
+            : "r"(addr), "r"(parity), "r"(PIPE_WAIT_HINT_NS)
             : "memory");
         if (done) {
             if (trace) *trace += clock64() - t0;
@@ -170,6 +181,47 @@ __device__ __forceinline__ void ring_visibility(const uint8_t* mask_row, int i, 
     }
 }
 
+// Copies a warp's accumulator lanes (only_lane < 0: all 32) to the FP32 partial planes and, on
+// request, zeroes them.  Lane k of the accumulators belongs to the key in ring slot k; `tl` is the
+// tensor-memory address of the warp's lane quarter, `key` the key of this thread's lane (< 0: none).
+template <int D>
+__device__ __noinline__ void flush_acc_lanes(uint32_t tl, int lane, int only_lane, int key, float* part_k,
+                                             float* part_v, float scale, bool rezero) {
+    constexpr uint32_t C_AK = 256, C_AV = 384;
+    const bool sel = only_lane < 0 || lane == only_lane;
+    const bool mine = sel && key >= 0;
+    uint32_t a[32];
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+        const uint32_t col = which ? C_AV : C_AK;
+        float* dst_base = which ? part_v : part_k;
+        const float mul = which ? 1.0f : scale;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+            tmem_ld32(tl + col + c * 32, a);
+            tmem_wait_ld();
+            if (mine) {
+                float4* dst = reinterpret_cast<float4*>(dst_base + static_cast<size_t>(key) * D + c * 32);
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+                    dst[t] = make_float4(mul * __uint_as_float(a[4 * t]), mul * __uint_as_float(a[4 * t + 1]),
+                                         mul * __uint_as_float(a[4 * t + 2]), mul * __uint_as_float(a[4 * t + 3]));
+            }
+            if (rezero) {
+                if (sel) {
+#pragma unroll
+                    for (int t = 0; t < 32; ++t) a[t] = 0;
+                }
+                tmem_st32(tl + col + c * 32, a);
+            }
+        }
+    }
+    if (rezero) {
+        tmem_wait_st();
+        tc_fence_before();
+    }
+}
+
 template <int D, bool WITH_DQ>
 __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdParams p) {
     using L = PipeSmem<D, WITH_DQ>;
@@ -177,7 +229,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     constexpr int DW = D / 2;            // packed words per row
     constexpr int HD = D / 2;            // d columns per E thread in the dQ collapse
     constexpr uint32_t TMEM_COLS = 512;
-    constexpr uint32_t C_XT = 0, C_DP = 128, C_AK = 256, C_AV = 384;
+    constexpr uint32_t C_R0 = 0, C_AK = 256, C_AV = 384;   // R1 = R0 + 128
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -187,6 +239,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     uint8_t* sG = smem + L::OFF_G;
     uint8_t* sKa = smem + L::OFF_KA;
     __nv_bfloat16* sStage = reinterpret_cast<__nv_bfloat16*>(smem + L::OFF_STAGE);
+    uint8_t* sNext = smem + L::OFF_NEXT;
     float* sRed = reinterpret_cast<float*>(smem + L::OFF_RED);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BARS);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::OFF_MISC);
@@ -199,24 +252,24 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     const int q1 = min(q0 + p.block_len, p.N);
     if (q0 >= q1) return;
     const int parity_buf = blockIdx.x & 1;
-    const bool is_e = warp < 8, is_h = warp >= 8 && warp < 12, is_mma = warp == 12;
+    const bool is_h = warp >= 8 && warp < 12, is_mma = warp == 12;
 
-    (void)is_e;
     if (is_mma) {
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
     }
     if (tid == 0) {
         // Arrival counts are in warps: one elected lane arrives for its warp (warp_arrive).
-        mbar_init(&bars[PB_H_FULL0], 4);    mbar_init(&bars[PB_H_FULL1], 4);
+        mbar_init(&bars[PB_QP_FULL0], 4);   mbar_init(&bars[PB_QP_FULL1], 4);
+        mbar_init(&bars[PB_GT_FULL0], 4);   mbar_init(&bars[PB_GT_FULL1], 4);
         mbar_init(&bars[PB_S_XT], 1);       mbar_init(&bars[PB_S_DP], 1);
         mbar_init(&bars[PB_P_FULL], 8);     mbar_init(&bars[PB_G_FULL], 8);
         mbar_init(&bars[PB_D_DONE0], 1);    mbar_init(&bars[PB_D_DONE1], 1);
         mbar_init(&bars[PB_V_DONE0], 1);    mbar_init(&bars[PB_V_DONE1], 1);
-        mbar_init(&bars[PB_W_FULL], 1);     mbar_init(&bars[PB_W_FREE], 8);
-        mbar_init(&bars[PB_E_SYNC], 8);     mbar_init(&bars[PB_E_SYNC2], 8);
-        mbar_init(&bars[PB_H_SYNC], 4);
+        mbar_init(&bars[PB_W_FULL], 1);     mbar_init(&bars[PB_B_FREE], 8);
+        mbar_init(&bars[PB_E_SYNC2], 8);    mbar_init(&bars[PB_H_SYNC], 4);
         mbar_init(&bars[PB_RING_FREE], WITH_DQ ? 9 : 1);
+        mbar_init(&bars[PB_FLUSH_DONE], 1); mbar_init(&bars[PB_ACC_DONE], 1);
         fence_mbar_init();
         *sFail = 0;
     }
@@ -237,63 +290,32 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     };
     const float c2 = p.scale * LOG2E;
 
-    // ------------------------------------------------------------------ H role state
-    const int hslot = tid - PIPE_E_THREADS;          // ring slot of an H thread (0..127)
-    uint32_t rKa[DW], rVa[DW];
-    auto h_load_slot = [&](int key) {
-        if (key >= 0) {
-            const uint4* ka4 = reinterpret_cast<const uint4*>(gKa + static_cast<size_t>(key) * D);
-            const uint4* va4 = reinterpret_cast<const uint4*>(gVa + static_cast<size_t>(key) * D);
-            const uint4* kb4 = reinterpret_cast<const uint4*>(gKb + static_cast<size_t>(key) * D);
-            const uint4* vb4 = reinterpret_cast<const uint4*>(gVb + static_cast<size_t>(key) * D);
-#pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                const uint4 a = __ldg(ka4 + c), v = __ldg(va4 + c);
-                rKa[4 * c] = a.x; rKa[4 * c + 1] = a.y; rKa[4 * c + 2] = a.z; rKa[4 * c + 3] = a.w;
-                rVa[4 * c] = v.x; rVa[4 * c + 1] = v.y; rVa[4 * c + 2] = v.z; rVa[4 * c + 3] = v.w;
-                *reinterpret_cast<uint4*>(sKb + sw128_offset<RING>(hslot, c)) = __ldg(kb4 + c);
-                *reinterpret_cast<uint4*>(sVb + sw128_offset<RING>(hslot, c)) = __ldg(vb4 + c);
-                if (WITH_DQ) *reinterpret_cast<uint4*>(sKa + sw128_offset<RING>(hslot, c)) = a;
-            }
-        } else {
-            const uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                rKa[4 * c] = rKa[4 * c + 1] = rKa[4 * c + 2] = rKa[4 * c + 3] = 0;
-                rVa[4 * c] = rVa[4 * c + 1] = rVa[4 * c + 2] = rVa[4 * c + 3] = 0;
-                *reinterpret_cast<uint4*>(sKb + sw128_offset<RING>(hslot, c)) = z;
-                *reinterpret_cast<uint4*>(sVb + sw128_offset<RING>(hslot, c)) = z;
-                if (WITH_DQ) *reinterpret_cast<uint4*>(sKa + sw128_offset<RING>(hslot, c)) = z;
-            }
-        }
-    };
-    auto h_stage = [&](int it) {          // H threads [0, 2*CH): one 16-byte chunk of the Q / dY row each
-        if (hslot < 2 * CH) {
-            const int which = hslot / CH, c = hslot % CH;
-            const __nv_bfloat16* src = (which == 0 ? p.Q : p.dY) + row_index(it) * D;
-            const uint32_t dst = smem_u32(sStage + ((it & 1) * 2 + which) * D) + c * 16;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
-                         "l"(reinterpret_cast<const uint4*>(src) + c)
-                         : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
     // Each role first sets its register budget (the CTA starts at 128 per thread: the last
     // warpgroup gives most of its registers away, the H threads take room for two ring rows,
     // the E warps keep theirs), does its share of the set-up and then meets the others at
     // one CTA barrier before the hand-off protocol starts.
-    // Optional cycle accounting of the hand-off waits (one thread per role of CTA 0).
+    // Optional cycle accounting of the hand-offs (one thread per role of CTA 0), compiled in only with
+    // -DATT3_PIPE_TRACE: the bookkeeping costs registers in every role.
+#ifdef ATT3_PIPE_TRACE
     const bool tracer = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&
                         (tid == 0 || tid == PIPE_E_THREADS || tid == PIPE_E_THREADS + PIPE_H_THREADS);
-    const long long t_begin = tracer ? clock64() : 0;
-#define TR(k) (tracer ? p.trace + (k) : nullptr)
+    const bool timed = p.trace && p.trace_mode == 2 && tid == PIPE_E_THREADS + PIPE_H_THREADS;   // every CTA
+    const long long t_begin = (tracer || timed) ? clock64() : 0;
+    unsigned long long ns_begin = 0;
+    if (timed) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
+    const bool tr_sum = tracer && p.trace_mode == 1, tr_line = tracer && p.trace_mode == 2;
+#define TR(k) (tr_sum ? p.trace + (k) : nullptr)
     // Timeline of six steady-state heads (time stamps of the hand-offs, one thread per role).
     constexpr int TL_FIRST = 804;
 #define TL(ev)                                                                                          \
     do {                                                                                                \
-        if (tracer && n >= TL_FIRST && n < TL_FIRST + 6)                                                \
+        if (tr_line && n >= TL_FIRST && n < TL_FIRST + 6)                                               \
             p.trace[32 + (WITH_DQ ? 0 : 192) + (n - TL_FIRST) * 32 + (ev)] = clock64();                 \
     } while (0)
+#else
+#define TR(k) nullptr
+#define TL(ev) do { } while (0)
+#endif
     uint32_t tmem_base = 0;
     auto cta_start_sync = [&]() {
         tc_fence_before();
@@ -305,32 +327,70 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     if (is_h) {
         // ================================================================== H warps
         reg_inc<184>();
-        h_load_slot(ring_key(q0, hslot));
-        h_stage(0);
+        const int hslot = tid - PIPE_E_THREADS;          // ring slot of an H thread (0..127) = its tensor-memory lane
+        uint32_t rKa[DW], rVa[DW];
+        {   // initial fill of this thread's ring slot: registers (other side) and operand tiles (own side)
+            const int key = ring_key(q0, hslot);
+            if (key >= 0) {
+                const uint4* ka4 = reinterpret_cast<const uint4*>(gKa + static_cast<size_t>(key) * D);
+                const uint4* va4 = reinterpret_cast<const uint4*>(gVa + static_cast<size_t>(key) * D);
+                const uint4* kb4 = reinterpret_cast<const uint4*>(gKb + static_cast<size_t>(key) * D);
+                const uint4* vb4 = reinterpret_cast<const uint4*>(gVb + static_cast<size_t>(key) * D);
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                    const uint4 a = __ldg(ka4 + c), v = __ldg(va4 + c);
+                    rKa[4 * c] = a.x; rKa[4 * c + 1] = a.y; rKa[4 * c + 2] = a.z; rKa[4 * c + 3] = a.w;
+                    rVa[4 * c] = v.x; rVa[4 * c + 1] = v.y; rVa[4 * c + 2] = v.z; rVa[4 * c + 3] = v.w;
+                    *reinterpret_cast<uint4*>(sKb + sw128_offset<RING>(hslot, c)) = __ldg(kb4 + c);
+                    *reinterpret_cast<uint4*>(sVb + sw128_offset<RING>(hslot, c)) = __ldg(vb4 + c);
+                    if (WITH_DQ) *reinterpret_cast<uint4*>(sKa + sw128_offset<RING>(hslot, c)) = a;
+                }
+            } else {
+                const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                    rKa[4 * c] = rKa[4 * c + 1] = rKa[4 * c + 2] = rKa[4 * c + 3] = 0;
+                    rVa[4 * c] = rVa[4 * c + 1] = rVa[4 * c + 2] = rVa[4 * c + 3] = 0;
+                    *reinterpret_cast<uint4*>(sKb + sw128_offset<RING>(hslot, c)) = z;
+                    *reinterpret_cast<uint4*>(sVb + sw128_offset<RING>(hslot, c)) = z;
+                    if (WITH_DQ) *reinterpret_cast<uint4*>(sKa + sw128_offset<RING>(hslot, c)) = z;
+                }
+            }
+        }
+        // Asynchronous staging, one commit group per call: the Q and dY rows of iteration `it`
+        // (threads [0, 2*CH)) and, when next_key >= 0, the four rows of the key that enters the
+        // ring with query next_key (threads [0, 4*CH)); both are waited for at the next H_sync.
+        auto h_stage = [&](int it, int next_key) {
+            if (it >= 0 && hslot < 2 * CH) {
+                const int which = hslot / CH, c = hslot % CH;
+                const __nv_bfloat16* src = (which == 0 ? p.Q : p.dY) + row_index(it) * D;
+                const uint32_t dst = smem_u32(sStage + ((it & 1) * 2 + which) * D) + c * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
+                             "l"(reinterpret_cast<const uint4*>(src) + c)
+                             : "memory");
+            }
+            if (next_key >= 0 && hslot < 4 * CH) {
+                const int which = hslot / CH, c = hslot % CH;
+                const __nv_bfloat16* base = which == 0 ? gKa : which == 1 ? gVa : which == 2 ? gKb : gVb;
+                const uint32_t dst = smem_u32(sNext + (next_key & 1) * L::NEXT_BYTES + which * (D * 2)) + c * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
+                             "l"(reinterpret_cast<const uint4*>(base + static_cast<size_t>(next_key) * D) + c)
+                             : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        h_stage(0, -1);
         fence_async_smem();
         cta_start_sync();
         constexpr int GB = L::G_BUFS;
+        constexpr int HB = 2;                 // staged chunks in flight per thread (registers: 4 per chunk)
         int n = 0, it = 0, n_query = 0, ring_phase = 0;
         bool ok = true;
         float l_next = __ldg(p.l + row_index(0));
         for (int i = q0; i < q1 && ok; ++i) {
-            if (i > q0) {
-                // Ring slot i mod 128 changes key: every MMA that reads the rings, and in the dQ
-                // pass the E warps' reads of the Kb rows, must have finished with the previous
-                // query.  RING_FREE completes once per query that had work, so every H thread sees
-                // each of its phases in turn (a per-head barrier would be observed here only now
-                // and then, and a one-bit phase parity cannot tell phases two apart).
-                if (n > n_query) {
-                    ok = pipe_wait(&bars[PB_RING_FREE], ring_phase & 1, sFail, TR(16));
-                    ++ring_phase;
-                    if (!ok) break;
-                }
-                if (hslot == (i & (RING - 1))) {
-                    h_load_slot(i);
-                    fence_async_smem();
-                }
-            }
+            const bool prev_work = n > n_query;      // the previous query issued MMAs: Ring_free completes for it
             n_query = n;
+            const int s = i & (RING - 1);
             uint32_t vw[4];
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
             const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
@@ -343,51 +403,143 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 ok = pipe_wait(&bars[PB_H_SYNC], it & 1, sFail, TR(17));
                 if (!ok) break;
                 TL(20);
-                if (it + 1 < n_iter) h_stage(it + 1);
-                if (!any_vis || !(l_i > 0.f)) continue;
-                // Buffer reuse: Qp[n&1] was last read by the dKb MMAs of head n-2, Gt[n%GB] by the dVb
-                // MMAs of head n-GB.  Each per-buffer barrier is waited on at every one of its phases.
+                const bool boundary = hh == 0 && i > q0;      // key i replaces key i-128 in slot s
+                const uint8_t* nx = sNext + (i & 1) * L::NEXT_BYTES;
+                if (boundary && hslot == s) {
+                    const uint4* ka4 = reinterpret_cast<const uint4*>(nx);
+                    const uint4* va4 = reinterpret_cast<const uint4*>(nx + D * 2);
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) {
+                        const uint4 a = ka4[c], v = va4[c];
+                        rKa[4 * c] = a.x; rKa[4 * c + 1] = a.y; rKa[4 * c + 2] = a.z; rKa[4 * c + 3] = a.w;
+                        rVa[4 * c] = v.x; rVa[4 * c + 1] = v.y; rVa[4 * c + 2] = v.z; rVa[4 * c + 3] = v.w;
+                    }
+                }
+                if (it + 1 < n_iter) h_stage(it + 1, (hh == 0 && i + 1 < q1) ? i + 1 : -1);
+                const bool work = any_vis && l_i > 0.f;
                 const int qb = n & 1, gb = n % GB;
-                if (n >= 2) ok = pipe_wait(&bars[PB_D_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, TR(18));
-                if (ok && n >= GB) ok = pipe_wait(&bars[PB_V_DONE0 + gb], ((n / GB) - 1) & 1, sFail, TR(18));
-                if (!ok) break;
-                TL(21);
                 uint8_t* dQp = sQp + qb * L::TILE;
                 uint8_t* dG = sG + gb * L::TILE;
-                const long long th0 = tracer ? clock64() : 0;
                 const uint4* q4 = reinterpret_cast<const uint4*>(sStage + (it & 1) * 2 * D);
                 const uint4* y4 = q4 + CH;
+                if (work) {
+                    // Buffer reuse: Qp[n&1] was last read by the dKb MMAs of head n-2.  Each per-buffer
+                    // barrier is waited on at every one of its phases.
+                    if (n >= 2) ok = pipe_wait(&bars[PB_D_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, TR(18));
+                    if (!ok) break;
+                    TL(21);
+                    // The staged row is read in batches of HB chunks ahead of the stores: the compiler
+                    // cannot tell that the tile stores do not alias the staging area, and would otherwise
+                    // run load -> multiply -> store one chunk at a time (about 100 cycles each).
 #pragma unroll
-                for (int c = 0; c < CH; ++c) {
-                    const uint4 q = q4[c], y = y4[c];
-                    uint4 o, gq;
-                    o.x = mul_bf16x2(q.x, rKa[4 * c]);      gq.x = mul_bf16x2(y.x, rVa[4 * c]);
-                    o.y = mul_bf16x2(q.y, rKa[4 * c + 1]);  gq.y = mul_bf16x2(y.y, rVa[4 * c + 1]);
-                    o.z = mul_bf16x2(q.z, rKa[4 * c + 2]);  gq.z = mul_bf16x2(y.z, rVa[4 * c + 2]);
-                    o.w = mul_bf16x2(q.w, rKa[4 * c + 3]);  gq.w = mul_bf16x2(y.w, rVa[4 * c + 3]);
-                    *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c)) = o;
-                    *reinterpret_cast<uint4*>(dG + sw128_offset<RING>(hslot, c)) = gq;
+                    for (int c0 = 0; c0 < CH; c0 += HB) {
+                        uint4 q[HB];
+#pragma unroll
+                        for (int c = 0; c < HB; ++c) q[c] = q4[c0 + c];
+#pragma unroll
+                        for (int c = 0; c < HB; ++c) {
+                            uint4 o;
+                            o.x = mul_bf16x2(q[c].x, rKa[4 * (c0 + c)]);
+                            o.y = mul_bf16x2(q[c].y, rKa[4 * (c0 + c) + 1]);
+                            o.z = mul_bf16x2(q[c].z, rKa[4 * (c0 + c) + 2]);
+                            o.w = mul_bf16x2(q[c].w, rKa[4 * (c0 + c) + 3]);
+                            *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c0 + c)) = o;
+                        }
+                    }
+                    TL(23);
                 }
-                const long long th1 = tracer ? clock64() : 0;
-                fence_async_smem();
-                warp_arrive(&bars[PB_H_FULL0 + qb], lane);
-                if (tracer) { p.trace[24] += th1 - th0; p.trace[25] += clock64() - th1; }
-                TL(22);
-                ++n;
+                if (boundary) {
+                    // The operand-tile rows of slot s change key only after every MMA that reads the
+                    // rings (and, in the dQ pass, the E warps' reads of the Kb rows) is done with the
+                    // previous query; the tile built above does not depend on it, so it costs nothing.
+                    if (prev_work) {
+                        ok = pipe_wait(&bars[PB_RING_FREE], ring_phase & 1, sFail, TR(16));
+                        ++ring_phase;
+                        if (!ok) break;
+                    }
+                    constexpr int NR = WITH_DQ ? 3 : 2;       // Kb, Vb (and Ka) rows
+                    if (hslot < NR * CH) {
+                        const int r = hslot / CH, c = hslot % CH;
+                        const uint4 v = *reinterpret_cast<const uint4*>(nx + (r == 2 ? 0 : (2 + r)) * (D * 2) + c * 16);
+                        uint8_t* tile = r == 0 ? sKb : r == 1 ? sVb : sKa;
+                        *reinterpret_cast<uint4*>(tile + sw128_offset<RING>(s, c)) = v;
+                    }
+                }
+                if (work || boundary) fence_async_smem();
+                TL(24);
+                if (work) {
+                    // the score product needs only this tile (and the rings)
+                    warp_arrive(&bars[PB_QP_FULL0 + qb], lane);
+                    TL(22);
+                    // Gt[n%GB] was last read by the dVb MMAs of head n-GB
+                    if (n >= GB) ok = pipe_wait(&bars[PB_V_DONE0 + gb], ((n / GB) - 1) & 1, sFail, TR(18));
+                    if (!ok) break;
+                    TL(25);
+#pragma unroll
+                    for (int c0 = 0; c0 < CH; c0 += HB) {
+                        uint4 y[HB];
+#pragma unroll
+                        for (int c = 0; c < HB; ++c) y[c] = y4[c0 + c];
+#pragma unroll
+                        for (int c = 0; c < HB; ++c) {
+                            uint4 gq;
+                            gq.x = mul_bf16x2(y[c].x, rVa[4 * (c0 + c)]);
+                            gq.y = mul_bf16x2(y[c].y, rVa[4 * (c0 + c) + 1]);
+                            gq.z = mul_bf16x2(y[c].z, rVa[4 * (c0 + c) + 2]);
+                            gq.w = mul_bf16x2(y[c].w, rVa[4 * (c0 + c) + 3]);
+                            *reinterpret_cast<uint4*>(dG + sw128_offset<RING>(hslot, c0 + c)) = gq;
+                        }
+                    }
+                    fence_async_smem();
+                    warp_arrive(&bars[PB_GT_FULL0 + gb], lane);
+                    TL(26);
+                }
+                if (work) ++n;
             }
         }
     } else if (warp >= 12) {
         reg_dec<72>();
         cta_start_sync();
+        // Accumulator flushes are the work of this warpgroup: warp 12 + q reaches the tensor-memory lanes
+        // of quarter q.  Quarters 1-3 belong to the three warps that otherwise only donate registers;
+        // quarter 0 is flushed by the MMA warp itself, between two runs of MMAs (one query in four).
+        const int fslot = (warp & 3) * 32 + lane;
+        const uint32_t tlf = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        // Out of line on purpose: the 32 registers of a tensor-memory load would otherwise count
+        // against the MMA warp's small budget throughout its issue loop.
+        auto acc_flush = [&](int only_lane, int i_ref, bool rezero) {
+            flush_acc_lanes<D>(tlf, lane, only_lane, ring_key(i_ref, fslot), gPartK, gPartV, p.scale, rezero);
+        };
+        const int n_bound = q1 - q0 - 1;      // query boundaries = single-lane flushes; Acc_done has one more phase
+        if (!is_mma) {
+            // ============================================================== flush warps (quarters 1-3)
+            bool okf = true;
+            for (int fb = 0; fb < n_bound && okf; ++fb) {
+                const int i = q0 + 1 + fb, s = i & (RING - 1);
+                okf = pipe_wait(&bars[PB_ACC_DONE], fb & 1, sFail);     // every MMA of the queries before i is complete
+                if (okf && (warp & 3) == (s >> 5)) {
+                    tc_fence_after();
+                    acc_flush(s & 31, i - 1, true);
+                    warp_arrive(&bars[PB_FLUSH_DONE], lane);
+                }
+            }
+            if (okf) okf = pipe_wait(&bars[PB_ACC_DONE], n_bound & 1, sFail);
+            if (okf) {
+                // Drain: every slot still holds a key of (q1 - 129, q1 - 1].
+                tc_fence_after();
+                acc_flush(-1, q1 - 1, false);
+            }
+        }
         if (is_mma) {
         // ================================================================== MMA warp
+        // The whole warp runs this role converged; the MMAs and commits are predicated on one
+        // elected lane (see umma_ss_pred for the measured difference to a lane-0 branch).
+        const uint32_t issuer = elect_one();
         const uint32_t idesc_s = make_idesc_bf16(RING, RING, 0, 0);     // score-shaped, both operands K-major
         const uint32_t idesc_acc = make_idesc_bf16(RING, D, 0, 1);      // A in TMEM, B MN-major, N = D
         // Descriptor bases are built once; a k-step only adds a compile-time constant to the
-        // start-address field (16-byte units).  Measured on one CTA (128x128x16 MMAs, 64 cycles
-        // of tensor-pipe time each): one thread issuing an unrolled run with precomputed
-        // descriptors sustains 64 cycles an MMA; electing a lane per MMA costs 102, and
-        // rebuilding descriptors per MMA 140-190.
+        // start-address field (16-byte units); rebuilding descriptors per MMA costs 140-190 cycles
+        // an MMA against 64 cycles of tensor-pipe time.
         const uint64_t dKb = make_smem_desc(smem_u32(sKb), 16, 1024, SWIZZLE_128B);           // A, K-major
         const uint64_t dVb = make_smem_desc(smem_u32(sVb), 16, 1024, SWIZZLE_128B);
         const uint64_t dQpK = make_smem_desc(smem_u32(sQp), 16, 1024, SWIZZLE_128B);          // B, K-major
@@ -395,105 +547,170 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         const uint64_t dQpM = make_smem_desc(smem_u32(sQp), RING * 128, 1024, SWIZZLE_128B);  // B, MN-major
         const uint64_t dGM = make_smem_desc(smem_u32(sG), RING * 128, 1024, SWIZZLE_128B);
         const uint64_t dKaM = make_smem_desc(smem_u32(sKa), RING * 128, 1024, SWIZZLE_128B);
-        const uint32_t tXT = tmem_base + C_XT, tDP = tmem_base + C_DP, tAK = tmem_base + C_AK, tAV = tmem_base + C_AV;
-        int n = 0, it = 0, n_query = 0;
-        bool ok = true;
+        const uint32_t tAK = tmem_base + C_AK, tAV = tmem_base + C_AV;
+        constexpr int GB = L::G_BUFS;
+        int n = 0, it = 0, n_query = 0, flushes_seen = 0;
+        bool ok = true, flush_pending = false, dk_pending = false;
+        (void)n_bound;
         float l_next = __ldg(p.l + row_index(0));
+
+        // A-operand column of k-step kk inside a region: the E thread of column half c keeps its
+        // BF16 results inside its own 64 score columns, P^T in the first 32 and gA^T in the last 32.
+        auto a_col = [](int kk) -> uint32_t { return 64u * (kk >> 2) + 8u * (kk & 3); };
+        // Boundary duties.  Acc_done is committed once per boundary, after the last accumulating MMA of
+        // the queries before it; the flush of the lane that changes key happens behind it, by a flush
+        // warp (observed through Flush_done) or, for quarter 0, right here.
+        int acc_commits = 0, self_i = 0;
+        bool acc_commit_pending = false, self_pending = false;
+        auto commit_acc = [&]() {
+            umma_commit_pred(&bars[PB_ACC_DONE], issuer);
+            ++acc_commits;
+            acc_commit_pending = false;
+        };
+        // dKb += gA^T(m) Qp(m) for the head m = n - 1 whose gA^T the E warps finish last.
+        auto issue_dk = [&](int m) {
+            bool r = pipe_wait(&bars[PB_G_FULL], m & 1, sFail, TR(5));
+            if (r) {
+                tc_fence_after();
+                const uint32_t tA = tmem_base + C_R0 + (m & 1) * 128 + 32;
+                const uint32_t qoff = (m & 1) * (L::TILE / 16);
+#pragma unroll
+                for (int kk = 0; kk < RING / 16; ++kk)
+                    umma_ts_pred(tAK, tA + a_col(kk), dQpM + (kk * (2048 / 16) + qoff), idesc_acc, 1, issuer);
+                umma_commit_pred(&bars[PB_D_DONE0 + (m & 1)], issuer);
+                if (acc_commit_pending) commit_acc();
+            }
+            return r;
+        };
+        auto settle_flush = [&]() {
+            bool r = true;
+            if (flush_pending) {
+                r = pipe_wait(&bars[PB_FLUSH_DONE], flushes_seen & 1, sFail, TR(2));
+                ++flushes_seen;
+                flush_pending = false;
+                if (r) tc_fence_after();
+            }
+            if (r && self_pending) {
+                // this warp made the commit, so it knows which phase it is waiting for
+                r = pipe_wait(&bars[PB_ACC_DONE], (acc_commits - 1) & 1, sFail, TR(2));
+                self_pending = false;
+                if (r) {
+                    tc_fence_after();
+                    acc_flush(self_i & 31, self_i - 1, true);
+                    __syncwarp();
+                    tc_fence_after();
+                }
+            }
+            return r;
+        };
         for (int i = q0; i < q1 && ok; ++i) {
+            if (i > q0) {
+                // A query without work leaves its boundary unsettled: do it now, so that commits, flushes
+                // and this warp's waits stay one phase apart.
+                if (flush_pending || self_pending) {
+                    if (dk_pending) { ok = issue_dk(n - 1); dk_pending = false; }
+                    if (ok) ok = settle_flush();
+                    if (!ok) break;
+                }
+                if (((i & (RING - 1)) >> 5) == 0) { self_pending = true; self_i = i; }
+                else flush_pending = true;
+                if (dk_pending) acc_commit_pending = true;   // committed right behind the kept-back dKb MMAs
+                else commit_acc();
+            }
             uint32_t vw[4];
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
             const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
                 const float l_i = l_next;
                 if (it + 1 < n_iter) l_next = __ldg(p.l + row_index(it + 1));
-                if (!any_vis || !(l_i > 0.f)) continue;
-                {   // the warp waits together; lane 0 issues each operand's MMAs back to back and commits them
-                    const uint32_t ph = n & 1;
-                    // The score MMAs overwrite the tensor-memory columns that the previous head's
-                    // accumulation and W MMAs read their A operand from; a later MMA is not held back
-                    // for an earlier one's operand reads, so wait for the previous head's last group.
-                    constexpr int GB = L::G_BUFS;
-                    const int qb = n & 1, gb = n % GB;
-                    const uint32_t qoff = qb * (L::TILE / 16), goff = gb * (L::TILE / 16);   // buffer offsets, 16-byte units
-                    if (n > 0)
-                        ok = WITH_DQ ? pipe_wait(&bars[PB_W_FULL], (n - 1) & 1, sFail, TR(0))
-                                     : pipe_wait(&bars[PB_D_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, TR(0));
-                    TL(0);
-                    if (ok) ok = pipe_wait(&bars[PB_H_FULL0 + qb], (n >> 1) & 1, sFail, TR(1));
-                    TL(1);
-                    if (ok) {
-                        tc_fence_after();
-                        if (lane == 0) {
-#pragma unroll
-                            for (int kk = 0; kk < D / 16; ++kk) {      // X^T = Kb Qp^T
-                                const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                                umma_ss(tXT, dKb + off, dQpK + (off + qoff), idesc_s, kk > 0);
-                            }
-                            umma_commit(&bars[PB_S_XT]);
-                        }
-                        __syncwarp();
-                        // dP^T lands on the columns that held W of the previous head
-                        TL(2);
-                        if (WITH_DQ && n > 0) ok = pipe_wait(&bars[PB_W_FREE], (n - 1) & 1, sFail, TR(3));
-                        TL(3);
-                    }
-                    if (ok) {
-                        if (lane == 0) {
-#pragma unroll
-                            for (int kk = 0; kk < D / 16; ++kk) {      // dP^T = Vb Gt^T
-                                const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                                umma_ss(tDP, dVb + off, dGK + (off + goff), idesc_s, kk > 0);
-                            }
-                            umma_commit(&bars[PB_S_DP]);
-                        }
-                        __syncwarp();
-                        TL(4);
-                        ok = pipe_wait(&bars[PB_P_FULL], ph, sFail, TR(4));
-                        TL(5);
-                    }
-                    if (ok) {
-                        tc_fence_after();
-                        if (lane == 0) {
-#pragma unroll
-                            for (int kk = 0; kk < RING / 16; ++kk)    // dVb += P^T Gt
-                                umma_ts(tAV, tXT + kk * 8, dGM + (kk * (2048 / 16) + goff), idesc_acc, 1);
-                            umma_commit(&bars[PB_V_DONE0 + gb]);
-                        }
-                        __syncwarp();
-                        TL(6);
-                        ok = pipe_wait(&bars[PB_G_FULL], ph, sFail, TR(5));
-                        TL(7);
-                    }
-                    if (ok) {
-                        tc_fence_after();
-                        if (lane == 0) {
-#pragma unroll
-                            for (int kk = 0; kk < RING / 16; ++kk)    // dKb += gA^T Qp
-                                umma_ts(tAK, tXT + 64 + kk * 8, dQpM + (kk * (2048 / 16) + qoff), idesc_acc, 1);
-                            umma_commit(&bars[PB_D_DONE0 + qb]);
-                            if (WITH_DQ) {
-#pragma unroll
-                                for (int kk = 0; kk < RING / 16; ++kk)    // W = gA^T Ka, over the consumed dP^T columns
-                                    umma_ts(tDP, tXT + 64 + kk * 8, dKaM + kk * (2048 / 16), idesc_acc, kk > 0);
-                                umma_commit(&bars[PB_W_FULL]);
-                            }
-                        }
-                        __syncwarp();
-                        TL(8);
-                    }
+                if (!any_vis || !(l_i > 0.f)) {
+                    // the H warps may be waiting for the kept-back MMAs before they build another tile
+                    if (dk_pending) { ok = issue_dk(n - 1); dk_pending = false; }
+                    continue;
                 }
-                ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+                const uint32_t ph = n & 1;
+                const int qb = n & 1, gb = n % GB;
+                const uint32_t qoff = qb * (L::TILE / 16), goff = gb * (L::TILE / 16);   // buffer offsets, 16-byte units
+                const uint32_t tA = tmem_base + C_R0 + (n & 1) * 128;          // X^T, then P^T | gA^T
+                const uint32_t tB = tmem_base + C_R0 + ((n & 1) ^ 1) * 128;    // dP^T, then W
+                TL(0);
+                ok = pipe_wait(&bars[PB_QP_FULL0 + qb], (n >> 1) & 1, sFail, TR(1));
+                // A(n) = B(n-1): the E warps have taken dP^T (or W) of the previous head out of it
+                if (ok && n > 0) ok = pipe_wait(&bars[PB_B_FREE], (n - 1) & 1, sFail, TR(3));
+                TL(1);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {      // X^T = Kb Qp^T
+                    const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
+                    umma_ss_pred(tA, dKb + off, dQpK + (off + qoff), idesc_s, kk > 0, issuer);
+                }
+                umma_commit_pred(&bars[PB_S_XT], issuer);
+                TL(2);
+                if (!WITH_DQ && dk_pending) {
+                    ok = issue_dk(n - 1);
+                    dk_pending = false;
+                    if (!ok) break;
+                }
+                TL(3);
+                // B(n) = A(n-1): the accumulation MMAs of the previous head read their A operand there,
+                // and a later MMA is not held back for an earlier one's operand reads
+                if (n > 0) ok = pipe_wait(&bars[PB_D_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, TR(0));
+                if (ok) ok = pipe_wait(&bars[PB_GT_FULL0 + gb], (n / GB) & 1, sFail, TR(1));
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {      // dP^T = Vb Gt^T
+                    const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
+                    umma_ss_pred(tB, dVb + off, dGK + (off + goff), idesc_s, kk > 0, issuer);
+                }
+                umma_commit_pred(&bars[PB_S_DP], issuer);
+                TL(4);
+                ok = pipe_wait(&bars[PB_P_FULL], ph, sFail, TR(4));
+                if (ok && (flush_pending || self_pending)) ok = settle_flush();   // the lane zeroed at the query boundary
+                TL(5);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < RING / 16; ++kk)    // dVb += P^T Gt
+                    umma_ts_pred(tAV, tA + a_col(kk), dGM + (kk * (2048 / 16) + goff), idesc_acc, 1, issuer);
+                umma_commit_pred(&bars[PB_V_DONE0 + gb], issuer);
+                TL(6);
+                if (WITH_DQ) {
+                    ok = pipe_wait(&bars[PB_G_FULL], ph, sFail, TR(5));
+                    TL(7);
+                    if (!ok) break;
+                    tc_fence_after();
+                    // W first: the E warps wait for it, nobody is in a hurry for dKb
+#pragma unroll
+                    for (int kk = 0; kk < RING / 16; ++kk)    // W = gA^T Ka, over the consumed dP^T columns
+                        umma_ts_pred(tB, tA + 32 + a_col(kk), dKaM + kk * (2048 / 16), idesc_acc, kk > 0, issuer);
+                    umma_commit_pred(&bars[PB_W_FULL], issuer);
+#pragma unroll
+                    for (int kk = 0; kk < RING / 16; ++kk)    // dKb += gA^T Qp
+                        umma_ts_pred(tAK, tA + 32 + a_col(kk), dQpM + (kk * (2048 / 16) + qoff), idesc_acc, 1, issuer);
+                    umma_commit_pred(&bars[PB_D_DONE0 + qb], issuer);
+                    TL(8);
+                } else {
+                    dk_pending = true;
+                }
                 ++n;
             }
-            // every MMA of this query has been issued: signal the ring rows free once they complete
-            if (n > n_query && ok && lane == 0) umma_commit(&bars[PB_RING_FREE]);
-            __syncwarp();
+            // Every MMA of this query that reads the ring tiles has been issued: signal the ring rows
+            // free once they complete.
+            if (n > n_query && ok) umma_commit_pred(&bars[PB_RING_FREE], issuer);
             n_query = n;
         }
-        // Let the last committed group finish before the tensor memory is released.
-        if (n > 0 && ok) {
-            if (WITH_DQ) pipe_wait(&bars[PB_W_FULL], (n - 1) & 1, sFail);
-            else pipe_wait(&bars[PB_D_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail);
+        if (ok && dk_pending) ok = issue_dk(n - 1);
+        if (ok) ok = settle_flush();
+        if (ok) {
+            // Final phase of Acc_done: everything has been issued; drain quarter 0 once it is complete.
+            commit_acc();
+            ok = pipe_wait(&bars[PB_ACC_DONE], (acc_commits - 1) & 1, sFail);
+            if (ok) {
+                tc_fence_after();
+                acc_flush(-1, q1 - 1, false);
+            }
         }
         __syncwarp();
         }
@@ -501,9 +718,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         // ================================================================== E warps
         cta_start_sync();
         const int slot = tid & (RING - 1);               // tensor-memory lane = ring slot
-        const int ch = tid >> 7;                          // which 32-column chunk of each half
+        const int ch = tid >> 7;                          // which 64-column half of the score tile
         const uint32_t tl = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-        {
+        {   // zero both accumulators: half 0 takes dKb, half 1 dVb
             uint32_t z[32];
 #pragma unroll
             for (int t = 0; t < 32; ++t) z[t] = 0;
@@ -512,38 +729,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             tmem_wait_st();
             tc_fence_before();
         }
-        auto flush = [&](int quarter, int only_lane, int i_ref, bool rezero) {
-            if ((warp & 3) != quarter) return;
-            const uint32_t col = ch ? C_AV : C_AK;
-            float* dst_base = ch ? gPartV : gPartK;
-            const float mul = ch ? 1.0f : p.scale;
-            const int key = ring_key(i_ref, slot);
-            const bool mine = (only_lane < 0 || lane == only_lane) && key >= 0;
-            uint32_t a[32];
-#pragma unroll 1
-            for (int c = 0; c < D / 32; ++c) {
-                tmem_ld32(tl + col + c * 32, a);
-                tmem_wait_ld();
-                if (mine) {
-                    float4* dst = reinterpret_cast<float4*>(dst_base + static_cast<size_t>(key) * D + c * 32);
-#pragma unroll
-                    for (int t = 0; t < 8; ++t)
-                        dst[t] = make_float4(mul * __uint_as_float(a[4 * t]), mul * __uint_as_float(a[4 * t + 1]),
-                                             mul * __uint_as_float(a[4 * t + 2]), mul * __uint_as_float(a[4 * t + 3]));
-                }
-                if (rezero) {
-                    if (only_lane < 0 || lane == only_lane) {
-#pragma unroll
-                        for (int t = 0; t < 32; ++t) a[t] = 0;
-                    }
-                    tmem_st32(tl + col + c * 32, a);
-                }
-            }
-            if (rezero) {
-                tmem_wait_st();
-                tc_fence_before();
-            }
-        };
+        // The accumulators must be zero before the first accumulating MMA; that MMA waits for
+        // P_full of the first head, which every E warp arrives on after this point.
         // per-head scalars, fetched one iteration ahead: this lane's slice of dY and Y, and m, l
         uint2 pre_dy = make_uint2(0, 0), pre_y = make_uint2(0, 0);
         uint32_t pre_dy2[2] = {0, 0}, pre_y2[2] = {0, 0};
@@ -561,29 +748,19 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             pre_l = __ldg(p.l + row);
         };
         prefetch(0);
-        // last MMA group of head k: W (dQ pass, one barrier, phase k) or dKb (per-buffer barrier, phase k/2)
-        auto wait_head_done = [&](int k, long long* tr) {
-            return WITH_DQ ? pipe_wait(&bars[PB_W_FULL], k & 1, sFail, tr)
-                           : pipe_wait(&bars[PB_D_DONE0 + (k & 1)], (k >> 1) & 1, sFail, tr);
-        };
         int n = 0, it = 0, n_query = 0;
         bool ok = true;
         for (int i = q0; i < q1 && ok; ++i) {
-            if (i > q0) {
-                if (n > 0) {
-                    ok = wait_head_done(n - 1, TR(13));
-                    if (!ok) break;
-                    tc_fence_after();
-                }
-                const int s = i & (RING - 1);
-                flush(s >> 5, s & 31, i - 1, true);
-            }
             uint32_t vw[4];
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
             const int n_vis = __popc(vw[0]) + __popc(vw[1]) + __popc(vw[2]) + __popc(vw[3]);
             const bool all_vis = n_vis == RING;
             const bool single = n_vis == 1;
             const bool my_vis = (vw[warp & 3] >> lane) & 1u;
+            // visibility words of this thread's two 32-column chunks
+            const uint32_t cw0 = my_vis ? (ch ? vw[2] : vw[0]) : 0u;
+            const uint32_t cw1 = my_vis ? (ch ? vw[3] : vw[1]) : 0u;
+            bool ring_arrived = false;
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
                 const size_t row = row_index(it);
                 // delta = dY . Y and lse (log2 units) of this head from the prefetched slices
@@ -606,92 +783,94 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 }
                 const float lse2 = m_i * LOG2E + __log2f(l_i);
                 const uint32_t ph = n & 1;
-                // ---- phase 1: P^T = exp2(X^T c - lse) for this thread's 64 columns, BF16 into X^T[0,64)
+                const uint32_t tA = tl + C_R0 + (n & 1) * 128 + ch * 64;          // this thread's 64 score columns
+                const uint32_t tB = tl + C_R0 + ((n & 1) ^ 1) * 128;
+                // ---- phase 1: P^T = exp2(X^T c2 - lse) for this thread's 64 columns, BF16 into the first 32
                 uint32_t pk[32];
                 TL(10);
                 ok = pipe_wait(&bars[PB_S_XT], ph, sFail, TR(8));
                 if (!ok) break;
-                TL(11);
                 tc_fence_after();
-                long long tt = tracer ? clock64() : 0;
-#pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    const int c = 2 * ch + cc;                      // 32-column chunk of the score tile
-                    uint32_t xr[32];
-                    tmem_ld32(tl + C_XT + c * 32, xr);
+                TL(11);
+                {
+                    uint32_t xa[32], xb[32];
+                    tmem_ld32(tA, xa);
+                    tmem_ld32(tA + 32, xb);
                     tmem_wait_ld();
-                    const uint32_t cw = my_vis ? (c == 0 ? vw[0] : c == 1 ? vw[1] : c == 2 ? vw[2] : vw[3]) : 0u;
 #pragma unroll
                     for (int t = 0; t < 32; t += 2) {
-                        float p0 = fast_exp2(fmaf(__uint_as_float(xr[t]), c2, -lse2));
-                        float p1 = fast_exp2(fmaf(__uint_as_float(xr[t + 1]), c2, -lse2));
+                        float p0 = fast_exp2(fmaf(__uint_as_float(xa[t]), c2, -lse2));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(xa[t + 1]), c2, -lse2));
+                        float p2 = fast_exp2(fmaf(__uint_as_float(xb[t]), c2, -lse2));
+                        float p3 = fast_exp2(fmaf(__uint_as_float(xb[t + 1]), c2, -lse2));
                         if (!all_vis) {
-                            if (!((cw >> t) & 1u)) p0 = 0.f;
-                            if (!((cw >> (t + 1)) & 1u)) p1 = 0.f;
+                            if (!((cw0 >> t) & 1u)) p0 = 0.f;
+                            if (!((cw0 >> (t + 1)) & 1u)) p1 = 0.f;
+                            if (!((cw1 >> t) & 1u)) p2 = 0.f;
+                            if (!((cw1 >> (t + 1)) & 1u)) p3 = 0.f;
                         }
-                        pk[cc * 16 + (t >> 1)] = pack_bf16x2(p0, p1);
+                        pk[t >> 1] = pack_bf16x2(p0, p1);
+                        pk[16 + (t >> 1)] = pack_bf16x2(p2, p3);
                     }
                 }
-                if (tracer) { const long long t2 = clock64(); p.trace[21] += t2 - tt; tt = t2; }
-                // the BF16 results land on score columns that other E threads read: all loads first
-                tc_fence_before();
                 TL(12);
-                warp_arrive(&bars[PB_E_SYNC], lane);
-                ok = pipe_wait(&bars[PB_E_SYNC], ph, sFail, TR(10));
-                if (!ok) break;
-                TL(13);
-                tc_fence_after();
-                tmem_st32(tl + C_XT + ch * 32, pk);
+                // both loads are complete, so the store lands on columns only this thread has read
+                tmem_st32(tA, pk);
                 tmem_wait_st();
                 tc_fence_before();
                 warp_arrive(&bars[PB_P_FULL], lane);
                 TL(14);
-                // ---- phase 2: gA^T = P^T o (dP^T - delta), BF16 into X^T[64,128)
+                // ---- phase 2: gA^T = P^T o (dP^T - delta), BF16 into the last 32 of this thread's columns
                 ok = pipe_wait(&bars[PB_S_DP], ph, sFail, TR(9));
                 if (!ok) break;
-                TL(15);
                 tc_fence_after();
-                if (tracer) tt = clock64();
+                TL(15);
                 {
-                    uint32_t gk[32];
-#pragma unroll
-                    for (int cc = 0; cc < 2; ++cc) {
-                        uint32_t dp[32];
-                        tmem_ld32(tl + C_DP + (2 * ch + cc) * 32, dp);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int t = 0; t < 32; t += 2) {
-                            const float2 pp = unpack_bf16x2(pk[cc * 16 + (t >> 1)]);
-                            float g0 = pp.x * (__uint_as_float(dp[t]) - delta);
-                            float g1 = pp.y * (__uint_as_float(dp[t + 1]) - delta);
-                            if (single) { g0 = 0.f; g1 = 0.f; }
-                            gk[cc * 16 + (t >> 1)] = pack_bf16x2(g0, g1);
-                        }
+                    uint32_t da[32], db[32];
+                    tmem_ld32(tB + ch * 64, da);
+                    tmem_ld32(tB + ch * 64 + 32, db);
+                    tmem_wait_ld();
+                    if (!WITH_DQ) {
+                        // dP^T is in registers: the next head's scores may land on these columns
+                        tc_fence_before();
+                        warp_arrive(&bars[PB_B_FREE], lane);
                     }
-                    tmem_st32(tl + C_XT + 64 + ch * 32, gk);
+#pragma unroll
+                    for (int t = 0; t < 32; t += 2) {
+                        const float2 pa = unpack_bf16x2(pk[t >> 1]);
+                        const float2 pb = unpack_bf16x2(pk[16 + (t >> 1)]);
+                        float g0 = pa.x * (__uint_as_float(da[t]) - delta);
+                        float g1 = pa.y * (__uint_as_float(da[t + 1]) - delta);
+                        float g2 = pb.x * (__uint_as_float(db[t]) - delta);
+                        float g3 = pb.y * (__uint_as_float(db[t + 1]) - delta);
+                        if (single) { g0 = 0.f; g1 = 0.f; g2 = 0.f; g3 = 0.f; }
+                        pk[t >> 1] = pack_bf16x2(g0, g1);
+                        pk[16 + (t >> 1)] = pack_bf16x2(g2, g3);
+                    }
+                    tmem_st32(tA + 32, pk);
                     tmem_wait_st();
                     tc_fence_before();
                 }
-                if (tracer) p.trace[22] += clock64() - tt;
                 warp_arrive(&bars[PB_G_FULL], lane);
                 TL(16);
-                if (!ok) break;
                 if (WITH_DQ) {
                     ok = pipe_wait(&bars[PB_W_FULL], ph, sFail, TR(11));
                     if (!ok) break;
-                    TL(17);
                     tc_fence_after();
-                    const long long te = tracer ? clock64() : 0;
+                    TL(17);
                     // dQ[d] = scale * sum_k Kb_k[d] * W[k][d]; this thread: lane k, d in its half.
-                    const uint32_t wcol = C_DP + ch * HD;
                     constexpr int NC = HD / 32;
                     float* red = sRed + (n & 1) * 4 * D;
-#pragma unroll 1
+                    uint32_t u[NC][32];
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) tmem_ld32(tB + ch * HD + c * 32, u[c]);
+                    tmem_wait_ld();
+                    // W is in registers: the next head's scores may land on these columns
+                    tc_fence_before();
+                    warp_arrive(&bars[PB_B_FREE], lane);
+#pragma unroll
                     for (int c = 0; c < NC; ++c) {
-                        uint32_t u[32];
                         float v[32];
-                        tmem_ld32(tl + wcol + c * 32, u);
-                        tmem_wait_ld();
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             const uint4 kb = *reinterpret_cast<const uint4*>(
@@ -700,19 +879,18 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const float2 kf = unpack_bf16x2(w4[e]);
-                                v[q * 8 + 2 * e] = kf.x * __uint_as_float(u[q * 8 + 2 * e]);
-                                v[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[q * 8 + 2 * e + 1]);
+                                v[q * 8 + 2 * e] = kf.x * __uint_as_float(u[c][q * 8 + 2 * e]);
+                                v[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[c][q * 8 + 2 * e + 1]);
                             }
                         }
-                        if (c == NC - 1) {
-                            // W and this thread's Kb row are in registers: the next head may overwrite them
-                            tc_fence_before();
-                            warp_arrive(&bars[PB_W_FREE], lane);
+                        // the query's last head: this warp is done with the Kb rows of the ring
+                        if (c == NC - 1 && hh == G - 1) {
+                            warp_arrive(&bars[PB_RING_FREE], lane);
+                            ring_arrived = true;
                         }
                         const float s = warp_transpose_sum(v, lane);
                         red[(warp & 3) * D + ch * HD + c * 32 + lane] = s;
                     }
-                    if (tracer) p.trace[23] += clock64() - te;
                     TL(18);
                     warp_arrive(&bars[PB_E_SYNC2], lane);
                     ok = pipe_wait(&bars[PB_E_SYNC2], ph, sFail, TR(12));
@@ -724,23 +902,34 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 }
                 ++n;
             }
-            // dQ pass: this warp has read the Kb rows of the query's last head (in its epilogue)
-            if (WITH_DQ && ok && n > n_query) warp_arrive(&bars[PB_RING_FREE], lane);
+            // dQ pass, when the query's last head had no work: the Kb rows were last read further up
+            if (WITH_DQ && ok && n > n_query && !ring_arrived) warp_arrive(&bars[PB_RING_FREE], lane);
             n_query = n;
         }
-        // Drain: every slot still holds a key of (q1 - 129, q1 - 1].
-        if (ok) {
-            if (n > 0) {
-                ok = wait_head_done(n - 1, nullptr);
-                tc_fence_after();
-            }
-            if (ok) {
-#pragma unroll 1
-                for (int quarter = 0; quarter < 4; ++quarter) flush(quarter, -1, q1 - 1, false);
+    }
+#ifdef ATT3_PIPE_TRACE
+    if (tr_sum) p.trace[tid == 0 ? 14 : (tid == PIPE_E_THREADS ? 19 : 6)] += clock64() - t_begin;
+    if (timed) {
+        unsigned long long ns_end;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
+        const long long cyc = clock64() - t_begin, ns = static_cast<long long>(ns_end - ns_begin);
+        if (tracer) {                                                          // cycles and nanoseconds of CTA 0
+            p.trace[24 + (WITH_DQ ? 0 : 2)] = cyc;
+            p.trace[25 + (WITH_DQ ? 0 : 2)] = ns;
+        }
+        {   // per-CTA record behind the timeline area: cycles, SM id (first 160 CTAs of each pass)
+            const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+            if (cta < 160) {
+                uint32_t smid;
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+                p.trace[32 + 384 + ((WITH_DQ ? 0 : 160) + cta) * 2] = cyc;
+                p.trace[32 + 384 + ((WITH_DQ ? 0 : 160) + cta) * 2 + 1] = smid;
             }
         }
+        atomicMax(reinterpret_cast<unsigned long long*>(p.trace) + 28 + (WITH_DQ ? 0 : 2), static_cast<unsigned long long>(cyc));
+        atomicMax(reinterpret_cast<unsigned long long*>(p.trace) + 29 + (WITH_DQ ? 0 : 2), static_cast<unsigned long long>(ns));
     }
-    if (tracer) p.trace[tid == 0 ? 14 : (tid == PIPE_E_THREADS ? 19 : 6)] += clock64() - t_begin;
+#endif
 #undef TR
 #undef TL
     tc_fence_before();

@@ -107,6 +107,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParam
     volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 12);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t issuer = elect_one();     // one lane per warp; warp 0 predicates its MMAs on it
     const int b = blockIdx.z, g = blockIdx.y;
     const int G = p.Hq / p.Hkv;
     const int q0 = p.q_begin + blockIdx.x * p.block_len;
@@ -223,32 +224,38 @@ __global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParam
             // --- Hadamard tile: Qp[j][d] = bf16(Q_i[d] * R_j[d]) ------------------
             {
                 const uint4* q4 = reinterpret_cast<const uint4*>(sQst + (it & 1) * D);
+                // Loads of the staged row in batches of eight chunks ahead of the tile stores: the
+                // compiler cannot rule out aliasing between the two shared-memory areas and would
+                // otherwise serialise load -> multiply -> store per chunk.
 #pragma unroll
-                for (int c = 0; c < CH; ++c) {
-                    const uint4 q = q4[c];
-                    uint4 o;
-                    o.x = mul_bf16x2(q.x, rR[4 * c]);
-                    o.y = mul_bf16x2(q.y, rR[4 * c + 1]);
-                    o.z = mul_bf16x2(q.z, rR[4 * c + 2]);
-                    o.w = mul_bf16x2(q.w, rR[4 * c + 3]);
-                    *reinterpret_cast<uint4*>(sQp + sw128_offset<RING>(tid, c)) = o;
+                for (int c0 = 0; c0 < CH; c0 += 8) {
+                    uint4 q[8];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) q[c] = q4[c0 + c];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        uint4 o;
+                        o.x = mul_bf16x2(q[c].x, rR[4 * (c0 + c)]);
+                        o.y = mul_bf16x2(q[c].y, rR[4 * (c0 + c) + 1]);
+                        o.z = mul_bf16x2(q[c].z, rR[4 * (c0 + c) + 2]);
+                        o.w = mul_bf16x2(q[c].w, rR[4 * (c0 + c) + 3]);
+                        *reinterpret_cast<uint4*>(sQp + sw128_offset<RING>(tid, c0 + c)) = o;
+                    }
                 }
             }
             fence_async_smem();
             tc_fence_before();
             __syncthreads();                                           // B1
             if (warp == 0) {
-                // one thread issues the whole unrolled run from precomputed descriptors and commits it
+                // the warp stays converged; the MMAs and the commit are predicated on its elected lane
                 tc_fence_after();
-                if (lane == 0) {
 #pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk) {
-                        const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                        umma_ss(tmem_base, dQp + off, dS + off, idesc_x, kk > 0);
-                    }
-                    umma_commit(bar);
-                    if (!mbar_wait(bar, phase)) *sFail = 1;
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
+                    umma_ss_pred(tmem_base, dQp + off, dS + off, idesc_x, kk > 0, issuer);
                 }
+                umma_commit_pred(bar, issuer);
+                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
                 __syncwarp();
             }
             phase ^= 1;
@@ -308,13 +315,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParam
             __syncthreads();                                           // B3
             if (warp == 0) {
                 tc_fence_after();
-                if (lane == 0) {
 #pragma unroll
-                    for (int kk = 0; kk < RING / 16; ++kk)
-                        umma_ts(tmem_base + 128, tmem_base + kk * 8, dVsM + kk * (2048 / 16), idesc_u, kk > 0);
-                    umma_commit(bar);
-                    if (!mbar_wait(bar, phase)) *sFail = 1;
-                }
+                for (int kk = 0; kk < RING / 16; ++kk)
+                    umma_ts_pred(tmem_base + 128, tmem_base + kk * 8, dVsM + kk * (2048 / 16), idesc_u, kk > 0, issuer);
+                umma_commit_pred(bar, issuer);
+                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
                 __syncwarp();
             }
             phase ^= 1;

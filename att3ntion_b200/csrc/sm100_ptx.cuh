@@ -177,47 +177,58 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         : "memory");
 }
 
-// Whole-warp variants: every lane executes the call with identical (warp-uniform)
-// operands and one elected lane issues the MMA.  Keeping the warp converged lets the
-// compiler hold descriptors and addresses in uniform registers, which is what the
-// instruction takes; issuing from a divergent `lane == 0` branch costs a register-file
-// round trip per operand and limits the issue rate to one MMA per 100-200 cycles.
-__device__ __forceinline__ void umma_ss_warp(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                             uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q;\n\t"
-        ".reg .b32 rx;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "elect.sync rx|q, 0xFFFFFFFF;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_ts_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                             uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q;\n\t"
-        ".reg .b32 rx;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "elect.sync rx|q, 0xFFFFFFFF;\n\t"
-        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-        "}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit_warp(uint64_t* bar) {
+// Whole-warp variants: every lane executes the call, and the instruction is predicated on
+// `issue`, which is non-zero in exactly one lane (elect_one(), taken once per role).  Measured
+// with MMAs short enough to expose the issue cost (M128 N16 K16): 11 cycles per MMA issued this
+// way against 47 from inside a divergent `if (lane == 0)` branch, whether or not the operands
+// are provably warp-uniform; electing a lane anew for every MMA costs more than either.
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t elected;
     asm volatile(
         "{\n\t"
         ".reg .pred q;\n\t"
         ".reg .b32 rx;\n\t"
         "elect.sync rx|q, 0xFFFFFFFF;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t"
+        "}\n"
+        : "=r"(elected));
+    return elected;
+}
+
+__device__ __forceinline__ void umma_ss_pred(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t issue) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issue)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_ts_pred(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate, uint32_t issue) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issue)
+        : "memory");
+}
+
+// Commit by the lane that issued (the commit covers the executing thread's MMAs).
+__device__ __forceinline__ void umma_commit_pred(uint64_t* bar, uint32_t issue) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
         "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
-        "}\n" ::"r"(smem_u32(bar))
+        "}\n" ::"r"(smem_u32(bar)), "r"(issue)
         : "memory");
 }
 

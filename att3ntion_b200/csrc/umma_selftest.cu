@@ -72,7 +72,10 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
 
     const int nwidth = (p.mode & 8) ? 64 : T;       // mode | 8: the same product restricted to N = 64 columns
     p.tight = (p.mode >> 4) & 3;                      // 1: elect per MMA, 2: lane-0 thread, 3: elected once
+    const int extra = p.mode & ~63;                   // rate-probe conditions, see below
     p.mode &= 7;
+    __shared__ volatile int s_done;
+    if (tid == 0) s_done = 0;
     const bool a_in_tmem = (p.mode == 3 || p.mode == 4);
     if (a_in_tmem) {
         // Thread m holds row m of A: 128 BF16 = 64 packed words = columns [0,64) of the A region.
@@ -95,8 +98,17 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
         // back; tight 3: the lane is elected once and then issues all MMAs.
         tc_fence_after();
         const uint32_t idesc = make_idesc_bf16(T, T, 0, 0);
-        const uint64_t da = make_smem_desc(smem_u32(sA), 16, 1024, SWIZZLE_128B);
-        const uint64_t db = make_smem_desc(smem_u32(sB), 16, 1024, SWIZZLE_128B);
+        uint64_t da = make_smem_desc(smem_u32(sA), 16, 1024, SWIZZLE_128B);
+        uint64_t db = make_smem_desc(smem_u32(sB), 16, 1024, SWIZZLE_128B);
+        // Mode bit 64: add an offset (zero) that the compiler cannot prove warp-uniform, as a
+        // buffer index derived from a data-dependent loop counter would be; bit 128: the same
+        // offset passed through a shuffle from lane 0, which marks it warp-uniform.
+        if (extra & (64 | 128)) {
+            uint32_t roff = static_cast<uint32_t>(p.status[3]);
+            if (extra & 128) roff = __shfl_sync(0xFFFFFFFFu, roff, 0);
+            da += roff;
+            db += roff;
+        }
         uint32_t elected = (tid == 0);
         if (p.tight == 3)
             asm volatile("{\n\t.reg .pred q;\n\t.reg .b32 rx;\n\telect.sync rx|q, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
@@ -108,7 +120,8 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
 #pragma unroll
                 for (int kk = 0; kk < T / 16; ++kk) {
                     const uint32_t koff = ((kk >> 2) * (T * 128) + (kk & 3) * 32) / 16;
-                    if (kk == 0) umma_ss(tmem_d, da + koff, db + koff, idesc, rep > 0);
+                    if (a_in_tmem) umma_ts(tmem_d, tmem_a + kk * 8, db + koff, idesc, (rep > 0 || kk > 0) ? 1u : 0u);
+                    else if (kk == 0) umma_ss(tmem_d, da + koff, db + koff, idesc, rep > 0);
                     else umma_ss(tmem_d, da + koff, db + koff, idesc, 1u);
                 }
             }
@@ -118,6 +131,26 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
         }
         __syncwarp();
         if (tid == 0) t_issue = elected ? t0 : clock64();
+    } else if (p.tight >= 2 && (extra & (256 | 512))) {
+        // Rate probe under load (warps 1-3): bit 256 keeps tensor-memory loads of columns the MMAs do
+        // not touch in flight, bit 512 keeps 16-byte shared-memory stores in flight, until the issuing
+        // thread has seen the MMAs complete (bounded).
+        uint32_t r[32];
+        uint32_t sink = 0;
+        uint8_t* scratch = smem + 2 * TILE_BYTES + (warp - 1) * 2048;
+        for (int itn = 0; itn < 40000 && !s_done; ++itn) {
+            if (extra & 256) {
+                tmem_ld32(tmem_base + 192 + lane_field, r);
+                tmem_wait_ld();
+                sink ^= r[itn & 31];
+            }
+            if (extra & 512) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(scratch + ((tid & 31) * 16 + c * 512)) = make_uint4(sink, itn, c, tid);
+            }
+        }
+        if (sink == 0x12345678u) p.status[3] = 1;
     } else if (p.tight && warp == 0) {
         // Rate probe: whole warp converged, descriptor bases precomputed, k-steps unrolled.
         tc_fence_after();
@@ -125,6 +158,7 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
         const uint32_t idesc = make_idesc_bf16(T, nwidth, 0, b_mn);
         const uint64_t da = make_smem_desc(smem_u32(sA), p.lbo_a, p.sbo_a, SWIZZLE_128B);
         const uint64_t db = make_smem_desc(smem_u32(sB), p.lbo_b, p.sbo_b, SWIZZLE_128B);
+        const uint32_t issuer = elect_one();
         const long long t0 = clock64();
         for (int rep = 0; rep < p.reps; ++rep) {
 #pragma unroll
@@ -132,12 +166,12 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
                 const uint32_t koff = ((kk >> 2) * (T * 128) + (kk & 3) * 32) / 16;
                 const uint32_t moff = kk * 2048 / 16;
                 const uint32_t acc = (rep > 0 || kk > 0) ? 1u : 0u;
-                if (a_in_tmem) umma_ts_warp(tmem_d, tmem_a + kk * 8, db + (b_mn ? moff : koff), idesc, acc);
-                else umma_ss_warp(tmem_d, da + koff, db + (b_mn ? moff : koff), idesc, acc);
+                if (a_in_tmem) umma_ts_pred(tmem_d, tmem_a + kk * 8, db + (b_mn ? moff : koff), idesc, acc, issuer);
+                else umma_ss_pred(tmem_d, da + koff, db + (b_mn ? moff : koff), idesc, acc, issuer);
             }
         }
         const long long t1 = clock64();
-        umma_commit_warp(&mma_bar);
+        umma_commit_pred(&mma_bar, issuer);
         if (tid == 0) { p.status[2] = static_cast<int>(t1 - t0); t_issue = t0; }
     } else if (!p.tight && tid == 0) {
         tc_fence_after();
@@ -173,6 +207,7 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
     if (tid == 0) {
         s_ok = mbar_wait(&mma_bar, 0) ? 1 : 0;
         p.status[1] = static_cast<int>(clock64() - t_issue);             // cycles from first issue to completion
+        s_done = 1;
     }
     __syncthreads();
     const bool ok = s_ok != 0;
@@ -202,7 +237,7 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
 extern "C" int att3_umma_selftest(const void* A, const void* B, float* D, int mode, int lbo_a, int sbo_a,
                                   int lbo_b, int sbo_b, int reps, int* status_dev, void* stream) {
     if (!A || !B || !D || !status_dev) return att3::set_error(ATT3_ERR_INVALID, "umma_selftest: null pointer");
-    if ((mode & 7) > 4 || mode < 0 || mode > 63 || ((mode & 16) && (mode & 7) == 2) || reps < 1 || reps > 64)
+    if ((mode & 7) > 4 || mode < 0 || mode > 1023 || ((mode & 16) && (mode & 7) == 2) || reps < 1 || reps > 64)
         return att3::set_error(ATT3_ERR_INVALID, "umma_selftest: mode must be 0..4 (+8: N = 64, +16: converged-warp issue) and reps 1..64");
     SelftestParams p;
     p.A = static_cast<const __nv_bfloat16*>(A);
@@ -213,11 +248,140 @@ extern "C" int att3_umma_selftest(const void* A, const void* B, float* D, int mo
     p.reps = reps;
     p.tight = 0;
     p.status = status_dev;
-    const int smem = 2 * TILE_BYTES + 1024;
+    const int smem = 2 * TILE_BYTES + 1024 + 3 * 2048;
     cudaError_t e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return att3::set_cuda_error(e, "umma_selftest: smem opt-in");
     umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return att3::set_cuda_error(e, "umma_selftest: launch");
     return ATT3_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Diagnostic (not in the public header): cycles per tcgen05.mma as seen by the issuing thread,
+// for several ways of writing the issue loop.  With N = 16 an MMA occupies the tensor pipe for a
+// few cycles only, so the figure is the issue cost itself; with N = 128 it is max(issue, 64).
+//   style 0  lane-0 branch, every operand a compile-time function of the shared-memory base
+//   style 1  lane-0 branch, descriptors and tensor-memory addresses offset by per-thread values
+//            (what a buffer index derived from a data-dependent loop counter looks like)
+//   style 2  as 1, the values passed through a shuffle from lane 0 (marks them warp-uniform)
+//   style 3  whole warp converged, one lane elected once, MMAs predicated on it; operands as in 2
+//   style 4  as 3 with the per-thread operands of style 1
+// ---------------------------------------------------------------------------
+namespace {
+
+template <int STYLE, bool TS, int NW>
+__global__ void __launch_bounds__(128, 1) umma_rate_kernel(int* status, int reps) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + TILE_BYTES;
+    __shared__ uint64_t mma_bar;
+    __shared__ uint32_t tmem_base_slot;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (warp == 0) {
+        tmem_alloc(&tmem_base_slot, 256);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        mbar_init(&mma_bar, 1);
+        fence_mbar_init();
+    }
+    for (int c = 0; c < 16; ++c) {
+        *reinterpret_cast<uint4*>(sA + tid * 256 + c * 16) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(sB + tid * 256 + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 0) {
+        uint32_t tmem_base = tmem_base_slot;
+        uint32_t roff = static_cast<uint32_t>(status[3]);      // zero, but only known at run time, per thread
+        if (STYLE == 0) roff = 0;
+        if (STYLE == 2 || STYLE == 3) {
+            roff = __shfl_sync(0xFFFFFFFFu, roff, 0);
+            tmem_base = __shfl_sync(0xFFFFFFFFu, tmem_base, 0);
+        }
+        const uint32_t idesc = make_idesc_bf16(T, NW, 0, 0);
+        const uint64_t da = make_smem_desc(smem_u32(sA), 16, 1024, SWIZZLE_128B) + roff;
+        const uint64_t db = make_smem_desc(smem_u32(sB), 16, 1024, SWIZZLE_128B) + roff;
+        const uint32_t tD = tmem_base + roff, tA = tmem_base + 128 + roff;
+        long long t0 = 0, t1 = 0;
+        if (STYLE <= 2) {
+            if (lane == 0) {
+                t0 = clock64();
+#pragma unroll 1
+                for (int rep = 0; rep < reps; ++rep) {
+#pragma unroll
+                    for (int kk = 0; kk < T / 16; ++kk) {
+                        const uint32_t koff = ((kk >> 2) * (T * 128) + (kk & 3) * 32) / 16;
+                        if (TS) umma_ts(tD, tA + kk * 8, db + koff, idesc, kk > 0);
+                        else umma_ss(tD, da + koff, db + koff, idesc, kk > 0);
+                    }
+                }
+                t1 = clock64();
+                umma_commit(&mma_bar);
+            }
+            __syncwarp();
+        } else {
+            const uint32_t elected = elect_one();
+            t0 = clock64();
+#pragma unroll 1
+            for (int rep = 0; rep < reps; ++rep) {
+#pragma unroll
+                for (int kk = 0; kk < T / 16; ++kk) {
+                    const uint32_t koff = ((kk >> 2) * (T * 128) + (kk & 3) * 32) / 16;
+                    if (TS) umma_ts_pred(tD, tA + kk * 8, db + koff, idesc, kk > 0, elected);
+                    else umma_ss_pred(tD, da + koff, db + koff, idesc, kk > 0, elected);
+                }
+            }
+            t1 = clock64();
+            if (elected) umma_commit(&mma_bar);
+            __syncwarp();
+        }
+        if (lane == 0) {
+            status[2] = static_cast<int>(t1 - t0);
+            status[0] = mbar_wait(&mma_bar, 0) ? 0 : 1;
+            status[1] = static_cast<int>(clock64() - t0);
+        }
+        __syncwarp();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base_slot, 256);
+}
+
+template <int STYLE, bool TS>
+int launch_rate(int nw, int* status, int reps, cudaStream_t st) {
+    const int smem = 2 * TILE_BYTES + 1024;
+    auto go = [&](auto kern) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return att3::set_cuda_error(e, "umma_rate: smem opt-in");
+        kern<<<1, 128, smem, st>>>(status, reps);
+        e = cudaGetLastError();
+        return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "umma_rate: launch");
+    };
+    return nw == 16 ? go(umma_rate_kernel<STYLE, TS, 16>) : go(umma_rate_kernel<STYLE, TS, 128>);
+}
+
+}  // namespace
+
+extern "C" int att3_debug_mma_rate(int style, int ts, int nwidth, int reps, int* status_dev, void* stream) {
+    if (!att3::require_sm100("umma_rate")) return ATT3_ERR_UNSUPPORTED;
+    if (style < 0 || style > 4 || (nwidth != 16 && nwidth != 128) || reps < 1 || reps > 4096 || !status_dev)
+        return att3::set_error(ATT3_ERR_INVALID, "umma_rate: style 0..4, nwidth 16|128, reps 1..4096");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (style * 2 + (ts ? 1 : 0)) {
+        case 0: return launch_rate<0, false>(nwidth, status_dev, reps, st);
+        case 1: return launch_rate<0, true>(nwidth, status_dev, reps, st);
+        case 2: return launch_rate<1, false>(nwidth, status_dev, reps, st);
+        case 3: return launch_rate<1, true>(nwidth, status_dev, reps, st);
+        case 4: return launch_rate<2, false>(nwidth, status_dev, reps, st);
+        case 5: return launch_rate<2, true>(nwidth, status_dev, reps, st);
+        case 6: return launch_rate<3, false>(nwidth, status_dev, reps, st);
+        case 7: return launch_rate<3, true>(nwidth, status_dev, reps, st);
+        case 8: return launch_rate<4, false>(nwidth, status_dev, reps, st);
+        default: return launch_rate<4, true>(nwidth, status_dev, reps, st);
+    }
 }
