@@ -181,6 +181,32 @@ __device__ __forceinline__ void ring_visibility(const uint8_t* mask_row, int i, 
     }
 }
 
+// Sum over the 32 lanes of a warp of 32 per-lane values given as two halves (va: values 0-15,
+// vb: values 16-31); lane L ends up with the total of value L.  Same exchange network as
+// warp_transpose_sum, with the first stage folding the two halves.
+__device__ __forceinline__ float warp_transpose_sum_2x16(float (&va)[16], float (&vb)[16], int lane) {
+    {
+        const bool up = (lane & 16) != 0;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const float send = up ? va[k] : vb[k];
+            const float keep = up ? vb[k] : va[k];
+            va[k] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, 16);
+        }
+    }
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int k = 0; k < o; ++k) {
+            const float send = up ? va[k] : va[k + o];
+            const float keep = up ? va[k + o] : va[k];
+            va[k] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, o);
+        }
+    }
+    return va[0];
+}
+
 // Copies a warp's accumulator lanes (only_lane < 0: all 32) to the FP32 partial planes and, on
 // request, zeroes them.  Lane k of the accumulators belongs to the key in ring slot k; `tl` is the
 // tensor-memory address of the warp's lane quarter, `key` the key of this thread's lane (< 0: none).
@@ -290,10 +316,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     };
     const float c2 = p.scale * LOG2E;
 
-    // Each role first sets its register budget (the CTA starts at 128 per thread: the last
-    // warpgroup gives most of its registers away, the H threads take room for two ring rows,
-    // the E warps keep theirs), does its share of the set-up and then meets the others at
-    // one CTA barrier before the hand-off protocol starts.
+    // Each role first sets its register budget (the CTA starts at 128 per thread: the E warps work in
+    // rolled rounds of 32 columns and give registers away, the H threads take room for two ring rows
+    // and the MMA warp for its descriptors and bookkeeping; 8*E + 4*H + 4*M = 512 registers per lane
+    // column), does its share of the set-up and then meets the others at one CTA barrier before the
+    // hand-off protocol starts.
+    constexpr int E_REGS = 88, H_REGS = 232, M_REGS = 104;
+    static_assert(8 * E_REGS + 4 * H_REGS + 4 * M_REGS <= 2048, "register file: 64K registers / 32 lanes");
     // Optional cycle accounting of the hand-offs (one thread per role of CTA 0), compiled in only with
     // -DATT3_PIPE_TRACE: the bookkeeping costs registers in every role.
 #ifdef ATT3_PIPE_TRACE
@@ -326,7 +355,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
 
     if (is_h) {
         // ================================================================== H warps
-        reg_inc<184>();
+        reg_inc<H_REGS>();
         const int hslot = tid - PIPE_E_THREADS;          // ring slot of an H thread (0..127) = its tensor-memory lane
         uint32_t rKa[DW], rVa[DW];
         {   // initial fill of this thread's ring slot: registers (other side) and operand tiles (own side)
@@ -383,7 +412,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         fence_async_smem();
         cta_start_sync();
         constexpr int GB = L::G_BUFS;
-        constexpr int HB = 2;                 // staged chunks in flight per thread (registers: 4 per chunk)
+        constexpr int HB = 8;                 // staged chunks in flight per thread (registers: 4 per chunk)
         int n = 0, it = 0, n_query = 0, ring_phase = 0;
         bool ok = true;
         float l_next = __ldg(p.l + row_index(0));
@@ -498,7 +527,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             }
         }
     } else if (warp >= 12) {
-        reg_dec<72>();
+        reg_dec<M_REGS>();
         cta_start_sync();
         // Accumulator flushes are the work of this warpgroup: warp 12 + q reaches the tensor-memory lanes
         // of quarter q.  Quarters 1-3 belong to the three warps that otherwise only donate registers;
@@ -716,6 +745,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         }
     } else {
         // ================================================================== E warps
+        reg_dec<E_REGS>();
         cta_start_sync();
         const int slot = tid & (RING - 1);               // tensor-memory lane = ring slot
         const int ch = tid >> 7;                          // which 64-column half of the score tile
@@ -785,37 +815,34 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 const uint32_t ph = n & 1;
                 const uint32_t tA = tl + C_R0 + (n & 1) * 128 + ch * 64;          // this thread's 64 score columns
                 const uint32_t tB = tl + C_R0 + ((n & 1) ^ 1) * 128;
-                // ---- phase 1: P^T = exp2(X^T c2 - lse) for this thread's 64 columns, BF16 into the first 32
-                uint32_t pk[32];
+                // ---- phase 1: P^T = exp2(X^T c2 - lse) for this thread's 64 columns, BF16 into the first 32.
+                // Both phases walk the columns in two rounds of 32 inside a rolled loop: half the registers
+                // and half the code of one straight-line pass, and the BF16 results of a round land on
+                // columns whose scores an earlier round (or this one) has already taken.
                 TL(10);
                 ok = pipe_wait(&bars[PB_S_XT], ph, sFail, TR(8));
                 if (!ok) break;
                 tc_fence_after();
                 TL(11);
-                {
-                    uint32_t xa[32], xb[32];
-                    tmem_ld32(tA, xa);
-                    tmem_ld32(tA + 32, xb);
+#pragma unroll 1
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t x[32], pk[16];
+                    tmem_ld32(tA + cc * 32, x);
                     tmem_wait_ld();
+                    const uint32_t cw = cc ? cw1 : cw0;
 #pragma unroll
                     for (int t = 0; t < 32; t += 2) {
-                        float p0 = fast_exp2(fmaf(__uint_as_float(xa[t]), c2, -lse2));
-                        float p1 = fast_exp2(fmaf(__uint_as_float(xa[t + 1]), c2, -lse2));
-                        float p2 = fast_exp2(fmaf(__uint_as_float(xb[t]), c2, -lse2));
-                        float p3 = fast_exp2(fmaf(__uint_as_float(xb[t + 1]), c2, -lse2));
+                        float p0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2, -lse2));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2, -lse2));
                         if (!all_vis) {
-                            if (!((cw0 >> t) & 1u)) p0 = 0.f;
-                            if (!((cw0 >> (t + 1)) & 1u)) p1 = 0.f;
-                            if (!((cw1 >> t) & 1u)) p2 = 0.f;
-                            if (!((cw1 >> (t + 1)) & 1u)) p3 = 0.f;
+                            if (!((cw >> t) & 1u)) p0 = 0.f;
+                            if (!((cw >> (t + 1)) & 1u)) p1 = 0.f;
                         }
                         pk[t >> 1] = pack_bf16x2(p0, p1);
-                        pk[16 + (t >> 1)] = pack_bf16x2(p2, p3);
                     }
+                    tmem_st16(tA + cc * 16, pk);
                 }
                 TL(12);
-                // both loads are complete, so the store lands on columns only this thread has read
-                tmem_st32(tA, pk);
                 tmem_wait_st();
                 tc_fence_before();
                 warp_arrive(&bars[PB_P_FULL], lane);
@@ -825,32 +852,29 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 if (!ok) break;
                 tc_fence_after();
                 TL(15);
-                {
-                    uint32_t da[32], db[32];
-                    tmem_ld32(tB + ch * 64, da);
-                    tmem_ld32(tB + ch * 64 + 32, db);
+#pragma unroll 1
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t dp[32], pk[16];
+                    tmem_ld32(tB + ch * 64 + cc * 32, dp);
+                    tmem_ld16(tA + cc * 16, pk);
                     tmem_wait_ld();
-                    if (!WITH_DQ) {
+                    if (!WITH_DQ && cc == 1) {
                         // dP^T is in registers: the next head's scores may land on these columns
                         tc_fence_before();
                         warp_arrive(&bars[PB_B_FREE], lane);
                     }
 #pragma unroll
                     for (int t = 0; t < 32; t += 2) {
-                        const float2 pa = unpack_bf16x2(pk[t >> 1]);
-                        const float2 pb = unpack_bf16x2(pk[16 + (t >> 1)]);
-                        float g0 = pa.x * (__uint_as_float(da[t]) - delta);
-                        float g1 = pa.y * (__uint_as_float(da[t + 1]) - delta);
-                        float g2 = pb.x * (__uint_as_float(db[t]) - delta);
-                        float g3 = pb.y * (__uint_as_float(db[t + 1]) - delta);
-                        if (single) { g0 = 0.f; g1 = 0.f; g2 = 0.f; g3 = 0.f; }
+                        const float2 pp = unpack_bf16x2(pk[t >> 1]);
+                        float g0 = pp.x * (__uint_as_float(dp[t]) - delta);
+                        float g1 = pp.y * (__uint_as_float(dp[t + 1]) - delta);
+                        if (single) { g0 = 0.f; g1 = 0.f; }
                         pk[t >> 1] = pack_bf16x2(g0, g1);
-                        pk[16 + (t >> 1)] = pack_bf16x2(g2, g3);
                     }
-                    tmem_st32(tA + 32, pk);
-                    tmem_wait_st();
-                    tc_fence_before();
+                    tmem_st16(tA + 32 + cc * 16, pk);
                 }
+                tmem_wait_st();
+                tc_fence_before();
                 warp_arrive(&bars[PB_G_FULL], lane);
                 TL(16);
                 if (WITH_DQ) {
@@ -861,26 +885,47 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     // dQ[d] = scale * sum_k Kb_k[d] * W[k][d]; this thread: lane k, d in its half.
                     constexpr int NC = HD / 32;
                     float* red = sRed + (n & 1) * 4 * D;
-                    uint32_t u[NC][32];
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) tmem_ld32(tB + ch * HD + c * 32, u[c]);
-                    tmem_wait_ld();
-                    // W is in registers: the next head's scores may land on these columns
-                    tc_fence_before();
-                    warp_arrive(&bars[PB_B_FREE], lane);
-#pragma unroll
+#pragma unroll 1
                     for (int c = 0; c < NC; ++c) {
-                        float v[32];
+                        // two rounds of 16 columns keep the live set small (this role runs on 80 registers)
+                        float va[16], vb[16];
+                        {
+                            uint32_t u[16];
+                            tmem_ld16(tB + ch * HD + c * 32, u);
+                            tmem_wait_ld();
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const uint4 kb = *reinterpret_cast<const uint4*>(
-                                sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + q));
-                            const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
+                            for (int q = 0; q < 2; ++q) {
+                                const uint4 kb = *reinterpret_cast<const uint4*>(
+                                    sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + q));
+                                const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float2 kf = unpack_bf16x2(w4[e]);
-                                v[q * 8 + 2 * e] = kf.x * __uint_as_float(u[c][q * 8 + 2 * e]);
-                                v[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[c][q * 8 + 2 * e + 1]);
+                                for (int e = 0; e < 4; ++e) {
+                                    const float2 kf = unpack_bf16x2(w4[e]);
+                                    va[q * 8 + 2 * e] = kf.x * __uint_as_float(u[q * 8 + 2 * e]);
+                                    va[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[q * 8 + 2 * e + 1]);
+                                }
+                            }
+                        }
+                        {
+                            uint32_t u[16];
+                            tmem_ld16(tB + ch * HD + c * 32 + 16, u);
+                            tmem_wait_ld();
+                            if (c == NC - 1) {
+                                // W is in registers: the next head's scores may land on these columns
+                                tc_fence_before();
+                                warp_arrive(&bars[PB_B_FREE], lane);
+                            }
+#pragma unroll
+                            for (int q = 0; q < 2; ++q) {
+                                const uint4 kb = *reinterpret_cast<const uint4*>(
+                                    sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + 2 + q));
+                                const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float2 kf = unpack_bf16x2(w4[e]);
+                                    vb[q * 8 + 2 * e] = kf.x * __uint_as_float(u[q * 8 + 2 * e]);
+                                    vb[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[q * 8 + 2 * e + 1]);
+                                }
                             }
                         }
                         // the query's last head: this warp is done with the Kb rows of the ring
@@ -888,7 +933,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                             warp_arrive(&bars[PB_RING_FREE], lane);
                             ring_arrived = true;
                         }
-                        const float s = warp_transpose_sum(v, lane);
+                        const float s = warp_transpose_sum_2x16(va, vb, lane);
                         red[(warp & 3) * D + ch * HD + c * 32 + lane] = s;
                     }
                     TL(18);
