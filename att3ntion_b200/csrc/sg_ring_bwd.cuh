@@ -148,6 +148,7 @@ __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volati
                                           long long* trace = nullptr) {
     const uint32_t addr = smem_u32(bar);
     const long long t0 = trace ? clock64() : 0;
+#pragma unroll 1
     for (uint32_t it = 0; it < (1u << 18); ++it) {
         uint32_t done;
         asm volatile(
@@ -310,10 +311,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     const uint8_t* mask_b = p.mask ? p.mask + static_cast<size_t>(b) * p.N * p.N : nullptr;
 
     const int n_iter = (q1 - q0) * G;
-    auto row_index = [&](int it) {
-        const int i = q0 + it / G, h = g * G + it % G;
-        return (static_cast<size_t>(b) * p.Hq + h) * p.N + i;
+    // Row of (query i, head hh of this KV group) in the [B,Hq,N] arrays; the successor of (i, hh) in
+    // iteration order is (i, hh + 1) or (i + 1, 0) -- no division by the group size in the loops.
+    auto row_at = [&](int i, int hh) {
+        return (static_cast<size_t>(b) * p.Hq + (g * G + hh)) * p.N + i;
     };
+    auto next_row = [&](int i, int hh) { return hh + 1 < G ? row_at(i, hh + 1) : row_at(i + 1, 0); };
     const float c2 = p.scale * LOG2E;
 
     // Each role first sets its register budget (the CTA starts at 128 per thread: the E warps work in
@@ -389,10 +392,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         // Asynchronous staging, one commit group per call: the Q and dY rows of iteration `it`
         // (threads [0, 2*CH)) and, when next_key >= 0, the four rows of the key that enters the
         // ring with query next_key (threads [0, 4*CH)); both are waited for at the next H_sync.
-        auto h_stage = [&](int it, int next_key) {
+        auto h_stage = [&](int it, size_t row, int next_key) {
             if (it >= 0 && hslot < 2 * CH) {
                 const int which = hslot / CH, c = hslot % CH;
-                const __nv_bfloat16* src = (which == 0 ? p.Q : p.dY) + row_index(it) * D;
+                const __nv_bfloat16* src = (which == 0 ? p.Q : p.dY) + row * D;
                 const uint32_t dst = smem_u32(sStage + ((it & 1) * 2 + which) * D) + c * 16;
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
                              "l"(reinterpret_cast<const uint4*>(src) + c)
@@ -408,14 +411,14 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        h_stage(0, -1);
+        h_stage(0, row_at(q0, 0), -1);
         fence_async_smem();
         cta_start_sync();
         constexpr int GB = L::G_BUFS;
         constexpr int HB = 8;                 // staged chunks in flight per thread (registers: 4 per chunk)
         int n = 0, it = 0, n_query = 0, ring_phase = 0;
         bool ok = true;
-        float l_next = __ldg(p.l + row_index(0));
+        float l_next = __ldg(p.l + row_at(q0, 0));
         for (int i = q0; i < q1 && ok; ++i) {
             const bool prev_work = n > n_query;      // the previous query issued MMAs: Ring_free completes for it
             n_query = n;
@@ -425,7 +428,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
                 const float l_i = l_next;
-                if (it + 1 < n_iter) l_next = __ldg(p.l + row_index(it + 1));
+                if (it + 1 < n_iter) l_next = __ldg(p.l + next_row(i, hh));
                 // the staged rows of this iteration have landed; everyone is past the previous build
                 asm volatile("cp.async.wait_all;" ::: "memory");
                 warp_arrive(&bars[PB_H_SYNC], lane);
@@ -444,7 +447,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                         rVa[4 * c] = v.x; rVa[4 * c + 1] = v.y; rVa[4 * c + 2] = v.z; rVa[4 * c + 3] = v.w;
                     }
                 }
-                if (it + 1 < n_iter) h_stage(it + 1, (hh == 0 && i + 1 < q1) ? i + 1 : -1);
+                if (it + 1 < n_iter) h_stage(it + 1, next_row(i, hh), (hh == 0 && i + 1 < q1) ? i + 1 : -1);
                 const bool work = any_vis && l_i > 0.f;
                 const int qb = n & 1, gb = n % GB;
                 uint8_t* dQp = sQp + qb * L::TILE;
@@ -581,11 +584,28 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         int n = 0, it = 0, n_query = 0, flushes_seen = 0;
         bool ok = true, flush_pending = false, dk_pending = false;
         (void)n_bound;
-        float l_next = __ldg(p.l + row_index(0));
+        float l_next = __ldg(p.l + row_at(q0, 0));
 
         // A-operand column of k-step kk inside a region: the E thread of column half c keeps its
         // BF16 results inside its own 64 score columns, P^T in the first 32 and gA^T in the last 32.
         auto a_col = [](int kk) -> uint32_t { return 64u * (kk >> 2) + 8u * (kk & 3); };
+        // The MMA runs are rolled loops: this warp's instruction stream is on the critical path of every
+        // hand-off, and with each run unrolled its code alone was 40 KB that the instruction cache kept
+        // refetching; the few extra instructions per MMA stay well under the 64 cycles an MMA occupies
+        // the tensor pipe.  K-major operands: k-step kk moves the start address (16-byte units) by
+        // 2 per step inside a 64-element block and RING*8 per block.  A from tensor memory: see a_col.
+        auto run_ss = [&](uint32_t tD, uint64_t dA, uint64_t dB) {
+#pragma unroll 1
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (kk >> 2) * (RING * 128 / 16) + (kk & 3) * 2;
+                umma_ss_pred(tD, dA + off, dB + off, idesc_s, kk > 0, issuer);
+            }
+        };
+        auto run_ts = [&](uint32_t tD, uint32_t tAop, uint64_t dB, uint32_t keep) {
+#pragma unroll 1
+            for (int kk = 0; kk < RING / 16; ++kk)
+                umma_ts_pred(tD, tAop + a_col(kk), dB + kk * (2048 / 16), idesc_acc, keep | (kk > 0), issuer);
+        };
         // Boundary duties.  Acc_done is committed once per boundary, after the last accumulating MMA of
         // the queries before it; the flush of the lane that changes key happens behind it, by a flush
         // warp (observed through Flush_done) or, for quarter 0, right here.
@@ -603,9 +623,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 tc_fence_after();
                 const uint32_t tA = tmem_base + C_R0 + (m & 1) * 128 + 32;
                 const uint32_t qoff = (m & 1) * (L::TILE / 16);
-#pragma unroll
-                for (int kk = 0; kk < RING / 16; ++kk)
-                    umma_ts_pred(tAK, tA + a_col(kk), dQpM + (kk * (2048 / 16) + qoff), idesc_acc, 1, issuer);
+                run_ts(tAK, tA, dQpM + qoff, 1);
                 umma_commit_pred(&bars[PB_D_DONE0 + (m & 1)], issuer);
                 if (acc_commit_pending) commit_acc();
             }
@@ -651,7 +669,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
                 const float l_i = l_next;
-                if (it + 1 < n_iter) l_next = __ldg(p.l + row_index(it + 1));
+                if (it + 1 < n_iter) l_next = __ldg(p.l + next_row(i, hh));
                 if (!any_vis || !(l_i > 0.f)) {
                     // the H warps may be waiting for the kept-back MMAs before they build another tile
                     if (dk_pending) { ok = issue_dk(n - 1); dk_pending = false; }
@@ -669,11 +687,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 TL(1);
                 if (!ok) break;
                 tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {      // X^T = Kb Qp^T
-                    const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                    umma_ss_pred(tA, dKb + off, dQpK + (off + qoff), idesc_s, kk > 0, issuer);
-                }
+                run_ss(tA, dKb, dQpK + qoff);                  // X^T = Kb Qp^T
                 umma_commit_pred(&bars[PB_S_XT], issuer);
                 TL(2);
                 if (!WITH_DQ && dk_pending) {
@@ -688,11 +702,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 if (ok) ok = pipe_wait(&bars[PB_GT_FULL0 + gb], (n / GB) & 1, sFail, TR(1));
                 if (!ok) break;
                 tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {      // dP^T = Vb Gt^T
-                    const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                    umma_ss_pred(tB, dVb + off, dGK + (off + goff), idesc_s, kk > 0, issuer);
-                }
+                run_ss(tB, dVb, dGK + goff);                   // dP^T = Vb Gt^T
                 umma_commit_pred(&bars[PB_S_DP], issuer);
                 TL(4);
                 ok = pipe_wait(&bars[PB_P_FULL], ph, sFail, TR(4));
@@ -700,9 +710,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 TL(5);
                 if (!ok) break;
                 tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < RING / 16; ++kk)    // dVb += P^T Gt
-                    umma_ts_pred(tAV, tA + a_col(kk), dGM + (kk * (2048 / 16) + goff), idesc_acc, 1, issuer);
+                run_ts(tAV, tA, dGM + goff, 1);                // dVb += P^T Gt
                 umma_commit_pred(&bars[PB_V_DONE0 + gb], issuer);
                 TL(6);
                 if (WITH_DQ) {
@@ -711,13 +719,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     if (!ok) break;
                     tc_fence_after();
                     // W first: the E warps wait for it, nobody is in a hurry for dKb
-#pragma unroll
-                    for (int kk = 0; kk < RING / 16; ++kk)    // W = gA^T Ka, over the consumed dP^T columns
-                        umma_ts_pred(tB, tA + 32 + a_col(kk), dKaM + kk * (2048 / 16), idesc_acc, kk > 0, issuer);
+                    run_ts(tB, tA + 32, dKaM, 0);              // W = gA^T Ka, over the consumed dP^T columns
                     umma_commit_pred(&bars[PB_W_FULL], issuer);
-#pragma unroll
-                    for (int kk = 0; kk < RING / 16; ++kk)    // dKb += gA^T Qp
-                        umma_ts_pred(tAK, tA + 32 + a_col(kk), dQpM + (kk * (2048 / 16) + qoff), idesc_acc, 1, issuer);
+                    run_ts(tAK, tA + 32, dQpM + qoff, 1);      // dKb += gA^T Qp
                     umma_commit_pred(&bars[PB_D_DONE0 + qb], issuer);
                     TL(8);
                 } else {
@@ -765,8 +769,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         uint2 pre_dy = make_uint2(0, 0), pre_y = make_uint2(0, 0);
         uint32_t pre_dy2[2] = {0, 0}, pre_y2[2] = {0, 0};
         float pre_m = 0.f, pre_l = 0.f;
-        auto prefetch = [&](int it) {
-            const size_t row = row_index(it);
+        auto prefetch = [&](size_t row) {
             if (D == 128) {
                 pre_dy = __ldg(reinterpret_cast<const uint2*>(p.dY + row * D) + lane);
                 pre_y = __ldg(reinterpret_cast<const uint2*>(p.Y + row * D) + lane);
@@ -777,7 +780,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             pre_m = __ldg(p.m + row);
             pre_l = __ldg(p.l + row);
         };
-        prefetch(0);
+        prefetch(row_at(q0, 0));
         int n = 0, it = 0, n_query = 0;
         bool ok = true;
         for (int i = q0; i < q1 && ok; ++i) {
@@ -792,7 +795,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             const uint32_t cw1 = my_vis ? (ch ? vw[3] : vw[1]) : 0u;
             bool ring_arrived = false;
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
-                const size_t row = row_index(it);
+                const size_t row = row_at(i, hh);
                 // delta = dY . Y and lse (log2 units) of this head from the prefetched slices
                 float delta;
                 if (D == 128) {
@@ -806,7 +809,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
 #pragma unroll
                 for (int o = 16; o >= 1; o >>= 1) delta += __shfl_xor_sync(0xFFFFFFFFu, delta, o);
                 const float m_i = pre_m, l_i = pre_l;
-                if (it + 1 < n_iter) prefetch(it + 1);
+                if (it + 1 < n_iter) prefetch(next_row(i, hh));
                 if (n_vis == 0 || !(l_i > 0.f)) {
                     if (WITH_DQ && tid < D) p.dQ[row * D + tid] = __float2bfloat16(0.f);
                     continue;
