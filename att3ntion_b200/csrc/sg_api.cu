@@ -78,7 +78,7 @@ extern "C" int att3_sg_query_blocks(int B, int Hq, int Hkv, int N, int q_begin, 
 extern "C" int att3_debug_trace(long long* out32) {
     cudaDeviceSynchronize();
     if (cudaMemcpyFromSymbol(out32, g_sg_trace, sizeof(long long) * 32) != cudaSuccess) return ATT3_ERR_CUDA;
-    long long z[32] = {0};
+    static long long z[32 + 384 + 640] = {0};
     cudaMemcpyToSymbol(g_sg_trace, z, sizeof(z));
     return ATT3_OK;
 }
@@ -129,7 +129,7 @@ static int launch_ring_fwd(const sgring::FwdParams& p, int nblk, cudaStream_t st
     }
     dim3 grid(nblk, p.Hkv, p.B);
     att3::TimedLaunch timed(att3::K_SG_FWD, stream);
-    sgring::sg_ring_fwd_kernel<D><<<grid, sgring::NTHREADS, L::ALLOC, stream>>>(p);
+    sgring::sg_ring_fwd_kernel<D><<<grid, sgring::PIPE_THREADS, L::ALLOC, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_forward: launch");
     att3::count_launch(0);
@@ -165,7 +165,8 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status_ptr();
-    const int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 2, 16, &p.block_len);
+    p.trace = trace_ptr();
+    const int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, 16, &p.block_len);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return D == 64 ? launch_ring_fwd<64>(p, nblk, st) : launch_ring_fwd<128>(p, nblk, st);
 }

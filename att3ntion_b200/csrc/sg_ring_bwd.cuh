@@ -64,7 +64,7 @@
 // error ends the kernel with a status code instead of hanging it.
 #pragma once
 
-#include "sg_ring_fwd.cuh"
+#include "sg_ring_common.cuh"
 
 namespace sgring {
 
@@ -91,29 +91,10 @@ struct BwdParams {
     int trace_mode;                  // 1: summed wait cycles per hand-off, 2: time stamps of six steady-state heads
 };
 
-constexpr int PIPE_E_THREADS = 256;
-constexpr int PIPE_H_THREADS = 128;
-// Four full warpgroups: E (2), H (1) and one whose first warp issues the MMAs while the
-// other three only hand their registers to the working roles (setmaxnreg below).
-constexpr int PIPE_THREADS = PIPE_E_THREADS + PIPE_H_THREADS + 128;
-
-template <int N>
-__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N>
-__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-
 enum PipeBar {
     PB_QP_FULL0 = 0, PB_QP_FULL1, PB_GT_FULL0, PB_GT_FULL1, PB_S_XT, PB_S_DP, PB_P_FULL, PB_G_FULL, PB_D_DONE0, PB_D_DONE1, PB_V_DONE0, PB_V_DONE1,
     PB_W_FULL, PB_B_FREE, PB_E_SYNC2, PB_H_SYNC, PB_RING_FREE, PB_FLUSH_DONE, PB_ACC_DONE, PB_COUNT
 };
-
-// One arrival per warp: the lanes' earlier writes are ordered before lane 0's releasing
-// arrive by the warp barrier.  256 per-thread arrivals on one barrier word serialise into
-// more than a thousand cycles per hand-off; eight do not.
-__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar);
-}
 
 template <int D, bool WITH_DQ>
 struct PipeSmem {
@@ -135,78 +116,6 @@ struct PipeSmem {
     static constexpr int BYTES = OFF_MISC + 16;
     static constexpr int ALLOC = BYTES + 1024;
 };
-
-// Bounded wait that also leaves when another thread has raised the CTA's failure flag.
-// Bounded wait on an mbarrier phase.  try_wait parks the thread in hardware until the phase
-// completes or a system time limit passes.  Measured alternatives on this part, same kernel:
-// all threads spinning on test_wait pulled the SM clock from 1.9 to 1.3 GHz under the power
-// cap (2x the run time); one polling lane per warp with __nanosleep(20) between polls was
-// 2.3x slower still (the sleep is far coarser than its argument).  The iteration count bounds
-// the total wait; the loop also leaves when another thread has raised the CTA's failure flag.
-constexpr uint32_t PIPE_WAIT_HINT_NS = 20000;   // suspend-time hint: a parked thread issues nothing until the phase flips
-__device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volatile int* fail,
-                                          long long* trace = nullptr) {
-    const uint32_t addr = smem_u32(bar);
-    const long long t0 = trace ? clock64() : 0;
-#pragma unroll 1
-    for (uint32_t it = 0; it < (1u << 18); ++it) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t"
-            ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t"
-            "}\n"
-            : "=r"(done)
-            : "r"(addr), "r"(parity), "r"(PIPE_WAIT_HINT_NS)
-            : "memory");
-        if (done) {
-            if (trace) *trace += clock64() - t0;
-            return true;
-        }
-        if ((it & 15u) == 15u && *fail) return false;
-    }
-    *fail = 1;
-    return false;
-}
-
-// Visibility of the 128 ring slots for query i as four ballot words; every warp
-// computes the same words (lane L looks at slots L, 32+L, 64+L, 96+L).
-__device__ __forceinline__ void ring_visibility(const uint8_t* mask_row, int i, int window, int lane, uint32_t (&vw)[4]) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const int key = ring_key(i, q * 32 + lane);
-        bool v = key >= 0 && key > i - window;
-        if (v && mask_row) v = mask_row[key] != 0;
-        vw[q] = __ballot_sync(0xFFFFFFFFu, v);
-    }
-}
-
-// Sum over the 32 lanes of a warp of 32 per-lane values given as two halves (va: values 0-15,
-// vb: values 16-31); lane L ends up with the total of value L.  Same exchange network as
-// warp_transpose_sum, with the first stage folding the two halves.
-__device__ __forceinline__ float warp_transpose_sum_2x16(float (&va)[16], float (&vb)[16], int lane) {
-    {
-        const bool up = (lane & 16) != 0;
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-            const float send = up ? va[k] : vb[k];
-            const float keep = up ? vb[k] : va[k];
-            va[k] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, 16);
-        }
-    }
-#pragma unroll
-    for (int o = 8; o >= 1; o >>= 1) {
-        const bool up = (lane & o) != 0;
-#pragma unroll
-        for (int k = 0; k < o; ++k) {
-            const float send = up ? va[k] : va[k + o];
-            const float keep = up ? va[k + o] : va[k];
-            va[k] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, o);
-        }
-    }
-    return va[0];
-}
 
 // Copies a warp's accumulator lanes (only_lane < 0: all 32) to the FP32 partial planes and, on
 // request, zeroes them.  Lane k of the accumulators belongs to the key in ring slot k; `tl` is the
@@ -595,14 +504,14 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         // the tensor pipe.  K-major operands: k-step kk moves the start address (16-byte units) by
         // 2 per step inside a 64-element block and RING*8 per block.  A from tensor memory: see a_col.
         auto run_ss = [&](uint32_t tD, uint64_t dA, uint64_t dB) {
-#pragma unroll 1
+#pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
                 const uint32_t off = (kk >> 2) * (RING * 128 / 16) + (kk & 3) * 2;
                 umma_ss_pred(tD, dA + off, dB + off, idesc_s, kk > 0, issuer);
             }
         };
         auto run_ts = [&](uint32_t tD, uint32_t tAop, uint64_t dB, uint32_t keep) {
-#pragma unroll 1
+#pragma unroll
             for (int kk = 0; kk < RING / 16; ++kk)
                 umma_ts_pred(tD, tAop + a_col(kk), dB + kk * (2048 / 16), idesc_acc, keep | (kk > 0), issuer);
         };

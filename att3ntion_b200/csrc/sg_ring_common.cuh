@@ -1,0 +1,130 @@
+// Pieces shared by the windowed single-gather kernels for sm_100a: the ring convention, the
+// role-specialised CTA skeleton (thread counts, register budgets), bounded mbarrier waits and the
+// warp-level reductions.
+#pragma once
+
+#include "sm100_ptx.cuh"
+
+namespace sgring {
+
+using namespace sm100;
+
+constexpr int RING = 128;          // keys resident per CTA = maximum window
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float NEG_INF_F = -1e30f;   // statistics value of a query with no visible pair
+
+// Key index held by ring slot `slot` while query i is processed: the unique
+// index congruent to slot (mod 128) in (i - 128, i].
+__device__ __forceinline__ int ring_key(int i, int slot) { return i - ((i - slot) & (RING - 1)); }
+
+// Sum over the 32 lanes of a warp of 32 per-lane values; lane L ends up with the
+// total of element L in v[0].  31 shuffles.
+__device__ __forceinline__ float warp_transpose_sum(float (&v)[32], int lane) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int k = 0; k < o; ++k) {
+            const float send = up ? v[k] : v[k + o];
+            const float keep = up ? v[k + o] : v[k];
+            v[k] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, o);
+        }
+    }
+    return v[0];
+}
+
+constexpr int PIPE_E_THREADS = 256;
+constexpr int PIPE_H_THREADS = 128;
+// Four full warpgroups: E (2), H (1) and one whose first warp issues the MMAs while the
+// other three only hand their registers to the working roles (setmaxnreg below).
+constexpr int PIPE_THREADS = PIPE_E_THREADS + PIPE_H_THREADS + 128;
+
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// One arrival per warp: the lanes' earlier writes are ordered before lane 0's releasing
+// arrive by the warp barrier.  256 per-thread arrivals on one barrier word serialise into
+// more than a thousand cycles per hand-off; eight do not.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+}
+
+// Bounded wait that also leaves when another thread has raised the CTA's failure flag.
+// Bounded wait on an mbarrier phase.  try_wait parks the thread in hardware until the phase
+// completes or a system time limit passes.  Measured alternatives on this part, same kernel:
+// all threads spinning on test_wait pulled the SM clock from 1.9 to 1.3 GHz under the power
+// cap (2x the run time); one polling lane per warp with __nanosleep(20) between polls was
+// 2.3x slower still (the sleep is far coarser than its argument).  The iteration count bounds
+// the total wait; the loop also leaves when another thread has raised the CTA's failure flag.
+constexpr uint32_t PIPE_WAIT_HINT_NS = 20000;   // suspend-time hint: a parked thread issues nothing until the phase flips
+__device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volatile int* fail,
+                                          long long* trace = nullptr, int code = 1) {
+    const uint32_t addr = smem_u32(bar);
+    const long long t0 = trace ? clock64() : 0;
+#pragma unroll 1
+    for (uint32_t it = 0; it < (1u << 18); ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity), "r"(PIPE_WAIT_HINT_NS)
+            : "memory");
+        if (done) {
+            if (trace) {
+                *trace += clock64() - t0;
+                trace[64] += it + 1;       // polls of this hand-off, next to its cycles
+            }
+            return true;
+        }
+        if ((it & 15u) == 15u && *fail) return false;
+    }
+    *fail = code;      // which wait gave up (reported through the status word)
+    return false;
+}
+
+// Visibility of the 128 ring slots for query i as four ballot words; every warp
+// computes the same words (lane L looks at slots L, 32+L, 64+L, 96+L).
+__device__ __forceinline__ void ring_visibility(const uint8_t* mask_row, int i, int window, int lane, uint32_t (&vw)[4]) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int key = ring_key(i, q * 32 + lane);
+        bool v = key >= 0 && key > i - window;
+        if (v && mask_row) v = mask_row[key] != 0;
+        vw[q] = __ballot_sync(0xFFFFFFFFu, v);
+    }
+}
+
+// Sum over the 32 lanes of a warp of 32 per-lane values given as two halves (va: values 0-15,
+// vb: values 16-31); lane L ends up with the total of value L.  Same exchange network as
+// warp_transpose_sum, with the first stage folding the two halves.
+__device__ __forceinline__ float warp_transpose_sum_2x16(float (&va)[16], float (&vb)[16], int lane) {
+    {
+        const bool up = (lane & 16) != 0;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const float send = up ? va[k] : vb[k];
+            const float keep = up ? vb[k] : va[k];
+            va[k] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, 16);
+        }
+    }
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int k = 0; k < o; ++k) {
+            const float send = up ? va[k] : va[k + o];
+            const float keep = up ? va[k + o] : va[k];
+            va[k] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, o);
+        }
+    }
+    return va[0];
+}
+
+}  // namespace sgring

@@ -1,4 +1,4 @@
-// Windowed single-gather forward for sm_100a ("ring" schedule).
+// Windowed single-gather forward for sm_100a ("ring" schedule, role-specialised and pipelined).
 //
 //   Y[i] = sum_{j,k} softmax_{(j,k)}( scale * sum_d Q_i[d] R_j[d] S_k[d] ) Vr[j] o Vs[k]
 //
@@ -14,27 +14,44 @@
 //    sliding the window by one query rewrites exactly one row and the MMA
 //    operands never move.  Contractions over the ring are order independent,
 //    which is what makes the rotated order legal.
-//  * Per (query, head):  X = (Q_i o R) S^T  is one 128x128xD tcgen05.mma with
-//    the Hadamard tile built in shared memory; thread j owns row j of X in
-//    tensor memory, takes its row maximum and writes P = exp2(.) back to tensor
-//    memory as BF16 over the consumed score columns; U = P Vs is the second MMA
-//    with A read from tensor memory and the Vs ring as an MN-major B operand;
-//    the epilogue collapses  sum_j w_j Vr_j o U_j  with warp shuffles, where
-//    w_j = exp(m_j - M) merges the per-row softmaxes into the joint one.
+//  * Per (query, head):  X = (Q_i o R) S^T  is one 128x128xD product with the
+//    Hadamard tile built in shared memory; the thread pair of row j takes the
+//    row maximum and writes P = exp2(.) back to tensor memory as BF16 over score
+//    columns it has consumed itself; U = P Vs is the second product with A read
+//    from tensor memory and the Vs ring as an MN-major B operand; the epilogue
+//    collapses  sum_j w_j Vr_j o U_j  with warp shuffles, where w_j = exp(m_j - M)
+//    merges the per-row softmaxes into the joint one.
 //  * The score scale is folded into the exp2 argument, so the only BF16
 //    rounding before the score MMA is the product Q_i[d] * R_j[d] itself.
+//
+// Schedule.  Tensor memory holds two (X, U) pairs, so two heads are in flight:
+//
+//   H warps (4)  build Qp = Q_i o R (one ring row per thread, two buffers), prefetch the rows of
+//                the key that enters the window next and replace the S ring row.
+//   MMA warp (1) issues X(n) = Qp(n) S^T, then U(n-1) = P(n-1) Vs, so the score product of the
+//                next head runs while the E warps still work on this one.
+//   E warps (8)  thread (row j, column half c): row maximum (exchanged with the other half through
+//                a 64-thread named barrier), P, row sum; then, one head behind, the epilogue of
+//                U(n-1).  They also replace the Vs ring row, behind the last U product that reads it.
+//
+// Hand-offs (mbarriers, one per buffer b = n & 1, phase = (n >> 1) & 1):
+//   Qp_full[b]  H -> MMA    tile written (and the S ring row current)
+//   X_done[b]   MMA -> E,H  scores in tensor memory; Qp[b] and the S ring read
+//   P_full[b]   E -> MMA    P stored (and the Vs ring row current)
+//   U_done[b]   MMA -> E    U in tensor memory; P(n) and the Vs ring read
+//   U_free[b]   E -> MMA    U(n) taken out of tensor memory
+//   Next_ready  H -> E      per query boundary: the prefetched rows of the entering key have landed
+// The E warps also meet each other on mbarriers rather than named barriers, so that these waits are
+// bounded like the rest, and both meetings are split so that nobody stands waiting: the two warps of a
+// lane quarter exchange their half-row maxima before the epilogue of the previous head and pick the
+// partner's value up after it; the output reduction of head m is finished at the start of the
+// epilogue of head m + 1.
+// Every wait is bounded and watches a CTA-wide failure flag (status code instead of a hang).
 #pragma once
 
-#include "sm100_ptx.cuh"
+#include "sg_ring_common.cuh"
 
 namespace sgring {
-
-using namespace sm100;
-
-constexpr int RING = 128;          // keys resident per CTA = maximum window
-constexpr int NTHREADS = 128;
-constexpr float LOG2E = 1.4426950408889634f;
-constexpr float NEG_INF_F = -1e30f;   // statistics value of a query with no visible pair
 
 struct FwdParams {
     const __nv_bfloat16* Q;        // [B,Hq,N,D]
@@ -49,49 +66,47 @@ struct FwdParams {
     int B, Hq, Hkv, N, window, q_begin, block_len;
     float scale;
     int* status;                   // device status word (bounded-wait failures)
+    long long* trace;              // diagnostic progress words (null: off)
 };
+
+enum FwdBar {
+    FB_QP_FULL0 = 0, FB_QP_FULL1, FB_X_DONE0, FB_X_DONE1, FB_P_FULL0, FB_P_FULL1, FB_U_DONE0, FB_U_DONE1,
+    FB_U_FREE0, FB_U_FREE1, FB_H_SYNC, FB_PAIR0, FB_PAIR1, FB_PAIR2, FB_PAIR3,
+    FB_E_SYNC, FB_NEXT_READY0, FB_COUNT = FB_NEXT_READY0 + 8
+};
+
+// The H warps can be up to five query boundaries ahead of the E warps' ring update (two tile buffers,
+// two score buffers and the product kept back), so the prefetched rows and their ready flags are
+// kept eight deep: neither a buffer nor a barrier phase comes round again before it is consumed.
+constexpr int NEXT_BUFS = 8;
 
 template <int D>
 struct FwdSmem {
     static constexpr int TILE = RING * D * 2;           // bytes of one [128][D] BF16 tile
     static constexpr int OFF_S = 0;
     static constexpr int OFF_VS = TILE;
-    static constexpr int OFF_QP = 2 * TILE;
-    static constexpr int OFF_QSTAGE = 3 * TILE;         // 2 x D bf16
-    static constexpr int OFF_RED = OFF_QSTAGE + 2 * D * 2;   // 4 x (D+1) floats
-    static constexpr int OFF_MPART = OFF_RED + 4 * (D + 4) * 4;
-    static constexpr int OFF_VIS = OFF_MPART + 16;      // 4 words
-    static constexpr int OFF_MISC = OFF_VIS + 16;       // mbarrier (8) + tmem slot (4) + fail (4)
+    static constexpr int OFF_QP = 2 * TILE;             // 2 buffers
+    static constexpr int OFF_QSTAGE = 4 * TILE;         // 2 x D bf16
+    static constexpr int NEXT_BYTES = 4 * D * 2;        // rows R, Vr, S, Vs of an entering key
+    static constexpr int OFF_NEXT = OFF_QSTAGE + 2 * D * 2;          // NEXT_BUFS buffers (query index mod NEXT_BUFS)
+    static constexpr int OFF_RED = OFF_NEXT + NEXT_BUFS * NEXT_BYTES;        // 2 x 4 x (D + 4) floats: y partials, l partials
+    static constexpr int OFF_MHALF = OFF_RED + 2 * 4 * (D + 4) * 4;  // 2 parities x 2 halves x 128 floats: half-row maxima
+    static constexpr int OFF_MPART = OFF_MHALF + 2 * 2 * RING * 4;   // 2 x 8 floats: warp maxima, per head parity
+    static constexpr int OFF_BARS = OFF_MPART + 2 * 8 * 4;
+    static constexpr int OFF_MISC = OFF_BARS + FB_COUNT * 8;         // tmem slot (4) + fail flag (4)
     static constexpr int BYTES = OFF_MISC + 16;
     static constexpr int ALLOC = BYTES + 1024;          // slack for manual 1024-byte alignment
 };
 
-// Key index held by ring slot `slot` while query i is processed: the unique
-// index congruent to slot (mod 128) in (i - 128, i].
-__device__ __forceinline__ int ring_key(int i, int slot) { return i - ((i - slot) & (RING - 1)); }
-
-// Sum over the 32 lanes of a warp of 32 per-lane values; lane L ends up with the
-// total of element L in v[0].  31 shuffles.
-__device__ __forceinline__ float warp_transpose_sum(float (&v)[32], int lane) {
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) {
-        const bool up = (lane & o) != 0;
-#pragma unroll
-        for (int k = 0; k < o; ++k) {
-            const float send = up ? v[k] : v[k + o];
-            const float keep = up ? v[k + o] : v[k];
-            v[k] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, o);
-        }
-    }
-    return v[0];
-}
-
 template <int D>
-__global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParams p) {
+__global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdParams p) {
     using L = FwdSmem<D>;
     constexpr int CH = D / 8;            // 16-byte chunks per row
     constexpr int DW = D / 2;            // packed bf16x2 words per row
-    constexpr uint32_t TMEM_COLS = 256;  // X/P [0,128), U [128,128+D)
+    constexpr int HD = D / 2;            // output columns per E thread
+    constexpr uint32_t TMEM_COLS = 512;  // buffer b: X/P at b*256, U at b*256 + 128
+    constexpr int E_REGS = 120, H_REGS = 152, M_REGS = 96;
+    static_assert(8 * E_REGS + 4 * H_REGS + 4 * M_REGS <= 2048, "register file: 64K registers / 32 lanes");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -99,27 +114,39 @@ __global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParam
     uint8_t* sVs = smem + L::OFF_VS;
     uint8_t* sQp = smem + L::OFF_QP;
     __nv_bfloat16* sQst = reinterpret_cast<__nv_bfloat16*>(smem + L::OFF_QSTAGE);
+    uint8_t* sNext = smem + L::OFF_NEXT;
     float* sRed = reinterpret_cast<float*>(smem + L::OFF_RED);
+    float* sMhalf = reinterpret_cast<float*>(smem + L::OFF_MHALF);
     float* sMpart = reinterpret_cast<float*>(smem + L::OFF_MPART);
-    uint32_t* sVis = reinterpret_cast<uint32_t*>(smem + L::OFF_VIS);
-    uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::OFF_MISC);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::OFF_MISC + 8);
-    volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 12);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BARS);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::OFF_MISC);
+    volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 4);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t issuer = elect_one();     // one lane per warp; warp 0 predicates its MMAs on it
     const int b = blockIdx.z, g = blockIdx.y;
     const int G = p.Hq / p.Hkv;
     const int q0 = p.q_begin + blockIdx.x * p.block_len;
     const int q1 = min(q0 + p.block_len, p.N);
     if (q0 >= q1) return;
+    const bool is_h = warp >= 8 && warp < 12, is_mma = warp == 12;
 
-    if (warp == 0) {
+    if (is_mma) {
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
     }
     if (tid == 0) {
-        mbar_init(bar, 1);
+        // Arrival counts are in warps: one elected lane arrives for its warp (warp_arrive).
+        for (int x = 0; x < 2; ++x) {
+            mbar_init(&bars[FB_QP_FULL0 + x], 4);
+            mbar_init(&bars[FB_X_DONE0 + x], 1);
+            mbar_init(&bars[FB_P_FULL0 + x], 8);
+            mbar_init(&bars[FB_U_DONE0 + x], 1);
+            mbar_init(&bars[FB_U_FREE0 + x], 8);
+        }
+        mbar_init(&bars[FB_H_SYNC], 4);
+        for (int x = 0; x < NEXT_BUFS; ++x) mbar_init(&bars[FB_NEXT_READY0 + x], 4);
+        for (int x = 0; x < 4; ++x) mbar_init(&bars[FB_PAIR0 + x], 2);
+        mbar_init(&bars[FB_E_SYNC], 8);
         fence_mbar_init();
         *sFail = 0;
     }
@@ -129,245 +156,457 @@ __global__ void __launch_bounds__(NTHREADS, 2) sg_ring_fwd_kernel(const FwdParam
     const __nv_bfloat16* gS = p.S + kv_base * D;
     const __nv_bfloat16* gVr = p.Vr + kv_base * D;
     const __nv_bfloat16* gVs = p.Vs + kv_base * D;
-
-    // Ring slot `tid`: R and Vr rows in registers, S and Vs rows in shared memory.
-    uint32_t rR[DW], rVr[DW];
-    auto load_slot = [&](int key) {
-        if (key >= 0) {
-            const uint4* r4 = reinterpret_cast<const uint4*>(gR + static_cast<size_t>(key) * D);
-            const uint4* vr4 = reinterpret_cast<const uint4*>(gVr + static_cast<size_t>(key) * D);
-            const uint4* s4 = reinterpret_cast<const uint4*>(gS + static_cast<size_t>(key) * D);
-            const uint4* vs4 = reinterpret_cast<const uint4*>(gVs + static_cast<size_t>(key) * D);
-#pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                const uint4 a = __ldg(r4 + c), v = __ldg(vr4 + c);
-                rR[4 * c] = a.x; rR[4 * c + 1] = a.y; rR[4 * c + 2] = a.z; rR[4 * c + 3] = a.w;
-                rVr[4 * c] = v.x; rVr[4 * c + 1] = v.y; rVr[4 * c + 2] = v.z; rVr[4 * c + 3] = v.w;
-                *reinterpret_cast<uint4*>(sS + sw128_offset<RING>(tid, c)) = __ldg(s4 + c);
-                *reinterpret_cast<uint4*>(sVs + sw128_offset<RING>(tid, c)) = __ldg(vs4 + c);
-            }
-        } else {
-            const uint4 z = make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                rR[4 * c] = rR[4 * c + 1] = rR[4 * c + 2] = rR[4 * c + 3] = 0;
-                rVr[4 * c] = rVr[4 * c + 1] = rVr[4 * c + 2] = rVr[4 * c + 3] = 0;
-                *reinterpret_cast<uint4*>(sS + sw128_offset<RING>(tid, c)) = z;
-                *reinterpret_cast<uint4*>(sVs + sw128_offset<RING>(tid, c)) = z;
-            }
-        }
-    };
-    load_slot(ring_key(q0, tid));
-
-    // Q row of the first (query, head) into stage 0.
-    auto q_row = [&](int it) {
-        const int i = q0 + it / G, h = g * G + it % G;
-        return p.Q + ((static_cast<size_t>(b) * p.Hq + h) * p.N + i) * D;
-    };
+    const uint8_t* mask_b = p.mask ? p.mask + static_cast<size_t>(b) * p.N * p.N : nullptr;
     const int n_iter = (q1 - q0) * G;
-    if (tid < CH) reinterpret_cast<uint4*>(sQst)[tid] = __ldg(reinterpret_cast<const uint4*>(q_row(0)) + tid);
-
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t tX = tmem_base + lane_field;          // scores, later P (BF16 pairs) in columns [0,64)
-    const uint32_t tU = tmem_base + lane_field + 128;    // P.Vs accumulator
-
-    const uint32_t idesc_x = make_idesc_bf16(RING, RING, 0, 0);
-    const uint32_t idesc_u = make_idesc_bf16(RING, D, 0, 1);
-    // descriptor bases, built once; a k-step adds a constant to the start-address field
-    const uint64_t dQp = make_smem_desc(smem_u32(sQp), 16, 1024, SWIZZLE_128B);           // A, K-major
-    const uint64_t dS = make_smem_desc(smem_u32(sS), 16, 1024, SWIZZLE_128B);             // B, K-major
-    const uint64_t dVsM = make_smem_desc(smem_u32(sVs), RING * 128, 1024, SWIZZLE_128B);  // B, MN-major
+    auto row_at = [&](int i, int hh) {
+        return (static_cast<size_t>(b) * p.Hq + (g * G + hh)) * p.N + i;
+    };
+    auto next_row = [&](int i, int hh) { return hh + 1 < G ? row_at(i, hh + 1) : row_at(i + 1, 0); };
     const float c2 = p.scale * LOG2E;
-    uint32_t phase = 0;
-    bool failed = false;
+#ifdef ATT3_PIPE_TRACE
+#define PROG(site) do { if (p.trace && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) \
+        p.trace[warp] = static_cast<long long>(n) * 1000 + (site); } while (0)
+#define PROGV(v, site) do { if (p.trace && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) \
+        p.trace[warp] = static_cast<long long>(v) * 1000 + (site); } while (0)
+#else
+#define PROG(site) do { } while (0)
+#define PROGV(v, site) do { } while (0)
+#endif
 
-    int it = 0;
-    for (int i = q0; i < q1 && !failed; ++i) {
-        // --- slide the window: slot (i mod 128) now holds key i ---------------
-        if (i > q0 && tid == (i & (RING - 1))) load_slot(i);
-        bool my_vis;
-        {
-            const int key = ring_key(i, tid);
-            my_vis = key >= 0 && key > i - p.window;
-            if (my_vis && p.mask) my_vis = p.mask[(static_cast<size_t>(b) * p.N + i) * p.N + key] != 0;
-            const uint32_t w = __ballot_sync(0xFFFFFFFFu, my_vis);
-            if (lane == 0) sVis[warp] = w;
-        }
+    uint32_t tmem_base = 0;
+    auto cta_start_sync = [&]() {
+        tc_fence_before();
         __syncthreads();
-        const uint32_t vw0 = sVis[0], vw1 = sVis[1], vw2 = sVis[2], vw3 = sVis[3];
-        const bool any_vis = (vw0 | vw1 | vw2 | vw3) != 0;
-        const bool all_vis = (vw0 & vw1 & vw2 & vw3) == 0xFFFFFFFFu;
+        tc_fence_after();
+        tmem_base = *tmem_slot;
+    };
 
-        for (int hh = 0; hh < G && !failed; ++hh, ++it) {
-            const int h = g * G + hh;
-            const size_t row = (static_cast<size_t>(b) * p.Hq + h) * p.N + i;
-            // prefetch the next (query, head)'s Q row into the other stage
-            if (tid < CH && it + 1 < n_iter) {
-                const uint32_t dst = smem_u32(sQst + ((it + 1) & 1) * D) + tid * 16;
-                const void* src = reinterpret_cast<const uint4*>(q_row(it + 1)) + tid;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-                asm volatile("cp.async.commit_group;" ::: "memory");
+    if (is_h) {
+        // ================================================================== H warps
+        reg_inc<H_REGS>();
+        const int hslot = tid - PIPE_E_THREADS;          // ring slot of this thread
+        uint32_t rR[DW];
+        {   // initial fill: R row in registers, S and Vs rows in the operand tiles
+            const int key = ring_key(q0, hslot);
+            if (key >= 0) {
+                const uint4* r4 = reinterpret_cast<const uint4*>(gR + static_cast<size_t>(key) * D);
+                const uint4* s4 = reinterpret_cast<const uint4*>(gS + static_cast<size_t>(key) * D);
+                const uint4* vs4 = reinterpret_cast<const uint4*>(gVs + static_cast<size_t>(key) * D);
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                    const uint4 a = __ldg(r4 + c);
+                    rR[4 * c] = a.x; rR[4 * c + 1] = a.y; rR[4 * c + 2] = a.z; rR[4 * c + 3] = a.w;
+                    *reinterpret_cast<uint4*>(sS + sw128_offset<RING>(hslot, c)) = __ldg(s4 + c);
+                    *reinterpret_cast<uint4*>(sVs + sw128_offset<RING>(hslot, c)) = __ldg(vs4 + c);
+                }
+            } else {
+                const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                    rR[4 * c] = rR[4 * c + 1] = rR[4 * c + 2] = rR[4 * c + 3] = 0;
+                    *reinterpret_cast<uint4*>(sS + sw128_offset<RING>(hslot, c)) = z;
+                    *reinterpret_cast<uint4*>(sVs + sw128_offset<RING>(hslot, c)) = z;
+                }
             }
-            if (!any_vis) {
-                // No visible pair: Y = 0, m = NEG_INF, l = 0 (cuda/common.cuh:24).
-                if (tid < D) p.Y[row * D + tid] = __float2bfloat16(0.f);
-                if (tid == 0) { p.m[row] = NEG_INF_F; p.l[row] = 0.f; }
-                if (tid < CH) asm volatile("cp.async.wait_all;" ::: "memory");
-                __syncthreads();
-                continue;
+        }
+        // Asynchronous staging, one commit group per call: the Q row of iteration `it` (threads [0, CH))
+        // and, when next_key >= 0, the four rows of the key that enters the ring with query next_key.
+        auto h_stage = [&](int it, size_t row, int next_key) {
+            if (it >= 0 && hslot < CH) {
+                const uint32_t dst = smem_u32(sQst + (it & 1) * D) + hslot * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
+                             "l"(reinterpret_cast<const uint4*>(p.Q + row * D) + hslot)
+                             : "memory");
             }
-
-            // --- Hadamard tile: Qp[j][d] = bf16(Q_i[d] * R_j[d]) ------------------
-            {
-                const uint4* q4 = reinterpret_cast<const uint4*>(sQst + (it & 1) * D);
-                // Loads of the staged row in batches of eight chunks ahead of the tile stores: the
-                // compiler cannot rule out aliasing between the two shared-memory areas and would
-                // otherwise serialise load -> multiply -> store per chunk.
+            if (next_key >= 0 && hslot < 4 * CH) {
+                const int which = hslot / CH, c = hslot % CH;
+                const __nv_bfloat16* base = which == 0 ? gR : which == 1 ? gVr : which == 2 ? gS : gVs;
+                const uint32_t dst = smem_u32(sNext + (next_key & (NEXT_BUFS - 1)) * L::NEXT_BYTES + which * (D * 2)) + c * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
+                             "l"(reinterpret_cast<const uint4*>(base + static_cast<size_t>(next_key) * D) + c)
+                             : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        h_stage(0, row_at(q0, 0), -1);
+        fence_async_smem();
+        cta_start_sync();
+        constexpr int HB = 8;                 // staged chunks in flight per thread
+        int n = 0, it = 0;
+        bool ok = true;
+        for (int i = q0; i < q1 && ok; ++i) {
+            const int s = i & (RING - 1);
+            uint32_t vw[4];
+            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
+            const bool work = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
+            for (int hh = 0; hh < G && ok; ++hh, ++it) {
+                // the staged rows of this iteration have landed; everyone is past the previous build
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                warp_arrive(&bars[FB_H_SYNC], lane);
+                ok = pipe_wait(&bars[FB_H_SYNC], it & 1, sFail, nullptr, 10);
+                if (!ok) break;
+                const bool boundary = hh == 0 && i > q0;      // key i replaces key i-128 in slot s
+                const uint8_t* nx = sNext + (i & (NEXT_BUFS - 1)) * L::NEXT_BYTES;
+                if (boundary) warp_arrive(&bars[FB_NEXT_READY0 + ((i - q0 - 1) & (NEXT_BUFS - 1))], lane);
+                if (boundary && hslot == s) {
+                    const uint4* r4 = reinterpret_cast<const uint4*>(nx);
 #pragma unroll
-                for (int c0 = 0; c0 < CH; c0 += 8) {
-                    uint4 q[8];
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) q[c] = q4[c0 + c];
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        uint4 o;
-                        o.x = mul_bf16x2(q[c].x, rR[4 * (c0 + c)]);
-                        o.y = mul_bf16x2(q[c].y, rR[4 * (c0 + c) + 1]);
-                        o.z = mul_bf16x2(q[c].z, rR[4 * (c0 + c) + 2]);
-                        o.w = mul_bf16x2(q[c].w, rR[4 * (c0 + c) + 3]);
-                        *reinterpret_cast<uint4*>(sQp + sw128_offset<RING>(tid, c0 + c)) = o;
+                    for (int c = 0; c < CH; ++c) {
+                        const uint4 a = r4[c];
+                        rR[4 * c] = a.x; rR[4 * c + 1] = a.y; rR[4 * c + 2] = a.z; rR[4 * c + 3] = a.w;
                     }
+                }
+                if (it + 1 < n_iter) h_stage(it + 1, next_row(i, hh), (hh == 0 && i + 1 < q1) ? i + 1 : -1);
+                const int qb = n & 1;
+                if (work) {
+                    // Qp[n&1] was last read by the score MMAs of head n-2
+                    PROG(11);
+                    if (n >= 2) ok = pipe_wait(&bars[FB_X_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, nullptr, 11);
+                    if (!ok) break;
+                    uint8_t* dQp = sQp + qb * L::TILE;
+                    const uint4* q4 = reinterpret_cast<const uint4*>(sQst + (it & 1) * D);
+                    // The staged row is read in batches ahead of the stores: the compiler cannot tell that the
+                    // tile stores do not alias the staging area and would otherwise serialise per chunk.
+#pragma unroll
+                    for (int c0 = 0; c0 < CH; c0 += HB) {
+                        uint4 q[HB];
+#pragma unroll
+                        for (int c = 0; c < HB; ++c) q[c] = q4[c0 + c];
+#pragma unroll
+                        for (int c = 0; c < HB; ++c) {
+                            uint4 o;
+                            o.x = mul_bf16x2(q[c].x, rR[4 * (c0 + c)]);
+                            o.y = mul_bf16x2(q[c].y, rR[4 * (c0 + c) + 1]);
+                            o.z = mul_bf16x2(q[c].z, rR[4 * (c0 + c) + 2]);
+                            o.w = mul_bf16x2(q[c].w, rR[4 * (c0 + c) + 3]);
+                            *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c0 + c)) = o;
+                        }
+                    }
+                }
+                if (boundary) {
+                    // The S row of slot s changes key once every score MMA issued so far is complete (the
+                    // last one is head n-1; this thread waits for the same phase again when it reuses
+                    // that tile buffer).
+                    PROG(12);
+                    if (n >= 1) ok = pipe_wait(&bars[FB_X_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, nullptr, 12);
+                    if (!ok) break;
+                    if (hslot < CH)
+                        *reinterpret_cast<uint4*>(sS + sw128_offset<RING>(s, hslot)) =
+                            *reinterpret_cast<const uint4*>(nx + 2 * (D * 2) + hslot * 16);
+                }
+                if (work || boundary) fence_async_smem();
+                if (work) {
+                    warp_arrive(&bars[FB_QP_FULL0 + qb], lane);
+                    ++n;
+                }
+            }
+        }
+    } else if (warp >= 12) {
+        reg_dec<M_REGS>();
+        cta_start_sync();
+        if (is_mma) {
+        // ================================================================== MMA warp
+        // The whole warp runs this role converged; MMAs and commits are predicated on one elected lane.
+        const uint32_t issuer = elect_one();
+        const uint32_t idesc_x = make_idesc_bf16(RING, RING, 0, 0);
+        const uint32_t idesc_u = make_idesc_bf16(RING, D, 0, 1);
+        const uint64_t dQp = make_smem_desc(smem_u32(sQp), 16, 1024, SWIZZLE_128B);           // A, K-major
+        const uint64_t dS = make_smem_desc(smem_u32(sS), 16, 1024, SWIZZLE_128B);             // B, K-major
+        const uint64_t dVsM = make_smem_desc(smem_u32(sVs), RING * 128, 1024, SWIZZLE_128B);  // B, MN-major
+        int n = 0;
+        bool ok = true, u_pending = false;
+        // U(m) = P(m) Vs.  P sits in the score columns: thread (row, half c) keeps its 32 packed columns
+        // at the start of its own 64, so k-step kk reads columns 64*(kk/4) + 8*(kk%4).
+        auto issue_u = [&](int m) {
+            const int ub = m & 1;
+            PROGV(m, 22);
+            bool r = pipe_wait(&bars[FB_P_FULL0 + ub], (m >> 1) & 1, sFail, nullptr, 22);
+            PROGV(m, 23);
+            if (r && m >= 2) r = pipe_wait(&bars[FB_U_FREE0 + ub], ((m >> 1) - 1) & 1, sFail, nullptr, 23);
+            if (r) {
+                tc_fence_after();
+                const uint32_t tX = tmem_base + ub * 256, tU = tX + 128;
+#pragma unroll 1
+                for (int kk = 0; kk < RING / 16; ++kk)
+                    umma_ts_pred(tU, tX + 64u * (kk >> 2) + 8u * (kk & 3), dVsM + kk * (2048 / 16), idesc_u, kk > 0,
+                                 issuer);
+                umma_commit_pred(&bars[FB_U_DONE0 + ub], issuer);
+            }
+            return r;
+        };
+        for (int i = q0; i < q1 && ok; ++i) {
+            uint32_t vw[4];
+            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
+            const bool work = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
+            for (int hh = 0; hh < G && ok; ++hh) {
+                if (!work) {
+                    // nothing follows that would carry the kept-back product: issue it now
+                    if (u_pending) { ok = issue_u(n - 1); u_pending = false; }
+                    continue;
+                }
+                const int qb = n & 1;
+                PROG(20);
+                ok = pipe_wait(&bars[FB_QP_FULL0 + qb], (n >> 1) & 1, sFail, nullptr, 20);
+                // X[qb] held P(n-2) until the U product of that head had read it
+                PROG(21);
+                if (ok && n >= 2) ok = pipe_wait(&bars[FB_U_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, nullptr, 21);
+                if (!ok) break;
+                tc_fence_after();
+                {
+                    const uint32_t tX = tmem_base + qb * 256;
+                    const uint64_t dA = dQp + qb * (L::TILE / 16);
+#pragma unroll 1
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        const uint32_t off = (kk >> 2) * (RING * 128 / 16) + (kk & 3) * 2;
+                        umma_ss_pred(tX, dA + off, dS + off, idesc_x, kk > 0, issuer);
+                    }
+                    umma_commit_pred(&bars[FB_X_DONE0 + qb], issuer);
+                }
+                if (u_pending) {
+                    ok = issue_u(n - 1);
+                    if (!ok) break;
+                }
+                u_pending = true;
+                ++n;
+            }
+        }
+        if (ok && u_pending) ok = issue_u(n - 1);
+        // the E warps wait for every U product, so nothing is in flight when they are done
+        __syncwarp();
+        }
+    } else {
+        // ================================================================== E warps
+        reg_dec<E_REGS>();
+        cta_start_sync();
+        const int slot = tid & (RING - 1);               // tensor-memory lane = ring slot = score row j
+        const int ch = tid >> 7;                          // column half of the scores / of the output
+        const int quarter = warp & 3;
+        const uint32_t tl = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        constexpr int VW = HD / 2;                        // packed words of this thread's half of a Vr row
+        uint32_t rVr[VW];
+        {
+            const int key = ring_key(q0, slot);
+            if (key >= 0) {
+                const uint4* v4 = reinterpret_cast<const uint4*>(gVr + static_cast<size_t>(key) * D + ch * HD);
+#pragma unroll
+                for (int c = 0; c < VW / 4; ++c) {
+                    const uint4 v = __ldg(v4 + c);
+                    rVr[4 * c] = v.x; rVr[4 * c + 1] = v.y; rVr[4 * c + 2] = v.z; rVr[4 * c + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < VW; ++c) rVr[c] = 0;
+            }
+        }
+        // Epilogue of head m, run one head late so that it overlaps the U product:
+        //   Y[d] = sum_j w_j Vr_j[d] U[j][d] / L,  w_j = exp2((m_j - M) c2),  L = sum_j w_j l_j
+        // with M the maximum over the rows (warp maxima left in shared memory by the softmax phase).
+        // Second half of an epilogue, run when the next one starts (or at the end): sum the four lane
+        // quarters' partials and write Y, m, l of head fin_m.
+        bool fin_pending = false;
+        int fin_m = 0;
+        size_t fin_row = 0;
+        float fin_M = 0.f;
+        auto finish = [&]() {
+            if (!fin_pending) return true;
+            fin_pending = false;
+            PROGV(fin_m, 33);
+            if (!pipe_wait(&bars[FB_E_SYNC], fin_m & 1, sFail, nullptr, 33)) return false;
+            const float* red = sRed + (fin_m & 1) * 4 * (D + 4);
+            float Lsum = 0.f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) Lsum += red[q * (D + 4) + D] + red[q * (D + 4) + D + 1];
+            if (tid < D) {
+                const float y = red[tid] + red[(D + 4) + tid] + red[2 * (D + 4) + tid] + red[3 * (D + 4) + tid];
+                p.Y[fin_row * D + tid] = __float2bfloat16(y / Lsum);
+            }
+            if (tid == 0) { p.m[fin_row] = fin_M * p.scale; p.l[fin_row] = Lsum; }
+            return true;
+        };
+        auto epilogue = [&](int m, size_t row, float m_row, float l_half) {
+            const int ub = m & 1;
+            if (!finish()) return false;
+            PROGV(m, 32);
+            bool r = pipe_wait(&bars[FB_U_DONE0 + ub], (m >> 1) & 1, sFail, nullptr, 32);
+            if (!r) return false;
+            tc_fence_after();
+            const float* mp = sMpart + ub * 8;
+            const float M = fmaxf(fmaxf(fmaxf(mp[0], mp[1]), fmaxf(mp[2], mp[3])),
+                                  fmaxf(fmaxf(mp[4], mp[5]), fmaxf(mp[6], mp[7])));
+            const float w_row = fast_exp2((m_row - M) * c2);          // 0 for a row without visible key
+            const uint32_t tU = tl + ub * 256 + 128 + ch * HD;
+            float* red = sRed + ub * 4 * (D + 4);
+            constexpr int NC = HD / 32;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {      // unrolled: rVr must be indexed with constants to stay in registers
+                // two rounds of 16 columns keep the live set small
+                float va[16], vb[16];
+                {
+                    uint32_t u[16];
+                    tmem_ld16(tU + c * 32, u);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int t = 0; t < 16; t += 2) {
+                        const float2 vr = unpack_bf16x2(rVr[c * 16 + (t >> 1)]);
+                        va[t] = w_row * vr.x * __uint_as_float(u[t]);
+                        va[t + 1] = w_row * vr.y * __uint_as_float(u[t + 1]);
+                    }
+                }
+                {
+                    uint32_t u[16];
+                    tmem_ld16(tU + c * 32 + 16, u);
+                    tmem_wait_ld();
+                    if (c == NC - 1) {
+                        // U is in registers: the product of head m + 2 may overwrite it
+                        tc_fence_before();
+                        warp_arrive(&bars[FB_U_FREE0 + ub], lane);
+                    }
+#pragma unroll
+                    for (int t = 0; t < 16; t += 2) {
+                        const float2 vr = unpack_bf16x2(rVr[c * 16 + 8 + (t >> 1)]);
+                        vb[t] = w_row * vr.x * __uint_as_float(u[t]);
+                        vb[t + 1] = w_row * vr.y * __uint_as_float(u[t + 1]);
+                    }
+                }
+                const float s = warp_transpose_sum_2x16(va, vb, lane);
+                red[quarter * (D + 4) + ch * HD + c * 32 + lane] = s;
+            }
+            float wl = w_row * l_half;
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) wl += __shfl_xor_sync(0xFFFFFFFFu, wl, o);
+            if (lane == 0) red[quarter * (D + 4) + D + ch] = wl;
+            warp_arrive(&bars[FB_E_SYNC], lane);
+            fin_pending = true; fin_m = m; fin_row = row; fin_M = M;
+            return true;
+        };
+        // Key i takes over slot s: the Vs ring row (every U product that read the old row is complete,
+        // because the caller has drained its epilogues) and this thread's half of the Vr row.
+        auto ring_update = [&](int i) {
+            const int s = i & (RING - 1), fb = i - q0 - 1;
+            const uint8_t* nx = sNext + (i & (NEXT_BUFS - 1)) * L::NEXT_BYTES;
+            PROGV(i, 34);
+            if (!pipe_wait(&bars[FB_NEXT_READY0 + (fb & (NEXT_BUFS - 1))], (fb >> 3) & 1, sFail, nullptr, 34)) return false;
+            if (tid < CH)
+                *reinterpret_cast<uint4*>(sVs + sw128_offset<RING>(s, tid)) =
+                    *reinterpret_cast<const uint4*>(nx + 3 * (D * 2) + tid * 16);
+            if (slot == s) {
+                const uint4* v4 = reinterpret_cast<const uint4*>(nx + D * 2 + ch * HD * 2);
+#pragma unroll
+                for (int c = 0; c < VW / 4; ++c) {
+                    const uint4 v = v4[c];
+                    rVr[4 * c] = v.x; rVr[4 * c + 1] = v.y; rVr[4 * c + 2] = v.z; rVr[4 * c + 3] = v.w;
                 }
             }
             fence_async_smem();
-            tc_fence_before();
-            __syncthreads();                                           // B1
-            if (warp == 0) {
-                // the warp stays converged; the MMAs and the commit are predicated on its elected lane
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = ((kk >> 2) * (RING * 128) + (kk & 3) * 32) / 16;
-                    umma_ss_pred(tmem_base, dQp + off, dS + off, idesc_x, kk > 0, issuer);
+            return true;
+        };
+        int n = 0;
+        bool ok = true, pend = false;
+        int pend_n = 0;
+        size_t pend_row = 0;
+        float pend_m = 0.f, pend_l = 0.f;
+        for (int i = q0; i < q1 && ok; ++i) {
+            uint32_t vw[4];
+            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
+            const int n_vis = __popc(vw[0]) + __popc(vw[1]) + __popc(vw[2]) + __popc(vw[3]);
+            const bool all_vis = n_vis == RING;
+            const bool my_vis = (vw[quarter] >> lane) & 1u;
+            // visibility words of this thread's two 32-column chunks
+            const uint32_t cw0 = my_vis ? (ch ? vw[2] : vw[0]) : 0u;
+            const uint32_t cw1 = my_vis ? (ch ? vw[3] : vw[1]) : 0u;
+            for (int hh = 0; hh < G && ok; ++hh) {
+                const size_t row = row_at(i, hh);
+                const bool boundary = hh == 0 && i > q0;
+                if (n_vis == 0) {
+                    // No visible pair: Y = 0, m = NEG_INF, l = 0 (cuda/common.cuh:24).
+                    if (pend) { ok = epilogue(pend_n, pend_row, pend_m, pend_l); pend = false; }
+                    if (!ok) break;
+                    if (boundary) ok = ring_update(i);
+                    if (!ok) break;
+                    if (tid < D) p.Y[row * D + tid] = __float2bfloat16(0.f);
+                    if (tid == 0) { p.m[row] = NEG_INF_F; p.l[row] = 0.f; }
+                    continue;
                 }
-                umma_commit_pred(bar, issuer);
-                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
-                __syncwarp();
-            }
-            phase ^= 1;
-            __syncthreads();                                           // B2
-            tc_fence_after();
-            if (*sFail) { failed = true; break; }
-
-            // --- per-row softmax over the 128 ring columns ------------------------
-            // tcgen05.ld/st are warp-collective, so every thread runs the same
-            // instruction stream; an invisible row is a row whose columns are all
-            // masked (rows and columns share one visibility set).
-            float m_row = -INFINITY, l_row = 0.f;
-            {
-                uint32_t x[32];
+                const int xb = n & 1;
+                const uint32_t tX = tl + xb * 256 + ch * 64;          // this thread's 64 score columns
+                PROG(30);
+                ok = pipe_wait(&bars[FB_X_DONE0 + xb], (n >> 1) & 1, sFail, nullptr, 30);
+                if (!ok) break;
+                tc_fence_after();
+                // ---- maximum of this thread's half row; the other half belongs to the thread with the same
+                //      lane in the partner warp, and the exchange completes behind the epilogue below
+                float mh = -INFINITY;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    tmem_ld32(tX + c * 32, x);
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t x[32];
+                    tmem_ld32(tX + cc * 32, x);
                     tmem_wait_ld();
+                    const uint32_t cw = cc ? cw1 : cw0;
                     if (all_vis) {
 #pragma unroll
-                        for (int t = 0; t < 32; ++t) m_row = fmaxf(m_row, __uint_as_float(x[t]));
+                        for (int t = 0; t < 32; ++t) mh = fmaxf(mh, __uint_as_float(x[t]));
                     } else {
-                        const uint32_t vw = my_vis ? (c == 0 ? vw0 : c == 1 ? vw1 : c == 2 ? vw2 : vw3) : 0u;
 #pragma unroll
                         for (int t = 0; t < 32; ++t)
-                            if ((vw >> t) & 1u) m_row = fmaxf(m_row, __uint_as_float(x[t]));
+                            if ((cw >> t) & 1u) mh = fmaxf(mh, __uint_as_float(x[t]));
                     }
                 }
-                const float mc = (my_vis ? m_row : 0.f) * c2;
+                float* mhalf = sMhalf + xb * 2 * RING;
+                mhalf[ch * RING + slot] = mh;
+                warp_arrive(&bars[FB_PAIR0 + quarter], lane);
+                // ---- epilogue of the previous head, behind its U product; then the ring rows of a new key
+                if (pend) { ok = epilogue(pend_n, pend_row, pend_m, pend_l); pend = false; }
+                if (ok && boundary) ok = ring_update(i);
+                if (!ok) break;
+                PROG(31);
+                ok = pipe_wait(&bars[FB_PAIR0 + quarter], n & 1, sFail, nullptr, 31);
+                if (!ok) break;
+                const float m_row = fmaxf(mh, mhalf[(ch ^ 1) * RING + slot]);
+                const float mc = my_vis ? m_row * c2 : 0.f;
+                // ---- P = exp2((x - m_row) c2), BF16 over the first 32 of this thread's columns; half-row sum
+                float l_half = 0.f;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    tmem_ld32(tX + c * 32, x);
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t x[32], pk[16];
+                    tmem_ld32(tX + cc * 32, x);
                     tmem_wait_ld();
-                    const uint32_t vw = my_vis ? (c == 0 ? vw0 : c == 1 ? vw1 : c == 2 ? vw2 : vw3) : 0u;
-                    uint32_t pk[16];
+                    const uint32_t cw = cc ? cw1 : cw0;
 #pragma unroll
                     for (int t = 0; t < 32; t += 2) {
                         float e0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2, -mc));
                         float e1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2, -mc));
                         if (!all_vis) {
-                            if (!((vw >> t) & 1u)) e0 = 0.f;
-                            if (!((vw >> (t + 1)) & 1u)) e1 = 0.f;
+                            if (!((cw >> t) & 1u)) e0 = 0.f;
+                            if (!((cw >> (t + 1)) & 1u)) e1 = 0.f;
                         }
-                        l_row += e0 + e1;
+                        l_half += e0 + e1;
                         pk[t >> 1] = pack_bf16x2(e0, e1);
                     }
-                    tmem_st16(tX + c * 16, pk);
+                    tmem_st16(tX + cc * 16, pk);
                 }
-            }
-            tmem_wait_st();
-            // warp maximum of the row maxima, for the joint-softmax merge
-            float m_w = m_row;
+                tmem_wait_st();
+                {
+                    float m_w = m_row;
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) m_w = fmaxf(m_w, __shfl_xor_sync(0xFFFFFFFFu, m_w, o));
-            if (lane == 0) sMpart[warp] = m_w;
-            tc_fence_before();
-            __syncthreads();                                           // B3
-            if (warp == 0) {
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < RING / 16; ++kk)
-                    umma_ts_pred(tmem_base + 128, tmem_base + kk * 8, dVsM + kk * (2048 / 16), idesc_u, kk > 0, issuer);
-                umma_commit_pred(bar, issuer);
-                if (lane == 0 && !mbar_wait(bar, phase)) *sFail = 1;
-                __syncwarp();
-            }
-            phase ^= 1;
-            const float M = fmaxf(fmaxf(sMpart[0], sMpart[1]), fmaxf(sMpart[2], sMpart[3]));
-            const float w_row = my_vis ? fast_exp2((m_row - M) * c2) : 0.f;
-            __syncthreads();                                           // B4
-            tc_fence_after();
-            if (*sFail) { failed = true; break; }
-
-            // --- epilogue: Y[d] = sum_j w_j Vr_j[d] U[j][d] / L ---------------------
-            {
-                uint32_t u[32];
-                float v[32];
-#pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    tmem_ld32(tU + c * 32, u);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int t = 0; t < 32; t += 2) {
-                        const float2 vr = unpack_bf16x2(rVr[c * 16 + (t >> 1)]);
-                        v[t] = w_row * vr.x * __uint_as_float(u[t]);
-                        v[t + 1] = w_row * vr.y * __uint_as_float(u[t + 1]);
-                    }
-                    const float s = warp_transpose_sum(v, lane);
-                    sRed[warp * (D + 4) + c * 32 + lane] = s;
+                    for (int o = 16; o >= 1; o >>= 1) m_w = fmaxf(m_w, __shfl_xor_sync(0xFFFFFFFFu, m_w, o));
+                    if (lane == 0) sMpart[xb * 8 + warp] = m_w;
                 }
-                float wl = w_row * l_row;
-#pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) wl += __shfl_xor_sync(0xFFFFFFFFu, wl, o);
-                if (lane == 0) sRed[warp * (D + 4) + D] = wl;
-            }
-            if (tid < CH) asm volatile("cp.async.wait_all;" ::: "memory");
-            tc_fence_before();
-            __syncthreads();                                           // B5
-            {
-                const float Lsum = sRed[D] + sRed[(D + 4) + D] + sRed[2 * (D + 4) + D] + sRed[3 * (D + 4) + D];
-                if (tid < D) {
-                    const float y = sRed[tid] + sRed[(D + 4) + tid] + sRed[2 * (D + 4) + tid] + sRed[3 * (D + 4) + tid];
-                    p.Y[row * D + tid] = __float2bfloat16(y / Lsum);
-                }
-                if (tid == 0) { p.m[row] = M * p.scale; p.l[row] = Lsum; }
+                tc_fence_before();
+                // P_full also tells the MMA warp that the Vs ring row is current (ring_update above)
+                warp_arrive(&bars[FB_P_FULL0 + xb], lane);
+                pend = true; pend_n = n; pend_row = row; pend_m = m_row; pend_l = l_half;
+                ++n;
             }
         }
+        if (ok && pend) ok = epilogue(pend_n, pend_row, pend_m, pend_l);
+        if (ok) ok = finish();
     }
-    if (failed && tid == 0) atomicExch(p.status, 1);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+#undef PROG
+#undef PROGV
+    if (*sFail && tid == 0) atomicExch(p.status, 100 + *sFail);
+    if (is_mma) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 }  // namespace sgring
