@@ -182,12 +182,20 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 4);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef ATT3_PIPE_TRACE
+    // diagnostic: trace mode 3 walks the work in the opposite order of the CTA indices
+    const bool rev = p.trace_mode == 3;
+    const int b = rev ? gridDim.z - 1 - blockIdx.z : blockIdx.z, g = blockIdx.y;
+    const int bx = rev ? gridDim.x - 1 - blockIdx.x : blockIdx.x;
+#else
     const int b = blockIdx.z, g = blockIdx.y;
+    const int bx = blockIdx.x;
+#endif
     const int G = p.Hq / p.Hkv;
-    const int q0 = p.q_begin + blockIdx.x * p.block_len;
+    const int q0 = p.q_begin + bx * p.block_len;
     const int q1 = min(q0 + p.block_len, p.N);
     if (q0 >= q1) return;
-    const int parity_buf = blockIdx.x & 1;
+    const int parity_buf = bx & 1;
     const bool is_h = warp >= 8 && warp < 12, is_mma = warp == 12;
 
     if (is_mma) {
@@ -240,7 +248,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
 #ifdef ATT3_PIPE_TRACE
     const bool tracer = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&
                         (tid == 0 || tid == PIPE_E_THREADS || tid == PIPE_E_THREADS + PIPE_H_THREADS);
-    const bool timed = p.trace && p.trace_mode == 2 && tid == PIPE_E_THREADS + PIPE_H_THREADS;   // every CTA
+    const bool timed = p.trace && p.trace_mode >= 2 && tid == PIPE_E_THREADS + PIPE_H_THREADS;   // every CTA
     const long long t_begin = (tracer || timed) ? clock64() : 0;
     unsigned long long ns_begin = 0;
     if (timed) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
@@ -775,13 +783,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                         tc_fence_before();
                         warp_arrive(&bars[PB_B_FREE], lane);
                     }
+                    // packed BF16 product: (dP - delta) is rounded to BF16 like P before them (both are MMA
+                    // operands in BF16 anyway); four instructions a pair instead of seven
 #pragma unroll
                     for (int t = 0; t < 32; t += 2) {
-                        const float2 pp = unpack_bf16x2(pk[t >> 1]);
-                        float g0 = pp.x * (__uint_as_float(dp[t]) - delta);
-                        float g1 = pp.y * (__uint_as_float(dp[t + 1]) - delta);
-                        if (single) { g0 = 0.f; g1 = 0.f; }
-                        pk[t >> 1] = pack_bf16x2(g0, g1);
+                        const uint32_t d2 = pack_bf16x2(__uint_as_float(dp[t]) - delta, __uint_as_float(dp[t + 1]) - delta);
+                        pk[t >> 1] = single ? 0u : mul_bf16x2(pk[t >> 1], d2);
                     }
                     tmem_st16(tA + 32 + cc * 16, pk);
                 }

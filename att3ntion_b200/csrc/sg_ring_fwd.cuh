@@ -15,12 +15,12 @@
 //    operands never move.  Contractions over the ring are order independent,
 //    which is what makes the rotated order legal.
 //  * Per (query, head):  X = (Q_i o R) S^T  is one 128x128xD product with the
-//    Hadamard tile built in shared memory; the thread pair of row j takes the
-//    row maximum and writes P = exp2(.) back to tensor memory as BF16 over score
-//    columns it has consumed itself; U = P Vs is the second product with A read
+//    Hadamard tile built in shared memory; the E warps take the maximum M over
+//    the whole tile (the softmax is joint over (j,k)) and the two threads of row j
+//    write P = exp2((x - M) c2) back to tensor memory as BF16 over score columns
+//    they have consumed themselves; U = P Vs is the second product with A read
 //    from tensor memory and the Vs ring as an MN-major B operand; the epilogue
-//    collapses  sum_j w_j Vr_j o U_j  with warp shuffles, where w_j = exp(m_j - M)
-//    merges the per-row softmaxes into the joint one.
+//    collapses  sum_j Vr_j o U_j  with warp shuffles and divides by L = sum P.
 //  * The score scale is folded into the exp2 argument, so the only BF16
 //    rounding before the score MMA is the product Q_i[d] * R_j[d] itself.
 //
@@ -30,8 +30,8 @@
 //                the key that enters the window next and replace the S ring row.
 //   MMA warp (1) issues X(n) = Qp(n) S^T, then U(n-1) = P(n-1) Vs, so the score product of the
 //                next head runs while the E warps still work on this one.
-//   E warps (8)  thread (row j, column half c): row maximum (exchanged with the other half through
-//                a 64-thread named barrier), P, row sum; then, one head behind, the epilogue of
+//   E warps (8)  thread (row j, column half c): maximum of its half row, joint maximum M over the CTA,
+//                P = exp2((x - M) c2) and its sum; then, one head behind, the epilogue of
 //                U(n-1).  They also replace the Vs ring row, behind the last U product that reads it.
 //
 // Hand-offs (mbarriers, one per buffer b = n & 1, phase = (n >> 1) & 1):
@@ -42,10 +42,9 @@
 //   U_free[b]   E -> MMA    U(n) taken out of tensor memory
 //   Next_ready  H -> E      per query boundary: the prefetched rows of the entering key have landed
 // The E warps also meet each other on mbarriers rather than named barriers, so that these waits are
-// bounded like the rest, and both meetings are split so that nobody stands waiting: the two warps of a
-// lane quarter exchange their half-row maxima before the epilogue of the previous head and pick the
-// partner's value up after it; the output reduction of head m is finished at the start of the
-// epilogue of head m + 1.
+// bounded like the rest, and both meetings are split so that nobody stands waiting: the warps post
+// their maxima before the epilogue of the previous head and pick the joint maximum up after it; the
+// output reduction of head m is finished at the start of the epilogue of head m + 1.
 // Every wait is bounded and watches a CTA-wide failure flag (status code instead of a hang).
 #pragma once
 
@@ -71,7 +70,7 @@ struct FwdParams {
 
 enum FwdBar {
     FB_QP_FULL0 = 0, FB_QP_FULL1, FB_X_DONE0, FB_X_DONE1, FB_P_FULL0, FB_P_FULL1, FB_U_DONE0, FB_U_DONE1,
-    FB_U_FREE0, FB_U_FREE1, FB_H_SYNC, FB_PAIR0, FB_PAIR1, FB_PAIR2, FB_PAIR3,
+    FB_U_FREE0, FB_U_FREE1, FB_H_SYNC, FB_M_SYNC,
     FB_E_SYNC, FB_NEXT_READY0, FB_COUNT = FB_NEXT_READY0 + 8
 };
 
@@ -90,8 +89,7 @@ struct FwdSmem {
     static constexpr int NEXT_BYTES = 4 * D * 2;        // rows R, Vr, S, Vs of an entering key
     static constexpr int OFF_NEXT = OFF_QSTAGE + 2 * D * 2;          // NEXT_BUFS buffers (query index mod NEXT_BUFS)
     static constexpr int OFF_RED = OFF_NEXT + NEXT_BUFS * NEXT_BYTES;        // 2 x 4 x (D + 4) floats: y partials, l partials
-    static constexpr int OFF_MHALF = OFF_RED + 2 * 4 * (D + 4) * 4;  // 2 parities x 2 halves x 128 floats: half-row maxima
-    static constexpr int OFF_MPART = OFF_MHALF + 2 * 2 * RING * 4;   // 2 x 8 floats: warp maxima, per head parity
+    static constexpr int OFF_MPART = OFF_RED + 2 * 4 * (D + 4) * 4;  // 2 x 8 floats: warp maxima, per head parity
     static constexpr int OFF_BARS = OFF_MPART + 2 * 8 * 4;
     static constexpr int OFF_MISC = OFF_BARS + FB_COUNT * 8;         // tmem slot (4) + fail flag (4)
     static constexpr int BYTES = OFF_MISC + 16;
@@ -116,7 +114,6 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
     __nv_bfloat16* sQst = reinterpret_cast<__nv_bfloat16*>(smem + L::OFF_QSTAGE);
     uint8_t* sNext = smem + L::OFF_NEXT;
     float* sRed = reinterpret_cast<float*>(smem + L::OFF_RED);
-    float* sMhalf = reinterpret_cast<float*>(smem + L::OFF_MHALF);
     float* sMpart = reinterpret_cast<float*>(smem + L::OFF_MPART);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BARS);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::OFF_MISC);
@@ -145,7 +142,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
         }
         mbar_init(&bars[FB_H_SYNC], 4);
         for (int x = 0; x < NEXT_BUFS; ++x) mbar_init(&bars[FB_NEXT_READY0 + x], 4);
-        for (int x = 0; x < 4; ++x) mbar_init(&bars[FB_PAIR0 + x], 2);
+        mbar_init(&bars[FB_M_SYNC], 8);
         mbar_init(&bars[FB_E_SYNC], 8);
         fence_mbar_init();
         *sFail = 0;
@@ -326,7 +323,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
             if (r) {
                 tc_fence_after();
                 const uint32_t tX = tmem_base + ub * 256, tU = tX + 128;
-#pragma unroll 1
+#pragma unroll
                 for (int kk = 0; kk < RING / 16; ++kk)
                     umma_ts_pred(tU, tX + 64u * (kk >> 2) + 8u * (kk & 3), dVsM + kk * (2048 / 16), idesc_u, kk > 0,
                                  issuer);
@@ -355,7 +352,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
                 {
                     const uint32_t tX = tmem_base + qb * 256;
                     const uint64_t dA = dQp + qb * (L::TILE / 16);
-#pragma unroll 1
+#pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         const uint32_t off = (kk >> 2) * (RING * 128 / 16) + (kk & 3) * 2;
                         umma_ss_pred(tX, dA + off, dS + off, idesc_x, kk > 0, issuer);
@@ -399,8 +396,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
             }
         }
         // Epilogue of head m, run one head late so that it overlaps the U product:
-        //   Y[d] = sum_j w_j Vr_j[d] U[j][d] / L,  w_j = exp2((m_j - M) c2),  L = sum_j w_j l_j
-        // with M the maximum over the rows (warp maxima left in shared memory by the softmax phase).
+        //   Y[d] = sum_j Vr_j[d] U[j][d] / L,  L = sum of all P  (P is taken against the joint maximum M,
+        //   so the rows need no further weights).
         // Second half of an epilogue, run when the next one starts (or at the end): sum the four lane
         // quarters' partials and write Y, m, l of head fin_m.
         bool fin_pending = false;
@@ -423,17 +420,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
             if (tid == 0) { p.m[fin_row] = fin_M * p.scale; p.l[fin_row] = Lsum; }
             return true;
         };
-        auto epilogue = [&](int m, size_t row, float m_row, float l_half) {
+        auto epilogue = [&](int m, size_t row, float M, float l_half) {
             const int ub = m & 1;
             if (!finish()) return false;
             PROGV(m, 32);
             bool r = pipe_wait(&bars[FB_U_DONE0 + ub], (m >> 1) & 1, sFail, nullptr, 32);
             if (!r) return false;
             tc_fence_after();
-            const float* mp = sMpart + ub * 8;
-            const float M = fmaxf(fmaxf(fmaxf(mp[0], mp[1]), fmaxf(mp[2], mp[3])),
-                                  fmaxf(fmaxf(mp[4], mp[5]), fmaxf(mp[6], mp[7])));
-            const float w_row = fast_exp2((m_row - M) * c2);          // 0 for a row without visible key
             const uint32_t tU = tl + ub * 256 + 128 + ch * HD;
             float* red = sRed + ub * 4 * (D + 4);
             constexpr int NC = HD / 32;
@@ -448,8 +441,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
 #pragma unroll
                     for (int t = 0; t < 16; t += 2) {
                         const float2 vr = unpack_bf16x2(rVr[c * 16 + (t >> 1)]);
-                        va[t] = w_row * vr.x * __uint_as_float(u[t]);
-                        va[t + 1] = w_row * vr.y * __uint_as_float(u[t + 1]);
+                        va[t] = vr.x * __uint_as_float(u[t]);
+                        va[t + 1] = vr.y * __uint_as_float(u[t + 1]);
                     }
                 }
                 {
@@ -464,14 +457,16 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
 #pragma unroll
                     for (int t = 0; t < 16; t += 2) {
                         const float2 vr = unpack_bf16x2(rVr[c * 16 + 8 + (t >> 1)]);
-                        vb[t] = w_row * vr.x * __uint_as_float(u[t]);
-                        vb[t + 1] = w_row * vr.y * __uint_as_float(u[t + 1]);
+                        vb[t] = vr.x * __uint_as_float(u[t]);
+                        vb[t + 1] = vr.y * __uint_as_float(u[t + 1]);
                     }
                 }
+                // (a shared-memory transpose for this lane sum was measured slower: it competes with the
+                //  MMA operand reads for shared-memory bandwidth)
                 const float s = warp_transpose_sum_2x16(va, vb, lane);
                 red[quarter * (D + 4) + ch * HD + c * 32 + lane] = s;
             }
-            float wl = w_row * l_half;
+            float wl = l_half;
 #pragma unroll
             for (int o = 16; o >= 1; o >>= 1) wl += __shfl_xor_sync(0xFFFFFFFFu, wl, o);
             if (lane == 0) red[quarter * (D + 4) + D + ch] = wl;
@@ -551,19 +546,25 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
                             if ((cw >> t) & 1u) mh = fmaxf(mh, __uint_as_float(x[t]));
                     }
                 }
-                float* mhalf = sMhalf + xb * 2 * RING;
-                mhalf[ch * RING + slot] = mh;
-                warp_arrive(&bars[FB_PAIR0 + quarter], lane);
+                {
+                    float m_w = mh;
+#pragma unroll
+                    for (int o = 16; o >= 1; o >>= 1) m_w = fmaxf(m_w, __shfl_xor_sync(0xFFFFFFFFu, m_w, o));
+                    if (lane == 0) sMpart[xb * 8 + warp] = m_w;
+                }
+                warp_arrive(&bars[FB_M_SYNC], lane);
                 // ---- epilogue of the previous head, behind its U product; then the ring rows of a new key
                 if (pend) { ok = epilogue(pend_n, pend_row, pend_m, pend_l); pend = false; }
                 if (ok && boundary) ok = ring_update(i);
                 if (!ok) break;
                 PROG(31);
-                ok = pipe_wait(&bars[FB_PAIR0 + quarter], n & 1, sFail, nullptr, 31);
+                ok = pipe_wait(&bars[FB_M_SYNC], n & 1, sFail, nullptr, 31);
                 if (!ok) break;
-                const float m_row = fmaxf(mh, mhalf[(ch ^ 1) * RING + slot]);
-                const float mc = my_vis ? m_row * c2 : 0.f;
-                // ---- P = exp2((x - m_row) c2), BF16 over the first 32 of this thread's columns; half-row sum
+                const float* mp = sMpart + xb * 8;
+                const float M = fmaxf(fmaxf(fmaxf(mp[0], mp[1]), fmaxf(mp[2], mp[3])),
+                                      fmaxf(fmaxf(mp[4], mp[5]), fmaxf(mp[6], mp[7])));
+                const float mc = M * c2;
+                // ---- P = exp2((x - M) c2), BF16 over the first 32 of this thread's columns; half-row sum
                 float l_half = 0.f;
 #pragma unroll 1
                 for (int cc = 0; cc < 2; ++cc) {
@@ -585,16 +586,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
                     tmem_st16(tX + cc * 16, pk);
                 }
                 tmem_wait_st();
-                {
-                    float m_w = m_row;
-#pragma unroll
-                    for (int o = 16; o >= 1; o >>= 1) m_w = fmaxf(m_w, __shfl_xor_sync(0xFFFFFFFFu, m_w, o));
-                    if (lane == 0) sMpart[xb * 8 + warp] = m_w;
-                }
                 tc_fence_before();
                 // P_full also tells the MMA warp that the Vs ring row is current (ring_update above)
                 warp_arrive(&bars[FB_P_FULL0 + xb], lane);
-                pend = true; pend_n = n; pend_row = row; pend_m = m_row; pend_l = l_half;
+                pend = true; pend_n = n; pend_row = row; pend_m = M; pend_l = l_half;
                 ++n;
             }
         }
