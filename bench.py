@@ -281,7 +281,7 @@ def run_ours(args):
                     "unit": "TFLOP/s", "frac": (achieved / sustained) if achieved else None,
                     "peak_source": f"{src} bf16_tflops_sustained (kernel timed inside the step loop)",
                     "frac_of_burst_peak": (achieved / burst) if achieved else None,
-                    "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(w),
+                    "traffic": traffic_bytes_per_launch(B, HQ, HKV, N, D, w),
                     "kernel_ms": {k: (v[0] / v[1] if v[1] else None) for k, v in ktime.items()},
                     "step_frac_of_sustained_peak": value / world / sustained}
         cpu_v, cpu_dt, cores = cpu_sample(w, queries=args.cpu_queries) if world == 1 and not args.no_cpu else (None, 0, 0)
@@ -370,9 +370,15 @@ def run_rows(args):
     dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one sg_ring_bwd_kernel launch at this workload, from the ncu
-# capture summarised under profiles/ (null until measured for a window).
-TRAFFIC_BYTES_PER_LAUNCH = {}
+# DRAM bytes (read + write) of one sg_ring_bwd_kernel launch, from the ncu capture summarised in
+# profiles/sg_ring_w128_d128_pipelined.md: 162.5 MB (key side S + dQ) and 140.0 MB (key side R) at
+# B4 Hq8 Hkv1 N4096 D128 w128, i.e. 9232 bytes per (batch, query) on average over the two launches
+# of a step.  The traffic is per-row streaming (Q, dY, Y rows, key rows, FP32 partial rows), so it
+# scales with B*N; other head counts, head sizes or windows have not been captured (None).
+def traffic_bytes_per_launch(B, Hq, Hkv, N, D, w):
+    if (Hq, Hkv, D, w) == (8, 1, 128, 128):
+        return 9232 * B * N
+    return None
 
 
 if __name__ == "__main__":
