@@ -6,6 +6,7 @@
 
 #include "att3_abi_internal.h"
 #include "ag_dense_bwd.cuh"
+#include "hg_scatter.cuh"
 
 namespace {
 
@@ -128,6 +129,103 @@ int plane_to_bf16(const float* src, void* out, size_t n, cudaStream_t st) {
 }  // namespace att3
 
 // ---------------------------------------------------------------------------------------------
+// Scatter terms (CUDA-core kernels, hg_scatter.cuh)
+// ---------------------------------------------------------------------------------------------
+
+template <int D, int DH, int MODE>
+static int launch_scatter_t(const hgscatter::Params& p, cudaStream_t st) {
+    const size_t smem = hgscatter::smem_bytes<D, DH>();
+    cudaError_t e = cudaFuncSetAttribute(hgscatter::hg_scatter_kernel<D, DH, MODE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return att3::set_cuda_error(e, "scatter: shared-memory opt-in");
+    dim3 grid(p.N / hgscatter::T, MODE == 0 ? 1 : p.N / hgscatter::T, p.B * p.H * (D / DH));
+    att3::TimedLaunch timed(att3::K_HG_AUX, st);
+    hgscatter::hg_scatter_kernel<D, DH, MODE><<<grid, hgscatter::THREADS, smem, st>>>(p);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "scatter: launch");
+}
+
+template <int MODE>
+static int launch_scatter(const hgscatter::Params& p, cudaStream_t st) {
+    switch (p.D) {
+        case 16: return launch_scatter_t<16, 16, MODE>(p, st);
+        case 32: return launch_scatter_t<32, 32, MODE>(p, st);
+        case 64: return launch_scatter_t<64, 64, MODE>(p, st);
+        default: return launch_scatter_t<128, 64, MODE>(p, st);
+    }
+}
+
+// One index of the operator in a given role: its keys, second value tensor and the statistics of the
+// softmax anchored at it.
+struct ScatterSide {
+    const void* keys; const void* v2; const float* m; const float* l;
+};
+
+static hgscatter::Params scatter_params(const ScatterSide& a, const ScatterSide& u, const ScatterSide& v,
+                                        const uint8_t* mask, int B, int H, int N, int D, int n_valid) {
+    hgscatter::Params p{};
+    p.A = static_cast<const __nv_bfloat16*>(a.keys);
+    p.U = static_cast<const __nv_bfloat16*>(u.keys);
+    p.V = static_cast<const __nv_bfloat16*>(v.keys);
+    p.Vu2 = static_cast<const __nv_bfloat16*>(u.v2);
+    p.Vv2 = static_cast<const __nv_bfloat16*>(v.v2);
+    p.m_u = u.m; p.l_u = u.l; p.m_v = v.m; p.l_v = v.l;
+    p.mask = mask;
+    p.B = B; p.H = H; p.N = N; p.D = D; p.n_valid = n_valid;
+    p.scale = 1.0f / sqrtf(static_cast<float>(D));
+    return p;
+}
+
+// out[a] = sum_{u,v} Pu Pv Vu2[u] o Vv2[v]   (forward of one scatter output)
+static int scatter_forward(const ScatterSide& a, const ScatterSide& u, const ScatterSide& v, const uint8_t* mask,
+                           void* out, int B, int H, int N, int D, int n_valid, cudaStream_t st) {
+    hgscatter::Params p = scatter_params(a, u, v, mask, B, H, N, D, n_valid);
+    p.out_bf16 = static_cast<__nv_bfloat16*>(out);
+    return launch_scatter<0>(p, st);
+}
+
+// Gradients of one scatter output under the cotangent g: into the FP32 planes of the three key tensors and
+// of the two second value tensors.  tmp: two planes + two [B,H,N] vectors of scratch.
+static int scatter_backward(const ScatterSide& a, const ScatterSide& u, const ScatterSide& v, const void* g,
+                            const uint8_t* mask, float* gA, float* gU, float* gV, float* gVu2, float* gVv2,
+                            float* tmp, int B, int H, int N, int D, int n_valid, cudaStream_t st) {
+    const size_t plane = static_cast<size_t>(B) * H * N * D, rows = static_cast<size_t>(B) * H * N;
+    float *tmpU = tmp, *tmpV = tmp + plane, *Cu = tmp + 2 * plane, *Cv = Cu + rows;
+    cudaMemsetAsync(tmp, 0, 2 * plane * sizeof(float), st);
+    int rc;
+    {   // value gradients of this term alone (their row dots are the softmax corrections)
+        hgscatter::Params p = scatter_params(a, u, v, mask, B, H, N, D, n_valid);
+        p.G = static_cast<const __nv_bfloat16*>(g);
+        p.out_u = tmpU;
+        if ((rc = launch_scatter<1>(p, st))) return rc;
+        hgscatter::Params q = scatter_params(a, v, u, mask, B, H, N, D, n_valid);
+        q.G = p.G;
+        q.out_u = tmpV;
+        if ((rc = launch_scatter<1>(q, st))) return rc;
+    }
+    const int wpb = 8;    // warps per block of the row-dot kernel
+    const unsigned nblk = static_cast<unsigned>((rows + wpb - 1) / wpb);
+    hgscatter::rowdot_kernel<<<nblk, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(u.v2), tmpU, Cu, rows, D);
+    hgscatter::rowdot_kernel<<<nblk, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(v.v2), tmpV, Cv, rows, D);
+    if ((rc = att3::add_planes(tmpU, 1, plane, gVu2, st))) return rc;
+    if ((rc = att3::add_planes(tmpV, 1, plane, gVv2, st))) return rc;
+    {   // key gradients: (a, u) from the first launch, v from the launch with u and v exchanged
+        hgscatter::Params p = scatter_params(a, u, v, mask, B, H, N, D, n_valid);
+        p.G = static_cast<const __nv_bfloat16*>(g);
+        p.Cu = Cu; p.Cv = Cv;
+        p.out_a = gA; p.out_u = gU;
+        if ((rc = launch_scatter<2>(p, st))) return rc;
+        hgscatter::Params q = scatter_params(a, v, u, mask, B, H, N, D, n_valid);
+        q.G = p.G;
+        q.Cu = Cv; q.Cv = Cu;
+        q.out_a = nullptr; q.out_u = gV;
+        if ((rc = launch_scatter<2>(q, st))) return rc;
+    }
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "scatter backward: launch");
+}
+
+// ---------------------------------------------------------------------------------------------
 // Three-gather forward
 // ---------------------------------------------------------------------------------------------
 
@@ -163,8 +261,6 @@ extern "C" int att3_hg_forward(const void* Q, const void* R, const void* S, cons
     if (scatter && (!Vq2 || !Vr2 || !Vs2))
         return att3::set_error(ATT3_ERR_INVALID, "att3_hg_forward: scatter needs the second value tensors");
     if (!att3::require_sm100("att3_hg_forward")) return ATT3_ERR_UNSUPPORTED;
-    if (scatter)
-        return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_hg_forward: scatter outputs unavailable (not built)");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t n = static_cast<size_t>(B) * H * N;
     const size_t bytes = n * D * 2;
@@ -186,6 +282,14 @@ extern "C" int att3_hg_forward(const void* Q, const void* R, const void* S, cons
     if ((rc = att3::dense_gather_forward(R, Q, S, Vq1, Vs1, mask, Yr, m_j, l_j, B, H, N, D, n_valid, st))) return rc;
     if ((rc = att3::dense_gather_forward(S, Q, R, Vq1, Vr1, mask, Ys, m_k, l_k, B, H, N, D, n_valid, st))) return rc;
     att3::count_launch(2, 2);
+    if (scatter) {
+        // each output weights a cell with the two softmaxes anchored at the other indices (cuda/forward.cu:941-1249)
+        const ScatterSide q{Q, Vq2, m_i, l_i}, r{R, Vr2, m_j, l_j}, s{S, Vs2, m_k, l_k};
+        if ((rc = scatter_forward(q, r, s, mask, Yq_, B, H, N, D, n_valid, st))) return rc;
+        if ((rc = scatter_forward(r, q, s, mask, Yr_, B, H, N, D, n_valid, st))) return rc;
+        if ((rc = scatter_forward(s, q, r, mask, Ys_, B, H, N, D, n_valid, st))) return rc;
+        att3::count_launch(2, 3);
+    }
     return ATT3_OK;
 }
 
@@ -197,7 +301,8 @@ extern "C" int att3_hg_forward(const void* Q, const void* R, const void* S, cons
 extern "C" size_t att3_hg_backward_workspace_bytes(int B, int H, int N, int D) {
     if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
     const size_t plane = static_cast<size_t>(B) * H * N * D * sizeof(float);
-    return plane * (9 + att3::dense_tiles(N, 0));
+    // the scatter terms use three planes of the same scratch area
+    return plane * (9 + std::max(att3::dense_tiles(N, 0), 3));
 }
 
 extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gYs, const void* gYq_,
@@ -209,7 +314,6 @@ extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gY
                                 void* dVq2, void* dVr1, void* dVr2, void* dVs1, void* dVs2, int B, int H, int N,
                                 int D, int n_valid, int gather_mode, int scatter, void* workspace,
                                 size_t workspace_bytes, void* stream) {
-    (void)gYq_; (void)gYr_; (void)gYs_; (void)Vq2; (void)Vr2; (void)Vs2;
     if (int rc = check_hg("att3_hg_backward", B, H, N, D)) return rc;
     if (!gYq || !Q || !R || !S || !Vq1 || !Vr1 || !Vs1 || !Yq || !m_i || !l_i || !dQ || !dR || !dS || !dVq1 || !dVq2 ||
         !dVr1 || !dVr2 || !dVs1 || !dVs2)
@@ -217,8 +321,10 @@ extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gY
     if (gather_mode == 0 && (!gYr || !gYs || !Yr || !Ys || !m_j || !l_j || !m_k || !l_k))
         return att3::set_error(ATT3_ERR_INVALID, "att3_hg_backward: null tensor pointer (R/S-anchored gathers)");
     if (!att3::require_sm100("att3_hg_backward")) return ATT3_ERR_UNSUPPORTED;
-    if (scatter)
-        return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_hg_backward: scatter gradients unavailable (not built)");
+    if (scatter && (gather_mode != 0 || !gYq_ || !gYr_ || !gYs_ || !Vq2 || !Vr2 || !Vs2))
+        return att3::set_error(ATT3_ERR_INVALID,
+                               "att3_hg_backward: scatter gradients need gather_mode 0, the three scatter cotangents "
+                               "and the second value tensors");
     const size_t need = att3_hg_backward_workspace_bytes(B, H, N, D);
     if (!workspace || workspace_bytes < need)
         return att3::set_error(ATT3_ERR_WORKSPACE, "att3_hg_backward: workspace of %zu bytes required, got %zu", need,
@@ -251,6 +357,13 @@ extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gY
     if (gather_mode == 0) {
         if ((rc = gather_bwd(R, gYr, Yr, m_j, l_j, Q, Vq1, S, Vs1, gR, gQ, gVq1, gS, gVs1))) return rc;
         if ((rc = gather_bwd(S, gYs, Ys, m_k, l_k, Q, Vq1, R, Vr1, gS, gQ, gVq1, gR, gVr1))) return rc;
+    }
+    if (scatter) {
+        const ScatterSide q{Q, Vq2, m_i, l_i}, r{R, Vr2, m_j, l_j}, s{S, Vs2, m_k, l_k};
+        if ((rc = scatter_backward(q, r, s, gYq_, mask, gQ, gR, gS, gVr2, gVs2, part, B, H, N, D, n_valid, st))) return rc;
+        if ((rc = scatter_backward(r, q, s, gYr_, mask, gR, gQ, gS, gVq2, gVs2, part, B, H, N, D, n_valid, st))) return rc;
+        if ((rc = scatter_backward(s, q, r, gYs_, mask, gS, gQ, gR, gVq2, gVr2, part, B, H, N, D, n_valid, st))) return rc;
+        att3::count_launch(3, 18);
     }
     void* outs[9] = {dQ, dR, dS, dVq1, dVq2, dVr1, dVr2, dVs1, dVs2};
     const float* srcs[9] = {gQ, gR, gS, gVq1, gVq2, gVr1, gVr2, gVs1, gVs2};

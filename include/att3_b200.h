@@ -133,7 +133,7 @@ int att3_sg_backward_static(const void* dY, const void* Q, const void* R, const 
  * (cuda/forward.cu:1252-1602, cuda/backward.cu:1716-2232; math in
  * cpp/torch_reference.cpp:24-57).  All nine inputs are [B,H,N,D] with
  * D in {16,32,64,128}.  Outputs Y_q, Y_r, Y_s (gathers) and Y_q_, Y_r_, Y_s_
- * (scatters; written only when scatter != 0, else zero-filled) are BF16
+ * (scatters, cuda/forward.cu:941-1249; computed when scatter != 0, else zero-filled) are BF16
  * [B,H,N,D]; the six statistics FP32 [B,H,N].  n_valid < N marks trailing
  * padding rows that are invisible in every role (0 or N: none).  gather_mode 1
  * computes only the Q-anchored gather; the other outputs are zero-filled and
@@ -151,7 +151,9 @@ size_t att3_hg_backward_workspace_bytes(int B, int H, int N, int D);
 
 /* Nine gradients (Q,R,S,Vq1,Vq2,Vr1,Vr2,Vs1,Vs2), BF16 [B,H,N,D].  g* are the
  * cotangents of the six outputs; pass scatter = 0 when the three scatter
- * cotangents are identically zero (att3ntion/_custom_op.py:73-96).  Yq, Yr, Ys
+ * cotangents are identically zero (att3ntion/_custom_op.py:73-96), scatter = 1
+ * adds the gradients of the scatter outputs (cuda/backward.cu:175-316, 949-1613;
+ * gather_mode 0 only, accumulated with FP32 atomics).  Yq, Yr, Ys
  * are the forward's gather outputs: the softmax Jacobian correction is taken as
  * rowsum(dY o Y), the reference's tensor-core path (cuda/backward.cu:1835-1837).
  * With gather_mode 1 only the Q-anchored tensors are read. */
