@@ -241,7 +241,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     // and the MMA warp for its descriptors and bookkeeping; 8*E + 4*H + 4*M = 512 registers per lane
     // column), does its share of the set-up and then meets the others at one CTA barrier before the
     // hand-off protocol starts.
-    constexpr int E_REGS = 88, H_REGS = 232, M_REGS = 104;
+#ifndef ATT3_BWD_E_REGS
+#define ATT3_BWD_E_REGS 88
+#define ATT3_BWD_H_REGS 232
+#define ATT3_BWD_M_REGS 104
+#endif
+    constexpr int E_REGS = ATT3_BWD_E_REGS, H_REGS = ATT3_BWD_H_REGS, M_REGS = ATT3_BWD_M_REGS;
     static_assert(8 * E_REGS + 4 * H_REGS + 4 * M_REGS <= 2048, "register file: 64K registers / 32 lanes");
     // Optional cycle accounting of the hand-offs (one thread per role of CTA 0), compiled in only with
     // -DATT3_PIPE_TRACE: the bookkeeping costs registers in every role.
@@ -332,7 +337,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         fence_async_smem();
         cta_start_sync();
         constexpr int GB = L::G_BUFS;
-        constexpr int HB = 8;                 // staged chunks in flight per thread (registers: 4 per chunk)
+#ifndef ATT3_BWD_HB
+#define ATT3_BWD_HB 8
+#endif
+        constexpr int HB = ATT3_BWD_HB;                 // staged chunks in flight per thread (registers: 4 per chunk)
         int n = 0, it = 0, n_query = 0, ring_phase = 0;
         bool ok = true;
         float l_next = __ldg(p.l + row_at(q0, 0));

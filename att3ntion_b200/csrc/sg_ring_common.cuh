@@ -59,7 +59,10 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
 // cap (2x the run time); one polling lane per warp with __nanosleep(20) between polls was
 // 2.3x slower still (the sleep is far coarser than its argument).  The iteration count bounds
 // the total wait; the loop also leaves when another thread has raised the CTA's failure flag.
-constexpr uint32_t PIPE_WAIT_HINT_NS = 20000;   // suspend-time hint: a parked thread issues nothing until the phase flips
+#ifndef ATT3_WAIT_HINT_NS
+#define ATT3_WAIT_HINT_NS 20000
+#endif
+constexpr uint32_t PIPE_WAIT_HINT_NS = ATT3_WAIT_HINT_NS;   // suspend-time hint: a parked thread issues nothing until the phase flips
 __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volatile int* fail,
                                           long long* trace = nullptr, int code = 1) {
     const uint32_t addr = smem_u32(bar);
