@@ -860,7 +860,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                             warp_arrive(&bars[PB_RING_FREE], lane);
                             ring_arrived = true;
                         }
-                        const float s = warp_transpose_sum_2x16(va, vb, lane);
+                        const float s = warp_transpose_sum_2x16_packed(va, vb, lane);
                         red[(warp & 3) * D + ch * HD + c * 32 + lane] = s;
                     }
                     TL(18);

@@ -130,4 +130,40 @@ __device__ __forceinline__ float warp_transpose_sum_2x16(float (&va)[16], float 
     return va[0];
 }
 
+// The same lane sum with the first four exchange stages on packed BF16 pairs (adjacent values of a
+// lane share a register), the last one and the result in FP32: 80 instead of ~125 instructions.  The
+// partial sums are rounded to BF16 at each of the four packed stages (relative 2^-9 each), which is the
+// precision of the MMA operands these sums are built from; the gates leave an order of magnitude of room.
+__device__ __forceinline__ float warp_transpose_sum_2x16_packed(const float (&va)[16], const float (&vb)[16], int lane) {
+    uint32_t w[16];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        w[k] = pack_bf16x2(va[2 * k], va[2 * k + 1]);           // values 2k, 2k+1
+        w[8 + k] = pack_bf16x2(vb[2 * k], vb[2 * k + 1]);       // values 16+2k, 16+2k+1
+    }
+    // stage o (in values) exchanges value v with v ^ o across lanes l and l ^ o; in packed registers that is
+    // register r with r ^ (o/2) for o >= 2
+#pragma unroll
+    for (int o = 16; o >= 2; o >>= 1) {
+        const bool up = (lane & o) != 0;
+        const int h = o >> 1;                                  // packed registers per half
+#pragma unroll
+        for (int k = 0; k < h; ++k) {
+            const uint32_t send = up ? w[k] : w[k + h];
+            const uint32_t keep = up ? w[k + h] : w[k];
+            const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, send, o);
+            __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&keep);
+            __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&got);
+            __nv_bfloat162 c = __hadd2(a, b);
+            w[k] = *reinterpret_cast<uint32_t*>(&c);
+        }
+    }
+    // one register left: the two values of this lane pair; even lanes finish the first, odd lanes the second
+    const float2 mine = unpack_bf16x2(w[0]);
+    const bool odd = (lane & 1) != 0;
+    const float send = odd ? mine.x : mine.y;
+    const float keep = odd ? mine.y : mine.x;
+    return keep + __shfl_xor_sync(0xFFFFFFFFu, send, 1);
+}
+
 }  // namespace sgring

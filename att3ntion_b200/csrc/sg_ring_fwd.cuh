@@ -463,7 +463,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
                 }
                 // (a shared-memory transpose for this lane sum was measured slower: it competes with the
                 //  MMA operand reads for shared-memory bandwidth)
-                const float s = warp_transpose_sum_2x16(va, vb, lane);
+                const float s = warp_transpose_sum_2x16_packed(va, vb, lane);
                 red[quarter * (D + 4) + ch * HD + c * 32 + lane] = s;
             }
             float wl = l_half;

@@ -407,6 +407,57 @@ def run_rows(args):
     dist.destroy_process_group()
 
 
+def run_other(args):
+    """Secondary configurations, one GPU, device-resident inputs, CUDA events, median of `--steps`
+    repeats: C3 = independent-head single gather B4 H8 N2048 D64 w128 (16*D*T FLOPs), C2 = three-gather
+    operator B8 H4 N256 D64 without mask or scatter (3*(4+14)*D*B*H*N^3 FLOPs, the reference's own count)."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the sm_100a kernels have no CPU path")
+    from att3ntion_b200 import _cuda_kernels as ck
+    dev = torch.device("cuda", 0)
+    reps = max(3, min(args.steps, 20))
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record(); torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    out = {}
+    g = torch.Generator(device="cpu").manual_seed(2)
+    b3, h3, n3, d3, w3 = 4, 8, 2048, 64, 128
+    t5 = [(torch.randn(b3, h3, n3, d3, generator=g) / math.sqrt(d3)).to(torch.bfloat16).to(dev) for _ in range(5)]
+    dy = torch.randn(b3, h3, n3, d3, generator=g).to(torch.bfloat16).to(dev)
+
+    def c3():
+        Y, m, l = ck.sg_forward_raw(*t5, None, w3)
+        ck.sg_backward_raw(dy, *t5, Y, m, l, None, w3)
+    ms = timed(c3)
+    fl = 16 * d3 * triplets(b3, h3, n3, w3)
+    out["C3 single gather B4 H8 N2048 D64 w128"] = {"ms": ms, "TFLOP/s": fl / ms / 1e9}
+
+    g = torch.Generator(device="cpu").manual_seed(1)
+    b2, h2, n2, d2 = 8, 4, 256, 64
+    ins = [(torch.randn(b2, h2, n2, d2, generator=g) * (0.5 if k < 3 else 1.0)).to(torch.bfloat16).to(dev) for k in range(9)]
+    for k in (4, 6, 8):
+        ins[k].zero_()
+    cot = [torch.randn(b2, h2, n2, d2, generator=g).to(torch.bfloat16).to(dev) for _ in range(3)] + \
+          [torch.zeros(b2, h2, n2, d2, dtype=torch.bfloat16, device=dev) for _ in range(3)]
+
+    def c2():
+        o = ck.forward(*ins, 0.0, -1, -1, -1, None, 0)
+        ck.backward(*cot, *ins, *o[6:12], 0.0, None, o[0], o[1], o[2])
+    ms = timed(c2)
+    fl = 3 * (4 + 14) * d2 * b2 * h2 * n2 ** 3
+    out["C2 three-gather B8 H4 N256 D64"] = {"ms": ms, "TFLOP/s": fl / ms / 1e9}
+    ck.device_status()
+    print(json.dumps({"secondary_configs": out, "repeats": reps, "data": "synthetic"}))
+
+
 # DRAM bytes (read + write) of one sg_ring_bwd_kernel launch, from the ncu capture summarised in
 # profiles/sg_ring_w128_d128_pipelined.md: 162.5 MB (key side S + dQ) and 140.0 MB (key side R) at
 # B4 Hq8 Hkv1 N4096 D128 w128, i.e. 9232 bytes per (batch, query) on average over the two launches
@@ -429,7 +480,7 @@ if __name__ == "__main__":
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--seq-len", type=int, default=N, help="sequence length (profiling captures use a smaller case)")
     ap.add_argument("--batch", type=int, default=B)
-    ap.add_argument("--workload", default="batch", choices=["batch", "rows"],
+    ap.add_argument("--workload", default="batch", choices=["batch", "rows", "other"],
                     help="batch: config 4, one batch per GPU (default); rows: config 5, one sequence row-sharded")
     ap.add_argument("--profile", action="store_true",
                     help="kernel-only run for profiler captures: exact warm-up count, no e2e and no CPU leg")
@@ -437,6 +488,8 @@ if __name__ == "__main__":
     N, B = a.seq_len, a.batch
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload == "other":
+        run_other(a)
     elif a.workload == "rows":
         run_rows(a)
     else:
