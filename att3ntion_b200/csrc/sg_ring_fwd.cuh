@@ -165,7 +165,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
         p.trace[warp] = static_cast<long long>(n) * 1000 + (site); } while (0)
 #define PROGV(v, site) do { if (p.trace && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) \
         p.trace[warp] = static_cast<long long>(v) * 1000 + (site); } while (0)
+    // cycles of thread 0 of CTA 0 between marks, summed per slot (16 + k)
+    long long cyc_mark = clock64();
+#define CYC(k) do { if (p.trace && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { \
+        const long long now_ = clock64(); p.trace[16 + (k)] += now_ - cyc_mark; cyc_mark = now_; } } while (0)
 #else
+#define CYC(k) do { } while (0)
 #define PROG(site) do { } while (0)
 #define PROGV(v, site) do { } while (0)
 #endif
@@ -424,9 +429,11 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
             const int ub = m & 1;
             if (!finish()) return false;
             PROGV(m, 32);
+            CYC(7);                                       // finish() of the head before
             bool r = pipe_wait(&bars[FB_U_DONE0 + ub], (m >> 1) & 1, sFail, nullptr, 32);
             if (!r) return false;
             tc_fence_after();
+            CYC(8);                                       // wait U_done
             const uint32_t tU = tl + ub * 256 + 128 + ch * HD;
             float* red = sRed + ub * 4 * (D + 4);
             constexpr int NC = HD / 32;
@@ -525,12 +532,16 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
                 const int xb = n & 1;
                 const uint32_t tX = tl + xb * 256 + ch * 64;          // this thread's 64 score columns
                 PROG(30);
+                CYC(0);                                   // loop overhead since the last mark
                 ok = pipe_wait(&bars[FB_X_DONE0 + xb], (n >> 1) & 1, sFail, nullptr, 30);
                 if (!ok) break;
                 tc_fence_after();
+                CYC(1);                                   // wait X_done
                 // ---- maximum of this thread's half row; the other half belongs to the thread with the same
                 //      lane in the partner warp, and the exchange completes behind the epilogue below
-                float mh = -INFINITY;
+                // four independent running maxima: one chain of 64 dependent max operations would cost
+                // more than the loads
+                float mh0 = -INFINITY, mh1 = -INFINITY, mh2 = -INFINITY, mh3 = -INFINITY;
 #pragma unroll 1
                 for (int cc = 0; cc < 2; ++cc) {
                     uint32_t x[32];
@@ -539,13 +550,23 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
                     const uint32_t cw = cc ? cw1 : cw0;
                     if (all_vis) {
 #pragma unroll
-                        for (int t = 0; t < 32; ++t) mh = fmaxf(mh, __uint_as_float(x[t]));
+                        for (int t = 0; t < 32; t += 8) {
+                            mh0 = fmaxf(mh0, fmaxf(__uint_as_float(x[t]), __uint_as_float(x[t + 1])));
+                            mh1 = fmaxf(mh1, fmaxf(__uint_as_float(x[t + 2]), __uint_as_float(x[t + 3])));
+                            mh2 = fmaxf(mh2, fmaxf(__uint_as_float(x[t + 4]), __uint_as_float(x[t + 5])));
+                            mh3 = fmaxf(mh3, fmaxf(__uint_as_float(x[t + 6]), __uint_as_float(x[t + 7])));
+                        }
                     } else {
 #pragma unroll
-                        for (int t = 0; t < 32; ++t)
-                            if ((cw >> t) & 1u) mh = fmaxf(mh, __uint_as_float(x[t]));
+                        for (int t = 0; t < 32; t += 4) {
+                            if ((cw >> t) & 1u) mh0 = fmaxf(mh0, __uint_as_float(x[t]));
+                            if ((cw >> (t + 1)) & 1u) mh1 = fmaxf(mh1, __uint_as_float(x[t + 1]));
+                            if ((cw >> (t + 2)) & 1u) mh2 = fmaxf(mh2, __uint_as_float(x[t + 2]));
+                            if ((cw >> (t + 3)) & 1u) mh3 = fmaxf(mh3, __uint_as_float(x[t + 3]));
+                        }
                     }
                 }
+                const float mh = fmaxf(fmaxf(mh0, mh1), fmaxf(mh2, mh3));
                 {
                     float m_w = mh;
 #pragma unroll
@@ -553,19 +574,23 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
                     if (lane == 0) sMpart[xb * 8 + warp] = m_w;
                 }
                 warp_arrive(&bars[FB_M_SYNC], lane);
+                CYC(2);                                   // maximum pass
                 // ---- epilogue of the previous head, behind its U product; then the ring rows of a new key
                 if (pend) { ok = epilogue(pend_n, pend_row, pend_m, pend_l); pend = false; }
+                CYC(3);                                   // epilogue incl. its waits
                 if (ok && boundary) ok = ring_update(i);
                 if (!ok) break;
+                CYC(4);                                   // ring update
                 PROG(31);
                 ok = pipe_wait(&bars[FB_M_SYNC], n & 1, sFail, nullptr, 31);
                 if (!ok) break;
+                CYC(5);                                   // wait M_sync
                 const float* mp = sMpart + xb * 8;
                 const float M = fmaxf(fmaxf(fmaxf(mp[0], mp[1]), fmaxf(mp[2], mp[3])),
                                       fmaxf(fmaxf(mp[4], mp[5]), fmaxf(mp[6], mp[7])));
                 const float mc = M * c2;
                 // ---- P = exp2((x - M) c2), BF16 over the first 32 of this thread's columns; half-row sum
-                float l_half = 0.f;
+                float ls[4] = {0.f, 0.f, 0.f, 0.f};          // independent partial sums (no 32-long add chain)
 #pragma unroll 1
                 for (int cc = 0; cc < 2; ++cc) {
                     uint32_t x[32], pk[16];
@@ -580,15 +605,17 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
                             if (!((cw >> t) & 1u)) e0 = 0.f;
                             if (!((cw >> (t + 1)) & 1u)) e1 = 0.f;
                         }
-                        l_half += e0 + e1;
+                        ls[(t >> 1) & 3] += e0 + e1;
                         pk[t >> 1] = pack_bf16x2(e0, e1);
                     }
                     tmem_st16(tX + cc * 16, pk);
                 }
+                const float l_half = (ls[0] + ls[1]) + (ls[2] + ls[3]);
                 tmem_wait_st();
                 tc_fence_before();
                 // P_full also tells the MMA warp that the Vs ring row is current (ring_update above)
                 warp_arrive(&bars[FB_P_FULL0 + xb], lane);
+                CYC(6);                                   // exponential pass
                 pend = true; pend_n = n; pend_row = row; pend_m = M; pend_l = l_half;
                 ++n;
             }
@@ -600,6 +627,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
     __syncthreads();
 #undef PROG
 #undef PROGV
+#undef CYC
     if (*sFail && tid == 0) atomicExch(p.status, 100 + *sFail);
     if (is_mma) tmem_dealloc(tmem_base, TMEM_COLS);
 }
