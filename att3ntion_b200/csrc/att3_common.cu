@@ -82,6 +82,32 @@ TimedLaunch::~TimedLaunch() {
     g_time_recs.push_back({id_, start_, stop});
 }
 
+int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int cols, const char* who) {
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        return reinterpret_cast<EncodeFn>(fn);
+    }();
+    if (!encode) return set_error(ATT3_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available from this driver", who);
+    if (cols <= 0 || cols > 256 || (cols * 2) % 16 != 0 || reinterpret_cast<uintptr_t>(base) % 16 != 0)
+        return set_error(ATT3_ERR_INVALID, "%s: row tensor map needs 16-byte aligned rows of at most 256 BF16", who);
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};       // bytes between rows
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(cols), 1};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(ATT3_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed (CUresult %d)", who, int(r));
+    return ATT3_OK;
+}
+
 }  // namespace att3
 
 extern "C" int att3_timing_enable(int on) { return att3::g_time_on.exchange(on ? 1 : 0); }

@@ -166,6 +166,15 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status_ptr();
     p.trace = trace_ptr();
+    {   // TMA descriptors for the kernel's row staging (one row per copy)
+        const size_t qrows = static_cast<size_t>(B) * Hq * N, krows = static_cast<size_t>(B) * Hkv * N;
+        int rc;
+        if ((rc = att3::make_row_tensor_map(&p.tmQ, Q, qrows, D, "att3_sg_forward"))) return rc;
+        if ((rc = att3::make_row_tensor_map(&p.tmR, R, krows, D, "att3_sg_forward"))) return rc;
+        if ((rc = att3::make_row_tensor_map(&p.tmVr, Vr, krows, D, "att3_sg_forward"))) return rc;
+        if ((rc = att3::make_row_tensor_map(&p.tmS, S, krows, D, "att3_sg_forward"))) return rc;
+        if ((rc = att3::make_row_tensor_map(&p.tmVs, Vs, krows, D, "att3_sg_forward"))) return rc;
+    }
     const int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, 16, &p.block_len);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return D == 64 ? launch_ring_fwd<64>(p, nblk, st) : launch_ring_fwd<128>(p, nblk, st);

@@ -48,6 +48,8 @@
 // Every wait is bounded and watches a CTA-wide failure flag (status code instead of a hang).
 #pragma once
 
+#include <cuda.h>
+
 #include "sg_ring_common.cuh"
 
 namespace sgring {
@@ -66,11 +68,13 @@ struct FwdParams {
     float scale;
     int* status;                   // device status word (bounded-wait failures)
     long long* trace;              // diagnostic progress words (null: off)
+    // TMA descriptors (box = one row) over Q viewed as [B*Hq*N, D] and R, Vr, S, Vs viewed as [B*Hkv*N, D]
+    CUtensorMap tmQ, tmR, tmVr, tmS, tmVs;
 };
 
 enum FwdBar {
     FB_QP_FULL0 = 0, FB_QP_FULL1, FB_X_DONE0, FB_X_DONE1, FB_P_FULL0, FB_P_FULL1, FB_U_DONE0, FB_U_DONE1,
-    FB_U_FREE0, FB_U_FREE1, FB_H_SYNC, FB_M_SYNC,
+    FB_U_FREE0, FB_U_FREE1, FB_H_SYNC, FB_M_SYNC, FB_STAGE0, FB_STAGE1,
     FB_E_SYNC, FB_NEXT_READY0, FB_COUNT = FB_NEXT_READY0 + 8
 };
 
@@ -97,7 +101,7 @@ struct FwdSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdParams p) {
+__global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __grid_constant__ FwdParams p) {
     using L = FwdSmem<D>;
     constexpr int CH = D / 8;            // 16-byte chunks per row
     constexpr int DW = D / 2;            // packed bf16x2 words per row
@@ -141,7 +145,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
             mbar_init(&bars[FB_U_FREE0 + x], 8);
         }
         mbar_init(&bars[FB_H_SYNC], 4);
-        for (int x = 0; x < NEXT_BUFS; ++x) mbar_init(&bars[FB_NEXT_READY0 + x], 4);
+        // staging barriers: one arrival (the issuing thread's expect_tx) plus the bytes the TMA copies deliver
+        for (int x = 0; x < NEXT_BUFS; ++x) mbar_init(&bars[FB_NEXT_READY0 + x], 1);
+        mbar_init(&bars[FB_STAGE0], 1);
+        mbar_init(&bars[FB_STAGE1], 1);
         mbar_init(&bars[FB_M_SYNC], 8);
         mbar_init(&bars[FB_E_SYNC], 8);
         fence_mbar_init();
@@ -211,28 +218,30 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
                 }
             }
         }
-        // Asynchronous staging, one commit group per call: the Q row of iteration `it` (threads [0, CH))
-        // and, when next_key >= 0, the four rows of the key that enters the ring with query next_key.
+        // Row staging by TMA, issued by one thread: the Q row of iteration `it` into its stage buffer and, when
+        // next_key >= 0, the four rows (R, Vr, S, Vs) of the key that enters the ring with query next_key.
+        // Each copy names an mbarrier that counts its bytes; the consumers wait on that barrier.
         auto h_stage = [&](int it, size_t row, int next_key) {
-            if (it >= 0 && hslot < CH) {
-                const uint32_t dst = smem_u32(sQst + (it & 1) * D) + hslot * 16;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
-                             "l"(reinterpret_cast<const uint4*>(p.Q + row * D) + hslot)
-                             : "memory");
+            if (hslot != 0) return;
+            if (it >= 0) {
+                uint64_t* bar = &bars[FB_STAGE0 + (it & 1)];
+                mbar_arrive_expect_tx(bar, D * 2);
+                tma_load_2d(sQst + (it & 1) * D, &p.tmQ, 0, static_cast<int>(row), bar);
             }
-            if (next_key >= 0 && hslot < 4 * CH) {
-                const int which = hslot / CH, c = hslot % CH;
-                const __nv_bfloat16* base = which == 0 ? gR : which == 1 ? gVr : which == 2 ? gS : gVs;
-                const uint32_t dst = smem_u32(sNext + (next_key & (NEXT_BUFS - 1)) * L::NEXT_BYTES + which * (D * 2)) + c * 16;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
-                             "l"(reinterpret_cast<const uint4*>(base + static_cast<size_t>(next_key) * D) + c)
-                             : "memory");
+            if (next_key >= 0) {
+                uint64_t* bar = &bars[FB_NEXT_READY0 + ((next_key - q0 - 1) & (NEXT_BUFS - 1))];
+                uint8_t* dst = sNext + (next_key & (NEXT_BUFS - 1)) * L::NEXT_BYTES;
+                const int krow = static_cast<int>(kv_base) + next_key;
+                mbar_arrive_expect_tx(bar, 4 * D * 2);
+                tma_load_2d(dst, &p.tmR, 0, krow, bar);
+                tma_load_2d(dst + D * 2, &p.tmVr, 0, krow, bar);
+                tma_load_2d(dst + 2 * D * 2, &p.tmS, 0, krow, bar);
+                tma_load_2d(dst + 3 * D * 2, &p.tmVs, 0, krow, bar);
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        h_stage(0, row_at(q0, 0), -1);
         fence_async_smem();
         cta_start_sync();
+        h_stage(0, row_at(q0, 0), -1);
         constexpr int HB = 8;                 // staged chunks in flight per thread
         int n = 0, it = 0;
         bool ok = true;
@@ -242,14 +251,21 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const FwdP
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
             const bool work = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
-                // the staged rows of this iteration have landed; everyone is past the previous build
-                asm volatile("cp.async.wait_all;" ::: "memory");
-                warp_arrive(&bars[FB_H_SYNC], lane);
-                ok = pipe_wait(&bars[FB_H_SYNC], it & 1, sFail, nullptr, 10);
-                if (!ok) break;
+                // The staged Q row of this iteration has landed (TMA byte counts; the issuing warp looks, the
+                // others learn it through H_sync, which that warp joins afterwards); everyone is past the
+                // previous build.
                 const bool boundary = hh == 0 && i > q0;      // key i replaces key i-128 in slot s
+                if (warp == 8) {
+                    ok = pipe_wait(&bars[FB_STAGE0 + (it & 1)], (it >> 1) & 1, sFail, nullptr, 13);
+                    if (ok && boundary) {
+                        const int fb = i - q0 - 1;            // the entering key's rows were requested one query ago
+                        ok = pipe_wait(&bars[FB_NEXT_READY0 + (fb & (NEXT_BUFS - 1))], (fb >> 3) & 1, sFail, nullptr, 14);
+                    }
+                }
+                warp_arrive(&bars[FB_H_SYNC], lane);
+                ok = ok & pipe_wait(&bars[FB_H_SYNC], it & 1, sFail, nullptr, 10);
+                if (!ok) break;
                 const uint8_t* nx = sNext + (i & (NEXT_BUFS - 1)) * L::NEXT_BYTES;
-                if (boundary) warp_arrive(&bars[FB_NEXT_READY0 + ((i - q0 - 1) & (NEXT_BUFS - 1))], lane);
                 if (boundary && hslot == s) {
                     const uint4* r4 = reinterpret_cast<const uint4*>(nx);
 #pragma unroll

@@ -87,6 +87,23 @@ __device__ __forceinline__ void fence_mbar_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
+// Arrive once and add `bytes` to the transaction count the current phase waits for (the bytes are
+// delivered by bulk / tensor copies that name this barrier).
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// TMA: one tile of a 2-D tensor map (box fixed in the map) from global to shared memory; completion is
+// counted in bytes on `bar`.  x is the innermost coordinate and must keep x * element size a multiple of 16
+// bytes (every call site passes 0); y may lie outside the tensor, where the fill value (zero) is read.
+// The destination must be 128-byte aligned.  No multicast: the copy lands in this CTA's shared memory only.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tensor_map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
 // Bounded parity wait.  Polls with the non-blocking test_wait so the bound is a
 // plain iteration count (a fraction of a second at the default limit).  Returns
 // true when the phase completed, false when the limit ran out.
