@@ -71,11 +71,8 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
     const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
 
     const int nwidth = (p.mode & 8) ? 64 : T;       // mode | 8: the same product restricted to N = 64 columns
-    p.tight = (p.mode >> 4) & 3;                      // 1: elect per MMA, 2: lane-0 thread, 3: elected once
-    const int extra = p.mode & ~63;                   // rate-probe conditions, see below
+    p.tight = (p.mode >> 4) & 1;                      // converged warp, one elected lane, precomputed descriptors
     p.mode &= 7;
-    __shared__ volatile int s_done;
-    if (tid == 0) s_done = 0;
     const bool a_in_tmem = (p.mode == 3 || p.mode == 4);
     if (a_in_tmem) {
         // Thread m holds row m of A: 128 BF16 = 64 packed words = columns [0,64) of the A region.
@@ -92,66 +89,7 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
     }
     __syncthreads();
 
-    if (p.tight >= 2 && warp == 0) {
-        // Rate probes for the plain SS product (mode 0): everything but the issue style is a
-        // compile-time constant.  tight 2: one thread (lane 0 branch) issues all MMAs back to
-        // back; tight 3: the lane is elected once and then issues all MMAs.
-        tc_fence_after();
-        const uint32_t idesc = make_idesc_bf16(T, T, 0, 0);
-        uint64_t da = make_smem_desc(smem_u32(sA), 16, 1024, SWIZZLE_128B);
-        uint64_t db = make_smem_desc(smem_u32(sB), 16, 1024, SWIZZLE_128B);
-        // Mode bit 64: add an offset (zero) that the compiler cannot prove warp-uniform, as a
-        // buffer index derived from a data-dependent loop counter would be; bit 128: the same
-        // offset passed through a shuffle from lane 0, which marks it warp-uniform.
-        if (extra & (64 | 128)) {
-            uint32_t roff = static_cast<uint32_t>(p.status[3]);
-            if (extra & 128) roff = __shfl_sync(0xFFFFFFFFu, roff, 0);
-            da += roff;
-            db += roff;
-        }
-        uint32_t elected = (tid == 0);
-        if (p.tight == 3)
-            asm volatile("{\n\t.reg .pred q;\n\t.reg .b32 rx;\n\telect.sync rx|q, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, q;\n\t}\n"
-                         : "=r"(elected));
-        long long t0 = 0, t1 = 0;
-        if (elected) {
-            t0 = clock64();
-            for (int rep = 0; rep < p.reps; ++rep) {
-#pragma unroll
-                for (int kk = 0; kk < T / 16; ++kk) {
-                    const uint32_t koff = ((kk >> 2) * (T * 128) + (kk & 3) * 32) / 16;
-                    if (a_in_tmem) umma_ts(tmem_d, tmem_a + kk * 8, db + koff, idesc, (rep > 0 || kk > 0) ? 1u : 0u);
-                    else if (kk == 0) umma_ss(tmem_d, da + koff, db + koff, idesc, rep > 0);
-                    else umma_ss(tmem_d, da + koff, db + koff, idesc, 1u);
-                }
-            }
-            t1 = clock64();
-            umma_commit(&mma_bar);
-            p.status[2] = static_cast<int>(t1 - t0);
-        }
-        __syncwarp();
-        if (tid == 0) t_issue = elected ? t0 : clock64();
-    } else if (p.tight >= 2 && (extra & (256 | 512))) {
-        // Rate probe under load (warps 1-3): bit 256 keeps tensor-memory loads of columns the MMAs do
-        // not touch in flight, bit 512 keeps 16-byte shared-memory stores in flight, until the issuing
-        // thread has seen the MMAs complete (bounded).
-        uint32_t r[32];
-        uint32_t sink = 0;
-        uint8_t* scratch = smem + 2 * TILE_BYTES + (warp - 1) * 2048;
-        for (int itn = 0; itn < 40000 && !s_done; ++itn) {
-            if (extra & 256) {
-                tmem_ld32(tmem_base + 192 + lane_field, r);
-                tmem_wait_ld();
-                sink ^= r[itn & 31];
-            }
-            if (extra & 512) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    *reinterpret_cast<uint4*>(scratch + ((tid & 31) * 16 + c * 512)) = make_uint4(sink, itn, c, tid);
-            }
-        }
-        if (sink == 0x12345678u) p.status[3] = 1;
-    } else if (p.tight && warp == 0) {
+    if (p.tight && warp == 0) {
         // Rate probe: whole warp converged, descriptor bases precomputed, k-steps unrolled.
         tc_fence_after();
         const int b_mn = (p.mode == 1 || p.mode == 3) ? 1 : 0;
@@ -207,7 +145,6 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
     if (tid == 0) {
         s_ok = mbar_wait(&mma_bar, 0) ? 1 : 0;
         p.status[1] = static_cast<int>(clock64() - t_issue);             // cycles from first issue to completion
-        s_done = 1;
     }
     __syncthreads();
     const bool ok = s_ok != 0;
@@ -237,7 +174,7 @@ __global__ void __launch_bounds__(128, 1) umma_selftest_kernel(SelftestParams p)
 extern "C" int att3_umma_selftest(const void* A, const void* B, float* D, int mode, int lbo_a, int sbo_a,
                                   int lbo_b, int sbo_b, int reps, int* status_dev, void* stream) {
     if (!A || !B || !D || !status_dev) return att3::set_error(ATT3_ERR_INVALID, "umma_selftest: null pointer");
-    if ((mode & 7) > 4 || mode < 0 || mode > 1023 || ((mode & 16) && (mode & 7) == 2) || reps < 1 || reps > 64)
+    if ((mode & 7) > 4 || mode < 0 || mode > 31 || ((mode & 16) && (mode & 7) == 2) || reps < 1 || reps > 64)
         return att3::set_error(ATT3_ERR_INVALID, "umma_selftest: mode must be 0..4 (+8: N = 64, +16: converged-warp issue) and reps 1..64");
     SelftestParams p;
     p.A = static_cast<const __nv_bfloat16*>(A);
@@ -248,7 +185,7 @@ extern "C" int att3_umma_selftest(const void* A, const void* B, float* D, int mo
     p.reps = reps;
     p.tight = 0;
     p.status = status_dev;
-    const int smem = 2 * TILE_BYTES + 1024 + 3 * 2048;
+    const int smem = 2 * TILE_BYTES + 1024;
     cudaError_t e = cudaFuncSetAttribute(umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return att3::set_cuda_error(e, "umma_selftest: smem opt-in");
     umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(p);

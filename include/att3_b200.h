@@ -210,7 +210,9 @@ int att3_timing_read(int kernel_id, double* total_ms, unsigned long long* launch
  * Self-test of the tensor-core building blocks: multiplies two 128x128 BF16
  * matrices on one CTA through the operand arrangement `mode` selects and
  * writes the FP32 product to D (mode | 8: only the first 64 output columns,
- * as an N = 64 instruction).  `reps` repeats the accumulation.  status_dev[0]
+ * as an N = 64 instruction; mode | 16: issued as the kernels issue, by a
+ * converged warp with one elected lane and precomputed descriptors).  `reps`
+ * repeats the accumulation.  status_dev[0]
  * receives 1 if a bounded wait ran out, status_dev[1] the cycles from the first
  * MMA issue to completion.  Used by the test-suite to pin the descriptor
  * encodings and by the throughput notes in profiles/.

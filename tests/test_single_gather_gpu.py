@@ -138,6 +138,33 @@ def test_extra_mask_dead_and_singleton_rows(ck, scale):
     assert grads["dQ"][:, :, 40].abs().max().item() == 0.0
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(1, 1), (8, 1)])
+def test_long_sequence_one_and_many_heads_per_key_head(ck, Hq, Hkv):
+    """Many query boundaries in one CTA, with one head per query (the H warps run several queries
+    ahead of the ring updates) and with eight."""
+    xs, dY = draw(1, Hq, Hkv, 1536 if Hq == 1 else 640, 128, seed=21)
+    ref = O.single_gather_banded(*[xs[n] for n in NAMES], window=128, dY=dY, chunk=64)
+    Y, m, l, grads = run_lowlevel(ck, xs, dY, None, 128)
+    check_all(Y, m, l, grads, ref)
+
+
+@pytest.mark.parametrize("Hq", [1, 4])
+def test_runs_of_dead_queries_between_live_ones(ck, Hq):
+    """Queries without any visible key in runs of one to five, also around multiples of 128: the
+    boundary duties (ring rows, accumulator flush) of queries that launch no MMA."""
+    B, N, D, w = 1, 400, 128, 64
+    xs, dY = draw(B, Hq, 1, N, D, seed=31)
+    mask = torch.ones(B, N, N, dtype=torch.bool)
+    for start, run in ((5, 1), (60, 3), (126, 5), (255, 2), (300, 4), (396, 4)):
+        mask[:, start:start + run, :] = False
+    ref = O.single_gather_banded(*[xs[n] for n in NAMES], window=w, dY=dY, mask=mask, chunk=40)
+    Y, m, l, grads = run_lowlevel(ck, xs, dY, mask, w)
+    check_all(Y, m, l, grads, ref)
+    dead = ~mask.any(-1)[0]
+    assert Y[:, :, dead].abs().max().item() == 0.0
+    assert grads["dQ"][:, :, dead].abs().max().item() == 0.0
+
+
 def test_all_masked_gives_zeros(ck):
     xs, dY = draw(1, 2, 1, 32, 128, seed=2)
     mask = torch.zeros(1, 32, 32, dtype=torch.bool)
