@@ -46,6 +46,12 @@ struct BwdParams {
     float* dKb;                      // [B,H,N,D] FP32, this kernel adds into it
     float* dVb;
     float* dA_part;                  // [n_tiles][B,H,N,D] FP32 partial planes, zero-filled by the caller
+    // Anchor chunks: with few (tile, batch, head) triples the anchors are split over a_chunks CTAs per
+    // triple (grid.x = n_tiles * a_chunks).  Chunk 0 adds into dKb / dVb; chunk 1 adds into its own
+    // zero-filled planes, which the caller adds afterwards, so the order of the sums stays fixed.
+    int a_chunks;                    // 1 or 2
+    float* dKb1;
+    float* dVb1;
     int B, H, N, D, n_valid;
     float scale;
     int* status;
@@ -90,11 +96,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
     const uint32_t issuer = elect_one();     // one lane per warp; warp 0 predicates its MMAs on it
     const int slot = tid & (TILE - 1);
     const int half = tid >> 7;
-    const int b = blockIdx.z, h = blockIdx.y, kb = blockIdx.x;
+    const int b = blockIdx.z, h = blockIdx.y;
     const int N = p.N, D = p.D;
     const int n_keys = (p.n_valid > 0 && p.n_valid < N) ? p.n_valid : N;
     const int n_tiles = (n_keys + TILE - 1) / TILE;
-    if (kb >= n_tiles) return;
+    const int kb = blockIdx.x % n_tiles, chunk = blockIdx.x / n_tiles;
+    const int a_begin = static_cast<int>((static_cast<long long>(N) * chunk) / p.a_chunks);
+    const int a_end = static_cast<int>((static_cast<long long>(N) * (chunk + 1)) / p.a_chunks);
 
     if (warp == 0) {
         tmem_alloc(tmem_slot, TMEM_COLS);
@@ -175,7 +183,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
         }
         fence_async_smem();
 
-        for (int a = 0; a < N && !failed; ++a) {
+        for (int a = a_begin; a < a_end && !failed; ++a) {
             // visibility from anchor a: own-side keys of this tile, other-side keys of tile jb
             {
                 bool vo = own_key < n_keys, vt = oth_key < n_keys;
@@ -339,7 +347,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
     }
     // Add the tile's accumulators into the FP32 outputs (this CTA is the only writer of these rows).
     if (!failed) {
-        float* dst_base = half ? p.dVb : p.dKb;
+        float* dst_base = chunk == 0 ? (half ? p.dVb : p.dKb) : (half ? p.dVb1 : p.dKb1);
         const float mul = half ? 1.0f : p.scale;
         uint32_t acc[32];
 #pragma unroll 1

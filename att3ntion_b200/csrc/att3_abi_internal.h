@@ -49,10 +49,12 @@ int dense_gather_forward(const void* A, const void* Rw, const void* C, const voi
                          cudaStream_t st);
 // Backward for one key side: adds d(Kb), d(Vb) into FP32 planes; if dA_part is non-null also
 // accumulates the anchor gradient into one zero-filled partial plane per 128-key tile of the own side.
+// chunk_scratch: optional two planes of scratch; with it, short sequences split their anchors over two CTAs
+// per (tile, batch, head) and the second CTA's sums are added from there afterwards (fixed order).
 int dense_gather_backward_side(const void* A, const void* dY, const void* Y, const float* m, const float* l,
                                const void* Ka, const void* Va, const void* Kb, const void* Vb, const uint8_t* mask,
                                float* dKb, float* dVb, float* dA_part, int B, int H, int N, int D, int n_valid,
-                               cudaStream_t st);
+                               cudaStream_t st, float* chunk_scratch = nullptr);
 int dense_tiles(int N, int n_valid);
 int add_planes(const float* src, int n_src, size_t plane, float* acc, cudaStream_t st);
 int plane_to_bf16(const float* src, void* out, size_t n, cudaStream_t st);

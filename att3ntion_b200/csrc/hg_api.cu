@@ -40,7 +40,7 @@ int launch_bwd(const agdense::BwdParams& p, int n_tiles, cudaStream_t st) {
     using L = agdense::BwdSmem<DP, WITH_DA>;
     if (int rc = opt_in_smem(agdense::ag_dense_bwd_kernel<DP, WITH_DA>, L::ALLOC, "dense gather backward: shared-memory opt-in"))
         return rc;
-    dim3 grid(n_tiles, p.H, p.B);
+    dim3 grid(n_tiles * p.a_chunks, p.H, p.B);
     att3::TimedLaunch timed(att3::K_DENSE_BWD, st);
     agdense::ag_dense_bwd_kernel<DP, WITH_DA><<<grid, agdense::BWD_THREADS, L::ALLOC, st>>>(p);
     cudaError_t e = cudaGetLastError();
@@ -92,7 +92,7 @@ int dense_gather_forward(const void* A, const void* Rw, const void* C, const voi
 int dense_gather_backward_side(const void* A, const void* dY, const void* Y, const float* m, const float* l,
                                const void* Ka, const void* Va, const void* Kb, const void* Vb, const uint8_t* mask,
                                float* dKb, float* dVb, float* dA_part, int B, int H, int N, int D, int n_valid,
-                               cudaStream_t st) {
+                               cudaStream_t st, float* chunk_scratch) {
     agdense::BwdParams p;
     p.A = static_cast<const __nv_bfloat16*>(A);
     p.dY = static_cast<const __nv_bfloat16*>(dY);
@@ -108,8 +108,19 @@ int dense_gather_backward_side(const void* A, const void* dY, const void* Y, con
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = ag_status_ptr();
     const int nt = dense_tiles(N, n_valid);
-    if (dA_part) return D > 64 ? launch_bwd<128, true>(p, nt, st) : launch_bwd<64, true>(p, nt, st);
-    return D > 64 ? launch_bwd<128, false>(p, nt, st) : launch_bwd<64, false>(p, nt, st);
+    // One CTA per (own tile, batch, head) leaves most SMs idle for short sequences: split the anchors in two
+    // when that still fits the machine and the caller has given room for the second chunk's planes.
+    const size_t plane = static_cast<size_t>(B) * H * N * D;
+    p.a_chunks = (chunk_scratch && 2 * nt * B * H <= sm_count() && N >= 2) ? 2 : 1;
+    p.dKb1 = chunk_scratch;
+    p.dVb1 = chunk_scratch ? chunk_scratch + plane : nullptr;
+    if (p.a_chunks == 2) cudaMemsetAsync(chunk_scratch, 0, 2 * plane * sizeof(float), st);
+    int rc;
+    if (dA_part) rc = D > 64 ? launch_bwd<128, true>(p, nt, st) : launch_bwd<64, true>(p, nt, st);
+    else rc = D > 64 ? launch_bwd<128, false>(p, nt, st) : launch_bwd<64, false>(p, nt, st);
+    if (rc || p.a_chunks == 1) return rc;
+    if ((rc = add_planes(p.dKb1, 1, plane, dKb, st))) return rc;
+    return add_planes(p.dVb1, 1, plane, dVb, st);
 }
 
 int add_planes(const float* src, int n_src, size_t plane, float* acc, cudaStream_t st) {
@@ -301,8 +312,8 @@ extern "C" int att3_hg_forward(const void* Q, const void* R, const void* S, cons
 extern "C" size_t att3_hg_backward_workspace_bytes(int B, int H, int N, int D) {
     if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
     const size_t plane = static_cast<size_t>(B) * H * N * D * sizeof(float);
-    // the scatter terms use three planes of the same scratch area
-    return plane * (9 + std::max(att3::dense_tiles(N, 0), 3));
+    // the scatter terms use three planes of the same scratch area; two more for the anchor chunks of short sequences
+    return plane * (9 + std::max(att3::dense_tiles(N, 0), 3) + 2);
 }
 
 extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gYs, const void* gYq_,
@@ -335,7 +346,7 @@ extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gY
     float* ws = static_cast<float*>(workspace);
     float *gQ = ws, *gR = ws + plane, *gS = ws + 2 * plane, *gVq1 = ws + 3 * plane, *gVq2 = ws + 4 * plane,
           *gVr1 = ws + 5 * plane, *gVr2 = ws + 6 * plane, *gVs1 = ws + 7 * plane, *gVs2 = ws + 8 * plane,
-          *part = ws + 9 * plane;
+          *part = ws + 9 * plane, *chunk_scratch = part + static_cast<size_t>(std::max(att3::dense_tiles(N, 0), 3)) * plane;
     cudaMemsetAsync(ws, 0, 9 * plane * sizeof(float), st);
 
     // One anchored gather: anchor A with statistics (m,l), rows (Kr,Vr), cols (Kc,Vc).
@@ -344,11 +355,11 @@ extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gY
                           float* gVc) -> int {
         cudaMemsetAsync(part, 0, static_cast<size_t>(nt) * plane * sizeof(float), st);
         int rc = att3::dense_gather_backward_side(A, gY, Y, m, l, Kr, Vr, Kc, Vc, mask, gKc, gVc, part, B, H, N, D,
-                                                  n_valid, st);
+                                                  n_valid, st, chunk_scratch);
         if (rc) return rc;
         if ((rc = att3::add_planes(part, nt, plane, gA, st))) return rc;
         rc = att3::dense_gather_backward_side(A, gY, Y, m, l, Kc, Vc, Kr, Vr, mask, gKr, gVr, nullptr, B, H, N, D,
-                                              n_valid, st);
+                                              n_valid, st, chunk_scratch);
         att3::count_launch(3, 3);
         return rc;
     };

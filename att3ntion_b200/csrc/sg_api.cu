@@ -190,7 +190,7 @@ extern "C" size_t att3_sg_backward_workspace_bytes(int B, int Hq, int Hkv, int N
     (void)Hq;
     if (B <= 0 || Hkv <= 0 || N <= 0 || D <= 0 || window < 0) return 0;
     if (window == 0)   // dense: five FP32 gradient planes + one anchor-gradient partial plane per 128-key tile
-        return static_cast<size_t>(5 + att3::dense_tiles(N, 0)) * B * Hq * N * D * sizeof(float);
+        return static_cast<size_t>(5 + att3::dense_tiles(N, 0) + 2) * B * Hq * N * D * sizeof(float);
     return static_cast<size_t>(4) * B * Hkv * N * D * sizeof(float);
 }
 
@@ -259,12 +259,14 @@ extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, co
         const int nt = att3::dense_tiles(N, 0);
         float* ws = static_cast<float*>(workspace);
         float *gQ = ws, *gR = ws + plane, *gS = ws + 2 * plane, *gVr = ws + 3 * plane, *gVs = ws + 4 * plane,
-              *part = ws + 5 * plane;
+              *part = ws + 5 * plane, *chunk_scratch = part + static_cast<size_t>(nt) * plane;
         cudaMemsetAsync(ws, 0, (5 + static_cast<size_t>(nt)) * plane * sizeof(float), st);
-        int rc = att3::dense_gather_backward_side(Q, dY, Y, m, l, R, Vr, S, Vs, mask, gS, gVs, part, B, Hq, N, D, 0, st);
+        int rc = att3::dense_gather_backward_side(Q, dY, Y, m, l, R, Vr, S, Vs, mask, gS, gVs, part, B, Hq, N, D, 0, st,
+                                                  chunk_scratch);
         if (rc) return rc;
         if ((rc = att3::add_planes(part, nt, plane, gQ, st))) return rc;
-        if ((rc = att3::dense_gather_backward_side(Q, dY, Y, m, l, S, Vs, R, Vr, mask, gR, gVr, nullptr, B, Hq, N, D, 0, st)))
+        if ((rc = att3::dense_gather_backward_side(Q, dY, Y, m, l, S, Vs, R, Vr, mask, gR, gVr, nullptr, B, Hq, N, D, 0, st,
+                                                   chunk_scratch)))
             return rc;
         att3::count_launch(1, 3);
         void* outs[5] = {dQ, dR, dS, dVr, dVs};
