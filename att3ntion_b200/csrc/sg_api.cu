@@ -69,7 +69,7 @@ int plan_blocks(int B, int Hkv, int N, int q_begin, int sm_count, int ctas_per_s
 extern "C" int att3_sg_query_blocks(int B, int Hq, int Hkv, int N, int q_begin, int sm_count, int* block_len) {
     (void)Hq;
     int len = 0;
-    const int n = plan_blocks(B, Hkv, N, q_begin, sm_count, 2, 16, &len);
+    const int n = plan_blocks(B, Hkv, N, q_begin, sm_count, 1, 16, &len);     // the forward: one CTA per SM
     if (block_len) *block_len = len;
     return n * B * Hkv;
 }
