@@ -2,7 +2,7 @@
 
 Run in a container that has the reference mounted:
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <path of the reference checkout>]
 
 What is imported from the reference (never copied):
   * tests/test_single_gather.py::reference      fp64 single-gather oracle (52-66)
