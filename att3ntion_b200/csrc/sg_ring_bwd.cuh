@@ -344,6 +344,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         int n = 0, it = 0, n_query = 0, ring_phase = 0;
         bool ok = true;
         float l_next = __ldg(p.l + row_at(q0, 0));
+#pragma unroll 1
         for (int i = q0; i < q1 && ok; ++i) {
             const bool prev_work = n > n_query;      // the previous query issued MMAs: Ring_free completes for it
             n_query = n;
@@ -351,6 +352,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             uint32_t vw[4];
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
             const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
+#pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
                 const float l_i = l_next;
                 if (it + 1 < n_iter) l_next = __ldg(p.l + next_row(i, hh));
@@ -471,6 +473,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         if (!is_mma) {
             // ============================================================== flush warps (quarters 1-3)
             bool okf = true;
+#pragma unroll 1
             for (int fb = 0; fb < n_bound && okf; ++fb) {
                 const int i = q0 + 1 + fb, s = i & (RING - 1);
                 okf = pipe_wait(&bars[PB_ACC_DONE], fb & 1, sFail);     // every MMA of the queries before i is complete
@@ -514,11 +517,11 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         // A-operand column of k-step kk inside a region: the E thread of column half c keeps its
         // BF16 results inside its own 64 score columns, P^T in the first 32 and gA^T in the last 32.
         auto a_col = [](int kk) -> uint32_t { return 64u * (kk >> 2) + 8u * (kk & 3); };
-        // The MMA runs are rolled loops: this warp's instruction stream is on the critical path of every
-        // hand-off, and with each run unrolled its code alone was 40 KB that the instruction cache kept
-        // refetching; the few extra instructions per MMA stay well under the 64 cycles an MMA occupies
-        // the tensor pipe.  K-major operands: k-step kk moves the start address (16-byte units) by
-        // 2 per step inside a 64-element block and RING*8 per block.  A from tensor memory: see a_col.
+        // The MMA runs are unrolled with compile-time operand offsets (rolled loops issued ~2 % slower), and the
+        // rest of this warp's code is kept compact: its instruction stream is on the critical path of every
+        // hand-off, and the three roles together are close to what the instruction cache holds.  K-major
+        // operands: k-step kk moves the start address (16-byte units) by 2 per step inside a 64-element
+        // block and RING*8 per block.  A from tensor memory: see a_col.
         auto run_ss = [&](uint32_t tD, uint64_t dA, uint64_t dB) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
@@ -575,6 +578,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             }
             return r;
         };
+#pragma unroll 1
         for (int i = q0; i < q1 && ok; ++i) {
             if (i > q0) {
                 // A query without work leaves its boundary unsettled: do it now, so that commits, flushes
@@ -592,6 +596,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             uint32_t vw[4];
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
             const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
+#pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
                 const float l_i = l_next;
                 if (it + 1 < n_iter) l_next = __ldg(p.l + next_row(i, hh));
@@ -708,6 +713,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         prefetch(row_at(q0, 0));
         int n = 0, it = 0, n_query = 0;
         bool ok = true;
+#pragma unroll 1
         for (int i = q0; i < q1 && ok; ++i) {
             uint32_t vw[4];
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
@@ -719,6 +725,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             const uint32_t cw0 = my_vis ? (ch ? vw[2] : vw[0]) : 0u;
             const uint32_t cw1 = my_vis ? (ch ? vw[3] : vw[1]) : 0u;
             bool ring_arrived = false;
+#pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
                 const size_t row = row_at(i, hh);
                 // delta = dY . Y and lse (log2 units) of this head from the prefetched slices

@@ -52,32 +52,52 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
     if (lane == 0) mbar_arrive(bar);
 }
 
-// Bounded wait that also leaves when another thread has raised the CTA's failure flag.
 // Bounded wait on an mbarrier phase.  try_wait parks the thread in hardware until the phase
-// completes or a system time limit passes.  Measured alternatives on this part, same kernel:
+// completes or a system time limit passes.  Measured alternatives on this part, same kernels:
 // all threads spinning on test_wait pulled the SM clock from 1.9 to 1.3 GHz under the power
 // cap (2x the run time); one polling lane per warp with __nanosleep(20) between polls was
-// 2.3x slower still (the sleep is far coarser than its argument).  The iteration count bounds
-// the total wait; the loop also leaves when another thread has raised the CTA's failure flag.
-#ifndef ATT3_WAIT_HINT_NS
-#define ATT3_WAIT_HINT_NS 20000
-#endif
-constexpr uint32_t PIPE_WAIT_HINT_NS = ATT3_WAIT_HINT_NS;   // suspend-time hint: a parked thread issues nothing until the phase flips
+// 2.3x slower still (the sleep is far coarser than its argument); one polling lane with the
+// result shuffled to the others costs 245 cycles on a complete phase against 50-90 for all
+// 32 lanes waiting together (the divergent branch, not the barrier, is what costs).  On a
+// complete phase test_wait and try_wait without a time hint return in ~50 cycles, try_wait
+// with a hint in ~90: the loop therefore gives no hint (forward 4.42 -> 4.27 ms, backward
+// 11.07 -> 10.68 ms on B4 Hq8 N8192), and TEST_FIRST puts a plain test in front of it, which
+// gained another 0.1 ms in the forward and lost as much in the backward.  The iteration
+// count bounds the total wait: a poll of a pending phase returns after the system limit,
+// measured at 7.8 k cycles (4 us), so a wait gives up after about 2 s; the loop also leaves
+// when another thread has raised the CTA's failure flag.
+template <bool TEST_FIRST = false>
 __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volatile int* fail,
                                           long long* trace = nullptr, int code = 1) {
     const uint32_t addr = smem_u32(bar);
-    const long long t0 = trace ? clock64() : 0;
-#pragma unroll 1
-    for (uint32_t it = 0; it < (1u << 18); ++it) {
+    if (TEST_FIRST) {
         uint32_t done;
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t"
             "}\n"
             : "=r"(done)
-            : "r"(addr), "r"(parity), "r"(PIPE_WAIT_HINT_NS)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) {
+            if (trace) trace[64] += 1;
+            return true;
+        }
+    }
+    const long long t0 = trace ? clock64() : 0;
+#pragma unroll 1
+    for (uint32_t it = 0; it < (1u << 19); ++it) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
             : "memory");
         if (done) {
             if (trace) {

@@ -245,25 +245,27 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         constexpr int HB = 8;                 // staged chunks in flight per thread
         int n = 0, it = 0;
         bool ok = true;
+#pragma unroll 1
         for (int i = q0; i < q1 && ok; ++i) {
             const int s = i & (RING - 1);
             uint32_t vw[4];
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
             const bool work = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
+#pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
                 // The staged Q row of this iteration has landed (TMA byte counts; the issuing warp looks, the
                 // others learn it through H_sync, which that warp joins afterwards); everyone is past the
                 // previous build.
                 const bool boundary = hh == 0 && i > q0;      // key i replaces key i-128 in slot s
                 if (warp == 8) {
-                    ok = pipe_wait(&bars[FB_STAGE0 + (it & 1)], (it >> 1) & 1, sFail, nullptr, 13);
+                    ok = pipe_wait<true>(&bars[FB_STAGE0 + (it & 1)], (it >> 1) & 1, sFail, nullptr, 13);
                     if (ok && boundary) {
                         const int fb = i - q0 - 1;            // the entering key's rows were requested one query ago
-                        ok = pipe_wait(&bars[FB_NEXT_READY0 + (fb & (NEXT_BUFS - 1))], (fb >> 3) & 1, sFail, nullptr, 14);
+                        ok = pipe_wait<true>(&bars[FB_NEXT_READY0 + (fb & (NEXT_BUFS - 1))], (fb >> 3) & 1, sFail, nullptr, 14);
                     }
                 }
                 warp_arrive(&bars[FB_H_SYNC], lane);
-                ok = ok & pipe_wait(&bars[FB_H_SYNC], it & 1, sFail, nullptr, 10);
+                ok = ok & pipe_wait<true>(&bars[FB_H_SYNC], it & 1, sFail, nullptr, 10);
                 if (!ok) break;
                 const uint8_t* nx = sNext + (i & (NEXT_BUFS - 1)) * L::NEXT_BYTES;
                 if (boundary && hslot == s) {
@@ -279,7 +281,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 if (work) {
                     // Qp[n&1] was last read by the score MMAs of head n-2
                     PROG(11);
-                    if (n >= 2) ok = pipe_wait(&bars[FB_X_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, nullptr, 11);
+                    if (n >= 2) ok = pipe_wait<true>(&bars[FB_X_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, nullptr, 11);
                     if (!ok) break;
                     uint8_t* dQp = sQp + qb * L::TILE;
                     const uint4* q4 = reinterpret_cast<const uint4*>(sQst + (it & 1) * D);
@@ -306,7 +308,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                     // last one is head n-1; this thread waits for the same phase again when it reuses
                     // that tile buffer).
                     PROG(12);
-                    if (n >= 1) ok = pipe_wait(&bars[FB_X_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, nullptr, 12);
+                    if (n >= 1) ok = pipe_wait<true>(&bars[FB_X_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, nullptr, 12);
                     if (!ok) break;
                     if (hslot < CH)
                         *reinterpret_cast<uint4*>(sS + sw128_offset<RING>(s, hslot)) =
@@ -338,9 +340,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         auto issue_u = [&](int m) {
             const int ub = m & 1;
             PROGV(m, 22);
-            bool r = pipe_wait(&bars[FB_P_FULL0 + ub], (m >> 1) & 1, sFail, nullptr, 22);
+            bool r = pipe_wait<true>(&bars[FB_P_FULL0 + ub], (m >> 1) & 1, sFail, nullptr, 22);
             PROGV(m, 23);
-            if (r && m >= 2) r = pipe_wait(&bars[FB_U_FREE0 + ub], ((m >> 1) - 1) & 1, sFail, nullptr, 23);
+            if (r && m >= 2) r = pipe_wait<true>(&bars[FB_U_FREE0 + ub], ((m >> 1) - 1) & 1, sFail, nullptr, 23);
             if (r) {
                 tc_fence_after();
                 const uint32_t tX = tmem_base + ub * 256, tU = tX + 128;
@@ -352,10 +354,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
             }
             return r;
         };
+#pragma unroll 1
         for (int i = q0; i < q1 && ok; ++i) {
             uint32_t vw[4];
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
             const bool work = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
+#pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh) {
                 if (!work) {
                     // nothing follows that would carry the kept-back product: issue it now
@@ -364,10 +368,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 }
                 const int qb = n & 1;
                 PROG(20);
-                ok = pipe_wait(&bars[FB_QP_FULL0 + qb], (n >> 1) & 1, sFail, nullptr, 20);
+                ok = pipe_wait<true>(&bars[FB_QP_FULL0 + qb], (n >> 1) & 1, sFail, nullptr, 20);
                 // X[qb] held P(n-2) until the U product of that head had read it
                 PROG(21);
-                if (ok && n >= 2) ok = pipe_wait(&bars[FB_U_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, nullptr, 21);
+                if (ok && n >= 2) ok = pipe_wait<true>(&bars[FB_U_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, nullptr, 21);
                 if (!ok) break;
                 tc_fence_after();
                 {
@@ -429,7 +433,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
             if (!fin_pending) return true;
             fin_pending = false;
             PROGV(fin_m, 33);
-            if (!pipe_wait(&bars[FB_E_SYNC], fin_m & 1, sFail, nullptr, 33)) return false;
+            if (!pipe_wait<true>(&bars[FB_E_SYNC], fin_m & 1, sFail, nullptr, 33)) return false;
             const float* red = sRed + (fin_m & 1) * 4 * (D + 4);
             float Lsum = 0.f;
 #pragma unroll
@@ -446,7 +450,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
             if (!finish()) return false;
             PROGV(m, 32);
             CYC(7);                                       // finish() of the head before
-            bool r = pipe_wait(&bars[FB_U_DONE0 + ub], (m >> 1) & 1, sFail, nullptr, 32);
+            bool r = pipe_wait<true>(&bars[FB_U_DONE0 + ub], (m >> 1) & 1, sFail, nullptr, 32);
             if (!r) return false;
             tc_fence_after();
             CYC(8);                                       // wait U_done
@@ -503,7 +507,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
             const int s = i & (RING - 1), fb = i - q0 - 1;
             const uint8_t* nx = sNext + (i & (NEXT_BUFS - 1)) * L::NEXT_BYTES;
             PROGV(i, 34);
-            if (!pipe_wait(&bars[FB_NEXT_READY0 + (fb & (NEXT_BUFS - 1))], (fb >> 3) & 1, sFail, nullptr, 34)) return false;
+            if (!pipe_wait<true>(&bars[FB_NEXT_READY0 + (fb & (NEXT_BUFS - 1))], (fb >> 3) & 1, sFail, nullptr, 34)) return false;
             if (tid < CH)
                 *reinterpret_cast<uint4*>(sVs + sw128_offset<RING>(s, tid)) =
                     *reinterpret_cast<const uint4*>(nx + 3 * (D * 2) + tid * 16);
@@ -523,6 +527,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         int pend_n = 0;
         size_t pend_row = 0;
         float pend_m = 0.f, pend_l = 0.f;
+#pragma unroll 1
         for (int i = q0; i < q1 && ok; ++i) {
             uint32_t vw[4];
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
@@ -532,6 +537,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
             // visibility words of this thread's two 32-column chunks
             const uint32_t cw0 = my_vis ? (ch ? vw[2] : vw[0]) : 0u;
             const uint32_t cw1 = my_vis ? (ch ? vw[3] : vw[1]) : 0u;
+#pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh) {
                 const size_t row = row_at(i, hh);
                 const bool boundary = hh == 0 && i > q0;
@@ -549,7 +555,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 const uint32_t tX = tl + xb * 256 + ch * 64;          // this thread's 64 score columns
                 PROG(30);
                 CYC(0);                                   // loop overhead since the last mark
-                ok = pipe_wait(&bars[FB_X_DONE0 + xb], (n >> 1) & 1, sFail, nullptr, 30);
+                ok = pipe_wait<true>(&bars[FB_X_DONE0 + xb], (n >> 1) & 1, sFail, nullptr, 30);
                 if (!ok) break;
                 tc_fence_after();
                 CYC(1);                                   // wait X_done
@@ -598,7 +604,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 if (!ok) break;
                 CYC(4);                                   // ring update
                 PROG(31);
-                ok = pipe_wait(&bars[FB_M_SYNC], n & 1, sFail, nullptr, 31);
+                ok = pipe_wait<true>(&bars[FB_M_SYNC], n & 1, sFail, nullptr, 31);
                 if (!ok) break;
                 CYC(5);                                   // wait M_sync
                 const float* mp = sMpart + xb * 8;
