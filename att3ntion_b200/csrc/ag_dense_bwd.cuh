@@ -55,6 +55,11 @@ struct BwdParams {
     int B, H, N, D, n_valid;
     float scale;
     int* status;
+    // Scatter forms (SC = 1, 2): statistics of the softmaxes anchored at the own and at the other index, and
+    // (SC = 2) the correction sums C[x] = V2[x] . dV2[x] of the two indices           [B,H,N] each
+    const float* m_own; const float* l_own;
+    const float* m_oth; const float* l_oth;
+    const float* C_own; const float* C_oth;
 };
 
 template <int DP, bool WITH_DA>
@@ -68,11 +73,21 @@ struct BwdSmem {
     static constexpr int OFF_RED = (WITH_DA ? 5 : 4) * TILE_BYTES;      // 4 x DP floats
     static constexpr int OFF_VIS = OFF_RED + 4 * DP * 4;                // 4 own words + 4 other words
     static constexpr int OFF_MISC = OFF_VIS + 32;
-    static constexpr int BYTES = OFF_MISC + 16;
+    static constexpr int OFF_COL = OFF_MISC + 16;                       // scatter forms: 2 x 128 other-side constants
+    static constexpr int BYTES = OFF_COL + 2 * TILE * 4;
     static constexpr int ALLOC = BYTES + 1024;
 };
 
-template <int DP, bool WITH_DA>
+// SC = 1 and SC = 2 are the two backward passes of one scatter output of the three-gather operator
+// (cuda/backward.cu:175-316, 949-1613) in the same schedule.  With the output index as the anchor a, the
+// cotangent g[a] in the place of dY, the second value tensors in the place of Va / Vb, and
+//   Po = exp(x - LSE_own[k]),  Pt = exp(x - LSE_oth[j]),  W = Po Pt,  c = sum_d g[a,d] Vb[k,d] Va[j,d]:
+//   SC = 1:  dVb[k] += sum_{a,j} W (g[a] o Va[j])                      (P^T := W, gA^T := 0)
+//   SC = 2:  dx = 2 W c - Po C_own[k] - Pt C_oth[j];  dKb[k] += scale sum_{a,j} dx (A_a o Ka_j) and, on
+//            request, dA[a] += scale sum_k Kb_k o (sum_j dx Ka_j)      (P^T := 0, gA^T := dx)
+// Po is live iff anchor k sees a and j (mask[k][a], mask[k][j]), Pt iff anchor j sees a and k; W needs both.
+// The MMA sequence is the gather's, so one of the two accumulations adds zeros in each pass.
+template <int DP, bool WITH_DA, int SC = 0>
 __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdParams p) {
     using L = BwdSmem<DP, WITH_DA>;
     constexpr int HD = DP / 2, HCH = HD / 8, HW = HD / 2;
@@ -91,6 +106,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::OFF_MISC);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::OFF_MISC + 8);
     volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 12);
+    float* sColL = reinterpret_cast<float*>(smem + L::OFF_COL);          // LSE of the other-side anchors (log2 units)
+    float* sColC = sColL + TILE;                                         // their correction sums
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t issuer = elect_one();     // one lane per warp; warp 0 predicates its MMAs on it
@@ -101,8 +118,9 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
     const int n_keys = (p.n_valid > 0 && p.n_valid < N) ? p.n_valid : N;
     const int n_tiles = (n_keys + TILE - 1) / TILE;
     const int kb = blockIdx.x % n_tiles, chunk = blockIdx.x / n_tiles;
-    const int a_begin = static_cast<int>((static_cast<long long>(N) * chunk) / p.a_chunks);
-    const int a_end = static_cast<int>((static_cast<long long>(N) * (chunk + 1)) / p.a_chunks);
+    const int n_anchors = SC ? n_keys : N;            // padded anchors take no part in a scatter sum
+    const int a_begin = static_cast<int>((static_cast<long long>(n_anchors) * chunk) / p.a_chunks);
+    const int a_end = static_cast<int>((static_cast<long long>(n_anchors) * (chunk + 1)) / p.a_chunks);
 
     if (warp == 0) {
         tmem_alloc(tmem_slot, TMEM_COLS);
@@ -164,6 +182,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
     uint32_t phase = 0;
     bool failed = false;
     float* gPart = WITH_DA ? p.dA_part + (static_cast<size_t>(kb) * p.B * p.H * N + bh) * D : nullptr;
+    // scatter forms: constants of this thread's own key; a dead or padded anchor gets an LSE that makes its
+    // softmax vanish
+    float lse_own = 1e30f, c_own = 0.f;
+    if (SC && own_key < n_keys) {
+        const float lo = __ldg(p.l_own + bh + own_key);
+        if (lo > 0.f) lse_own = __ldg(p.m_own + bh + own_key) * LOG2E + __log2f(lo);
+        if (SC == 2) c_own = __ldg(p.C_own + bh + own_key);
+    }
 
     for (int jb = 0; jb < n_tiles && !failed; ++jb) {
         // other-side tile: this thread's half row of Ka and Va in registers (Ka also in smem for W)
@@ -181,13 +207,47 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
             rVa[4 * c] = v.x; rVa[4 * c + 1] = v.y; rVa[4 * c + 2] = v.z; rVa[4 * c + 3] = v.w;
             if (WITH_DA) *reinterpret_cast<uint4*>(sKa + sw128_offset<TILE>(slot, cc)) = a;
         }
+        // scatter forms: constants of the other-side keys of this tile, and for this thread's two 32-column
+        // chunks (c = 2 rd + half) the pairs in which anchor k sees j (pbo) and anchor j sees k (pbt)
+        uint32_t pbo0 = 0, pbo1 = 0, pbt0 = 0, pbt1 = 0;
+        if (SC) {
+            if (half == 0) {
+                float lt = 1e30f, ct = 0.f;
+                if (oth_key < n_keys) {
+                    const float l = __ldg(p.l_oth + bh + oth_key);
+                    if (l > 0.f) lt = __ldg(p.m_oth + bh + oth_key) * LOG2E + __log2f(l);
+                    if (SC == 2) ct = __ldg(p.C_oth + bh + oth_key);
+                }
+                sColL[slot] = lt;
+                sColC[slot] = ct;
+            }
+            if (own_key < n_keys) {
+#pragma unroll 1
+                for (int rd = 0; rd < 2; ++rd) {
+                    uint32_t wo = 0, wt = 0;
+                    for (int t = 0; t < 32; ++t) {
+                        const int j = jb * TILE + (2 * rd + half) * 32 + t;
+                        if (j >= n_keys) break;
+                        const bool so = !mask_b || mask_b[static_cast<size_t>(own_key) * N + j] != 0;
+                        const bool st = !mask_b || mask_b[static_cast<size_t>(j) * N + own_key] != 0;
+                        wo |= static_cast<uint32_t>(so) << t;
+                        wt |= static_cast<uint32_t>(st) << t;
+                    }
+                    if (rd == 0) { pbo0 = wo; pbt0 = wt; } else { pbo1 = wo; pbt1 = wt; }
+                }
+            }
+        }
         fence_async_smem();
 
         for (int a = a_begin; a < a_end && !failed; ++a) {
             // visibility from anchor a: own-side keys of this tile, other-side keys of tile jb
             {
                 bool vo = own_key < n_keys, vt = oth_key < n_keys;
-                if (mask_b) {
+                if (mask_b && SC) {
+                    // the anchors of the two softmaxes are the own and the other key: each must see a
+                    if (vo) vo = mask_b[static_cast<size_t>(own_key) * N + a] != 0;
+                    if (vt) vt = mask_b[static_cast<size_t>(oth_key) * N + a] != 0;
+                } else if (mask_b) {
                     const uint8_t* mrow = mask_b + static_cast<size_t>(a) * N;
                     if (vo) vo = mrow[own_key] != 0;
                     if (vt) vt = mrow[oth_key] != 0;
@@ -195,7 +255,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
                 const uint32_t wo = __ballot_sync(0xFFFFFFFFu, vo), wt = __ballot_sync(0xFFFFFFFFu, vt);
                 if (lane == 0 && warp < 4) { sVis[warp] = wo; sVis[4 + warp] = wt; }
             }
-            const float m_a = __ldg(p.m + bh + a), l_a = __ldg(p.l + bh + a);
+            const float m_a = SC ? 0.f : __ldg(p.m + bh + a), l_a = SC ? 1.f : __ldg(p.l + bh + a);
             tc_fence_before();
             __syncthreads();
             tc_fence_after();
@@ -208,10 +268,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
             }
             // delta = dY_a . Y_a (same value in every warp), log-sum-exp in log2 units
             float delta = 0.f;
-            for (int t = lane; t < D; t += 32)
-                delta += __bfloat162float(gdY[static_cast<size_t>(a) * D + t]) * __bfloat162float(gY[static_cast<size_t>(a) * D + t]);
+            if (!SC) {
+                for (int t = lane; t < D; t += 32)
+                    delta += __bfloat162float(gdY[static_cast<size_t>(a) * D + t]) * __bfloat162float(gY[static_cast<size_t>(a) * D + t]);
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) delta += __shfl_xor_sync(0xFFFFFFFFu, delta, o);
+                for (int o = 16; o >= 1; o >>= 1) delta += __shfl_xor_sync(0xFFFFFFFFu, delta, o);
+            }
             const float lse2 = m_a * LOG2E + __log2f(l_a);
 
             // --- Hadamard tiles (this thread: half a row) -----------------------------------------
@@ -265,17 +327,44 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
                 tmem_ld32(tl + C_XT + c * 32, x);
                 tmem_ld32(tl + C_DP + c * 32, dp);
                 tmem_wait_ld();
-                const uint32_t cw = my_vis ? (rd == 0 ? (half ? vt1 : vt0) : (half ? vt3 : vt2)) : 0u;
+                const uint32_t vtw = rd == 0 ? (half ? vt1 : vt0) : (half ? vt3 : vt2);
+                const uint32_t cw = my_vis ? vtw : 0u;
+                if (SC) {
+                    // supports: Po needs anchor k to see a (my_vis) and j (pbo); Pt needs anchor j to see a (vtw) and k (pbt)
+                    const uint32_t so = my_vis ? (rd == 0 ? pbo0 : pbo1) : 0u;
+                    const uint32_t st = vtw & (rd == 0 ? pbt0 : pbt1);
+                    const float* lt = sColL + c * 32;
+                    const float* ct = sColC + c * 32;
 #pragma unroll
-                for (int t = 0; t < 32; t += 2) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2, -lse2));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2, -lse2));
-                    if (!((cw >> t) & 1u)) p0 = 0.f;
-                    if (!((cw >> (t + 1)) & 1u)) p1 = 0.f;
-                    const float g0 = p0 * (__uint_as_float(dp[t]) - delta);
-                    const float g1 = p1 * (__uint_as_float(dp[t + 1]) - delta);
-                    pk[t >> 1] = pack_bf16x2(p0, p1);
-                    gk[t >> 1] = pack_bf16x2(g0, g1);
+                    for (int t = 0; t < 32; t += 2) {
+                        const float xs0 = __uint_as_float(x[t]) * c2, xs1 = __uint_as_float(x[t + 1]) * c2;
+                        const float po0 = ((so >> t) & 1u) ? fast_exp2(xs0 - lse_own) : 0.f;
+                        const float po1 = ((so >> (t + 1)) & 1u) ? fast_exp2(xs1 - lse_own) : 0.f;
+                        const float pt0 = ((st >> t) & 1u) ? fast_exp2(xs0 - lt[t]) : 0.f;
+                        const float pt1 = ((st >> (t + 1)) & 1u) ? fast_exp2(xs1 - lt[t + 1]) : 0.f;
+                        const float w0 = po0 * pt0, w1 = po1 * pt1;
+                        if (SC == 1) {
+                            pk[t >> 1] = pack_bf16x2(w0, w1);
+                            gk[t >> 1] = 0u;
+                        } else {
+                            const float d0 = 2.f * w0 * __uint_as_float(dp[t]) - po0 * c_own - pt0 * ct[t];
+                            const float d1 = 2.f * w1 * __uint_as_float(dp[t + 1]) - po1 * c_own - pt1 * ct[t + 1];
+                            pk[t >> 1] = 0u;
+                            gk[t >> 1] = pack_bf16x2(d0, d1);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int t = 0; t < 32; t += 2) {
+                        float p0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2, -lse2));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2, -lse2));
+                        if (!((cw >> t) & 1u)) p0 = 0.f;
+                        if (!((cw >> (t + 1)) & 1u)) p1 = 0.f;
+                        const float g0 = p0 * (__uint_as_float(dp[t]) - delta);
+                        const float g1 = p1 * (__uint_as_float(dp[t + 1]) - delta);
+                        pk[t >> 1] = pack_bf16x2(p0, p1);
+                        gk[t >> 1] = pack_bf16x2(g0, g1);
+                    }
                 }
                 if (rd == 0) {
                     tc_fence_before();
@@ -346,7 +435,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
         }
     }
     // Add the tile's accumulators into the FP32 outputs (this CTA is the only writer of these rows).
-    if (!failed) {
+    // (scatter forms: only the accumulator that received something is added, dVb in pass 1, dKb in pass 2)
+    if (!failed && (SC == 0 || (SC == 1) == (half == 1))) {
         float* dst_base = chunk == 0 ? (half ? p.dVb : p.dKb) : (half ? p.dVb1 : p.dKb1);
         const float mul = half ? 1.0f : p.scale;
         uint32_t acc[32];
@@ -388,6 +478,19 @@ __global__ void ag_add_planes(const float* src, int n_src, size_t plane, float* 
         for (int k = 0; k < n_src; ++k) s += src[k * plane + i];
         acc[i] = s;
     }
+}
+
+
+// row . row over D for two [n, D] tensors (bf16 x fp32): C[n] = sum_d V2[n,d] * dV2[n,d]
+__global__ void rowdot_kernel(const __nv_bfloat16* v2, const float* dv2, float* out, size_t rows, int D) {
+    const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) / 32;
+    const int lane = threadIdx.x & 31;
+    if (warp >= rows) return;
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) s += __bfloat162float(v2[warp * D + d]) * dv2[warp * D + d];
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+    if (lane == 0) out[warp] = s;
 }
 
 }  // namespace agdense

@@ -48,6 +48,9 @@ struct FwdParams {
     int B, H, N, D, n_valid, group;
     float scale;
     int* status;
+    // Scatter form (SC kernels only): statistics of the softmaxes anchored at the row index and at the col index
+    const float* m_row; const float* l_row;
+    const float* m_col; const float* l_col;
 };
 
 template <int DP>
@@ -61,7 +64,8 @@ struct FwdSmem {
     static constexpr int OFF_MPART = OFF_RED + 4 * (DP + 4) * 4;
     static constexpr int OFF_VIS = OFF_MPART + 16;                         // 4 row words + 4 col words
     static constexpr int OFF_MISC = OFF_VIS + 32;
-    static constexpr int BYTES = OFF_MISC + 16;
+    static constexpr int OFF_COLL = OFF_MISC + 16;                         // scatter form: 128 col constants
+    static constexpr int BYTES = OFF_COLL + TILE * 4;
     static constexpr int ALLOC = BYTES + 1024;
 };
 
@@ -76,7 +80,16 @@ __device__ __forceinline__ void load_row_padded(const __nv_bfloat16* base, int i
     }
 }
 
-template <int DP>
+// SC = true turns the gather into one scatter output of the three-gather operator
+// (cpp/torch_reference.cpp:51-54, cuda/forward.cu:941-1249): with the output index as the anchor a and the
+// two other indices as rows u and cols v,
+//   out[a] = sum_{u,v} W[a,u,v] Vrow[u] o Vcol[v],   W = Pu Pv = exp(2 x - LSE_u[u] - LSE_v[v]),
+// Pu being the softmax anchored at u (taken over (a, v)) and Pv the one anchored at v, both finished by
+// earlier gathers whose statistics arrive as (m_row, l_row) and (m_col, l_col).  The exponent is <= 0 because
+// each LSE is taken over a set that contains the cell, so there is no running maximum and no normalisation:
+// the tile loop just adds.  A cell is live iff anchor u sees a and v and anchor v sees a and u
+// (mask[u][a], mask[u][v], mask[v][a], mask[v][u]) and all three indices are below the valid length.
+template <int DP, bool SC = false>
 __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdParams p) {
     using L = FwdSmem<DP>;
     constexpr int CH = DP / 8, DW = DP / 2;
@@ -94,15 +107,16 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem + L::OFF_MISC);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::OFF_MISC + 8);
     volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 12);
+    float* sColL = reinterpret_cast<float*>(smem + L::OFF_COLL);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t issuer = elect_one();     // one lane per warp; warp 0 predicates its MMAs on it
     const int b = blockIdx.z, h = blockIdx.y;
-    const int a0 = blockIdx.x * p.group;
-    const int a1 = min(a0 + p.group, p.N);
-    if (a0 >= a1) return;
     const int N = p.N, D = p.D;
     const int n_keys = (p.n_valid > 0 && p.n_valid < N) ? p.n_valid : N;   // keys at or past this index are padding
+    const int a0 = blockIdx.x * p.group;
+    const int a1 = min(a0 + p.group, SC ? n_keys : p.N);     // padded anchors take no part in a scatter sum
+    if (a0 >= a1) return;
 
     if (warp == 0) {
         tmem_alloc(tmem_slot, TMEM_COLS);
@@ -146,6 +160,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
         const int jrow = jb * TILE + tid;
         load_row_padded<DP>(gRw, jrow, n_keys, D, rRw);
         load_row_padded<DP>(gVrow, jrow, n_keys, D, rVr);
+        // scatter form: LSE (log2 units) of the softmax anchored at this thread's row; an anchor without any
+        // visible cell (l = 0) or a padded one gets a value that makes every weight vanish
+        float lse_row = 1e30f;
+        if (SC && jrow < n_keys) {
+            const float lu = __ldg(p.l_row + bh + jrow);
+            if (lu > 0.f) lse_row = __ldg(p.m_row + bh + jrow) * LOG2E + __log2f(lu);
+        }
         for (int kb = 0; kb < n_tiles && !failed; ++kb) {
             // stage the col tile; every MMA that read the previous one has been waited for
             {
@@ -162,13 +183,40 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                     *reinterpret_cast<uint4*>(sVc + sw128_offset<TILE>(tid, c)) =
                         make_uint4(t[4 * c], t[4 * c + 1], t[4 * c + 2], t[4 * c + 3]);
             }
+            // scatter form: col constants of the tile, and the pairs (u, v) in which each anchor sees the other
+            uint32_t pw0 = 0xFFFFFFFFu, pw1 = 0xFFFFFFFFu, pw2 = 0xFFFFFFFFu, pw3 = 0xFFFFFFFFu;
+            if (SC) {
+                const int krow = kb * TILE + tid;
+                float lc = 1e30f;
+                if (krow < n_keys) {
+                    const float lv = __ldg(p.l_col + bh + krow);
+                    if (lv > 0.f) lc = __ldg(p.m_col + bh + krow) * LOG2E + __log2f(lv);
+                }
+                sColL[tid] = lc;
+                if (mask_b) {
+                    uint32_t w[4] = {0, 0, 0, 0};
+                    if (jrow < n_keys) {
+                        for (int t = 0; t < TILE; ++t) {
+                            const int v = kb * TILE + t;
+                            if (v < n_keys && mask_b[static_cast<size_t>(jrow) * N + v] != 0 &&
+                                mask_b[static_cast<size_t>(v) * N + jrow] != 0)
+                                w[t >> 5] |= 1u << (t & 31);
+                        }
+                    }
+                    pw0 = w[0]; pw1 = w[1]; pw2 = w[2]; pw3 = w[3];
+                }
+            }
             fence_async_smem();
             for (int a = a0; a < a1 && !failed; ++a) {
                 // visibility of this tile's rows and cols from anchor a
                 {
                     const int krow = kb * TILE + tid;
                     bool vr = jrow < n_keys, vc = krow < n_keys;
-                    if (mask_b) {
+                    if (mask_b && SC) {
+                        // the anchors of the two softmaxes are the row and the col: each must see a
+                        if (vr) vr = mask_b[static_cast<size_t>(jrow) * N + a] != 0;
+                        if (vc) vc = mask_b[static_cast<size_t>(krow) * N + a] != 0;
+                    } else if (mask_b) {
                         const uint8_t* mrow = mask_b + static_cast<size_t>(a) * N;
                         if (vr) vr = mrow[jrow] != 0;
                         if (vc) vc = mrow[krow] != 0;
@@ -219,7 +267,30 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
 
                 // --- per-row softmax over the tile's visible columns ------------------------------
                 float m_row = -INFINITY, l_row = 0.f;
-                {
+                if (SC) {
+                    // weights of the scatter form: one pass, no maximum
+                    uint32_t x[32];
+                    const float c2x2 = 2.f * c2;
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        tmem_ld32(tX + c * 32, x);
+                        tmem_wait_ld();
+                        const uint32_t vw = my_vis ? ((c == 0 ? vc0 : c == 1 ? vc1 : c == 2 ? vc2 : vc3) &
+                                                      (c == 0 ? pw0 : c == 1 ? pw1 : c == 2 ? pw2 : pw3)) : 0u;
+                        const float* lc = sColL + c * 32;
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int t = 0; t < 32; t += 2) {
+                            float e0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2x2, -(lse_row + lc[t])));
+                            float e1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2x2, -(lse_row + lc[t + 1])));
+                            if (!((vw >> t) & 1u)) e0 = 0.f;
+                            if (!((vw >> (t + 1)) & 1u)) e1 = 0.f;
+                            pk[t >> 1] = pack_bf16x2(e0, e1);
+                        }
+                        tmem_st16(tX + c * 16, pk);
+                    }
+                    m_row = 0.f;
+                } else {
                     uint32_t x[32];
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
@@ -269,7 +340,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                 }
                 phase ^= 1;
                 const float Mt = fmaxf(fmaxf(sMpart[0], sMpart[1]), fmaxf(sMpart[2], sMpart[3]));
-                const float w_row = (m_row > -INFINITY) ? fast_exp2((m_row - Mt) * c2) : 0.f;
+                const float w_row = SC ? 1.f : (m_row > -INFINITY) ? fast_exp2((m_row - Mt) * c2) : 0.f;
                 __syncthreads();
                 tc_fence_after();
                 if (*sFail) { failed = true; break; }
@@ -298,7 +369,11 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                 }
                 tc_fence_before();
                 __syncthreads();
-                if (Mt > -INFINITY) {
+                if (SC) {
+                    float* st = sState + (a - a0) * (DP + 4);
+                    if (tid < DP)
+                        st[tid] += sRed[tid] + sRed[(DP + 4) + tid] + sRed[2 * (DP + 4) + tid] + sRed[3 * (DP + 4) + tid];
+                } else if (Mt > -INFINITY) {
                     float* st = sState + (a - a0) * (DP + 4);
                     const float M_old = st[DP];
                     const float M_new = fmaxf(M_old, Mt);
@@ -322,6 +397,10 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
             const float* st = sState + (a - a0) * (DP + 4);
             const float M = st[DP], Ls = st[DP + 1];
             const size_t row = bh + a;
+            if (SC) {
+                if (tid < D) p.Y[row * D + tid] = __float2bfloat16(st[tid]);
+                continue;
+            }
             const bool live = M > -INFINITY && Ls > 0.f;
             if (tid < D) p.Y[row * D + tid] = __float2bfloat16(live ? st[tid] / Ls : 0.f);
             if (tid == 0) { p.m[row] = live ? M * p.scale : NEG_INF_F; p.l[row] = live ? Ls : 0.f; }

@@ -6,7 +6,6 @@
 
 #include "att3_abi_internal.h"
 #include "ag_dense_bwd.cuh"
-#include "hg_scatter.cuh"
 
 namespace {
 
@@ -24,25 +23,25 @@ int opt_in_smem(K kernel, int bytes, const char* who) {
     return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, who);
 }
 
-template <int DP>
+template <int DP, bool SC = false>
 int launch_fwd(const agdense::FwdParams& p, cudaStream_t st) {
     using L = agdense::FwdSmem<DP>;
-    if (int rc = opt_in_smem(agdense::ag_dense_fwd_kernel<DP>, L::ALLOC, "dense gather forward: shared-memory opt-in")) return rc;
+    if (int rc = opt_in_smem(agdense::ag_dense_fwd_kernel<DP, SC>, L::ALLOC, "dense gather forward: shared-memory opt-in")) return rc;
     dim3 grid((p.N + p.group - 1) / p.group, p.H, p.B);
     att3::TimedLaunch timed(att3::K_DENSE_FWD, st);
-    agdense::ag_dense_fwd_kernel<DP><<<grid, agdense::NTHREADS, L::ALLOC, st>>>(p);
+    agdense::ag_dense_fwd_kernel<DP, SC><<<grid, agdense::NTHREADS, L::ALLOC, st>>>(p);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "dense gather forward: launch");
 }
 
-template <int DP, bool WITH_DA>
+template <int DP, bool WITH_DA, int SC = 0>
 int launch_bwd(const agdense::BwdParams& p, int n_tiles, cudaStream_t st) {
     using L = agdense::BwdSmem<DP, WITH_DA>;
-    if (int rc = opt_in_smem(agdense::ag_dense_bwd_kernel<DP, WITH_DA>, L::ALLOC, "dense gather backward: shared-memory opt-in"))
+    if (int rc = opt_in_smem(agdense::ag_dense_bwd_kernel<DP, WITH_DA, SC>, L::ALLOC, "dense gather backward: shared-memory opt-in"))
         return rc;
     dim3 grid(n_tiles * p.a_chunks, p.H, p.B);
     att3::TimedLaunch timed(att3::K_DENSE_BWD, st);
-    agdense::ag_dense_bwd_kernel<DP, WITH_DA><<<grid, agdense::BWD_THREADS, L::ALLOC, st>>>(p);
+    agdense::ag_dense_bwd_kernel<DP, WITH_DA, SC><<<grid, agdense::BWD_THREADS, L::ALLOC, st>>>(p);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "dense gather backward: launch");
 }
@@ -68,10 +67,10 @@ int dense_tiles(int N, int n_valid) {
     return (n_keys + agdense::TILE - 1) / agdense::TILE;
 }
 
-int dense_gather_forward(const void* A, const void* Rw, const void* C, const void* Vrow, const void* Vcol,
-                         const uint8_t* mask, void* Y, float* m, float* l, int B, int H, int N, int D, int n_valid,
-                         cudaStream_t st) {
-    agdense::FwdParams p;
+static agdense::FwdParams fwd_params(const void* A, const void* Rw, const void* C, const void* Vrow, const void* Vcol,
+                                     const uint8_t* mask, void* Y, float* m, float* l, int B, int H, int N, int D,
+                                     int n_valid) {
+    agdense::FwdParams p{};
     p.A = static_cast<const __nv_bfloat16*>(A);
     p.Rw = static_cast<const __nv_bfloat16*>(Rw);
     p.C = static_cast<const __nv_bfloat16*>(C);
@@ -86,7 +85,24 @@ int dense_gather_forward(const void* A, const void* Rw, const void* C, const voi
     // anchors per CTA: enough CTAs to fill the device twice over, at most 16 anchors each
     const long ctas_at_16 = static_cast<long>((N + 15) / 16) * H * B;
     p.group = ctas_at_16 >= 2L * sm_count() ? 16 : (ctas_at_16 * 2 >= 2L * sm_count() ? 8 : 4);
+    return p;
+}
+
+int dense_gather_forward(const void* A, const void* Rw, const void* C, const void* Vrow, const void* Vcol,
+                         const uint8_t* mask, void* Y, float* m, float* l, int B, int H, int N, int D, int n_valid,
+                         cudaStream_t st) {
+    const agdense::FwdParams p = fwd_params(A, Rw, C, Vrow, Vcol, mask, Y, m, l, B, H, N, D, n_valid);
     return D > 64 ? launch_fwd<128>(p, st) : launch_fwd<64>(p, st);
+}
+
+// One scatter output: anchor = the output index, rows / cols = the two other indices with their second value
+// tensors and the statistics of the softmaxes anchored at them.
+int dense_scatter_forward(const void* A, const void* Rw, const void* C, const void* Vrow2, const void* Vcol2,
+                          const float* m_row, const float* l_row, const float* m_col, const float* l_col,
+                          const uint8_t* mask, void* out, int B, int H, int N, int D, int n_valid, cudaStream_t st) {
+    agdense::FwdParams p = fwd_params(A, Rw, C, Vrow2, Vcol2, mask, out, nullptr, nullptr, B, H, N, D, n_valid);
+    p.m_row = m_row; p.l_row = l_row; p.m_col = m_col; p.l_col = l_col;
+    return D > 64 ? launch_fwd<128, true>(p, st) : launch_fwd<64, true>(p, st);
 }
 
 int dense_gather_backward_side(const void* A, const void* dY, const void* Y, const float* m, const float* l,
@@ -123,6 +139,40 @@ int dense_gather_backward_side(const void* A, const void* dY, const void* Y, con
     return add_planes(p.dVb1, 1, plane, dVb, st);
 }
 
+// One pass of a scatter output's backward for one own side (pass 1: second-value gradient into `out_own`;
+// pass 2: key gradient into `out_own` and, with dA_part, the anchor-gradient partial planes).
+int dense_scatter_backward_side(int pass, const void* A, const void* G, const void* K_oth, const void* V2_oth,
+                                const void* K_own, const void* V2_own, const float* m_own, const float* l_own,
+                                const float* m_oth, const float* l_oth, const float* C_own, const float* C_oth,
+                                const uint8_t* mask, float* out_own, float* dA_part, int B, int H, int N, int D,
+                                int n_valid, cudaStream_t st, float* chunk_scratch) {
+    agdense::BwdParams p{};
+    p.A = static_cast<const __nv_bfloat16*>(A);
+    p.dY = static_cast<const __nv_bfloat16*>(G);
+    p.Y = p.dY;                       // not read by the scatter passes
+    p.Ka = static_cast<const __nv_bfloat16*>(K_oth);
+    p.Va = static_cast<const __nv_bfloat16*>(V2_oth);
+    p.Kb = static_cast<const __nv_bfloat16*>(K_own);
+    p.Vb = static_cast<const __nv_bfloat16*>(V2_own);
+    p.mask = mask;
+    p.dKb = out_own; p.dVb = out_own; p.dA_part = dA_part;
+    p.m_own = m_own; p.l_own = l_own; p.m_oth = m_oth; p.l_oth = l_oth; p.C_own = C_own; p.C_oth = C_oth;
+    p.B = B; p.H = H; p.N = N; p.D = D; p.n_valid = n_valid;
+    p.scale = 1.0f / sqrtf(static_cast<float>(D));
+    p.status = ag_status_ptr();
+    const int nt = dense_tiles(N, n_valid);
+    const size_t plane = static_cast<size_t>(B) * H * N * D;
+    p.a_chunks = (chunk_scratch && 2 * nt * B * H <= sm_count() && N >= 2) ? 2 : 1;
+    p.dKb1 = chunk_scratch; p.dVb1 = chunk_scratch;
+    if (p.a_chunks == 2) cudaMemsetAsync(chunk_scratch, 0, plane * sizeof(float), st);
+    int rc;
+    if (pass == 1) rc = D > 64 ? launch_bwd<128, false, 1>(p, nt, st) : launch_bwd<64, false, 1>(p, nt, st);
+    else if (dA_part) rc = D > 64 ? launch_bwd<128, true, 2>(p, nt, st) : launch_bwd<64, true, 2>(p, nt, st);
+    else rc = D > 64 ? launch_bwd<128, false, 2>(p, nt, st) : launch_bwd<64, false, 2>(p, nt, st);
+    if (rc || p.a_chunks == 1) return rc;
+    return add_planes(chunk_scratch, 1, plane, out_own, st);
+}
+
 int add_planes(const float* src, int n_src, size_t plane, float* acc, cudaStream_t st) {
     TimedLaunch timed(K_HG_AUX, st);
     agdense::ag_add_planes<<<grid_for(plane), 256, 0, st>>>(src, n_src, plane, acc, plane);
@@ -140,31 +190,8 @@ int plane_to_bf16(const float* src, void* out, size_t n, cudaStream_t st) {
 }  // namespace att3
 
 // ---------------------------------------------------------------------------------------------
-// Scatter terms (CUDA-core kernels, hg_scatter.cuh)
+// Scatter terms: the dense kernels in their scatter forms (tensor cores)
 // ---------------------------------------------------------------------------------------------
-
-template <int D, int DH, int MODE>
-static int launch_scatter_t(const hgscatter::Params& p, cudaStream_t st) {
-    const size_t smem = hgscatter::smem_bytes<D, DH>();
-    cudaError_t e = cudaFuncSetAttribute(hgscatter::hg_scatter_kernel<D, DH, MODE>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return att3::set_cuda_error(e, "scatter: shared-memory opt-in");
-    dim3 grid(p.N / hgscatter::T, MODE == 0 ? 1 : p.N / hgscatter::T, p.B * p.H * (D / DH));
-    att3::TimedLaunch timed(att3::K_HG_AUX, st);
-    hgscatter::hg_scatter_kernel<D, DH, MODE><<<grid, hgscatter::THREADS, smem, st>>>(p);
-    e = cudaGetLastError();
-    return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "scatter: launch");
-}
-
-template <int MODE>
-static int launch_scatter(const hgscatter::Params& p, cudaStream_t st) {
-    switch (p.D) {
-        case 16: return launch_scatter_t<16, 16, MODE>(p, st);
-        case 32: return launch_scatter_t<32, 32, MODE>(p, st);
-        case 64: return launch_scatter_t<64, 64, MODE>(p, st);
-        default: return launch_scatter_t<128, 64, MODE>(p, st);
-    }
-}
 
 // One index of the operator in a given role: its keys, second value tensor and the statistics of the
 // softmax anchored at it.
@@ -172,66 +199,53 @@ struct ScatterSide {
     const void* keys; const void* v2; const float* m; const float* l;
 };
 
-static hgscatter::Params scatter_params(const ScatterSide& a, const ScatterSide& u, const ScatterSide& v,
-                                        const uint8_t* mask, int B, int H, int N, int D, int n_valid) {
-    hgscatter::Params p{};
-    p.A = static_cast<const __nv_bfloat16*>(a.keys);
-    p.U = static_cast<const __nv_bfloat16*>(u.keys);
-    p.V = static_cast<const __nv_bfloat16*>(v.keys);
-    p.Vu2 = static_cast<const __nv_bfloat16*>(u.v2);
-    p.Vv2 = static_cast<const __nv_bfloat16*>(v.v2);
-    p.m_u = u.m; p.l_u = u.l; p.m_v = v.m; p.l_v = v.l;
-    p.mask = mask;
-    p.B = B; p.H = H; p.N = N; p.D = D; p.n_valid = n_valid;
-    p.scale = 1.0f / sqrtf(static_cast<float>(D));
-    return p;
-}
-
 // out[a] = sum_{u,v} Pu Pv Vu2[u] o Vv2[v]   (forward of one scatter output)
 static int scatter_forward(const ScatterSide& a, const ScatterSide& u, const ScatterSide& v, const uint8_t* mask,
                            void* out, int B, int H, int N, int D, int n_valid, cudaStream_t st) {
-    hgscatter::Params p = scatter_params(a, u, v, mask, B, H, N, D, n_valid);
-    p.out_bf16 = static_cast<__nv_bfloat16*>(out);
-    return launch_scatter<0>(p, st);
+    return att3::dense_scatter_forward(a.keys, u.keys, v.keys, u.v2, v.v2, u.m, u.l, v.m, v.l, mask, out, B, H, N, D,
+                                       n_valid, st);
 }
 
 // Gradients of one scatter output under the cotangent g: into the FP32 planes of the three key tensors and
-// of the two second value tensors.  tmp: two planes + two [B,H,N] vectors of scratch.
+// of the two second value tensors.  tmp: two planes (this term's value gradients), one plane holding the two
+// [B,H,N] correction vectors, and one anchor-gradient partial plane per 128-key tile.
 static int scatter_backward(const ScatterSide& a, const ScatterSide& u, const ScatterSide& v, const void* g,
                             const uint8_t* mask, float* gA, float* gU, float* gV, float* gVu2, float* gVv2,
-                            float* tmp, int B, int H, int N, int D, int n_valid, cudaStream_t st) {
+                            float* tmp, float* chunk_scratch, int B, int H, int N, int D, int n_valid,
+                            cudaStream_t st) {
     const size_t plane = static_cast<size_t>(B) * H * N * D, rows = static_cast<size_t>(B) * H * N;
-    float *tmpU = tmp, *tmpV = tmp + plane, *Cu = tmp + 2 * plane, *Cv = Cu + rows;
+    const int nt = att3::dense_tiles(N, n_valid);
+    float *tmpU = tmp, *tmpV = tmp + plane, *Cu = tmp + 2 * plane, *Cv = Cu + rows, *part = tmp + 3 * plane;
     cudaMemsetAsync(tmp, 0, 2 * plane * sizeof(float), st);
     int rc;
-    {   // value gradients of this term alone (their row dots are the softmax corrections)
-        hgscatter::Params p = scatter_params(a, u, v, mask, B, H, N, D, n_valid);
-        p.G = static_cast<const __nv_bfloat16*>(g);
-        p.out_u = tmpU;
-        if ((rc = launch_scatter<1>(p, st))) return rc;
-        hgscatter::Params q = scatter_params(a, v, u, mask, B, H, N, D, n_valid);
-        q.G = p.G;
-        q.out_u = tmpV;
-        if ((rc = launch_scatter<1>(q, st))) return rc;
-    }
+    // pass 1: value gradients of this term alone (their row dots are the softmax corrections of pass 2)
+    if ((rc = att3::dense_scatter_backward_side(1, a.keys, g, v.keys, v.v2, u.keys, u.v2, u.m, u.l, v.m, v.l, nullptr,
+                                                nullptr, mask, tmpU, nullptr, B, H, N, D, n_valid, st, chunk_scratch)))
+        return rc;
+    if ((rc = att3::dense_scatter_backward_side(1, a.keys, g, u.keys, u.v2, v.keys, v.v2, v.m, v.l, u.m, u.l, nullptr,
+                                                nullptr, mask, tmpV, nullptr, B, H, N, D, n_valid, st, chunk_scratch)))
+        return rc;
     const int wpb = 8;    // warps per block of the row-dot kernel
     const unsigned nblk = static_cast<unsigned>((rows + wpb - 1) / wpb);
-    hgscatter::rowdot_kernel<<<nblk, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(u.v2), tmpU, Cu, rows, D);
-    hgscatter::rowdot_kernel<<<nblk, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(v.v2), tmpV, Cv, rows, D);
+    {
+        att3::TimedLaunch timed(att3::K_HG_AUX, st);
+        agdense::rowdot_kernel<<<nblk, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(u.v2), tmpU, Cu, rows, D);
+    }
+    {
+        att3::TimedLaunch timed(att3::K_HG_AUX, st);
+        agdense::rowdot_kernel<<<nblk, wpb * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(v.v2), tmpV, Cv, rows, D);
+    }
     if ((rc = att3::add_planes(tmpU, 1, plane, gVu2, st))) return rc;
     if ((rc = att3::add_planes(tmpV, 1, plane, gVv2, st))) return rc;
-    {   // key gradients: (a, u) from the first launch, v from the launch with u and v exchanged
-        hgscatter::Params p = scatter_params(a, u, v, mask, B, H, N, D, n_valid);
-        p.G = static_cast<const __nv_bfloat16*>(g);
-        p.Cu = Cu; p.Cv = Cv;
-        p.out_a = gA; p.out_u = gU;
-        if ((rc = launch_scatter<2>(p, st))) return rc;
-        hgscatter::Params q = scatter_params(a, v, u, mask, B, H, N, D, n_valid);
-        q.G = p.G;
-        q.Cu = Cv; q.Cv = Cu;
-        q.out_a = nullptr; q.out_u = gV;
-        if ((rc = launch_scatter<2>(q, st))) return rc;
-    }
+    // pass 2: key gradients; the launch with own = u also produces the anchor gradient
+    cudaMemsetAsync(part, 0, static_cast<size_t>(nt) * plane * sizeof(float), st);
+    if ((rc = att3::dense_scatter_backward_side(2, a.keys, g, v.keys, v.v2, u.keys, u.v2, u.m, u.l, v.m, v.l, Cu, Cv,
+                                                mask, gU, part, B, H, N, D, n_valid, st, chunk_scratch)))
+        return rc;
+    if ((rc = att3::add_planes(part, nt, plane, gA, st))) return rc;
+    if ((rc = att3::dense_scatter_backward_side(2, a.keys, g, u.keys, u.v2, v.keys, v.v2, v.m, v.l, u.m, u.l, Cv, Cu,
+                                                mask, gV, nullptr, B, H, N, D, n_valid, st, chunk_scratch)))
+        return rc;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "scatter backward: launch");
 }
@@ -312,8 +326,8 @@ extern "C" int att3_hg_forward(const void* Q, const void* R, const void* S, cons
 extern "C" size_t att3_hg_backward_workspace_bytes(int B, int H, int N, int D) {
     if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
     const size_t plane = static_cast<size_t>(B) * H * N * D * sizeof(float);
-    // the scatter terms use three planes of the same scratch area; two more for the anchor chunks of short sequences
-    return plane * (9 + std::max(att3::dense_tiles(N, 0), 3) + 2);
+    // the scatter terms use three more planes next to the partial planes; two more for the anchor chunks of short sequences
+    return plane * (9 + att3::dense_tiles(N, 0) + 3 + 2);
 }
 
 extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gYs, const void* gYq_,
@@ -346,7 +360,7 @@ extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gY
     float* ws = static_cast<float*>(workspace);
     float *gQ = ws, *gR = ws + plane, *gS = ws + 2 * plane, *gVq1 = ws + 3 * plane, *gVq2 = ws + 4 * plane,
           *gVr1 = ws + 5 * plane, *gVr2 = ws + 6 * plane, *gVs1 = ws + 7 * plane, *gVs2 = ws + 8 * plane,
-          *part = ws + 9 * plane, *chunk_scratch = part + static_cast<size_t>(std::max(att3::dense_tiles(N, 0), 3)) * plane;
+          *part = ws + 9 * plane, *chunk_scratch = part + static_cast<size_t>(att3::dense_tiles(N, 0) + 3) * plane;
     cudaMemsetAsync(ws, 0, 9 * plane * sizeof(float), st);
 
     // One anchored gather: anchor A with statistics (m,l), rows (Kr,Vr), cols (Kc,Vc).
@@ -371,10 +385,10 @@ extern "C" int att3_hg_backward(const void* gYq, const void* gYr, const void* gY
     }
     if (scatter) {
         const ScatterSide q{Q, Vq2, m_i, l_i}, r{R, Vr2, m_j, l_j}, s{S, Vs2, m_k, l_k};
-        if ((rc = scatter_backward(q, r, s, gYq_, mask, gQ, gR, gS, gVr2, gVs2, part, B, H, N, D, n_valid, st))) return rc;
-        if ((rc = scatter_backward(r, q, s, gYr_, mask, gR, gQ, gS, gVq2, gVs2, part, B, H, N, D, n_valid, st))) return rc;
-        if ((rc = scatter_backward(s, q, r, gYs_, mask, gS, gQ, gR, gVq2, gVr2, part, B, H, N, D, n_valid, st))) return rc;
-        att3::count_launch(3, 18);
+        if ((rc = scatter_backward(q, r, s, gYq_, mask, gQ, gR, gS, gVr2, gVs2, part, chunk_scratch, B, H, N, D, n_valid, st))) return rc;
+        if ((rc = scatter_backward(r, q, s, gYr_, mask, gR, gQ, gS, gVq2, gVs2, part, chunk_scratch, B, H, N, D, n_valid, st))) return rc;
+        if ((rc = scatter_backward(s, q, r, gYs_, mask, gS, gQ, gR, gVq2, gVr2, part, chunk_scratch, B, H, N, D, n_valid, st))) return rc;
+        att3::count_launch(3, 12);
     }
     void* outs[9] = {dQ, dR, dS, dVq1, dVq2, dVr1, dVr2, dVs1, dVs2};
     const float* srcs[9] = {gQ, gR, gS, gVq1, gVq2, gVr1, gVr2, gVs1, gVs2};

@@ -410,7 +410,8 @@ def run_rows(args):
 def run_other(args):
     """Secondary configurations, one GPU, device-resident inputs, CUDA events, median of `--steps`
     repeats: C3 = independent-head single gather B4 H8 N2048 D64 w128 (16*D*T FLOPs), C2 = three-gather
-    operator B8 H4 N256 D64 without mask or scatter (3*(4+14)*D*B*H*N^3 FLOPs, the reference's own count)."""
+    operator B8 H4 N256 D64 without mask or scatter (3*(4+14)*D*B*H*N^3 FLOPs, the reference's own count), and
+    the same shape with the scatter outputs switched on (time only)."""
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the sm_100a kernels have no CPU path")
     from att3ntion_b200 import _cuda_kernels as ck
@@ -454,6 +455,20 @@ def run_other(args):
     ms = timed(c2)
     fl = 3 * (4 + 14) * d2 * b2 * h2 * n2 ** 3
     out["C2 three-gather B8 H4 N256 D64"] = {"ms": ms, "TFLOP/s": fl / ms / 1e9}
+
+    # The same shape with the second value tensors in use (module option scatter=True): three scatter outputs
+    # and their cross terms in all nine gradients, on CUDA cores.  No FLOP model is published for this part,
+    # so only the time is reported.
+    ins2 = [t.clone() for t in ins]
+    for k in (4, 6, 8):
+        ins2[k] = torch.randn(b2, h2, n2, d2, generator=g).to(torch.bfloat16).to(dev)
+    cot2 = cot[:3] + [torch.randn(b2, h2, n2, d2, generator=g).to(torch.bfloat16).to(dev) for _ in range(3)]
+
+    def c2s():
+        o = ck.forward(*ins2, 0.0, -1, -1, -1, None, 0)
+        ck.backward(*cot2, *ins2, *o[6:12], 0.0, None, o[0], o[1], o[2])
+    ms = timed(c2s)
+    out["C2 with scatter outputs (second value tensors non-zero)"] = {"ms": ms}
     ck.device_status()
     print(json.dumps({"secondary_configs": out, "repeats": reps, "data": "synthetic"}))
 

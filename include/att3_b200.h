@@ -153,7 +153,8 @@ size_t att3_hg_backward_workspace_bytes(int B, int H, int N, int D);
  * cotangents of the six outputs; pass scatter = 0 when the three scatter
  * cotangents are identically zero (att3ntion/_custom_op.py:73-96), scatter = 1
  * adds the gradients of the scatter outputs (cuda/backward.cu:175-316, 949-1613;
- * gather_mode 0 only, accumulated with FP32 atomics).  Yq, Yr, Ys
+ * gather_mode 0 only; the same tensor-core kernels in their scatter forms,
+ * fixed summation order).  Yq, Yr, Ys
  * are the forward's gather outputs: the softmax Jacobian correction is taken as
  * rowsum(dY o Y), the reference's tensor-core path (cuda/backward.cu:1835-1837).
  * With gather_mode 1 only the Q-anchored tensors are read. */

@@ -273,7 +273,8 @@ def test_lowlevel_rejections(ck):
 
 def test_full_size_properties_c4_shape(ck):
     """Shared-KV B4 Hq8 N8192 D128 w128: too large for the dense oracle, so check
-    (i) a 192-query slice of one batch against the banded FP64 oracle, (ii) that
+    (i) a 192-query slice of one batch against the banded FP64 oracle (Y, LSE, dQ
+    and the 65 complete rows of the four key gradients), (ii) that
     interior rows are invariant to shifting the sequence by one window, and
     (iii) repeat-call equality of the KV gradients."""
     B, Hq, N, D, w = 4, 8, 8192, 128, 128
@@ -292,6 +293,11 @@ def test_full_size_properties_c4_shape(ck):
     O.check_gate("Y", Y[b:b + 1, :, lo:hi].float().cpu(), ref["Y"][:, :, 127:])
     O.check_lse(m[b:b + 1, :, lo:hi], l[b:b + 1, :, lo:hi], ref["lse"][:, :, 127:])
     O.check_gate("dQ", grads[0][b:b + 1, :, lo:hi].float().cpu(), ref["dQ"][:, :, 127:])
+    # key k collects from queries k .. k+127: the slice holds all of them for keys lo .. hi-128, so the head-summed
+    # key gradients of those rows are complete in the oracle (partial planes + reduction at full size)
+    nk = hi - lo - 127
+    for gi, gname in enumerate(["dR", "dS", "dVr", "dVs"], start=1):
+        O.check_gate(gname, grads[gi][b:b + 1, :, lo:lo + nk].float().cpu(), ref[gname][:, :, 127:127 + nk])
     # shift invariance: drop the first 128 positions, rows >= 255 of the original are unchanged
     qs = [t[:, :, 128:].contiguous() for t in q]
     Ys, ms, ls = ck.sg_forward_raw(*qs, None, w)
