@@ -596,6 +596,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             uint32_t vw[4];
             ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
             const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
+            bool ring_committed = false;
 #pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
                 const float l_i = l_next;
@@ -635,6 +636,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 run_ss(tB, dVb, dGK + goff);                   // dP^T = Vb Gt^T
                 umma_commit_pred(&bars[PB_S_DP], issuer);
                 TL(4);
+                if (!WITH_DQ && hh == G - 1) {
+                    // The query's last reads of the ring tiles have been issued (without the dQ product only
+                    // the two score-shaped products read them): the H warps may bring in the next key as
+                    // soon as these complete, not only after the accumulation MMAs further down.
+                    umma_commit_pred(&bars[PB_RING_FREE], issuer);
+                    ring_committed = true;
+                }
                 ok = pipe_wait(&bars[PB_P_FULL], ph, sFail, TR(4));
                 if (ok && (flush_pending || self_pending)) ok = settle_flush();   // the lane zeroed at the query boundary
                 TL(5);
@@ -661,7 +669,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             }
             // Every MMA of this query that reads the ring tiles has been issued: signal the ring rows
             // free once they complete.
-            if (n > n_query && ok) umma_commit_pred(&bars[PB_RING_FREE], issuer);
+            if (n > n_query && ok && !ring_committed) umma_commit_pred(&bars[PB_RING_FREE], issuer);
             n_query = n;
         }
         if (ok && dk_pending) ok = issue_dk(n - 1);
