@@ -23,6 +23,7 @@ SIGNATURES = {
     "att3_sg_backward_workspace_bytes": (_sz, [_i] * 6),
     "att3_sg_forward": (_i, [_vp] * 9 + [_i] * 7 + [_vp]),
     "att3_sg_backward": (_i, [_vp] * 15 + [_i] * 7 + [_vp, _sz, _vp]),
+    "att3_sg_backward_kv32": (_i, [_vp] * 15 + [_i] * 7 + [_vp, _sz, _vp]),
     "att3_sg_backward_static_max_bytes": (_sz, []),
     "att3_sg_backward_static": (_i, [_vp] * 15 + [_i] * 7 + [_vp]),
     "att3_hg_forward": (_i, [_vp] * 22 + [_i] * 7 + [_vp]),

@@ -143,15 +143,17 @@ def sg_forward_raw(Q, R, S, Vr, Vs, mask, window: int, q_begin: int = 0):
     return Y, m, l
 
 
-def sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, window: int, q_begin: int = 0):
+def sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, window: int, q_begin: int = 0, kv_f32: bool = False):
+    """kv_f32: leave dR, dS, dVr, dVs in FP32 (partial sums of a process that holds only part of the
+    query heads of a KV head; windowed path only)."""
     B, Hq, N, D = Q.shape
     Hkv = R.shape[1]
     with torch.cuda.device(Q.device):
         dQ = torch.zeros_like(Q) if q_begin else torch.empty_like(Q)
-        dR, dS, dVr, dVs = (torch.empty_like(R) for _ in range(4))
+        dR, dS, dVr, dVs = (torch.empty_like(R, dtype=torch.float32 if kv_f32 else R.dtype) for _ in range(4))
         nbytes = lib.att3_sg_backward_workspace_bytes(B, Hq, Hkv, N, D, int(window))
         ws = _workspace(Q.device, nbytes)
-        _call(lib.att3_sg_backward, dY.data_ptr(), Q.data_ptr(), R.data_ptr(), S.data_ptr(), Vr.data_ptr(),
+        _call(lib.att3_sg_backward_kv32 if kv_f32 else lib.att3_sg_backward, dY.data_ptr(), Q.data_ptr(), R.data_ptr(), S.data_ptr(), Vr.data_ptr(),
               Vs.data_ptr(), Y.data_ptr(), m.data_ptr(), l.data_ptr(), _ptr(mask),
               dQ.data_ptr(), dR.data_ptr(), dS.data_ptr(), dVr.data_ptr(), dVs.data_ptr(),
               B, Hq, Hkv, N, D, int(window), int(q_begin), ws.data_ptr(), nbytes, _stream(Q))

@@ -1,6 +1,6 @@
 """Multi-GPU execution of the windowed single gather, one process per GPU.
 
-Two partitionings, neither of which puts a collective on the data path of the kernels:
+Three partitionings, none of which puts a collective inside the kernels:
 
 * batch / head sharding (``shard_batch``): independent problems, no communication.
 * query-row sharding of one long sequence (``RowShardedGather``): rank r owns the
@@ -13,6 +13,9 @@ Two partitionings, neither of which puts a collective on the data path of the ke
   messages of (window-1) x D elements per tensor: latency-bound, one exchange per
   pass, no all-reduce.  Shard starts are multiples of 128 so every key keeps its ring
   slot and the sharded result is bit-identical to the single-GPU one for Y and dQ.
+
+* head sharding of shared-KV problems (``HeadShardedGather``): the query heads of one KV head on
+  different ranks; the key-side gradients are FP32 partials summed with one all-reduce per backward.
 
 The reference has no multi-device path (its library never touches a communicator);
 this module is new.  The compute step is injectable so the host logic (partitioning,
@@ -156,6 +159,56 @@ class RowShardedGather:
             acc = torch.promote_types(own.dtype, torch.float32)       # BF16 partials are added in FP32
             own[:, :, :, n_own - n_recv:] = (own[:, :, :, n_own - n_recv:].to(acc) + recv.to(acc)).to(own.dtype)
         return (dQ[:, :, p.halo:p.halo + n_own], own[0], own[1], own[2], own[3])
+
+
+class HeadShardedGather:
+    """Shared-KV single gather with the query heads of each KV head split over the ranks of `group`
+    (the second axis of the (batch, head) partition: batches go to different groups, the heads of one
+    batch to the ranks of one group).  Rank r holds Q[:, heads_r] and dY[:, heads_r] and the whole key
+    side R, S, Vr, Vs ([B,Hkv,N,D], the same on every rank of the group).
+
+    The forward is local.  In the backward dQ is local, while every rank's key-side gradients are sums
+    over its own heads only: the four FP32 partial tensors are stacked and summed over the group with
+    one all-reduce (4 x [B,Hkv,N,D] floats) and rounded once afterwards -- the reduction the reference
+    performs over its per-head partial buffers inside one GPU (cuda/backward.cu:2548-2575), done across
+    GPUs.  ``compute_fwd(Q,R,S,Vr,Vs,window) -> (Y,m,l)`` and ``compute_bwd(dY,Q,R,S,Vr,Vs,Y,m,l,window)
+    -> (dQ, dR, dS, dVr, dVs)`` with FP32 key gradients default to the CUDA kernels."""
+
+    def __init__(self, window: int, group=None, compute_fwd: Optional[Callable] = None,
+                 compute_bwd: Optional[Callable] = None):
+        if not 1 <= window <= RING:
+            raise ValueError(f"window must be in [1,{RING}], got {window}")
+        self.group, self.window = group, window
+        if compute_fwd is None or compute_bwd is None:
+            from . import _cuda_kernels as ck
+            compute_fwd = compute_fwd or (lambda Q, R, S, Vr, Vs, w: ck.sg_forward_raw(Q, R, S, Vr, Vs, None, w))
+            compute_bwd = compute_bwd or (lambda dY, Q, R, S, Vr, Vs, Y, m, l, w:
+                                          ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, None, w, kv_f32=True))
+        self._fwd, self._bwd = compute_fwd, compute_bwd
+        self._saved = None
+
+    @staticmethod
+    def local_heads(hq: int, hkv: int, world: int, rank: int) -> list[int]:
+        """Query heads of rank `rank`: the same share of every KV head's group of hq // hkv heads."""
+        per_kv = hq // hkv
+        if per_kv % world:
+            raise ValueError(f"{per_kv} query heads per KV head do not split over {world} ranks")
+        share = per_kv // world
+        return [g * per_kv + rank * share + t for g in range(hkv) for t in range(share)]
+
+    def forward(self, Q, R, S, Vr, Vs):
+        Y, m, l = self._fwd(Q, R, S, Vr, Vs, self.window)
+        self._saved = (Q, R, S, Vr, Vs, Y, m, l)
+        return Y
+
+    def backward(self, dY, out_dtype=None):
+        """(dQ of the local heads, dR, dS, dVr, dVs summed over every rank's heads)."""
+        Q, R, S, Vr, Vs, Y, m, l = self._saved
+        dQ, dR, dS, dVr, dVs = self._bwd(dY, Q, R, S, Vr, Vs, Y, m, l, self.window)
+        part = torch.stack([dR, dS, dVr, dVs]).to(torch.promote_types(dR.dtype, torch.float32))
+        dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
+        kv = part.to(out_dtype or R.dtype)
+        return dQ, kv[0], kv[1], kv[2], kv[3]
 
 
 def gather_rows(local: torch.Tensor, shards: Sequence[tuple[int, int]], group=None) -> torch.Tensor:

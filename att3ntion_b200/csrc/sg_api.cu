@@ -215,12 +215,15 @@ static int launch_ring_bwd(const sgring::BwdParams& p, int nblk, cudaStream_t st
     return ATT3_OK;
 }
 
-static int launch_reduce(const sgring::BwdParams& p, int nblk, int D, void* dK, void* dV, cudaStream_t stream) {
+static int launch_reduce(const sgring::BwdParams& p, int nblk, int D, void* dK, void* dV, cudaStream_t stream,
+                         bool f32 = false) {
     sgring::ReduceParams r;
     r.part_K = p.part_K;
     r.part_V = p.part_V;
-    r.dK = static_cast<__nv_bfloat16*>(dK);
-    r.dV = static_cast<__nv_bfloat16*>(dV);
+    r.dK = f32 ? nullptr : static_cast<__nv_bfloat16*>(dK);
+    r.dV = f32 ? nullptr : static_cast<__nv_bfloat16*>(dV);
+    r.dK32 = f32 ? static_cast<float*>(dK) : nullptr;
+    r.dV32 = f32 ? static_cast<float*>(dV) : nullptr;
     r.rows = p.B * p.Hkv;
     r.N = p.N; r.D = D; r.q_begin = p.q_begin; r.block_len = p.block_len; r.nblk = nblk;
     const size_t total = static_cast<size_t>(r.rows) * p.N * (D / 4);
@@ -234,7 +237,7 @@ static int launch_reduce(const sgring::BwdParams& p, int nblk, int D, void* dK, 
     return ATT3_OK;
 }
 
-extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+static int sg_backward_impl(bool kv_f32, const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
                                 const void* Vs, const void* Y, const float* m, const float* l,
                                 const uint8_t* mask, void* dQ, void* dR, void* dS, void* dVr, void* dVs, int B,
                                 int Hq, int Hkv, int N, int D, int window, int q_begin, void* workspace,
@@ -253,6 +256,8 @@ extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, co
     if (reinterpret_cast<uintptr_t>(workspace) % 16 != 0)
         return att3::set_error(ATT3_ERR_WORKSPACE, "att3_sg_backward: workspace must be 16-byte aligned");
 
+    if (window == 0 && kv_f32)
+        return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_sg_backward_kv32: only the windowed path (window 1..128) is offered");
     if (window == 0) {
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         const size_t plane = static_cast<size_t>(B) * Hq * N * D;
@@ -299,7 +304,7 @@ extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, co
     p.Vb = static_cast<const __nv_bfloat16*>(Vs);
     int rc = D == 64 ? launch_ring_bwd<64, true>(p, nblk, st) : launch_ring_bwd<128, true>(p, nblk, st);
     if (rc) return rc;
-    if ((rc = launch_reduce(p, nblk, D, dS, dVs, st))) return rc;
+    if ((rc = launch_reduce(p, nblk, D, dS, dVs, st, kv_f32))) return rc;
     // Pass 2: sides exchanged -> dR, dVr.
     p.Ka = static_cast<const __nv_bfloat16*>(S);
     p.Va = static_cast<const __nv_bfloat16*>(Vs);
@@ -307,7 +312,27 @@ extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, co
     p.Vb = static_cast<const __nv_bfloat16*>(Vr);
     rc = D == 64 ? launch_ring_bwd<64, false>(p, nblk, st) : launch_ring_bwd<128, false>(p, nblk, st);
     if (rc) return rc;
-    return launch_reduce(p, nblk, D, dR, dVr, st);
+    return launch_reduce(p, nblk, D, dR, dVr, st, kv_f32);
+}
+
+extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+                                const void* Vs, const void* Y, const float* m, const float* l,
+                                const uint8_t* mask, void* dQ, void* dR, void* dS, void* dVr, void* dVs, int B,
+                                int Hq, int Hkv, int N, int D, int window, int q_begin, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+    return sg_backward_impl(false, dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv, N, D, window,
+                            q_begin, workspace, workspace_bytes, stream);
+}
+
+// The same backward with the four key-side gradients left in FP32 ([B,Hkv,N,D] floats): for a rank that holds
+// only part of the query heads of a KV head, whose sums are partials to be added across ranks before rounding.
+extern "C" int att3_sg_backward_kv32(const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+                                     const void* Vs, const void* Y, const float* m, const float* l,
+                                     const uint8_t* mask, void* dQ, float* dR, float* dS, float* dVr, float* dVs,
+                                     int B, int Hq, int Hkv, int N, int D, int window, int q_begin, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+    return sg_backward_impl(true, dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv, N, D, window,
+                            q_begin, workspace, workspace_bytes, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -934,6 +934,8 @@ struct ReduceParams {
     const float* part_V;
     __nv_bfloat16* dK;
     __nv_bfloat16* dV;
+    float* dK32;         // when non-null the sums are written here in FP32 instead (partials of a rank whose
+    float* dV32;         // query heads are only a part of the KV head's: summed across ranks before rounding)
     int rows;            // B * Hkv
     int N, D, q_begin, block_len, nblk;
 };
@@ -958,6 +960,11 @@ __global__ void sg_bwd_reduce_kernel(const ReduceParams p) {
                 sk.x += a.x; sk.y += a.y; sk.z += a.z; sk.w += a.w;
                 sv.x += v.x; sv.y += v.y; sv.z += v.z; sv.w += v.w;
             }
+        }
+        if (p.dK32) {
+            *reinterpret_cast<float4*>(p.dK32 + rk * p.D + c * 4) = sk;
+            *reinterpret_cast<float4*>(p.dV32 + rk * p.D + c * 4) = sv;
+            continue;
         }
         uint2 ok, ov;
         ok.x = pack_bf16x2(sk.x, sk.y); ok.y = pack_bf16x2(sk.z, sk.w);

@@ -407,6 +407,83 @@ def run_rows(args):
     dist.destroy_process_group()
 
 
+def run_heads(args):
+    """Config 4 itself (B4 Hq8 Hkv1 N8192 D128) partitioned over the ranks by (batch, head): up to four
+    ranks take one or more batches each (no collective); beyond that the query heads of a batch are split
+    over `world // 4` ranks, whose FP32 key-gradient partials are summed with one NCCL all-reduce per step
+    (4 x [b,1,N,128] floats).  Total work is fixed, so the scaling is strong.  --head-groups forces the head
+    split at smaller rank counts."""
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from att3ntion_b200 import _cabi, _cuda_kernels as ck
+    from att3ntion_b200._dist import HeadShardedGather, shard_batch
+    n, w, Bt = args.seq_len, args.window, args.batch
+    hg = args.head_groups or max(1, world // min(world, Bt))
+    if world % hg or HQ % hg:
+        raise SystemExit(f"bench.py: {world} ranks do not split into head groups of {hg}")
+    bshards = world // hg
+    brank, hrank = rank // hg, rank % hg
+    groups = [dist.new_group(list(range(b * hg, (b + 1) * hg))) for b in range(bshards)]
+    op = HeadShardedGather(w, group=groups[brank])
+    batches = list(shard_batch(Bt, bshards, brank))
+    heads = HeadShardedGather.local_heads(HQ, 1, hg, hrank)
+    g = torch.Generator(device="cpu").manual_seed(3)
+    s = 1.0 / math.sqrt(D)
+    def draw(nh, scale, hsel=None):
+        t = (torch.randn(Bt, nh, n, D, generator=g) * scale).to(torch.bfloat16)[batches]
+        return (t[:, hsel] if hsel is not None else t).contiguous().to(dev)
+    Q = draw(HQ, s, heads); R = draw(1, s); S = draw(1, s); Vr = draw(1, s); Vs = draw(1, s); dY = draw(HQ, 1.0, heads)
+    flops_step = 16 * D * triplets(Bt, HQ, n, w)
+
+    def step():
+        if not batches:
+            return None
+        y = op.forward(Q, R, S, Vr, Vs)
+        return y, op.backward(dY)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    dist.barrier(); torch.cuda.synchronize()
+    l0 = sum(_cabi.lib.att3_launch_count(i) for i in range(4))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = step()
+    e1.record()
+    dist.barrier(); torch.cuda.synchronize()
+    ck.device_status()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    launches = sum(_cabi.lib.att3_launch_count(i) for i in range(4)) - l0
+    chk = torch.zeros(3, device=dev)
+    if out is not None:
+        # Y and dQ summed over everything; the key gradient counted once per batch shard (head rank 0)
+        chk = torch.stack([out[0].float().abs().sum(), out[1][0].float().abs().sum(),
+                           out[1][1].float().abs().sum() * (1.0 if hrank == 0 else 0.0)])
+    dist.all_reduce(chk)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "fwd+bwd TFLOP/s, shared-KV causal w=128 d=128, (batch, head) partition",
+            "value": flops_step / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"shared-KV B{Bt} Hq{HQ} Hkv1 N{n} D{D} causal window {w}, {bshards} batch shard(s) x "
+                                   f"{hg} head group(s); key-gradient partials all-reduced inside a batch shard",
+                       "allreduce_bytes_per_step": (4 * len(batches) * n * D * 4) if hg > 1 else 0,
+                       "flops_per_step": flops_step},
+            "gpu_launches": int(launches), "checksum": [round(v, 3) for v in chk.tolist()],
+        }))
+    dist.destroy_process_group()
+
+
 def run_other(args):
     """Secondary configurations, one GPU, device-resident inputs, CUDA events, median of `--steps`
     repeats: C3 = independent-head single gather B4 H8 N2048 D64 w128 (16*D*T FLOPs), C2 = three-gather
@@ -495,8 +572,10 @@ if __name__ == "__main__":
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--seq-len", type=int, default=N, help="sequence length (profiling captures use a smaller case)")
     ap.add_argument("--batch", type=int, default=B)
-    ap.add_argument("--workload", default="batch", choices=["batch", "rows", "other"],
-                    help="batch: config 4, one batch per GPU (default); rows: config 5, one sequence row-sharded")
+    ap.add_argument("--workload", default="batch", choices=["batch", "rows", "heads", "other"],
+                    help="batch: config 4, one batch per GPU (default); rows: config 5, one sequence row-sharded; "
+                         "heads: config 4 split by (batch, head) with the key-gradient all-reduce (strong scaling)")
+    ap.add_argument("--head-groups", type=int, default=0, help="heads workload: ranks per batch shard (default: world // 4)")
     ap.add_argument("--profile", action="store_true",
                     help="kernel-only run for profiler captures: exact warm-up count, no e2e and no CPU leg")
     a = ap.parse_args()
@@ -507,5 +586,7 @@ if __name__ == "__main__":
         run_other(a)
     elif a.workload == "rows":
         run_rows(a)
+    elif a.workload == "heads":
+        run_heads(a)
     else:
         run_ours(a)

@@ -101,6 +101,18 @@ int att3_sg_backward(const void* dY, const void* Q, const void* R, const void* S
                      int B, int Hq, int Hkv, int N, int D, int window, int q_begin,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* att3_sg_backward with the four key-side gradients left in FP32
+ * ([B,Hkv,N,D] floats, same workspace): for a process that holds only part of
+ * the query heads of a KV head (heads sharded over GPUs), whose key gradients
+ * are partial sums to be added across processes before they are rounded --
+ * the reduction the reference performs over its per-head partial buffers inside
+ * one GPU (cuda/backward.cu:2548-2575).  Windowed path only (window 1..128). */
+int att3_sg_backward_kv32(const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+                          const void* Vs, const void* Y, const float* m, const float* l,
+                          const uint8_t* mask, void* dQ, float* dR, float* dS, float* dVr, float* dVs,
+                          int B, int Hq, int Hkv, int N, int D, int window, int q_begin,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
 /* att3_sg_backward for callers that cannot allocate device memory.  It has no
  * counterpart in the reference, whose launchers allocate their own buffers
  * through torch.  Meant for hosts where an allocator call is impossible or

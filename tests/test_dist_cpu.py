@@ -63,6 +63,45 @@ def test_row_sharding_matches_unsharded(tmp_path, world, n, window, hkv):
     assert all(lo % 128 == 0 for lo, _ in res["shards"])
 
 
+def _head_worker(rank, world, port, hkv, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from att3ntion_b200._dist import HeadShardedGather
+        n, window, hq = 160, 48, 4 * hkv
+        g = torch.Generator().manual_seed(9)
+        full = {"Q": torch.randn(2, hq, n, 16, generator=g, dtype=torch.float64)}
+        for k in NAMES[1:]:
+            full[k] = torch.randn(2, hkv, n, 16, generator=g, dtype=torch.float64)
+        dY = torch.randn(2, hq, n, 16, generator=g, dtype=torch.float64)
+        fwd = lambda Q, R, S, Vr, Vs, w: _oracle_fwd(Q, R, S, Vr, Vs, w, 0)
+        bwd = lambda dY_, Q, R, S, Vr, Vs, Y, m, l, w: _oracle_bwd(dY_, Q, R, S, Vr, Vs, Y, m, l, w, 0)
+        op = HeadShardedGather(window, compute_fwd=fwd, compute_bwd=bwd)
+        heads = HeadShardedGather.local_heads(hq, hkv, world, rank)
+        Y = op.forward(full["Q"][:, heads].contiguous(), *[full[k] for k in NAMES[1:]])
+        dQ, dR, dS, dVr, dVs = op.backward(dY[:, heads].contiguous())
+        ref = O.single_gather_banded(*[full[k] for k in NAMES], window=window, dY=dY, chunk=32)
+        errs = [(Y - ref["Y"][:, heads]).abs().max().item(), (dQ - ref["dQ"][:, heads]).abs().max().item()]
+        errs += [(a - ref[k]).abs().max().item() for a, k in zip((dR, dS, dVr, dVs), ["dR", "dS", "dVr", "dVs"])]
+        torch.save({"errs": errs, "heads": heads}, f"{out}.{rank}")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("hkv", [1, 2])
+def test_head_sharding_sums_key_gradients_over_ranks(tmp_path, hkv):
+    """Two ranks, each with half of the query heads of every KV head: Y and dQ are the local slices of
+    the unsharded result, the key gradients on every rank are the full sums."""
+    out = str(tmp_path / "res.pt")
+    mp.spawn(_head_worker, args=(2, _free_port(), hkv, out), nprocs=2, join=True)
+    seen = []
+    for rank in range(2):
+        res = torch.load(f"{out}.{rank}")
+        assert max(res["errs"]) < 1e-9, res
+        seen += res["heads"]
+    assert sorted(seen) == list(range(4 * hkv))
+
+
 def test_partition_helpers():
     from att3ntion_b200._dist import row_shards, shard_batch
     assert row_shards(131072, 8) == [(i * 16384, (i + 1) * 16384) for i in range(8)]

@@ -271,6 +271,33 @@ def test_lowlevel_rejections(ck):
     assert "win=32" in ck.sg_dispatch()["shared_forward"]
 
 
+def test_head_split_partials_sum_to_the_full_key_gradients(ck):
+    """Query heads split in two (as two GPUs of one batch shard would hold them): Y and dQ of each half are
+    bit-identical to the full run's slices, and the FP32 key-gradient partials of the halves add up to the
+    full run's key gradients (summation order differs, so to FP32 rounding before the final BF16 rounding)."""
+    B, Hq, N, D, w = 2, 8, 400, 128, 128
+    g = torch.Generator(device="cpu").manual_seed(17)
+    Q = (torch.randn(B, Hq, N, D, generator=g) / math.sqrt(D)).to(torch.bfloat16).cuda()
+    kv = [(torch.randn(B, 1, N, D, generator=g) / math.sqrt(D)).to(torch.bfloat16).cuda() for _ in range(4)]
+    dY = torch.randn(B, Hq, N, D, generator=g).to(torch.bfloat16).cuda()
+    Y, m, l = ck.sg_forward_raw(Q, *kv, None, w)
+    full = ck.sg_backward_raw(dY, Q, *kv, Y, m, l, None, w)
+    parts = []
+    for heads in (slice(0, 4), slice(4, 8)):
+        Qh, dYh = Q[:, heads].contiguous(), dY[:, heads].contiguous()
+        Yh, mh, lh = ck.sg_forward_raw(Qh, *kv, None, w)
+        assert torch.equal(Yh, Y[:, heads]) and torch.equal(mh, m[:, heads]) and torch.equal(lh, l[:, heads])
+        gh = ck.sg_backward_raw(dYh, Qh, *kv, Yh, mh, lh, None, w, kv_f32=True)
+        assert gh[1].dtype == torch.float32
+        assert torch.equal(gh[0], full[0][:, heads])
+        parts.append(gh)
+    ck.device_status()
+    for k in range(1, 5):
+        total = (parts[0][k] + parts[1][k])
+        rel, mx = O.errors(total, full[k].float())
+        assert rel < 4e-3 and mx < 8e-3, (k, rel, mx)       # BF16 rounding of the full run's output only
+
+
 def test_full_size_properties_c4_shape(ck):
     """Shared-KV B4 Hq8 N8192 D128 w128: too large for the dense oracle, so check
     (i) a 192-query slice of one batch against the banded FP64 oracle (Y, LSE, dQ
