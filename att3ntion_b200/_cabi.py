@@ -35,7 +35,8 @@ SIGNATURES = {
     "att3_launch_count": (C.c_ulonglong, [_i]),
     "att3_timing_enable": (_i, [_i]),
     "att3_timing_read": (_i, [_i, C.POINTER(C.c_double), C.POINTER(C.c_ulonglong)]),
-    "att3_umma_selftest": (_i, [_vp, _vp, _vp] + [_i] * 6 + [_vp, _vp]),
+    "att3_umma_selftest": (_i, [_vp, _vp, _vp, _i, _vp, _vp]),
+    "att3_wait_selftest": (_i, [C.c_uint, _vp]),
 }
 
 

@@ -22,6 +22,7 @@ _cfg = {k: 0 for k in ("fwd_warps", "fwd_bk", "bwd_a_warps", "bwd_a_bk", "bwd_r_
 _last = {"sg_fwd": "", "sg_bwd": "", "shared_fwd": "", "shared_bwd": ""}
 _enabled = [True, True]
 _workspaces: dict = {}
+_MAX_WORKSPACES = 8          # (device, stream) pairs kept; the least recently used buffer is dropped beyond that
 
 
 def _call(fn, *args):
@@ -39,13 +40,22 @@ def _ptr(t):
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
-    """Scratch buffer cached per device and stream; grown, never shrunk."""
+    """Scratch buffer cached per device and stream (two streams must not share one: their kernels may
+    overlap).  A buffer grows on demand; at most `_MAX_WORKSPACES` are kept, least recently used first
+    out, and `release_workspaces()` drops them all."""
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
-    buf = _workspaces.get(key)
+    buf = _workspaces.pop(key, None)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
-        _workspaces[key] = buf
+    _workspaces[key] = buf                       # re-inserted last: dicts keep insertion order
+    while len(_workspaces) > _MAX_WORKSPACES:
+        _workspaces.pop(next(iter(_workspaces)))
     return buf
+
+
+def release_workspaces() -> None:
+    """Drops every cached scratch buffer (they are re-created on the next backward)."""
+    _workspaces.clear()
 
 
 # --------------------------------------------------------------------------- checks
@@ -309,7 +319,14 @@ def forward(Q, R, S, Vq_1, Vq_2, Vr_1, Vr_2, Vs_1, Vs_2, dropout_rate=0.0, I_val
     ts = [Q, R, S, Vq_1, Vq_2, Vr_1, Vr_2, Vs_1, Vs_2]
     mask = _check_hg(ts, mask, "forward")
     B, H, N, D = Q.shape
-    n_valid = int(I_valid) if 0 < int(I_valid) < N else 0
+    # The reference takes one valid length per role (cuda/forward.cu:1300-1302) and defaults each to the
+    # padded length.  These kernels take one length for all three roles; a call that asks for different
+    # ones would silently see other keys than it asked for, so it is rejected.
+    valid = [int(v) if 0 < int(v) <= N else N for v in (I_valid, J_valid, K_valid)]
+    if not (valid[0] == valid[1] == valid[2]):
+        raise RuntimeError(f"forward: I_valid, J_valid and K_valid must agree (one valid length for all three "
+                           f"roles), got {tuple(valid)}")
+    n_valid = valid[0] if valid[0] < N else 0
     scatter = 1 if (gather_mode == 0 and _scatter_in_use(Vq_2, Vr_2, Vs_2)) else 0
     with torch.cuda.device(Q.device):
         outs = [torch.empty_like(Q) for _ in range(6)]

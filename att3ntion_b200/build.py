@@ -27,8 +27,6 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     "-Xcompiler", "-fPIC",
     "-Xptxas", "-v",
-    # extra flags for diagnostic builds, e.g. ATT3_NVCC_EXTRA=-DATT3_PIPE_TRACE (hand-off cycle counters)
-    *os.environ.get("ATT3_NVCC_EXTRA", "").split(),
 ]
 
 

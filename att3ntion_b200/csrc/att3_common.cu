@@ -138,7 +138,7 @@ extern "C" int att3_timing_read(int kernel_id, double* total_ms, unsigned long l
 
 extern "C" const char* att3_last_error(void) { return att3::g_err; }
 
-extern "C" int att3_abi_version(void) { return 1; }
+extern "C" int att3_abi_version(void) { return 2; }
 
 extern "C" unsigned long long att3_launch_count(int which) {
     return (which >= 0 && which < 4) ? att3::g_launches[which].load() : 0ull;

@@ -6,32 +6,26 @@
 #include "att3_abi_internal.h"
 #include "sg_ring_fwd.cuh"
 #include "sg_ring_bwd.cuh"
-#include <cstdlib>
 
 namespace {
 
 // Sticky status word of this translation unit's kernels (bounded-wait failures).
 __device__ int g_sg_status = 0;
 
-// Cycle counters of the pipelined backward (diagnostic; filled when ATT3_TRACE=1).
-__device__ long long g_sg_trace[32 + 384 + 640];
-
-int trace_mode() {
-    static const int mode = [] { const char* e = getenv("ATT3_TRACE"); return e ? atoi(e) : 0; }();
-    return mode;
-}
-
-long long* trace_ptr() {
-    if (trace_mode() <= 0) return nullptr;
-    long long* p = nullptr;
-    cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_sg_trace);
-    return p;
-}
-
+// Device address of the status word on the current device.  The symbol is resolved once per
+// device and thread (a thread-local table, so concurrent callers never share a slot that is
+// being written); a failed look-up returns null and the entry point reports it.
 int* status_ptr() {
-    int* p = nullptr;
-    cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_sg_status);
-    return p;
+    constexpr int kMaxDevices = 64;
+    static thread_local int* cached[kMaxDevices] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    if (!cached[dev]) {
+        int* p = nullptr;
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_sg_status) != cudaSuccess) return nullptr;
+        cached[dev] = p;
+    }
+    return cached[dev];
 }
 
 // Validation shared by forward and backward; mirrors single_gather_check and
@@ -74,31 +68,6 @@ extern "C" int att3_sg_query_blocks(int B, int Hq, int Hkv, int N, int q_begin, 
     return n * B * Hkv;
 }
 
-// Diagnostic: copies and clears the 32 cycle counters (not part of the public header).
-extern "C" int att3_debug_trace(long long* out32) {
-    cudaDeviceSynchronize();
-    if (cudaMemcpyFromSymbol(out32, g_sg_trace, sizeof(long long) * 32) != cudaSuccess) return ATT3_ERR_CUDA;
-    static long long z[32 + 384 + 640] = {0};
-    cudaMemcpyToSymbol(g_sg_trace, z, sizeof(z));
-    return ATT3_OK;
-}
-
-// Diagnostic: the hand-off time stamps of six steady-state heads, 32 events each, dQ pass then the other.
-extern "C" int att3_debug_timeline(long long* out384) {
-    cudaDeviceSynchronize();
-    if (cudaMemcpyFromSymbol(out384, g_sg_trace, sizeof(long long) * 384, sizeof(long long) * 32) != cudaSuccess)
-        return ATT3_ERR_CUDA;
-    return ATT3_OK;
-}
-
-// Diagnostic: per-CTA (cycles, SM id) pairs of the two backward launches, 160 CTAs each.
-extern "C" int att3_debug_cta_cycles(long long* out640) {
-    cudaDeviceSynchronize();
-    if (cudaMemcpyFromSymbol(out640, g_sg_trace, sizeof(long long) * 640, sizeof(long long) * (32 + 384)) != cudaSuccess)
-        return ATT3_ERR_CUDA;
-    return ATT3_OK;
-}
-
 extern "C" int att3_device_status(void* stream) {
     cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_device_status: synchronize");
@@ -113,6 +82,31 @@ extern "C" int att3_device_status(void* stream) {
         return att3::set_error(ATT3_ERR_TIMEOUT, "a bounded device-side wait ran out (status %d)", h);
     }
     return ATT3_OK;
+}
+
+// A kernel whose only job is to let a bounded wait run out: one thread waits on an mbarrier that
+// nobody ever arrives on, gives up after `limit` polls, records the fact in the status word and
+// the kernel returns normally.  It is how the failure path (status word -> att3_device_status ->
+// ATT3_ERR_TIMEOUT) is exercised without a fault, a trap or a hang.
+__global__ void wait_selftest_kernel(int* status, unsigned limit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        sm100::mbar_init(&bar, 1);
+        sm100::fence_mbar_init();
+        if (!sm100::mbar_wait(&bar, 0, limit)) atomicExch(status, 7);
+        sm100::mbar_inval(&bar);
+    }
+}
+
+extern "C" int att3_wait_selftest(unsigned limit, void* stream) {
+    if (limit == 0 || limit > (1u << 20))
+        return att3::set_error(ATT3_ERR_INVALID, "att3_wait_selftest: limit must be in [1, 2^20] polls");
+    if (!att3::require_sm100("att3_wait_selftest")) return ATT3_ERR_UNSUPPORTED;
+    int* st = status_ptr();
+    if (!st) return att3::set_error(ATT3_ERR_CUDA, "att3_wait_selftest: status word not resolvable");
+    wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(st, limit);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "att3_wait_selftest: launch");
 }
 
 template <int D>
@@ -165,7 +159,7 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status_ptr();
-    p.trace = trace_ptr();
+    if (!p.status) return att3::set_error(ATT3_ERR_CUDA, "att3_sg_forward: status word not resolvable");
     {   // TMA descriptors for the kernel's row staging (one row per copy)
         const size_t qrows = static_cast<size_t>(B) * Hq * N, krows = static_cast<size_t>(B) * Hkv * N;
         int rc;
@@ -292,8 +286,7 @@ static int sg_backward_impl(bool kv_f32, const void* dY, const void* Q, const vo
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status_ptr();
-    p.trace = trace_ptr();
-    p.trace_mode = trace_mode();
+    if (!p.status) return att3::set_error(ATT3_ERR_CUDA, "att3_sg_backward: status word not resolvable");
     const int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, sgring::BWD_MIN_BLOCK, &p.block_len);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 

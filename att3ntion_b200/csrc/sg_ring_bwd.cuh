@@ -87,8 +87,6 @@ struct BwdParams {
     int B, Hq, Hkv, N, window, q_begin, block_len;
     float scale;
     int* status;
-    long long* trace;                // optional cycle counters of the pipelined schedule (null: off)
-    int trace_mode;                  // 1: summed wait cycles per hand-off, 2: time stamps of six steady-state heads
 };
 
 enum PipeBar {
@@ -182,15 +180,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     volatile int* sFail = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 4);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef ATT3_PIPE_TRACE
-    // diagnostic: trace mode 3 walks the work in the opposite order of the CTA indices
-    const bool rev = p.trace_mode == 3;
-    const int b = rev ? gridDim.z - 1 - blockIdx.z : blockIdx.z, g = blockIdx.y;
-    const int bx = rev ? gridDim.x - 1 - blockIdx.x : blockIdx.x;
-#else
     const int b = blockIdx.z, g = blockIdx.y;
     const int bx = blockIdx.x;
-#endif
     const int G = p.Hq / p.Hkv;
     const int q0 = p.q_begin + bx * p.block_len;
     const int q1 = min(q0 + p.block_len, p.N);
@@ -241,35 +232,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     // and the MMA warp for its descriptors and bookkeeping; 8*E + 4*H + 4*M = 512 registers per lane
     // column), does its share of the set-up and then meets the others at one CTA barrier before the
     // hand-off protocol starts.
-#ifndef ATT3_BWD_E_REGS
-#define ATT3_BWD_E_REGS 88
-#define ATT3_BWD_H_REGS 232
-#define ATT3_BWD_M_REGS 104
-#endif
-    constexpr int E_REGS = ATT3_BWD_E_REGS, H_REGS = ATT3_BWD_H_REGS, M_REGS = ATT3_BWD_M_REGS;
+    constexpr int E_REGS = 88, H_REGS = 232, M_REGS = 104;
     static_assert(8 * E_REGS + 4 * H_REGS + 4 * M_REGS <= 2048, "register file: 64K registers / 32 lanes");
-    // Optional cycle accounting of the hand-offs (one thread per role of CTA 0), compiled in only with
-    // -DATT3_PIPE_TRACE: the bookkeeping costs registers in every role.
-#ifdef ATT3_PIPE_TRACE
-    const bool tracer = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&
-                        (tid == 0 || tid == PIPE_E_THREADS || tid == PIPE_E_THREADS + PIPE_H_THREADS);
-    const bool timed = p.trace && p.trace_mode >= 2 && tid == PIPE_E_THREADS + PIPE_H_THREADS;   // every CTA
-    const long long t_begin = (tracer || timed) ? clock64() : 0;
-    unsigned long long ns_begin = 0;
-    if (timed) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
-    const bool tr_sum = tracer && p.trace_mode == 1, tr_line = tracer && p.trace_mode == 2;
-#define TR(k) (tr_sum ? p.trace + (k) : nullptr)
-    // Timeline of six steady-state heads (time stamps of the hand-offs, one thread per role).
-    constexpr int TL_FIRST = 804;
-#define TL(ev)                                                                                          \
-    do {                                                                                                \
-        if (tr_line && n >= TL_FIRST && n < TL_FIRST + 6)                                               \
-            p.trace[32 + (WITH_DQ ? 0 : 192) + (n - TL_FIRST) * 32 + (ev)] = clock64();                 \
-    } while (0)
-#else
-#define TR(k) nullptr
-#define TL(ev) do { } while (0)
-#endif
     uint32_t tmem_base = 0;
     auto cta_start_sync = [&]() {
         tc_fence_before();
@@ -337,10 +301,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         fence_async_smem();
         cta_start_sync();
         constexpr int GB = L::G_BUFS;
-#ifndef ATT3_BWD_HB
-#define ATT3_BWD_HB 8
-#endif
-        constexpr int HB = ATT3_BWD_HB;                 // staged chunks in flight per thread (registers: 4 per chunk)
+        constexpr int HB = 8;                 // staged chunks in flight per thread (registers: 4 per chunk)
         int n = 0, it = 0, n_query = 0, ring_phase = 0;
         bool ok = true;
         float l_next = __ldg(p.l + row_at(q0, 0));
@@ -359,9 +320,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 // the staged rows of this iteration have landed; everyone is past the previous build
                 asm volatile("cp.async.wait_all;" ::: "memory");
                 warp_arrive(&bars[PB_H_SYNC], lane);
-                ok = pipe_wait(&bars[PB_H_SYNC], it & 1, sFail, TR(17));
+                ok = pipe_wait(&bars[PB_H_SYNC], it & 1, sFail);
                 if (!ok) break;
-                TL(20);
                 const bool boundary = hh == 0 && i > q0;      // key i replaces key i-128 in slot s
                 const uint8_t* nx = sNext + (i & 1) * L::NEXT_BYTES;
                 if (boundary && hslot == s) {
@@ -384,9 +344,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 if (work) {
                     // Buffer reuse: Qp[n&1] was last read by the dKb MMAs of head n-2.  Each per-buffer
                     // barrier is waited on at every one of its phases.
-                    if (n >= 2) ok = pipe_wait(&bars[PB_D_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, TR(18));
+                    if (n >= 2) ok = pipe_wait(&bars[PB_D_DONE0 + qb], ((n >> 1) - 1) & 1, sFail);
                     if (!ok) break;
-                    TL(21);
                     // The staged row is read in batches of HB chunks ahead of the stores: the compiler
                     // cannot tell that the tile stores do not alias the staging area, and would otherwise
                     // run load -> multiply -> store one chunk at a time (about 100 cycles each).
@@ -405,14 +364,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                             *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c0 + c)) = o;
                         }
                     }
-                    TL(23);
                 }
                 if (boundary) {
                     // The operand-tile rows of slot s change key only after every MMA that reads the
                     // rings (and, in the dQ pass, the E warps' reads of the Kb rows) is done with the
                     // previous query; the tile built above does not depend on it, so it costs nothing.
                     if (prev_work) {
-                        ok = pipe_wait(&bars[PB_RING_FREE], ring_phase & 1, sFail, TR(16));
+                        ok = pipe_wait(&bars[PB_RING_FREE], ring_phase & 1, sFail);
                         ++ring_phase;
                         if (!ok) break;
                     }
@@ -425,15 +383,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     }
                 }
                 if (work || boundary) fence_async_smem();
-                TL(24);
                 if (work) {
                     // the score product needs only this tile (and the rings)
                     warp_arrive(&bars[PB_QP_FULL0 + qb], lane);
-                    TL(22);
                     // Gt[n%GB] was last read by the dVb MMAs of head n-GB
-                    if (n >= GB) ok = pipe_wait(&bars[PB_V_DONE0 + gb], ((n / GB) - 1) & 1, sFail, TR(18));
+                    if (n >= GB) ok = pipe_wait(&bars[PB_V_DONE0 + gb], ((n / GB) - 1) & 1, sFail);
                     if (!ok) break;
-                    TL(25);
 #pragma unroll
                     for (int c0 = 0; c0 < CH; c0 += HB) {
                         uint4 y[HB];
@@ -451,7 +406,6 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     }
                     fence_async_smem();
                     warp_arrive(&bars[PB_GT_FULL0 + gb], lane);
-                    TL(26);
                 }
                 if (work) ++n;
             }
@@ -546,7 +500,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         };
         // dKb += gA^T(m) Qp(m) for the head m = n - 1 whose gA^T the E warps finish last.
         auto issue_dk = [&](int m) {
-            bool r = pipe_wait(&bars[PB_G_FULL], m & 1, sFail, TR(5));
+            bool r = pipe_wait(&bars[PB_G_FULL], m & 1, sFail);
             if (r) {
                 tc_fence_after();
                 const uint32_t tA = tmem_base + C_R0 + (m & 1) * 128 + 32;
@@ -560,14 +514,14 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         auto settle_flush = [&]() {
             bool r = true;
             if (flush_pending) {
-                r = pipe_wait(&bars[PB_FLUSH_DONE], flushes_seen & 1, sFail, TR(2));
+                r = pipe_wait(&bars[PB_FLUSH_DONE], flushes_seen & 1, sFail);
                 ++flushes_seen;
                 flush_pending = false;
                 if (r) tc_fence_after();
             }
             if (r && self_pending) {
                 // this warp made the commit, so it knows which phase it is waiting for
-                r = pipe_wait(&bars[PB_ACC_DONE], (acc_commits - 1) & 1, sFail, TR(2));
+                r = pipe_wait(&bars[PB_ACC_DONE], (acc_commits - 1) & 1, sFail);
                 self_pending = false;
                 if (r) {
                     tc_fence_after();
@@ -611,31 +565,26 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 const uint32_t qoff = qb * (L::TILE / 16), goff = gb * (L::TILE / 16);   // buffer offsets, 16-byte units
                 const uint32_t tA = tmem_base + C_R0 + (n & 1) * 128;          // X^T, then P^T | gA^T
                 const uint32_t tB = tmem_base + C_R0 + ((n & 1) ^ 1) * 128;    // dP^T, then W
-                TL(0);
-                ok = pipe_wait(&bars[PB_QP_FULL0 + qb], (n >> 1) & 1, sFail, TR(1));
+                ok = pipe_wait(&bars[PB_QP_FULL0 + qb], (n >> 1) & 1, sFail);
                 // A(n) = B(n-1): the E warps have taken dP^T (or W) of the previous head out of it
-                if (ok && n > 0) ok = pipe_wait(&bars[PB_B_FREE], (n - 1) & 1, sFail, TR(3));
-                TL(1);
+                if (ok && n > 0) ok = pipe_wait(&bars[PB_B_FREE], (n - 1) & 1, sFail);
                 if (!ok) break;
                 tc_fence_after();
                 run_ss(tA, dKb, dQpK + qoff);                  // X^T = Kb Qp^T
                 umma_commit_pred(&bars[PB_S_XT], issuer);
-                TL(2);
                 if (!WITH_DQ && dk_pending) {
                     ok = issue_dk(n - 1);
                     dk_pending = false;
                     if (!ok) break;
                 }
-                TL(3);
                 // B(n) = A(n-1): the accumulation MMAs of the previous head read their A operand there,
                 // and a later MMA is not held back for an earlier one's operand reads
-                if (n > 0) ok = pipe_wait(&bars[PB_D_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, TR(0));
-                if (ok) ok = pipe_wait(&bars[PB_GT_FULL0 + gb], (n / GB) & 1, sFail, TR(1));
+                if (n > 0) ok = pipe_wait(&bars[PB_D_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail);
+                if (ok) ok = pipe_wait(&bars[PB_GT_FULL0 + gb], (n / GB) & 1, sFail);
                 if (!ok) break;
                 tc_fence_after();
                 run_ss(tB, dVb, dGK + goff);                   // dP^T = Vb Gt^T
                 umma_commit_pred(&bars[PB_S_DP], issuer);
-                TL(4);
                 if (!WITH_DQ && hh == G - 1) {
                     // The query's last reads of the ring tiles have been issued (without the dQ product only
                     // the two score-shaped products read them): the H warps may bring in the next key as
@@ -643,17 +592,14 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     umma_commit_pred(&bars[PB_RING_FREE], issuer);
                     ring_committed = true;
                 }
-                ok = pipe_wait(&bars[PB_P_FULL], ph, sFail, TR(4));
+                ok = pipe_wait(&bars[PB_P_FULL], ph, sFail);
                 if (ok && (flush_pending || self_pending)) ok = settle_flush();   // the lane zeroed at the query boundary
-                TL(5);
                 if (!ok) break;
                 tc_fence_after();
                 run_ts(tAV, tA, dGM + goff, 1);                // dVb += P^T Gt
                 umma_commit_pred(&bars[PB_V_DONE0 + gb], issuer);
-                TL(6);
                 if (WITH_DQ) {
-                    ok = pipe_wait(&bars[PB_G_FULL], ph, sFail, TR(5));
-                    TL(7);
+                    ok = pipe_wait(&bars[PB_G_FULL], ph, sFail);
                     if (!ok) break;
                     tc_fence_after();
                     // W first: the E warps wait for it, nobody is in a hurry for dKb
@@ -661,7 +607,6 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     umma_commit_pred(&bars[PB_W_FULL], issuer);
                     run_ts(tAK, tA + 32, dQpM + qoff, 1);      // dKb += gA^T Qp
                     umma_commit_pred(&bars[PB_D_DONE0 + qb], issuer);
-                    TL(8);
                 } else {
                     dk_pending = true;
                 }
@@ -762,11 +707,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 // Both phases walk the columns in two rounds of 32 inside a rolled loop: half the registers
                 // and half the code of one straight-line pass, and the BF16 results of a round land on
                 // columns whose scores an earlier round (or this one) has already taken.
-                TL(10);
-                ok = pipe_wait(&bars[PB_S_XT], ph, sFail, TR(8));
+                ok = pipe_wait(&bars[PB_S_XT], ph, sFail);
                 if (!ok) break;
                 tc_fence_after();
-                TL(11);
 #pragma unroll 1
                 for (int cc = 0; cc < 2; ++cc) {
                     uint32_t x[32], pk[16];
@@ -785,16 +728,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     }
                     tmem_st16(tA + cc * 16, pk);
                 }
-                TL(12);
                 tmem_wait_st();
                 tc_fence_before();
                 warp_arrive(&bars[PB_P_FULL], lane);
-                TL(14);
                 // ---- phase 2: gA^T = P^T o (dP^T - delta), BF16 into the last 32 of this thread's columns
-                ok = pipe_wait(&bars[PB_S_DP], ph, sFail, TR(9));
+                ok = pipe_wait(&bars[PB_S_DP], ph, sFail);
                 if (!ok) break;
                 tc_fence_after();
-                TL(15);
 #pragma unroll 1
                 for (int cc = 0; cc < 2; ++cc) {
                     uint32_t dp[32], pk[16];
@@ -818,12 +758,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 tmem_wait_st();
                 tc_fence_before();
                 warp_arrive(&bars[PB_G_FULL], lane);
-                TL(16);
                 if (WITH_DQ) {
-                    ok = pipe_wait(&bars[PB_W_FULL], ph, sFail, TR(11));
+                    ok = pipe_wait(&bars[PB_W_FULL], ph, sFail);
                     if (!ok) break;
                     tc_fence_after();
-                    TL(17);
                     // dQ[d] = scale * sum_k Kb_k[d] * W[k][d]; this thread: lane k, d in its half.
                     constexpr int NC = HD / 32;
                     float* red = sRed + (n & 1) * 4 * D;
@@ -878,11 +816,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                         const float s = warp_transpose_sum_2x16_packed(va, vb, lane);
                         red[(warp & 3) * D + ch * HD + c * 32 + lane] = s;
                     }
-                    TL(18);
                     warp_arrive(&bars[PB_E_SYNC2], lane);
-                    ok = pipe_wait(&bars[PB_E_SYNC2], ph, sFail, TR(12));
+                    ok = pipe_wait(&bars[PB_E_SYNC2], ph, sFail);
                     if (!ok) break;
-                    TL(19);
                     if (tid < D)
                         p.dQ[row * D + tid] =
                             __float2bfloat16(p.scale * (red[tid] + red[D + tid] + red[2 * D + tid] + red[3 * D + tid]));
@@ -894,31 +830,6 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             n_query = n;
         }
     }
-#ifdef ATT3_PIPE_TRACE
-    if (tr_sum) p.trace[tid == 0 ? 14 : (tid == PIPE_E_THREADS ? 19 : 6)] += clock64() - t_begin;
-    if (timed) {
-        unsigned long long ns_end;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
-        const long long cyc = clock64() - t_begin, ns = static_cast<long long>(ns_end - ns_begin);
-        if (tracer) {                                                          // cycles and nanoseconds of CTA 0
-            p.trace[24 + (WITH_DQ ? 0 : 2)] = cyc;
-            p.trace[25 + (WITH_DQ ? 0 : 2)] = ns;
-        }
-        {   // per-CTA record behind the timeline area: cycles, SM id (first 160 CTAs of each pass)
-            const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-            if (cta < 160) {
-                uint32_t smid;
-                asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-                p.trace[32 + 384 + ((WITH_DQ ? 0 : 160) + cta) * 2] = cyc;
-                p.trace[32 + 384 + ((WITH_DQ ? 0 : 160) + cta) * 2 + 1] = smid;
-            }
-        }
-        atomicMax(reinterpret_cast<unsigned long long*>(p.trace) + 28 + (WITH_DQ ? 0 : 2), static_cast<unsigned long long>(cyc));
-        atomicMax(reinterpret_cast<unsigned long long*>(p.trace) + 29 + (WITH_DQ ? 0 : 2), static_cast<unsigned long long>(ns));
-    }
-#endif
-#undef TR
-#undef TL
     tc_fence_before();
     __syncthreads();
     if (*sFail && tid == 0) atomicExch(p.status, 3);

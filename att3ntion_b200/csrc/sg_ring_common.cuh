@@ -67,8 +67,7 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
 // measured at 7.8 k cycles (4 us), so a wait gives up after about 2 s; the loop also leaves
 // when another thread has raised the CTA's failure flag.
 template <bool TEST_FIRST = false>
-__device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volatile int* fail,
-                                          long long* trace = nullptr, int code = 1) {
+__device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volatile int* fail, int code = 1) {
     const uint32_t addr = smem_u32(bar);
     if (TEST_FIRST) {
         uint32_t done;
@@ -81,12 +80,8 @@ __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volati
             : "=r"(done)
             : "r"(addr), "r"(parity)
             : "memory");
-        if (done) {
-            if (trace) trace[64] += 1;
-            return true;
-        }
+        if (done) return true;
     }
-    const long long t0 = trace ? clock64() : 0;
 #pragma unroll 1
     for (uint32_t it = 0; it < (1u << 19); ++it) {
         uint32_t done;
@@ -99,13 +94,7 @@ __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volati
             : "=r"(done)
             : "r"(addr), "r"(parity)
             : "memory");
-        if (done) {
-            if (trace) {
-                *trace += clock64() - t0;
-                trace[64] += it + 1;       // polls of this hand-off, next to its cycles
-            }
-            return true;
-        }
+        if (done) return true;
         if ((it & 15u) == 15u && *fail) return false;
     }
     *fail = code;      // which wait gave up (reported through the status word)

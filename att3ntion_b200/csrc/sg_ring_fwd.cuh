@@ -67,7 +67,6 @@ struct FwdParams {
     int B, Hq, Hkv, N, window, q_begin, block_len;
     float scale;
     int* status;                   // device status word (bounded-wait failures)
-    long long* trace;              // diagnostic progress words (null: off)
     // TMA descriptors (box = one row) over Q viewed as [B*Hq*N, D] and R, Vr, S, Vs viewed as [B*Hkv*N, D]
     CUtensorMap tmQ, tmR, tmVr, tmS, tmVs;
 };
@@ -167,20 +166,6 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
     };
     auto next_row = [&](int i, int hh) { return hh + 1 < G ? row_at(i, hh + 1) : row_at(i + 1, 0); };
     const float c2 = p.scale * LOG2E;
-#ifdef ATT3_PIPE_TRACE
-#define PROG(site) do { if (p.trace && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) \
-        p.trace[warp] = static_cast<long long>(n) * 1000 + (site); } while (0)
-#define PROGV(v, site) do { if (p.trace && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) \
-        p.trace[warp] = static_cast<long long>(v) * 1000 + (site); } while (0)
-    // cycles of thread 0 of CTA 0 between marks, summed per slot (16 + k)
-    long long cyc_mark = clock64();
-#define CYC(k) do { if (p.trace && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) { \
-        const long long now_ = clock64(); p.trace[16 + (k)] += now_ - cyc_mark; cyc_mark = now_; } } while (0)
-#else
-#define CYC(k) do { } while (0)
-#define PROG(site) do { } while (0)
-#define PROGV(v, site) do { } while (0)
-#endif
 
     uint32_t tmem_base = 0;
     auto cta_start_sync = [&]() {
@@ -258,14 +243,14 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 // previous build.
                 const bool boundary = hh == 0 && i > q0;      // key i replaces key i-128 in slot s
                 if (warp == 8) {
-                    ok = pipe_wait<true>(&bars[FB_STAGE0 + (it & 1)], (it >> 1) & 1, sFail, nullptr, 13);
+                    ok = pipe_wait<true>(&bars[FB_STAGE0 + (it & 1)], (it >> 1) & 1, sFail, 13);
                     if (ok && boundary) {
                         const int fb = i - q0 - 1;            // the entering key's rows were requested one query ago
-                        ok = pipe_wait<true>(&bars[FB_NEXT_READY0 + (fb & (NEXT_BUFS - 1))], (fb >> 3) & 1, sFail, nullptr, 14);
+                        ok = pipe_wait<true>(&bars[FB_NEXT_READY0 + (fb & (NEXT_BUFS - 1))], (fb >> 3) & 1, sFail, 14);
                     }
                 }
                 warp_arrive(&bars[FB_H_SYNC], lane);
-                ok = ok & pipe_wait<true>(&bars[FB_H_SYNC], it & 1, sFail, nullptr, 10);
+                ok = ok & pipe_wait<true>(&bars[FB_H_SYNC], it & 1, sFail, 10);
                 if (!ok) break;
                 const uint8_t* nx = sNext + (i & (NEXT_BUFS - 1)) * L::NEXT_BYTES;
                 if (boundary && hslot == s) {
@@ -280,8 +265,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 const int qb = n & 1;
                 if (work) {
                     // Qp[n&1] was last read by the score MMAs of head n-2
-                    PROG(11);
-                    if (n >= 2) ok = pipe_wait<true>(&bars[FB_X_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, nullptr, 11);
+                    if (n >= 2) ok = pipe_wait<true>(&bars[FB_X_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, 11);
                     if (!ok) break;
                     uint8_t* dQp = sQp + qb * L::TILE;
                     const uint4* q4 = reinterpret_cast<const uint4*>(sQst + (it & 1) * D);
@@ -307,8 +291,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                     // The S row of slot s changes key once every score MMA issued so far is complete (the
                     // last one is head n-1; this thread waits for the same phase again when it reuses
                     // that tile buffer).
-                    PROG(12);
-                    if (n >= 1) ok = pipe_wait<true>(&bars[FB_X_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, nullptr, 12);
+                    if (n >= 1) ok = pipe_wait<true>(&bars[FB_X_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, 12);
                     if (!ok) break;
                     if (hslot < CH)
                         *reinterpret_cast<uint4*>(sS + sw128_offset<RING>(s, hslot)) =
@@ -339,10 +322,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         // at the start of its own 64, so k-step kk reads columns 64*(kk/4) + 8*(kk%4).
         auto issue_u = [&](int m) {
             const int ub = m & 1;
-            PROGV(m, 22);
-            bool r = pipe_wait<true>(&bars[FB_P_FULL0 + ub], (m >> 1) & 1, sFail, nullptr, 22);
-            PROGV(m, 23);
-            if (r && m >= 2) r = pipe_wait<true>(&bars[FB_U_FREE0 + ub], ((m >> 1) - 1) & 1, sFail, nullptr, 23);
+            bool r = pipe_wait<true>(&bars[FB_P_FULL0 + ub], (m >> 1) & 1, sFail, 22);
+            if (r && m >= 2) r = pipe_wait<true>(&bars[FB_U_FREE0 + ub], ((m >> 1) - 1) & 1, sFail, 23);
             if (r) {
                 tc_fence_after();
                 const uint32_t tX = tmem_base + ub * 256, tU = tX + 128;
@@ -367,11 +348,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                     continue;
                 }
                 const int qb = n & 1;
-                PROG(20);
-                ok = pipe_wait<true>(&bars[FB_QP_FULL0 + qb], (n >> 1) & 1, sFail, nullptr, 20);
+                ok = pipe_wait<true>(&bars[FB_QP_FULL0 + qb], (n >> 1) & 1, sFail, 20);
                 // X[qb] held P(n-2) until the U product of that head had read it
-                PROG(21);
-                if (ok && n >= 2) ok = pipe_wait<true>(&bars[FB_U_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, nullptr, 21);
+                if (ok && n >= 2) ok = pipe_wait<true>(&bars[FB_U_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, 21);
                 if (!ok) break;
                 tc_fence_after();
                 {
@@ -432,8 +411,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         auto finish = [&]() {
             if (!fin_pending) return true;
             fin_pending = false;
-            PROGV(fin_m, 33);
-            if (!pipe_wait<true>(&bars[FB_E_SYNC], fin_m & 1, sFail, nullptr, 33)) return false;
+            if (!pipe_wait<true>(&bars[FB_E_SYNC], fin_m & 1, sFail, 33)) return false;
             const float* red = sRed + (fin_m & 1) * 4 * (D + 4);
             float Lsum = 0.f;
 #pragma unroll
@@ -448,12 +426,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         auto epilogue = [&](int m, size_t row, float M, float l_half) {
             const int ub = m & 1;
             if (!finish()) return false;
-            PROGV(m, 32);
-            CYC(7);                                       // finish() of the head before
-            bool r = pipe_wait<true>(&bars[FB_U_DONE0 + ub], (m >> 1) & 1, sFail, nullptr, 32);
+            bool r = pipe_wait<true>(&bars[FB_U_DONE0 + ub], (m >> 1) & 1, sFail, 32);
             if (!r) return false;
             tc_fence_after();
-            CYC(8);                                       // wait U_done
             const uint32_t tU = tl + ub * 256 + 128 + ch * HD;
             float* red = sRed + ub * 4 * (D + 4);
             constexpr int NC = HD / 32;
@@ -506,8 +481,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         auto ring_update = [&](int i) {
             const int s = i & (RING - 1), fb = i - q0 - 1;
             const uint8_t* nx = sNext + (i & (NEXT_BUFS - 1)) * L::NEXT_BYTES;
-            PROGV(i, 34);
-            if (!pipe_wait<true>(&bars[FB_NEXT_READY0 + (fb & (NEXT_BUFS - 1))], (fb >> 3) & 1, sFail, nullptr, 34)) return false;
+            if (!pipe_wait<true>(&bars[FB_NEXT_READY0 + (fb & (NEXT_BUFS - 1))], (fb >> 3) & 1, sFail, 34)) return false;
             if (tid < CH)
                 *reinterpret_cast<uint4*>(sVs + sw128_offset<RING>(s, tid)) =
                     *reinterpret_cast<const uint4*>(nx + 3 * (D * 2) + tid * 16);
@@ -553,12 +527,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 }
                 const int xb = n & 1;
                 const uint32_t tX = tl + xb * 256 + ch * 64;          // this thread's 64 score columns
-                PROG(30);
-                CYC(0);                                   // loop overhead since the last mark
-                ok = pipe_wait<true>(&bars[FB_X_DONE0 + xb], (n >> 1) & 1, sFail, nullptr, 30);
+                ok = pipe_wait<true>(&bars[FB_X_DONE0 + xb], (n >> 1) & 1, sFail, 30);
                 if (!ok) break;
                 tc_fence_after();
-                CYC(1);                                   // wait X_done
                 // ---- maximum of this thread's half row; the other half belongs to the thread with the same
                 //      lane in the partner warp, and the exchange completes behind the epilogue below
                 // four independent running maxima: one chain of 64 dependent max operations would cost
@@ -596,17 +567,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                     if (lane == 0) sMpart[xb * 8 + warp] = m_w;
                 }
                 warp_arrive(&bars[FB_M_SYNC], lane);
-                CYC(2);                                   // maximum pass
                 // ---- epilogue of the previous head, behind its U product; then the ring rows of a new key
                 if (pend) { ok = epilogue(pend_n, pend_row, pend_m, pend_l); pend = false; }
-                CYC(3);                                   // epilogue incl. its waits
                 if (ok && boundary) ok = ring_update(i);
                 if (!ok) break;
-                CYC(4);                                   // ring update
-                PROG(31);
-                ok = pipe_wait<true>(&bars[FB_M_SYNC], n & 1, sFail, nullptr, 31);
+                ok = pipe_wait<true>(&bars[FB_M_SYNC], n & 1, sFail, 31);
                 if (!ok) break;
-                CYC(5);                                   // wait M_sync
                 const float* mp = sMpart + xb * 8;
                 const float M = fmaxf(fmaxf(fmaxf(mp[0], mp[1]), fmaxf(mp[2], mp[3])),
                                       fmaxf(fmaxf(mp[4], mp[5]), fmaxf(mp[6], mp[7])));
@@ -637,7 +603,6 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 tc_fence_before();
                 // P_full also tells the MMA warp that the Vs ring row is current (ring_update above)
                 warp_arrive(&bars[FB_P_FULL0 + xb], lane);
-                CYC(6);                                   // exponential pass
                 pend = true; pend_n = n; pend_row = row; pend_m = M; pend_l = l_half;
                 ++n;
             }
@@ -647,9 +612,6 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
     }
     tc_fence_before();
     __syncthreads();
-#undef PROG
-#undef PROGV
-#undef CYC
     if (*sFail && tid == 0) atomicExch(p.status, 100 + *sFail);
     if (is_mma) tmem_dealloc(tmem_base, TMEM_COLS);
 }

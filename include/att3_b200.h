@@ -220,18 +220,30 @@ int att3_timing_enable(int on);
 int att3_timing_read(int kernel_id, double* total_ms, unsigned long long* launches);
 
 /* ------------------------------------------------------------------------- *
- * Self-test of the tensor-core building blocks: multiplies two 128x128 BF16
- * matrices on one CTA through the operand arrangement `mode` selects and
- * writes the FP32 product to D (mode | 8: only the first 64 output columns,
- * as an N = 64 instruction; mode | 16: issued as the kernels issue, by a
- * converged warp with one elected lane and precomputed descriptors).  `reps`
- * repeats the accumulation.  status_dev[0]
- * receives 1 if a bounded wait ran out, status_dev[1] the cycles from the first
- * MMA issue to completion.  Used by the test-suite to pin the descriptor
- * encodings and by the throughput notes in profiles/.
+ * Self-tests (no counterpart in the reference, whose kernels have neither
+ * operand descriptors nor device-side waits).
+ *
+ * att3_umma_selftest multiplies two 128x128 BF16 matrices on one CTA through
+ * the operand arrangement `mode` selects and writes the FP32 product to D
+ * (row-major [128][128]); the shared-memory descriptor encodings are the fixed
+ * ones the kernels use.
+ *   mode 0: D = A B^T   (A and B K-major in shared memory)
+ *   mode 1: D = A B     (A K-major, B MN-major)
+ *   mode 2: D = A^T B   (A and B MN-major)
+ *   mode 3: D = A B     (A in tensor memory, B MN-major)
+ *   mode 4: D = A B^T   (A in tensor memory, B K-major)
+ *   mode | 8: issued as an N = 64 instruction; only the first 64 columns of D are written.
+ * status_dev[0] receives 1 if the bounded wait for the product ran out.
+ *
+ * att3_wait_selftest launches a kernel in which one thread waits, for at most
+ * `limit` polls, on a barrier that nothing arrives on.  The wait gives up, the
+ * kernel records that in the device status word and returns normally; the next
+ * att3_device_status() on that device reports ATT3_ERR_TIMEOUT and clears the
+ * word.  This is the whole failure path of the kernels' bounded waits, driven
+ * without a fault or a hang.
  * ------------------------------------------------------------------------- */
-int att3_umma_selftest(const void* A, const void* B, float* D, int mode, int lbo_a, int sbo_a,
-                       int lbo_b, int sbo_b, int reps, int* status_dev, void* stream);
+int att3_umma_selftest(const void* A, const void* B, float* D, int mode, int* status_dev, void* stream);
+int att3_wait_selftest(unsigned limit, void* stream);
 
 #ifdef __cplusplus
 }

@@ -16,6 +16,10 @@ if str(REPO) not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100a)")
+    # Test modules import the ctypes binding at import time, i.e. during collection: the native
+    # library has to exist before that (a fresh checkout has none; it is not kept in version control).
+    from att3ntion_b200 import build
+    build.build()
 
 
 def pytest_collection_modifyitems(config, items):
@@ -25,13 +29,6 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
-
-
-@pytest.fixture(scope="session", autouse=True)
-def _native_library():
-    """Build the library once per session if it is missing or stale."""
-    from att3ntion_b200 import build
-    build.build()
 
 
 def golden_files(prefix):

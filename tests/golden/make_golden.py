@@ -215,7 +215,7 @@ def bounds(ref: Path):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     a = ap.parse_args()
     ref = Path(a.reference)
     torch.set_num_threads(os.cpu_count())

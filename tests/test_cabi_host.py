@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_abi_version_and_error_text():
-    assert _cabi.lib.att3_abi_version() == 1
+    assert _cabi.lib.att3_abi_version() == 2
     rc = _cabi.lib.att3_sg_forward(None, None, None, None, None, None, None, None, None, 1, 2, 1, 24, 128, 128, 0, None)
     assert rc == _cabi.ERR_INVALID and "multiple of 16" in _cabi.last_error()
     rc = _cabi.lib.att3_sg_forward(None, None, None, None, None, None, None, None, None, 0, 2, 1, 32, 128, 128, 0, None)
