@@ -24,6 +24,7 @@ SIGNATURES = {
     "att3_sg_forward": (_i, [_vp] * 9 + [_i] * 7 + [_vp]),
     "att3_sg_backward": (_i, [_vp] * 15 + [_i] * 7 + [_vp, _sz, _vp]),
     "att3_sg_backward_kv32": (_i, [_vp] * 15 + [_i] * 7 + [_vp, _sz, _vp]),
+    "att3_sg_backward_kv32_side": (_i, [_i] + [_vp] * 15 + [_i] * 7 + [_vp, _sz, _vp]),
     "att3_sg_backward_static_max_bytes": (_sz, []),
     "att3_sg_backward_static": (_i, [_vp] * 15 + [_i] * 7 + [_vp]),
     "att3_hg_forward": (_i, [_vp] * 22 + [_i] * 7 + [_vp]),
@@ -32,6 +33,7 @@ SIGNATURES = {
     "att3_sg_tile_ranges": (_i, [_i] * 6 + [C.POINTER(_i), _i]),
     "att3_pack_mask32": (C.c_uint32, [_vp, _i]),
     "att3_sg_query_blocks": (_i, [_i] * 6 + [C.POINTER(_i)]),
+    "att3_sg_set_query_block": (_i, [_i, _i]),
     "att3_launch_count": (C.c_ulonglong, [_i]),
     "att3_timing_enable": (_i, [_i]),
     "att3_timing_read": (_i, [_i, C.POINTER(C.c_double), C.POINTER(C.c_ulonglong)]),

@@ -170,6 +170,28 @@ def sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, window: int, q_begin: in
     return dQ, dR, dS, dVr, dVs
 
 
+def sg_backward_sides_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, window: int, q_begin: int = 0, between=None):
+    """The windowed backward with FP32 key gradients, one key side per C-ABI call.  Returns
+    (dQ, kv32) with kv32 an FP32 [4,B,Hkv,N,D] tensor holding dS, dVs, dR, dVr in that order: the
+    first two are complete after side 0, and `between(kv32[:2])`, if given, is called at that point
+    (e.g. to start an all-reduce of them that overlaps side 1)."""
+    B, Hq, N, D = Q.shape
+    Hkv = R.shape[1]
+    with torch.cuda.device(Q.device):
+        dQ = torch.zeros_like(Q) if q_begin else torch.empty_like(Q)
+        kv32 = torch.empty((4, B, Hkv, N, D), dtype=torch.float32, device=Q.device)
+        nbytes = lib.att3_sg_backward_workspace_bytes(B, Hq, Hkv, N, D, int(window))
+        ws = _workspace(Q.device, nbytes)
+        for side in (0, 1):
+            _call(lib.att3_sg_backward_kv32_side, side, dY.data_ptr(), Q.data_ptr(), R.data_ptr(), S.data_ptr(),
+                  Vr.data_ptr(), Vs.data_ptr(), Y.data_ptr(), m.data_ptr(), l.data_ptr(), _ptr(mask), dQ.data_ptr(),
+                  kv32[2].data_ptr(), kv32[0].data_ptr(), kv32[3].data_ptr(), kv32[1].data_ptr(),
+                  B, Hq, Hkv, N, D, int(window), int(q_begin), ws.data_ptr(), nbytes, _stream(Q))
+            if side == 0 and between is not None:
+                between(kv32[:2])
+    return dQ, kv32
+
+
 def device_status(device=None) -> None:
     """Synchronises the current stream and raises if a bounded device-side wait ran out."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)

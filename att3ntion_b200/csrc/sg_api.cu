@@ -1,6 +1,7 @@
 // C-ABI entry points of the single query gather (independent and shared KV
 // heads): argument validation, query-block partitioning and kernel launches.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 
 #include "att3_abi_internal.h"
@@ -58,7 +59,32 @@ int plan_blocks(int B, int Hkv, int N, int q_begin, int sm_count, int ctas_per_s
     return nblk;
 }
 
+// Schedule overrides (att3_sg_set_query_block): queries per CTA of the forward and of the backward
+// passes, 0 = the built-in choice.
+std::atomic<int> g_fwd_block{0}, g_bwd_block{0};
+
+// Backward partition: one block per SM where the problem allows it, blocks never shorter than
+// BWD_MIN_BLOCK queries.  The block length is a function of (B, Hkv, N) only -- not of q_begin -- so
+// that the workspace size, which depends on it through the number of partial planes, can be asked
+// for without knowing where the caller's queries start.  (Many short blocks handed out by the
+// hardware's CTA scheduler were measured instead: 32 queries per block, 1024 CTAs on 148 SMs, ran
+// 2 % slower than the even split, 128 and 64 per block 12 % slower.)
+int bwd_block_len(int B, int Hkv, int N) {
+    if (const int v = g_bwd_block.load()) return std::max(v, sgring::BWD_MIN_BLOCK);
+    int len = 0;
+    plan_blocks(B, Hkv, N, 0, att3::sm_count(), 1, sgring::BWD_MIN_BLOCK, &len);
+    return len;
+}
+
 }  // namespace
+
+extern "C" int att3_sg_set_query_block(int fwd_len, int bwd_len) {
+    if (fwd_len < 0 || bwd_len < 0 || (fwd_len && fwd_len < 16) || (bwd_len && bwd_len < sgring::BWD_MIN_BLOCK))
+        return att3::set_error(ATT3_ERR_INVALID, "att3_sg_set_query_block: lengths must be 0 (automatic) or >= 16");
+    g_fwd_block.store(fwd_len);
+    g_bwd_block.store(bwd_len);
+    return ATT3_OK;
+}
 
 extern "C" int att3_sg_query_blocks(int B, int Hq, int Hkv, int N, int q_begin, int sm_count, int* block_len) {
     (void)Hq;
@@ -169,7 +195,11 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
         if ((rc = att3::make_row_tensor_map(&p.tmS, S, krows, D, "att3_sg_forward"))) return rc;
         if ((rc = att3::make_row_tensor_map(&p.tmVs, Vs, krows, D, "att3_sg_forward"))) return rc;
     }
-    const int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, 16, &p.block_len);
+    int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, 16, &p.block_len);
+    if (const int forced = g_fwd_block.load()) {
+        p.block_len = forced;
+        nblk = (N - q_begin + forced - 1) / forced;
+    }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return D == 64 ? launch_ring_fwd<64>(p, nblk, st) : launch_ring_fwd<128>(p, nblk, st);
 }
@@ -178,14 +208,14 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
 // Backward
 // ---------------------------------------------------------------------------
 
-// Workspace: FP32 partials of the two gradients of one key side, two parities
-// each; the second pass reuses the space after the first pass's reduction.
+// Workspace: FP32 partial planes of the two gradients of one key side (bwd_planes
+// of them each); the second pass reuses the space after the first pass's reduction.
 extern "C" size_t att3_sg_backward_workspace_bytes(int B, int Hq, int Hkv, int N, int D, int window) {
     (void)Hq;
     if (B <= 0 || Hkv <= 0 || N <= 0 || D <= 0 || window < 0) return 0;
     if (window == 0)   // dense: five FP32 gradient planes + one anchor-gradient partial plane per 128-key tile
         return static_cast<size_t>(5 + att3::dense_tiles(N, 0) + 2) * B * Hq * N * D * sizeof(float);
-    return static_cast<size_t>(4) * B * Hkv * N * D * sizeof(float);
+    return static_cast<size_t>(2 * sgring::bwd_planes(bwd_block_len(B, Hkv, N))) * B * Hkv * N * D * sizeof(float);
 }
 
 template <int D, bool WITH_DQ>
@@ -219,7 +249,7 @@ static int launch_reduce(const sgring::BwdParams& p, int nblk, int D, void* dK, 
     r.dK32 = f32 ? static_cast<float*>(dK) : nullptr;
     r.dV32 = f32 ? static_cast<float*>(dV) : nullptr;
     r.rows = p.B * p.Hkv;
-    r.N = p.N; r.D = D; r.q_begin = p.q_begin; r.block_len = p.block_len; r.nblk = nblk;
+    r.N = p.N; r.D = D; r.q_begin = p.q_begin; r.block_len = p.block_len; r.nblk = nblk; r.planes = p.planes;
     const size_t total = static_cast<size_t>(r.rows) * p.N * (D / 4);
     const int threads = 256;
     const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
@@ -231,14 +261,17 @@ static int launch_reduce(const sgring::BwdParams& p, int nblk, int D, void* dK, 
     return ATT3_OK;
 }
 
-static int sg_backward_impl(bool kv_f32, const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+// passes: bit 0 = key side (S, Vs) with dQ, bit 1 = key side (R, Vr); both for a whole backward.
+static int sg_backward_impl(int passes, bool kv_f32, const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
                                 const void* Vs, const void* Y, const float* m, const float* l,
                                 const uint8_t* mask, void* dQ, void* dR, void* dS, void* dVr, void* dVs, int B,
                                 int Hq, int Hkv, int N, int D, int window, int q_begin, void* workspace,
                                 size_t workspace_bytes, void* stream) {
     if (int rc = check_shapes("att3_sg_backward", B, Hq, Hkv, N, D, window, q_begin)) return rc;
-    if (!dY || !Q || !R || !S || !Vr || !Vs || !Y || !m || !l || !dQ || !dR || !dS || !dVr || !dVs)
+    if (!dY || !Q || !R || !S || !Vr || !Vs || !Y || !m || !l)
         return att3::set_error(ATT3_ERR_INVALID, "att3_sg_backward: null tensor pointer");
+    if (((passes & 1) && (!dQ || !dS || !dVs)) || ((passes & 2) && (!dR || !dVr)))
+        return att3::set_error(ATT3_ERR_INVALID, "att3_sg_backward: null gradient pointer");
     if (!att3::require_sm100("att3_sg_backward")) return ATT3_ERR_UNSUPPORTED;
     if (window == 0 && Hkv != Hq)
         return att3::set_error(ATT3_ERR_UNSUPPORTED, "att3_sg_backward: shared KV heads need a window (1..128)");
@@ -282,22 +315,28 @@ static int sg_backward_impl(bool kv_f32, const void* dY, const void* Q, const vo
     p.mask = mask;
     p.dQ = static_cast<__nv_bfloat16*>(dQ);
     p.part_K = static_cast<float*>(workspace);
-    p.part_V = p.part_K + static_cast<size_t>(2) * B * Hkv * N * D;
+    p.block_len = bwd_block_len(B, Hkv, N);
+    const int nblk = (N - q_begin + p.block_len - 1) / p.block_len;
+    p.planes = sgring::bwd_planes(p.block_len);
+    p.part_V = p.part_K + static_cast<size_t>(p.planes) * B * Hkv * N * D;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status_ptr();
     if (!p.status) return att3::set_error(ATT3_ERR_CUDA, "att3_sg_backward: status word not resolvable");
-    const int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, sgring::BWD_MIN_BLOCK, &p.block_len);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-    // Pass 1: own side (S, Vs) -> dS, dVs, and dQ.
-    p.Ka = static_cast<const __nv_bfloat16*>(R);
-    p.Va = static_cast<const __nv_bfloat16*>(Vr);
-    p.Kb = static_cast<const __nv_bfloat16*>(S);
-    p.Vb = static_cast<const __nv_bfloat16*>(Vs);
-    int rc = D == 64 ? launch_ring_bwd<64, true>(p, nblk, st) : launch_ring_bwd<128, true>(p, nblk, st);
-    if (rc) return rc;
-    if ((rc = launch_reduce(p, nblk, D, dS, dVs, st, kv_f32))) return rc;
+    int rc = ATT3_OK;
+    if (passes & 1) {
+        // Pass 1: own side (S, Vs) -> dS, dVs, and dQ.
+        p.Ka = static_cast<const __nv_bfloat16*>(R);
+        p.Va = static_cast<const __nv_bfloat16*>(Vr);
+        p.Kb = static_cast<const __nv_bfloat16*>(S);
+        p.Vb = static_cast<const __nv_bfloat16*>(Vs);
+        rc = D == 64 ? launch_ring_bwd<64, true>(p, nblk, st) : launch_ring_bwd<128, true>(p, nblk, st);
+        if (rc) return rc;
+        if ((rc = launch_reduce(p, nblk, D, dS, dVs, st, kv_f32))) return rc;
+    }
+    if (!(passes & 2)) return ATT3_OK;
     // Pass 2: sides exchanged -> dR, dVr.
     p.Ka = static_cast<const __nv_bfloat16*>(S);
     p.Va = static_cast<const __nv_bfloat16*>(Vs);
@@ -313,7 +352,7 @@ extern "C" int att3_sg_backward(const void* dY, const void* Q, const void* R, co
                                 const uint8_t* mask, void* dQ, void* dR, void* dS, void* dVr, void* dVs, int B,
                                 int Hq, int Hkv, int N, int D, int window, int q_begin, void* workspace,
                                 size_t workspace_bytes, void* stream) {
-    return sg_backward_impl(false, dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv, N, D, window,
+    return sg_backward_impl(3, false, dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv, N, D, window,
                             q_begin, workspace, workspace_bytes, stream);
 }
 
@@ -324,8 +363,21 @@ extern "C" int att3_sg_backward_kv32(const void* dY, const void* Q, const void* 
                                      const uint8_t* mask, void* dQ, float* dR, float* dS, float* dVr, float* dVs,
                                      int B, int Hq, int Hkv, int N, int D, int window, int q_begin, void* workspace,
                                      size_t workspace_bytes, void* stream) {
-    return sg_backward_impl(true, dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv, N, D, window,
+    return sg_backward_impl(3, true, dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv, N, D, window,
                             q_begin, workspace, workspace_bytes, stream);
+}
+
+// One key side of att3_sg_backward_kv32 at a time, so that a caller can start exchanging the first side's
+// sums (dS, dVs) with other processes while the second side is computed.
+extern "C" int att3_sg_backward_kv32_side(int side, const void* dY, const void* Q, const void* R, const void* S,
+                                          const void* Vr, const void* Vs, const void* Y, const float* m,
+                                          const float* l, const uint8_t* mask, void* dQ, float* dR, float* dS,
+                                          float* dVr, float* dVs, int B, int Hq, int Hkv, int N, int D, int window,
+                                          int q_begin, void* workspace, size_t workspace_bytes, void* stream) {
+    if (side != 0 && side != 1)
+        return att3::set_error(ATT3_ERR_INVALID, "att3_sg_backward_kv32_side: side must be 0 (S, Vs, dQ) or 1 (R, Vr)");
+    return sg_backward_impl(side == 0 ? 1 : 2, true, dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv,
+                            N, D, window, q_begin, workspace, workspace_bytes, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -361,9 +413,10 @@ extern "C" int att3_sg_backward_static(const void* dY, const void* Q, const void
     const size_t need = att3_sg_backward_workspace_bytes(B, Hq, Hkv, N, D, window);
     if (need > ATT3_STATIC_SCRATCH_BYTES)
         return att3::set_error(ATT3_ERR_WORKSPACE,
-                               "att3_sg_backward_static: these sizes need %zu bytes of scratch, the built-in array "
-                               "holds %zu (B*Hkv*N*D must not exceed %zu); use att3_sg_backward with a workspace",
-                               need, ATT3_STATIC_SCRATCH_BYTES, ATT3_STATIC_SCRATCH_BYTES / 16);
+                               "att3_sg_backward_static: these sizes need %zu bytes of scratch "
+                               "(att3_sg_backward_workspace_bytes), the built-in array holds %zu; use "
+                               "att3_sg_backward with a workspace",
+                               need, ATT3_STATIC_SCRATCH_BYTES);
     // Device address of the array, resolved on the first call per device (keep that call outside
     // any stream capture) and cached afterwards.
     constexpr int kMaxDevices = 64;

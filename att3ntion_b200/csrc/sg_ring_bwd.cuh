@@ -26,11 +26,11 @@
 //    The forward statistics (m, l) make P purely elementwise, so no row reduction
 //    is needed here.
 //  * When query i reuses slot i mod 128 the lane holding key i-128 is final for
-//    this CTA: it is copied to an FP32 partial buffer and zeroed (by the H warp of that lane quarter).  Neighbouring
-//    query blocks write partial buffers of opposite parity and blocks are at
-//    least 127 queries long, so every partial row has exactly one writer and the
-//    final sum (reduce kernel below) has a fixed order: repeated calls are
-//    bit-identical.
+//    this CTA: it is copied to an FP32 partial buffer and zeroed (by the flush warp of that lane quarter).  Query
+//    block x writes partial plane x mod P with P large enough that blocks sharing a
+//    plane touch disjoint key rows (bwd_planes), so every partial row has exactly
+//    one writer and the final sum (reduce kernel below) has a fixed order: repeated
+//    calls are bit-identical.
 //
 // Schedule.  Tensor memory holds the two accumulators (2 x 128 columns) and two 128-column
 // regions R0, R1 for everything transient, so only one head's P^T/gA^T can be live at a time;
@@ -68,7 +68,11 @@
 
 namespace sgring {
 
-constexpr int BWD_MIN_BLOCK = 128;   // queries per block >= window so each partial row has one writer
+// Partial planes.  A block of L queries flushes the key rows (q0 - 128, q1); block x writes plane x mod P.
+// Blocks x and x + P then touch disjoint rows iff P * L - 127 >= L, i.e. P >= 127 / L + 1 (rounded up):
+// every partial row of a plane has exactly one writer, whatever the block length.
+constexpr int BWD_MIN_BLOCK = 16;
+__host__ __device__ constexpr int bwd_planes(int block_len) { return (RING - 1 + block_len - 1) / block_len + 1; }
 
 struct BwdParams {
     const __nv_bfloat16* Q;          // [B,Hq,N,D]
@@ -82,9 +86,9 @@ struct BwdParams {
     const __nv_bfloat16* Vb;
     const uint8_t* mask;             // [B,N,N] or null
     __nv_bfloat16* dQ;               // [B,Hq,N,D], written only by the WITH_DQ instantiation
-    float* part_K;                   // [2][B,Hkv,N,D] FP32 partials of dKb (parity-major)
-    float* part_V;                   // [2][B,Hkv,N,D] FP32 partials of dVb
-    int B, Hq, Hkv, N, window, q_begin, block_len;
+    float* part_K;                   // [planes][B,Hkv,N,D] FP32 partials of dKb (plane-major)
+    float* part_V;                   // [planes][B,Hkv,N,D] FP32 partials of dVb
+    int B, Hq, Hkv, N, window, q_begin, block_len, planes;
     float scale;
     int* status;
 };
@@ -186,7 +190,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     const int q0 = p.q_begin + bx * p.block_len;
     const int q1 = min(q0 + p.block_len, p.N);
     if (q0 >= q1) return;
-    const int parity_buf = bx & 1;
+    const int parity_buf = bx % p.planes;
     const bool is_h = warp >= 8 && warp < 12, is_mma = warp == 12;
 
     if (is_mma) {
@@ -836,10 +840,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     if (is_mma) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-// Sums the parity partials of one key side into BF16 outputs.  Row k of batch b,
+// Sums the partial planes of one key side into BF16 outputs.  Row k of batch b,
 // KV head g was written by the query blocks that contain a query in [k, k+127]
-// (clipped to [q_begin, N)); consecutive blocks use opposite parities, so at
-// most one block per parity contributes and the order of the sum is fixed.
+// (clipped to [q_begin, N)); those are at most `planes` consecutive blocks, each in
+// a plane of its own, so the order of the sum is fixed.
 struct ReduceParams {
     const float* part_K;
     const float* part_V;
@@ -848,7 +852,7 @@ struct ReduceParams {
     float* dK32;         // when non-null the sums are written here in FP32 instead (partials of a rank whose
     float* dV32;         // query heads are only a part of the KV head's: summed across ranks before rounding)
     int rows;            // B * Hkv
-    int N, D, q_begin, block_len, nblk;
+    int N, D, q_begin, block_len, nblk, planes;
 };
 
 __global__ void sg_bwd_reduce_kernel(const ReduceParams p) {
@@ -865,7 +869,7 @@ __global__ void sg_bwd_reduce_kernel(const ReduceParams p) {
         if (q_lo <= q_hi) {
             const int b_lo = (q_lo - p.q_begin) / p.block_len, b_hi = (q_hi - p.q_begin) / p.block_len;
             for (int blk = b_lo; blk <= b_hi; ++blk) {
-                const size_t off = static_cast<size_t>(blk & 1) * plane + rk * p.D + c * 4;
+                const size_t off = static_cast<size_t>(blk % p.planes) * plane + rk * p.D + c * 4;
                 const float4 a = *reinterpret_cast<const float4*>(p.part_K + off);
                 const float4 v = *reinterpret_cast<const float4*>(p.part_V + off);
                 sk.x += a.x; sk.y += a.y; sk.z += a.z; sk.w += a.w;

@@ -113,6 +113,18 @@ int att3_sg_backward_kv32(const void* dY, const void* Q, const void* R, const vo
                           int B, int Hq, int Hkv, int N, int D, int window, int q_begin,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* One key side of att3_sg_backward_kv32 per call: side 0 writes dQ, dS, dVs
+ * (the other gradient pointers may be NULL), side 1 writes dR, dVr.  Two calls,
+ * side 0 then side 1, equal one att3_sg_backward_kv32 bit for bit; in between a
+ * multi-GPU caller can start summing the first side's partials across
+ * processes while the second side is computed (the reference reduces its
+ * per-head partials only after all passes, cuda/backward.cu:2558-2575). */
+int att3_sg_backward_kv32_side(int side, const void* dY, const void* Q, const void* R, const void* S,
+                               const void* Vr, const void* Vs, const void* Y, const float* m, const float* l,
+                               const uint8_t* mask, void* dQ, float* dR, float* dS, float* dVr, float* dVs,
+                               int B, int Hq, int Hkv, int N, int D, int window, int q_begin,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
 /* att3_sg_backward for callers that cannot allocate device memory.  It has no
  * counterpart in the reference, whose launchers allocate their own buffers
  * through torch.  Meant for hosts where an allocator call is impossible or
@@ -124,9 +136,10 @@ int att3_sg_backward_kv32(const void* dY, const void* Q, const void* R, const vo
  * loads the library until the process exits), so the call itself allocates
  * nothing: no cudaMalloc/cudaFree, no allocating library routine (leave
  * att3_timing_enable off, it creates events).
- *   - windowed path only (1 <= window <= 128); sizes whose scratch,
- *     16 * B * Hkv * N * D bytes, exceeds the array are rejected with
- *     ATT3_ERR_WORKSPACE and a message naming the limit;
+ *   - windowed path only (1 <= window <= 128); sizes whose scratch
+ *     (att3_sg_backward_workspace_bytes: 16 * B * Hkv * N * D bytes when the
+ *     query blocks are at least 127 long, more for shorter blocks) exceeds the
+ *     array are rejected with ATT3_ERR_WORKSPACE and a message naming both;
  *   - the first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current) and caches it: make that
  *     first call before any stream capture;
@@ -202,6 +215,14 @@ uint32_t att3_pack_mask32(const uint8_t* row, int lim);
 /* Query-block partition the windowed kernels use: number of CTAs launched and
  * queries per block for these sizes on a device with `sm_count` SMs. */
 int att3_sg_query_blocks(int B, int Hq, int Hkv, int N, int q_begin, int sm_count, int* block_len);
+
+/* Schedule override, the counterpart of the reference's tile overrides (SgConfig,
+ * cpp/cuda_bindings.h:18-48; sg_set_config, cpp/cuda_bindings.cpp:88-106): queries
+ * per CTA of the windowed forward and of the windowed backward passes; 0 restores
+ * the built-in choice, other values must be >= 16.  Process-wide.  The backward's
+ * workspace size depends on its block length (shorter blocks need more partial
+ * planes): query att3_sg_backward_workspace_bytes after changing it. */
+int att3_sg_set_query_block(int fwd_len, int bwd_len);
 
 /* Launch counters, the counterpart of att3_tc::State (cpp/cuda_bindings.h:18-48).
  * which: 0 single-gather forward, 1 single-gather backward, 2 three-gather

@@ -280,3 +280,45 @@ def check_lse(m, l, lse_ref) -> None:
     if (~dead).any():
         err = (lse[~dead] - lse_ref[~dead]).abs().max().item()
         assert err <= LSE_MAX, f"LSE max err {err:.4f}"
+
+
+def slice_gate(host, got, window, b, lo, hi, mask=None, heads=None):
+    """Full-size check of the windowed single gather on one slice: queries [lo, hi) of batch `b`
+    against the banded FP64 oracle, as the reference gates a shape before it publishes a timing for it
+    (benchmarks/bench_single_gather.py:887-961), restricted to a slice because the whole problem is out
+    of the oracle's reach.
+
+    host  (Q, R, S, Vr, Vs, dY) CPU tensors of the whole problem
+    got   dict with the device results as tensors indexable like the whole problem: Y, m, l, dQ, and
+          dR, dS, dVr, dVs (summed over query heads; only rows whose 128 contributing queries all lie in
+          the slice are compared, i.e. keys lo .. hi-128 when the slice is longer than a window, so the
+          result must come from a run over all query heads of the KV head)
+    heads query heads the device run held (default: all); Y, m, l, dQ are compared for these only,
+          `got` then holds them in this order
+
+    Raises AssertionError on a failed gate; returns {name: rel-L2}.  Needs lo >= 127 or lo == 0.
+    """
+    Q, R, S, Vr, Vs, dY = host
+    pre = min(lo, RING_ROWS - 1)
+    sl = slice(lo - pre, hi)
+    msk = None if mask is None else mask[b:b + 1, sl, sl]
+    ref = single_gather_banded(Q[b:b + 1, :, sl], *[t[b:b + 1, :, sl] for t in (R, S, Vr, Vs)], window=window,
+                               dY=dY[b:b + 1, :, sl], q_begin=pre, chunk=32, mask=msk)
+    hs = list(range(Q.shape[1])) if heads is None else list(heads)
+    rels = {}
+
+    def gate(name, a, r):
+        check_gate(name, a.float().cpu(), r)
+        rels[name] = errors(a, r)[0]
+
+    gate("Y", got["Y"][b:b + 1, :, lo:hi], ref["Y"][:, hs, pre:])
+    check_lse(got["m"][b:b + 1, :, lo:hi], got["l"][b:b + 1, :, lo:hi], ref["lse"][:, hs, pre:])
+    gate("dQ", got["dQ"][b:b + 1, :, lo:hi], ref["dQ"][:, hs, pre:])
+    nk = hi - lo - (RING_ROWS - 1)
+    if nk > 0 and all(k in got for k in ("dR", "dS", "dVr", "dVs")):
+        for name in ("dR", "dS", "dVr", "dVs"):
+            gate(name, got[name][b:b + 1, :, lo:lo + nk], ref[name][:, :, pre:pre + nk])
+    return rels
+
+
+RING_ROWS = 128   # keys a query can see at most (the kernels' resident ring); a key collects from 128 queries

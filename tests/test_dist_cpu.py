@@ -1,8 +1,12 @@
-"""World-size-2 (and 3) gloo runs of the row-sharding host logic on CPU: partitioning,
-halo exchange and the hand-back of halo key gradients.  The compute step is the CPU
-oracle here (the kernels need a GPU); what is under test is att3ntion_b200/_dist.py."""
+"""World-size-2 (and 3) gloo runs of the multi-GPU host logic on CPU: partitioning,
+halo exchange, the hand-back of halo key gradients, the per-side all-reduce of the head
+partition and what a rank sees when its neighbour fails before an exchange.  The compute
+step is the CPU oracle here (the kernels need a GPU); what is under test is
+att3ntion_b200/_dist.py."""
+import datetime
 import os
 import socket
+import time
 
 import pytest
 import torch
@@ -75,7 +79,11 @@ def _head_worker(rank, world, port, hkv, out):
             full[k] = torch.randn(2, hkv, n, 16, generator=g, dtype=torch.float64)
         dY = torch.randn(2, hq, n, 16, generator=g, dtype=torch.float64)
         fwd = lambda Q, R, S, Vr, Vs, w: _oracle_fwd(Q, R, S, Vr, Vs, w, 0)
-        bwd = lambda dY_, Q, R, S, Vr, Vs, Y, m, l, w: _oracle_bwd(dY_, Q, R, S, Vr, Vs, Y, m, l, w, 0)
+        def bwd(dY_, Q, R, S, Vr, Vs, Y, m, l, w, between):
+            dQ, dR, dS, dVr, dVs = _oracle_bwd(dY_, Q, R, S, Vr, Vs, Y, m, l, w, 0)
+            kv = torch.stack([dS, dVs, dR, dVr])
+            between(kv[:2])                      # the first key side is summed while the second is "computed"
+            return dQ, kv
         op = HeadShardedGather(window, compute_fwd=fwd, compute_bwd=bwd)
         heads = HeadShardedGather.local_heads(hq, hkv, world, rank)
         Y = op.forward(full["Q"][:, heads].contiguous(), *[full[k] for k in NAMES[1:]])
@@ -100,6 +108,55 @@ def test_head_sharding_sums_key_gradients_over_ranks(tmp_path, hkv):
         assert max(res["errs"]) < 1e-9, res
         seen += res["heads"]
     assert sorted(seen) == list(range(4 * hkv))
+
+
+def _failing_worker(rank, world, port, mode, out):
+    """Rank 1 fails before the halo exchange of the forward.  mode "store": it records the failure on the
+    store first (guard), so rank 0 stops at its host-side check; mode "silent": it just never joins, so
+    rank 0's exchange runs into the process group's timeout.  Either way rank 0 must get PeerExchangeError
+    instead of blocking."""
+    store = dist.TCPStore("127.0.0.1", port, world, rank == 0, timeout=datetime.timedelta(seconds=20))
+    dist.init_process_group("gloo", store=store, rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=4))
+    from att3ntion_b200 import _dist
+    n, window = 400, 64
+    g = torch.Generator().manual_seed(1)
+    full = [torch.randn(1, 2, n, 16, generator=g, dtype=torch.float64)] + \
+           [torch.randn(1, 1, n, 16, generator=g, dtype=torch.float64) for _ in range(4)]
+    op = _dist.RowShardedGather(n, window, compute_fwd=_oracle_fwd, compute_bwd=_oracle_bwd, store=store)
+    lo, hi = op.plan.lo, op.plan.hi
+    t0 = time.monotonic()
+    result = "completed"
+    try:
+        with _dist.guard(store, rank):
+            if rank == 1:
+                if mode == "store":
+                    raise ValueError("injected failure before the halo exchange")
+                time.sleep(8)                     # silent: outlives the peer's timeout without joining
+                result = "slept"
+            else:
+                if mode == "store":
+                    time.sleep(1.0)               # let the failure note land first
+                op.forward(*[t[:, :, lo:hi].contiguous() for t in full])
+    except _dist.PeerExchangeError as e:
+        result = f"peer-error: {e}"
+    except ValueError as e:
+        result = f"raised: {e}"
+    torch.save({"result": result, "seconds": time.monotonic() - t0}, f"{out}.{rank}")
+    # no destroy_process_group: a rank whose peer is gone must not wait for it at shutdown either
+    os._exit(0)
+
+
+@pytest.mark.parametrize("mode", ["store", "silent"])
+def test_neighbour_failure_is_reported_not_waited_for(tmp_path, mode):
+    out = str(tmp_path / "res.pt")
+    mp.spawn(_failing_worker, args=(2, _free_port(), mode, out), nprocs=2, join=True)
+    r0, r1 = torch.load(f"{out}.0"), torch.load(f"{out}.1")
+    assert r0["result"].startswith("peer-error"), r0
+    assert r0["seconds"] < 7.5, r0                                 # bounded by the 4 s group timeout, not by the peer
+    if mode == "store":
+        assert "injected failure" in r0["result"] and r1["result"].startswith("raised"), (r0, r1)
+        assert r0["seconds"] < 3.0, r0                             # learnt on the host, no exchange attempted
 
 
 def test_partition_helpers():
