@@ -98,3 +98,31 @@ def test_window_mask_and_gates():
         O.check_gate("Y", torch.ones(1, 1, 4, 4) * 1.2, torch.ones(1, 1, 4, 4))
     with pytest.raises(AssertionError):                  # dead-row sets must agree
         O.check_lse(torch.tensor([[0.0]]), torch.tensor([[1.0]]), torch.tensor([[float("-inf")]]))
+
+
+def test_three_gather_oracle_matches_the_reference_naive_module():
+    """tests/golden/naive_c1.pt holds the reference's CPU naive module (att3ntion/_naive.py:80-160,
+    _HypergraphAttentionNaive with head subspaces) at B2 N64 d_model 64 H4, seed 0: its weights, input,
+    output and the gradients of the input and of the six projections.  Restating its forward around the
+    oracle's three-gather (projections, head split, gelu(Y_q) + gelu(Y_r) + gelu(Y_s), heads merged) must
+    give the same numbers: this pins hypergraph_dense and its autograd gradients to the reference module."""
+    g = load_golden("naive_c1.pt")
+    H = 4
+    names = ["Wq", "Wr", "Ws", "Wv_q", "Wv_r", "Wv_s"]
+    ws = [g["state_dict"][f"{n}.weight"].double().requires_grad_(True) for n in names]
+    x = g["x"].double().requires_grad_(True)
+
+    def heads(t):
+        b, n, dm = t.shape
+        return t.reshape(b, n, H, dm // H).permute(0, 2, 1, 3)
+
+    Q, R, S, Vq, Vr, Vs = (heads(x @ w.T) for w in ws)
+    z = torch.zeros_like(Q)
+    outs, _ = O.hypergraph_dense(Q, R, S, Vq, z, Vr, z, Vs, z, scatter=False)
+    gelu = lambda t: t * torch.sigmoid(1.702 * t)
+    y = (gelu(outs[0]) + gelu(outs[1]) + gelu(outs[2])).permute(0, 2, 1, 3).reshape(x.shape)
+    y.backward(g["dY"].double())
+    close(y.detach(), g["y"], 1e-4)
+    close(x.grad, g["dx"], 1e-4)
+    for n, w in zip(names, ws):
+        close(w.grad, g["dW"][f"{n}.weight"], 1e-4)
