@@ -34,6 +34,7 @@ SIGNATURES = {
     "att3_pack_mask32": (C.c_uint32, [_vp, _i]),
     "att3_sg_query_blocks": (_i, [_i] * 6 + [C.POINTER(_i)]),
     "att3_sg_set_query_block": (_i, [_i, _i]),
+    "att3_sg_set_packed": (_i, [_i]),
     "att3_launch_count": (C.c_ulonglong, [_i]),
     "att3_timing_enable": (_i, [_i]),
     "att3_timing_read": (_i, [_i, C.POINTER(C.c_double), C.POINTER(C.c_ulonglong)]),

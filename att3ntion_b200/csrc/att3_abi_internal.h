@@ -37,10 +37,10 @@ private:
     cudaEvent_t start_ = nullptr;
 };
 
-// Tensor map over a row-major BF16 matrix [rows, cols] whose TMA box is one row (cols <= 256): the
-// descriptor behind the kernels' row staging.  Encoded through the driver entry point obtained from
+// Tensor map over a row-major BF16 matrix [rows, cols] whose TMA box is `box_rows` whole rows (cols <= 256):
+// the descriptor behind the kernels' row staging.  Encoded through the driver entry point obtained from
 // the runtime (no link-time dependency on the driver library).  Returns ATT3_OK or records the error.
-int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int cols, const char* who);
+int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int cols, const char* who, int box_rows = 1);
 
 // ---- dense anchored gather (hg_api.cu), shared with the single-gather entry points ----------
 // Forward of one anchored gather: anchor A, rows (Rw, Vrow), cols (C, Vcol), all [B,H,N,D] BF16.

@@ -82,7 +82,7 @@ TimedLaunch::~TimedLaunch() {
     g_time_recs.push_back({id_, start_, stop});
 }
 
-int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int cols, const char* who) {
+int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int cols, const char* who, int box_rows) {
     using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -99,7 +99,8 @@ int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int col
         return set_error(ATT3_ERR_INVALID, "%s: row tensor map needs 16-byte aligned rows of at most 256 BF16", who);
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};       // bytes between rows
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(cols), 1};
+    if (box_rows < 1 || box_rows > 256) return set_error(ATT3_ERR_INVALID, "%s: tensor map box of %d rows", who, box_rows);
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(cols), static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,

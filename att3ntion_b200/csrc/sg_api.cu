@@ -7,6 +7,8 @@
 #include "att3_abi_internal.h"
 #include "sg_ring_fwd.cuh"
 #include "sg_ring_bwd.cuh"
+#include "sg_pack_q.cuh"
+#include "sg_pack_kv.cuh"
 
 namespace {
 
@@ -63,6 +65,15 @@ int plan_blocks(int B, int Hkv, int N, int q_begin, int sm_count, int ctas_per_s
 // passes, 0 = the built-in choice.
 std::atomic<int> g_fwd_block{0}, g_bwd_block{0};
 
+// Packed schedule (sg_pack_q.cuh, sg_pack_kv.cuh): windows of at most 64 keys, D = 128, at least four query
+// heads per KV head, q_begin a multiple of 8 (of every QB).  g_pack_off switches it off (schedule override).
+std::atomic<int> g_pack_off{0};
+bool pack_eligible(int Hq, int Hkv, int D, int window, int q_begin) {
+    return !g_pack_off.load() && D == 128 && window >= 1 && window <= 64 && Hq / Hkv >= 4 && q_begin % 8 == 0;
+}
+int pack_slots(int window) { return window <= 16 ? 16 : window <= 32 ? 32 : 64; }
+int round_up8(int v) { return (v + 7) / 8 * 8; }
+
 // Backward partition: one block per SM where the problem allows it, blocks never shorter than
 // BWD_MIN_BLOCK queries.  The block length is a function of (B, Hkv, N) only -- not of q_begin -- so
 // that the workspace size, which depends on it through the number of partial planes, can be asked
@@ -84,6 +95,11 @@ extern "C" int att3_sg_set_query_block(int fwd_len, int bwd_len) {
     g_fwd_block.store(fwd_len);
     g_bwd_block.store(bwd_len);
     return ATT3_OK;
+}
+
+extern "C" int att3_sg_set_packed(int on) {
+    const int prev = g_pack_off.exchange(on ? 0 : 1);
+    return prev ? 0 : 1;
 }
 
 extern "C" int att3_sg_query_blocks(int B, int Hq, int Hkv, int N, int q_begin, int sm_count, int* block_len) {
@@ -156,6 +172,68 @@ static int launch_ring_fwd(const sgring::FwdParams& p, int nblk, cudaStream_t st
     return ATT3_OK;
 }
 
+template <int W, int MODE>
+static int launch_pack_q(const sgpack::QParams& p, int nblk, cudaStream_t stream, const char* who) {
+    using L = sgpack::QSmem<128, W, MODE>;
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(sgpack::sg_pack_q_kernel<128, W, MODE>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, L::ALLOC);
+        if (e != cudaSuccess) return att3::set_cuda_error(e, who);
+        configured_dev = dev;
+    }
+    dim3 grid(nblk, p.Hkv, p.B);
+    att3::TimedLaunch timed(MODE == sgpack::PQ_FWD ? att3::K_SG_FWD : att3::K_SG_BWD, stream);
+    sgpack::sg_pack_q_kernel<128, W, MODE><<<grid, sgring::PIPE_THREADS, L::ALLOC, stream>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return att3::set_cuda_error(e, who);
+    att3::count_launch(MODE == sgpack::PQ_FWD ? 0 : 1);
+    return ATT3_OK;
+}
+
+// Query-anchored packed kernel (forward, or dQ when dY is given) for a window of at most 64 keys.
+static int run_pack_q(int mode, const void* Q, const void* R, const void* S, const void* Vr, const void* Vs,
+                      const uint8_t* mask, void* Y, float* m, float* l, const void* dY, const float* delta, void* dQ,
+                      int B, int Hq, int Hkv, int N, int window, int q_begin, int* status, cudaStream_t st,
+                      const char* who) {
+    const int W = pack_slots(window), QB = 128 / W, D = 128;
+    sgpack::QParams p{};
+    p.Q = static_cast<const __nv_bfloat16*>(Q);
+    p.R = static_cast<const __nv_bfloat16*>(R);
+    p.S = static_cast<const __nv_bfloat16*>(S);
+    p.Vr = static_cast<const __nv_bfloat16*>(Vr);
+    p.Vs = static_cast<const __nv_bfloat16*>(Vs);
+    p.mask = mask;
+    if (mode == sgpack::PQ_FWD) {
+        p.Y = static_cast<__nv_bfloat16*>(Y); p.m = m; p.l = l;
+    } else {
+        p.m_in = m; p.l_in = l; p.delta = delta; p.dQ = static_cast<__nv_bfloat16*>(dQ);
+    }
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
+    p.scale = 1.0f / sqrtf(static_cast<float>(D));
+    p.status = status;
+    const size_t qrows = static_cast<size_t>(B) * Hq * N, krows = static_cast<size_t>(B) * Hkv * N;
+    int rc;
+    if ((rc = att3::make_row_tensor_map(&p.tmQ, Q, qrows, D, who, QB))) return rc;
+    if (mode == sgpack::PQ_DQ && (rc = att3::make_row_tensor_map(&p.tmdY, dY, qrows, D, who, QB))) return rc;
+    if ((rc = att3::make_row_tensor_map(&p.tmR, R, krows, D, who, QB))) return rc;
+    if ((rc = att3::make_row_tensor_map(&p.tmVr, Vr, krows, D, who, QB))) return rc;
+    if ((rc = att3::make_row_tensor_map(&p.tmS, S, krows, D, who, QB))) return rc;
+    if ((rc = att3::make_row_tensor_map(&p.tmVs, Vs, krows, D, who, QB))) return rc;
+    int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, 16, &p.block_len);
+    if (const int forced = g_fwd_block.load()) p.block_len = forced;
+    p.block_len = round_up8(p.block_len);
+    nblk = (N - q_begin + p.block_len - 1) / p.block_len;
+    const bool fwd = mode == sgpack::PQ_FWD;
+    switch (W) {
+        case 16: return fwd ? launch_pack_q<16, sgpack::PQ_FWD>(p, nblk, st, who) : launch_pack_q<16, sgpack::PQ_DQ>(p, nblk, st, who);
+        case 32: return fwd ? launch_pack_q<32, sgpack::PQ_FWD>(p, nblk, st, who) : launch_pack_q<32, sgpack::PQ_DQ>(p, nblk, st, who);
+        default: return fwd ? launch_pack_q<64, sgpack::PQ_FWD>(p, nblk, st, who) : launch_pack_q<64, sgpack::PQ_DQ>(p, nblk, st, who);
+    }
+}
+
 extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, const void* Vr, const void* Vs,
                                const uint8_t* mask, void* Y, float* m, float* l, int B, int Hq, int Hkv, int N,
                                int D, int window, int q_begin, void* stream) {
@@ -171,6 +249,12 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
         att3::count_launch(0);
         return att3::dense_gather_forward(Q, R, S, Vr, Vs, mask, Y, m, l, B, Hq, N, D, 0,
                                           static_cast<cudaStream_t>(stream));
+    }
+    if (pack_eligible(Hq, Hkv, D, window, q_begin)) {
+        int* status = status_ptr();
+        if (!status) return att3::set_error(ATT3_ERR_CUDA, "att3_sg_forward: status word not resolvable");
+        return run_pack_q(sgpack::PQ_FWD, Q, R, S, Vr, Vs, mask, Y, m, l, nullptr, nullptr, nullptr, B, Hq, Hkv, N, window,
+                          q_begin, status, static_cast<cudaStream_t>(stream), "att3_sg_forward");
     }
     sgring::FwdParams p;
     p.Q = static_cast<const __nv_bfloat16*>(Q);
@@ -211,11 +295,12 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
 // Workspace: FP32 partial planes of the two gradients of one key side (bwd_planes
 // of them each); the second pass reuses the space after the first pass's reduction.
 extern "C" size_t att3_sg_backward_workspace_bytes(int B, int Hq, int Hkv, int N, int D, int window) {
-    (void)Hq;
-    if (B <= 0 || Hkv <= 0 || N <= 0 || D <= 0 || window < 0) return 0;
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0 || D <= 0 || window < 0) return 0;
     if (window == 0)   // dense: five FP32 gradient planes + one anchor-gradient partial plane per 128-key tile
         return static_cast<size_t>(5 + att3::dense_tiles(N, 0) + 2) * B * Hq * N * D * sizeof(float);
-    return static_cast<size_t>(2 * sgring::bwd_planes(bwd_block_len(B, Hkv, N))) * B * Hkv * N * D * sizeof(float);
+    // partial planes of one key side, then delta = rowsum(dY o Y) per (batch, query head, query) for the packed schedule
+    return static_cast<size_t>(2 * sgring::bwd_planes(bwd_block_len(B, Hkv, N))) * B * Hkv * N * D * sizeof(float) +
+           static_cast<size_t>(B) * Hq * N * sizeof(float);
 }
 
 template <int D, bool WITH_DQ>
@@ -240,8 +325,9 @@ static int launch_ring_bwd(const sgring::BwdParams& p, int nblk, cudaStream_t st
 }
 
 static int launch_reduce(const sgring::BwdParams& p, int nblk, int D, void* dK, void* dV, cudaStream_t stream,
-                         bool f32 = false) {
+                         bool f32 = false, int lead = 0) {
     sgring::ReduceParams r;
+    r.lead = lead;
     r.part_K = p.part_K;
     r.part_V = p.part_V;
     r.dK = f32 ? nullptr : static_cast<__nv_bfloat16*>(dK);
@@ -259,6 +345,86 @@ static int launch_reduce(const sgring::BwdParams& p, int nblk, int D, void* dK, 
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: reduce launch");
     att3::count_launch(1);
     return ATT3_OK;
+}
+
+template <int W>
+static int launch_pack_kv(const sgpack::KvParams& p, int nblk, cudaStream_t stream) {
+    using L = sgpack::KvSmem<128, W>;
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(sgpack::sg_pack_kv_kernel<128, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             L::ALLOC);
+        if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: shared-memory opt-in");
+        configured_dev = dev;
+    }
+    dim3 grid(nblk, p.Hkv, p.B);
+    att3::TimedLaunch timed(att3::K_SG_BWD, stream);
+    sgpack::sg_pack_kv_kernel<128, W><<<grid, sgring::PIPE_THREADS, L::ALLOC, stream>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: launch");
+    att3::count_launch(1);
+    return ATT3_OK;
+}
+
+// The backward on the packed schedule: delta, dQ from the query-anchored kernel, then one key-side kernel per side.
+static int pack_backward(int passes, bool kv_f32, const void* dY, const void* Q, const void* R, const void* S,
+                         const void* Vr, const void* Vs, const void* Y, const float* m, const float* l,
+                         const uint8_t* mask, void* dQ, void* dR, void* dS, void* dVr, void* dVs, int B, int Hq, int Hkv,
+                         int N, int window, int q_begin, void* workspace, cudaStream_t st) {
+    constexpr int D = 128;
+    int* status = status_ptr();
+    if (!status) return att3::set_error(ATT3_ERR_CUDA, "att3_sg_backward: status word not resolvable");
+    const int W = pack_slots(window), QB = 128 / W;
+    const int block_len = round_up8(bwd_block_len(B, Hkv, N));
+    const int planes = sgring::bwd_planes(block_len);
+    const int nblk = (N - q_begin + block_len - 1) / block_len;
+    const size_t plane = static_cast<size_t>(B) * Hkv * N * D;
+    float* part_K = static_cast<float*>(workspace);
+    float* part_V = part_K + static_cast<size_t>(planes) * plane;
+    // delta sits behind the planes the workspace was sized for (which may be more than this launch uses)
+    float* delta = part_K + static_cast<size_t>(2 * sgring::bwd_planes(bwd_block_len(B, Hkv, N))) * plane;
+    {
+        const size_t rows = static_cast<size_t>(B) * Hq * N;
+        const int threads = 256;
+        const unsigned blocks = static_cast<unsigned>((rows * 32 + threads - 1) / threads);
+        att3::TimedLaunch timed(att3::K_SG_REDUCE, st);
+        sgpack::sg_delta_kernel<D><<<blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(dY),
+                                                               static_cast<const __nv_bfloat16*>(Y), delta, rows);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: delta launch");
+        att3::count_launch(1);
+    }
+    int rc = ATT3_OK;
+    sgpack::KvParams p{};
+    p.Q = static_cast<const __nv_bfloat16*>(Q);
+    p.dY = static_cast<const __nv_bfloat16*>(dY);
+    p.m = m; p.l = l; p.delta = delta;
+    p.mask = mask;
+    p.part_K = part_K; p.part_V = part_V;
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
+    p.block_len = block_len; p.planes = planes;
+    p.scale = 1.0f / sqrtf(static_cast<float>(D));
+    p.status = status;
+    sgring::BwdParams rp{};        // what launch_reduce reads
+    rp.part_K = part_K; rp.part_V = part_V; rp.B = B; rp.Hkv = Hkv; rp.N = N; rp.q_begin = q_begin;
+    rp.block_len = block_len; rp.planes = planes;
+    auto kv_pass = [&](const void* ka, const void* va, const void* kb, const void* vb, void* dK, void* dV) {
+        p.Ka = static_cast<const __nv_bfloat16*>(ka); p.Va = static_cast<const __nv_bfloat16*>(va);
+        p.Kb = static_cast<const __nv_bfloat16*>(kb); p.Vb = static_cast<const __nv_bfloat16*>(vb);
+        int r = W == 16 ? launch_pack_kv<16>(p, nblk, st) : W == 32 ? launch_pack_kv<32>(p, nblk, st) : launch_pack_kv<64>(p, nblk, st);
+        if (r) return r;
+        return launch_reduce(rp, nblk, D, dK, dV, st, kv_f32, QB - 1);
+    };
+    if (passes & 1) {
+        if ((rc = run_pack_q(sgpack::PQ_DQ, Q, R, S, Vr, Vs, mask, nullptr, const_cast<float*>(m), const_cast<float*>(l), dY,
+                             delta, dQ, B, Hq, Hkv, N, window, q_begin, status, st, "att3_sg_backward")))
+            return rc;
+        if ((rc = kv_pass(R, Vr, S, Vs, dS, dVs))) return rc;
+    }
+    if (passes & 2) rc = kv_pass(S, Vs, R, Vr, dR, dVr);
+    return rc;
 }
 
 // passes: bit 0 = key side (S, Vs) with dQ, bit 1 = key side (R, Vr); both for a whole backward.
@@ -307,6 +473,9 @@ static int sg_backward_impl(int passes, bool kv_f32, const void* dY, const void*
             if ((rc = att3::plane_to_bf16(srcs[k], outs[k], plane, st))) return rc;
         return ATT3_OK;
     }
+    if (pack_eligible(Hq, Hkv, D, window, q_begin))
+        return pack_backward(passes, kv_f32, dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv, N, window,
+                             q_begin, workspace, static_cast<cudaStream_t>(stream));
     sgring::BwdParams p;
     p.Q = static_cast<const __nv_bfloat16*>(Q);
     p.dY = static_cast<const __nv_bfloat16*>(dY);

@@ -853,6 +853,7 @@ struct ReduceParams {
     float* dV32;         // query heads are only a part of the KV head's: summed across ranks before rounding)
     int rows;            // B * Hkv
     int N, D, q_begin, block_len, nblk, planes;
+    int lead;            // the writer's ring is positioned `lead` queries ahead of its first query (packed schedule: QB - 1)
 };
 
 __global__ void sg_bwd_reduce_kernel(const ReduceParams p) {
@@ -864,7 +865,9 @@ __global__ void sg_bwd_reduce_kernel(const ReduceParams p) {
         const int c = static_cast<int>(idx % chunks);
         const size_t rk = idx / chunks;
         const int k = static_cast<int>(rk % p.N);
-        const int q_lo = max(k, p.q_begin), q_hi = min(k + RING - 1, p.N - 1);
+        // a block that starts at q0 holds (and later flushes) the keys (q0 + lead - 128, ...]: row k is written by
+        // the blocks that start at or before k + 127 - lead and end after k
+        const int q_lo = max(k, p.q_begin), q_hi = min(k + RING - 1 - p.lead, p.N - 1);
         float4 sk = make_float4(0.f, 0.f, 0.f, 0.f), sv = sk;
         if (q_lo <= q_hi) {
             const int b_lo = (q_lo - p.q_begin) / p.block_len, b_hi = (q_hi - p.q_begin) / p.block_len;

@@ -224,6 +224,13 @@ int att3_sg_query_blocks(int B, int Hq, int Hkv, int N, int q_begin, int sm_coun
  * planes): query att3_sg_backward_workspace_bytes after changing it. */
 int att3_sg_set_query_block(int fwd_len, int bwd_len);
 
+/* Windows of at most 64 keys run a schedule that packs 128 / W queries into one tensor-core tile (D = 128,
+ * at least four query heads per KV head, q_begin a multiple of 8); everything else runs the 128-slot ring
+ * schedule.  on = 0 sends every windowed call to the ring schedule (the counterpart of fwd_group / rs_group
+ * selecting a fixed schedule in the reference, cuda/forward.cu:1739, cuda/backward.cu:2518-2525).  Returns the
+ * previous setting.  Process-wide. */
+int att3_sg_set_packed(int on);
+
 /* Launch counters, the counterpart of att3_tc::State (cpp/cuda_bindings.h:18-48).
  * which: 0 single-gather forward, 1 single-gather backward, 2 three-gather
  * forward, 3 three-gather backward.  Returns kernels launched so far. */

@@ -167,7 +167,7 @@ KNOWN_STRESS_FAILURES = {
     (64, "concentrated", 1): ["dR", "dVr"],
     (128, "scale4", 0): ["dQ", "dR", "dS", "dVr"],
     (128, "scale4", 1): ["Y", "dQ", "dR", "dS", "dVr", "dVs"],
-    (128, "concentrated", 0): ["dR", "dVr"],
+    (128, "concentrated", 0): ["dQ", "dR", "dS", "dVr"],      # dQ, dS: one head just over its per-head gate
     (128, "concentrated", 1): ["dR", "dVr"],
 }
 
