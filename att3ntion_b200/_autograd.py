@@ -18,7 +18,7 @@ import torch.nn as nn
 from torch.autograd import Function
 
 from . import _custom_op  # noqa: F401  (registers torch.ops.att3ntion.hypergraph_{forward,backward})
-from ._single_gather import single_gather_attention, window_mask
+from ._single_gather import single_gather_attention, single_gather_heads_last, window_mask
 
 TILE = 16
 _CHECK_GRADS = os.getenv("ATT3NTION_CHECK_GRADS", "0").lower() in {"1", "true", "yes", "on"}
@@ -163,6 +163,14 @@ class HypergraphAttention(nn.Module):
         if self.window:
             win = window_mask(n, self.window, x.device)
             mask = win if mask is None else mask.to(device=x.device, dtype=torch.bool) & win
+
+        if self.gather_mode == 1 and self.head_dim in (64, 128) and window_only and self.window <= 128 and n % TILE == 0:
+            # window-only calls read the projections where they lie ([B,N,H,D] views, no permute-and-copy) and take
+            # the activation from the kernel's epilogue
+            split = lambda t: t.view(b, n, self.n_heads, self.head_dim)
+            y = single_gather_heads_last(split(Q), split(R), split(S), split(self.Wv_r(x)), split(self.Wv_s(x)),
+                                         min(self.window, n), act=True)
+            return self.Wo(y.reshape(b, n, self.n_heads * self.head_dim))
 
         if self.gather_mode == 1 and self.head_dim in (64, 128):
             y = single_gather_attention(self._heads(Q), self._heads(R), self._heads(S), self._heads(self.Wv_r(x)),

@@ -24,6 +24,9 @@ SIGNATURES = {
     "att3_sg_forward": (_i, [_vp] * 9 + [_i] * 7 + [_vp]),
     "att3_sg_backward": (_i, [_vp] * 15 + [_i] * 7 + [_vp, _sz, _vp]),
     "att3_sg_backward_kv32": (_i, [_vp] * 15 + [_i] * 7 + [_vp, _sz, _vp]),
+    "att3_sg_forward_ext": (_i, [_vp] * 9 + [_i] * 7 + [_vp, _vp]),
+    "att3_sg_backward_ext": (_i, [_vp] * 15 + [_i] * 7 + [_vp, _sz, _vp, _vp]),
+    "att3_sg_pack_mask": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "att3_sg_backward_kv32_side": (_i, [_i] + [_vp] * 15 + [_i] * 7 + [_vp, _sz, _vp]),
     "att3_sg_backward_static_max_bytes": (_sz, []),
     "att3_sg_backward_static": (_i, [_vp] * 15 + [_i] * 7 + [_vp]),
@@ -41,6 +44,11 @@ SIGNATURES = {
     "att3_umma_selftest": (_i, [_vp, _vp, _vp, _i, _vp, _vp]),
     "att3_wait_selftest": (_i, [C.c_uint, _vp]),
 }
+
+
+class SgExt(C.Structure):
+    """att3_sg_ext of include/att3_b200.h."""
+    _fields_ = [("window_s", C.c_int), ("mask_words", C.c_void_p), ("layout", C.c_int), ("Y_act", C.c_void_p)]
 
 
 class Att3Error(RuntimeError):

@@ -137,36 +137,83 @@ def _check_state(Q, tensors, who):
 
 # --------------------------------------------------------------------------- raw ops (mask optional)
 
-def sg_forward_raw(Q, R, S, Vr, Vs, mask, window: int, q_begin: int = 0):
+def pack_mask(mask: torch.Tensor, window: int = 0, with_support: bool = False):
+    """Bool/byte mask [B,N,N] -> packed words int32 [B,N,ceil(N/32)] (bit t of word c = key 32 c + t), restricted to
+    the causal window when window > 0; with_support also returns the per-query count of visible keys saturated at
+    2 ([B,N] uint8).  The packed form is what `mask_words=` of the raw calls takes."""
+    B, N, _ = mask.shape
+    mask = mask.contiguous()
+    with torch.cuda.device(mask.device):
+        words = torch.empty((B, N, (N + 31) // 32), dtype=torch.int32, device=mask.device)
+        support = torch.empty((B, N), dtype=torch.uint8, device=mask.device) if with_support else None
+        _call(lib.att3_sg_pack_mask, mask.data_ptr(), words.data_ptr(), _ptr(support), B, N, int(window), _stream(mask))
+    return (words, support) if with_support else words
+
+
+def _ext(window_s: int, mask_words, bnhd: bool = False, y_act=None):
+    """att3_sg_ext for a call, or None for the plain entry points."""
+    if not window_s and mask_words is None and not bnhd and y_act is None:
+        return None
+    return _cabi.SgExt(int(window_s), _ptr(mask_words), 1 if bnhd else 0, _ptr(y_act))
+
+
+def _dims(Q, R, bnhd: bool):
+    """(B, Hq, Hkv, N, D) of operands laid out [B,H,N,D] or, with bnhd, [B,N,H,D]."""
+    if bnhd:
+        B, N, Hq, D = Q.shape
+        return B, Hq, R.shape[2], N, D
+    B, Hq, N, D = Q.shape
+    return B, Hq, R.shape[1], N, D
+
+
+def sg_forward_raw(Q, R, S, Vr, Vs, mask, window: int, q_begin: int = 0, window_s: int = 0, mask_words=None,
+                   bnhd: bool = False, act: bool = False):
     """Windowed/dense single gather on already-validated BF16 tensors.  mask may be
     None: with window > 0 the causal window is generated from indices inside the
-    kernel, so no [B,N,N] tensor is ever materialised."""
-    B, Hq, N, D = Q.shape
-    Hkv = R.shape[1]
+    kernel, so no [B,N,N] tensor is ever materialised.  window_s > 0: another window on the
+    S / Vs key axis (`window` is then the R / Vr axis's); mask_words: the mask as packed words
+    (see pack_mask) instead of `mask`; bnhd: the operands (and Y) are [B,N,H,D] contiguous
+    instead of [B,H,N,D]; act: also return QuickGELU(Y) as a fourth result, written by the
+    forward's epilogue.  m, l are [B,H,N] either way."""
+    B, Hq, Hkv, N, D = _dims(Q, R, bnhd)
     with torch.cuda.device(Q.device):
         Y = torch.empty_like(Q)
+        Ya = torch.empty_like(Q) if act else None
         m = torch.empty((B, Hq, N), dtype=torch.float32, device=Q.device)
         l = torch.empty_like(m)
-        _call(lib.att3_sg_forward, Q.data_ptr(), R.data_ptr(), S.data_ptr(), Vr.data_ptr(), Vs.data_ptr(),
-              _ptr(mask), Y.data_ptr(), m.data_ptr(), l.data_ptr(), B, Hq, Hkv, N, D, int(window), int(q_begin),
-              _stream(Q))
-    return Y, m, l
+        ext = _ext(window_s, mask_words, bnhd, Ya)
+        args = (Q.data_ptr(), R.data_ptr(), S.data_ptr(), Vr.data_ptr(), Vs.data_ptr(),
+                _ptr(mask), Y.data_ptr(), m.data_ptr(), l.data_ptr(), B, Hq, Hkv, N, D, int(window), int(q_begin),
+                _stream(Q))
+        if ext is None:
+            _call(lib.att3_sg_forward, *args)
+        else:
+            _call(lib.att3_sg_forward_ext, *args, C.byref(ext))
+    return (Y, m, l, Ya) if act else (Y, m, l)
 
 
-def sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, window: int, q_begin: int = 0, kv_f32: bool = False):
+def sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, window: int, q_begin: int = 0, kv_f32: bool = False,
+                    window_s: int = 0, mask_words=None, bnhd: bool = False):
     """kv_f32: leave dR, dS, dVr, dVs in FP32 (partial sums of a process that holds only part of the
-    query heads of a KV head; windowed path only)."""
-    B, Hq, N, D = Q.shape
-    Hkv = R.shape[1]
+    query heads of a KV head; windowed path only).  window_s, mask_words, bnhd: as in sg_forward_raw
+    (with bnhd the gradients come back [B,N,H,D] too)."""
+    B, Hq, Hkv, N, D = _dims(Q, R, bnhd)
+    ext = _ext(window_s, mask_words, bnhd)
+    if ext is not None and kv_f32:
+        raise RuntimeError("sg_backward_raw: kv_f32 and the extended options do not combine")
     with torch.cuda.device(Q.device):
         dQ = torch.zeros_like(Q) if q_begin else torch.empty_like(Q)
         dR, dS, dVr, dVs = (torch.empty_like(R, dtype=torch.float32 if kv_f32 else R.dtype) for _ in range(4))
         nbytes = lib.att3_sg_backward_workspace_bytes(B, Hq, Hkv, N, D, int(window))
         ws = _workspace(Q.device, nbytes)
-        _call(lib.att3_sg_backward_kv32 if kv_f32 else lib.att3_sg_backward, dY.data_ptr(), Q.data_ptr(), R.data_ptr(), S.data_ptr(), Vr.data_ptr(),
-              Vs.data_ptr(), Y.data_ptr(), m.data_ptr(), l.data_ptr(), _ptr(mask),
-              dQ.data_ptr(), dR.data_ptr(), dS.data_ptr(), dVr.data_ptr(), dVs.data_ptr(),
-              B, Hq, Hkv, N, D, int(window), int(q_begin), ws.data_ptr(), nbytes, _stream(Q))
+        args = (dY.data_ptr(), Q.data_ptr(), R.data_ptr(), S.data_ptr(), Vr.data_ptr(),
+                Vs.data_ptr(), Y.data_ptr(), m.data_ptr(), l.data_ptr(), _ptr(mask),
+                dQ.data_ptr(), dR.data_ptr(), dS.data_ptr(), dVr.data_ptr(), dVs.data_ptr(),
+                B, Hq, Hkv, N, D, int(window), int(q_begin), ws.data_ptr(), nbytes, _stream(Q))
+        if ext is not None:
+            _call(lib.att3_sg_backward_ext, *args, C.byref(ext))
+        else:
+            _call(lib.att3_sg_backward_kv32 if kv_f32 else lib.att3_sg_backward, *args)
     return dQ, dR, dS, dVr, dVs
 
 

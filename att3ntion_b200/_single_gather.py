@@ -9,7 +9,11 @@ result is cropped and cast back.  Differences, both invisible to callers:
 an equal causal window (``window`` in 1..128, no extra mask) is generated from
 indices inside the kernel instead of being materialised as a [B,N,N] tensor,
 and the padding rows of such a call need no mask either, because a causal
-window never lets a real query see a later (padded) key.
+window never lets a real query see a later (padded) key.  A mask that comes with
+such a window is packed into words once per forward (1/32 of the bytes) and the
+words serve the forward and the backward.  Beyond the reference: ``window`` may be
+a pair (w_r, w_s), one causal window per key axis (the reference lists independent
+windows as an open item, docs/KERNEL_HISTORY.md:180).
 """
 from __future__ import annotations
 
@@ -43,31 +47,53 @@ def _prepare_mask(mask, batch: int, n: int, n_pad: int, device):
     return torch.nn.functional.pad(mask, (0, n_pad, 0, n_pad), value=False).contiguous()
 
 
+def _window_pair(window, n: int):
+    """(w_r, w_s) from an int or a pair, each clipped to the sequence length (>= N: causal); 0 = no window."""
+    if isinstance(window, (tuple, list)):
+        if len(window) != 2:
+            raise ValueError("single_gather_attention: window is an int or a pair (w_r, w_s)")
+        wr, ws = int(window[0]), int(window[1])
+        if (wr > 0) != (ws > 0):
+            raise ValueError("single_gather_attention: a pair of windows needs both positive")
+    else:
+        wr = ws = int(window) if window else 0
+    return (min(wr, n) if wr else 0), (min(ws, n) if ws else 0)
+
+
 class _SingleGatherFn(Function):
     @staticmethod
     def forward(ctx, Q, R, S, Vr, Vs, mask, window):
         n = Q.size(2)
         n_pad = (-n) % TILE
         xs = [_pad_rows(x.contiguous().to(torch.bfloat16), n_pad) for x in (Q, R, S, Vr, Vs)]
-        window = min(int(window), n) if window else 0
-        ring = 0 < window <= 128
-        if window and not ring and mask is None:
-            mask = window_mask(n, window, Q.device)          # wider than the resident ring: dense schedule
+        window, window_s = _window_pair(window, n)
+        ring = 0 < window <= 128 and 0 < window_s <= 128
+        if (window or window_s) and not ring:
+            if window != window_s:
+                raise ValueError("single_gather_attention: a pair of windows needs both in 1..128")
+            if mask is None:
+                mask = window_mask(n, window, Q.device)      # wider than the resident ring: dense schedule
         if mask is None and n_pad and not ring:
             mask = torch.ones(Q.size(0), n, n, dtype=torch.bool, device=Q.device)
         mask = _prepare_mask(mask, Q.size(0), n, n_pad, Q.device)
         win = window if ring else 0
-        Y, m, l = _ck.sg_forward_raw(*xs, mask, win)
-        ctx.save_for_backward(*xs, Y, m, l, mask if mask is not None else torch.empty(0))
-        ctx.n, ctx.dtype, ctx.win = n, Q.dtype, win
+        win_s = window_s if (ring and window_s != window) else 0
+        words = None
+        if ring and mask is not None:
+            words, mask = _ck.pack_mask(mask), None          # the window itself comes from indices inside the kernels
+        Y, m, l = _ck.sg_forward_raw(*xs, mask, win, 0, win_s, words)
+        keep = words if words is not None else (mask if mask is not None else torch.empty(0))
+        ctx.save_for_backward(*xs, Y, m, l, keep)
+        ctx.n, ctx.dtype, ctx.win, ctx.win_s, ctx.packed = n, Q.dtype, win, win_s, words is not None
         return Y[:, :, :n].to(Q.dtype)
 
     @staticmethod
     def backward(ctx, dY):
-        Q, R, S, Vr, Vs, Y, m, l, mask = ctx.saved_tensors
-        mask = mask if mask.numel() else None
+        Q, R, S, Vr, Vs, Y, m, l, keep = ctx.saved_tensors
+        mask = keep if (keep.numel() and not ctx.packed) else None
+        words = keep if ctx.packed else None
         dY = _pad_rows(dY.contiguous().to(torch.bfloat16), Q.size(2) - ctx.n)
-        grads = _ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, ctx.win)
+        grads = _ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, ctx.win, 0, False, ctx.win_s, words)
         return tuple(g[:, :, :ctx.n].to(ctx.dtype) for g in grads) + (None, None)
 
 
@@ -76,5 +102,45 @@ def single_gather_attention(Q, R, S, Vr, Vs, mask=None, window=0):
     True = visible; query i attends the pairs (j,k) whose members are both visible
     to it, and a fully masked query returns zeros.  window > 0 declares an equal
     causal window of that width on both key axes (>= N: causal); with no mask the
-    window is the visibility, with a mask the two are intersected."""
+    window is the visibility, with a mask the two are intersected.  window = (w_r, w_s)
+    gives the R / Vr axis and the S / Vs axis a causal window each (both in 1..128)."""
     return _SingleGatherFn.apply(Q, R, S, Vr, Vs, mask, window)
+
+
+class _SingleGatherHeadsLastFn(Function):
+    """The windowed gather on operands laid out [B,N,H,D] -- the projections' own output viewed as heads -- with
+    the module's activation optionally taken from the forward's epilogue.  The reference's module permutes every
+    operand to [B,H,N,D] and copies it before the op, and runs QuickGELU as a separate pass afterwards
+    (att3ntion/_autograd.py:349-363, 395-403); none of that happens here."""
+
+    @staticmethod
+    def forward(ctx, Q, R, S, Vr, Vs, window, act):
+        xs = [x.contiguous().to(torch.bfloat16) for x in (Q, R, S, Vr, Vs)]
+        out = _ck.sg_forward_raw(*xs, None, int(window), bnhd=True, act=bool(act))
+        Y, m, l = out[:3]
+        ctx.save_for_backward(*xs, Y, m, l)
+        ctx.window, ctx.act, ctx.dtype = int(window), bool(act), Q.dtype
+        return (out[3] if act else Y).to(Q.dtype)
+
+    @staticmethod
+    def backward(ctx, dOut):
+        Q, R, S, Vr, Vs, Y, m, l = ctx.saved_tensors
+        dOut = dOut.contiguous()
+        if ctx.act:
+            # d/dy [y sigmoid(a y)] = s (1 + a y (1 - s)), s = sigmoid(a y), a = 1.702
+            y = Y.float()
+            sg = torch.sigmoid(1.702 * y)
+            dY = (dOut.float() * sg * (1.0 + 1.702 * y * (1.0 - sg))).to(torch.bfloat16)
+        else:
+            dY = dOut.to(torch.bfloat16)
+        grads = _ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, None, ctx.window, bnhd=True)
+        return tuple(g.to(ctx.dtype) for g in grads) + (None, None)
+
+
+def single_gather_heads_last(Q, R, S, Vr, Vs, window, act=False):
+    """Q [B,N,Hq,D], R, S, Vr, Vs [B,N,Hkv,D] (Hq a multiple of Hkv), D in {64,128}, N a multiple of 16, causal
+    window in 1..128 on both key axes and no extra mask.  Returns Y, or QuickGELU(Y) with act=True, as [B,N,Hq,D]."""
+    n = Q.size(1)
+    if n % TILE or not 0 < int(window) <= 128:
+        raise ValueError("single_gather_heads_last: needs N % 16 == 0 and a window in 1..128")
+    return _SingleGatherHeadsLastFn.apply(Q, R, S, Vr, Vs, min(int(window), n), act)

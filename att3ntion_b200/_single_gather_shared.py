@@ -8,7 +8,8 @@ as [B,1,N,128] (summed over query heads).
 
 The reference materialises the window as a dense [B,N,N] bool tensor on every
 call; here the kernels derive it from indices, and only a caller-supplied extra
-mask is passed through.
+mask is passed on, packed into one bit per key (the form of the reference's mask
+metadata, cuda/shared_kv/shared_mask_metadata.cuh:8-31).
 """
 from __future__ import annotations
 
@@ -30,17 +31,19 @@ class _SharedFn(Function):
         _ck._check_shared(xs[0], xs[1:], None, window, 1 if fwd_group == 0 else fwd_group, need_mask=False)
         _ck._check_shared(xs[0], xs[1:], None, window, 1 if rs_group == 0 else rs_group, need_mask=False)
         mask = _prepare_mask(mask, Q.size(0), n, n_pad, Q.device)
-        Y, m, l = _ck.sg_forward_raw(*xs, mask, window)
-        ctx.save_for_backward(*xs, Y, m, l, mask if mask is not None else torch.empty(0))
+        # an extra mask is packed into words once (1/32 of the bytes) and serves the forward and the backward
+        words = _ck.pack_mask(mask) if mask is not None else None
+        Y, m, l = _ck.sg_forward_raw(*xs, None, window, 0, 0, words)
+        ctx.save_for_backward(*xs, Y, m, l, words if words is not None else torch.empty(0))
         ctx.n, ctx.dtype, ctx.window = n, Q.dtype, window
         return Y[:, :, :n].to(Q.dtype)
 
     @staticmethod
     def backward(ctx, dY):
-        Q, R, S, Vr, Vs, Y, m, l, mask = ctx.saved_tensors
-        mask = mask if mask.numel() else None
+        Q, R, S, Vr, Vs, Y, m, l, words = ctx.saved_tensors
+        words = words if words.numel() else None
         dY = _pad_rows(dY.contiguous().to(torch.bfloat16), Q.size(2) - ctx.n)
-        grads = _ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, ctx.window)
+        grads = _ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, None, ctx.window, 0, False, 0, words)
         return tuple(g[:, :, :ctx.n].to(ctx.dtype) for g in grads) + (None, None, None, None)
 
 

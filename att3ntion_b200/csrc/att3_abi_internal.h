@@ -40,7 +40,12 @@ private:
 // Tensor map over a row-major BF16 matrix [rows, cols] whose TMA box is `box_rows` whole rows (cols <= 256):
 // the descriptor behind the kernels' row staging.  Encoded through the driver entry point obtained from
 // the runtime (no link-time dependency on the driver library).  Returns ATT3_OK or records the error.
-int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int cols, const char* who, int box_rows = 1);
+int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int cols, const char* who, int box_rows = 1,
+                        int pitch_cols = 0);
+// The same over a [B,H,N,D] operand in either memory layout (0: [B,H,N,D] -> [B*H*N, D]; 1: [B,N,H,D] -> [B*N, H*D],
+// the head being a column offset of the box): the (x, y) a kernel passes come from sgring::RowAddr::tma.
+int make_head_tensor_map(CUtensorMap* out, const void* base, int B, int H, int N, int D, int bnhd, int box_rows,
+                         const char* who);
 
 // ---- dense anchored gather (hg_api.cu), shared with the single-gather entry points ----------
 // Forward of one anchored gather: anchor A, rows (Rw, Vrow), cols (C, Vcol), all [B,H,N,D] BF16.

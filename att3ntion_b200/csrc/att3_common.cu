@@ -82,7 +82,8 @@ TimedLaunch::~TimedLaunch() {
     g_time_recs.push_back({id_, start_, stop});
 }
 
-int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int cols, const char* who, int box_rows) {
+int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int cols, const char* who, int box_rows,
+                        int pitch_cols) {
     using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -97,8 +98,11 @@ int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int col
     if (!encode) return set_error(ATT3_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available from this driver", who);
     if (cols <= 0 || cols > 256 || (cols * 2) % 16 != 0 || reinterpret_cast<uintptr_t>(base) % 16 != 0)
         return set_error(ATT3_ERR_INVALID, "%s: row tensor map needs 16-byte aligned rows of at most 256 BF16", who);
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};       // bytes between rows
+    if (pitch_cols <= 0) pitch_cols = cols;
+    if (pitch_cols % cols != 0) return set_error(ATT3_ERR_INVALID, "%s: row pitch must be a multiple of the row length", who);
+    // the matrix is [rows, pitch_cols]; a box is `box_rows` rows of `cols` columns starting at a multiple of `cols`
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(pitch_cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_cols) * 2};       // bytes between rows
     if (box_rows < 1 || box_rows > 256) return set_error(ATT3_ERR_INVALID, "%s: tensor map box of %d rows", who, box_rows);
     const cuuint32_t box[2] = {static_cast<cuuint32_t>(cols), static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t estr[2] = {1, 1};
@@ -107,6 +111,12 @@ int make_row_tensor_map(CUtensorMap* out, const void* base, size_t rows, int col
                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return set_error(ATT3_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed (CUresult %d)", who, int(r));
     return ATT3_OK;
+}
+
+int make_head_tensor_map(CUtensorMap* out, const void* base, int B, int H, int N, int D, int bnhd, int box_rows,
+                         const char* who) {
+    if (bnhd) return make_row_tensor_map(out, base, static_cast<size_t>(B) * N, D, who, box_rows, H * D);
+    return make_row_tensor_map(out, base, static_cast<size_t>(B) * H * N, D, who, box_rows, D);
 }
 
 }  // namespace att3

@@ -65,11 +65,19 @@ int plan_blocks(int B, int Hkv, int N, int q_begin, int sm_count, int ctas_per_s
 // passes, 0 = the built-in choice.
 std::atomic<int> g_fwd_block{0}, g_bwd_block{0};
 
+// Extensions of the current call (att3_sg_forward_ext / att3_sg_backward_ext set them around the regular entry
+// point on the calling thread): the window of the S / Vs key axis when it differs from the R / Vr axis's, and the
+// caller's mask as packed words.
+struct SgExt { int window_s; const uint32_t* mask_words; int layout; void* Y_act; };
+thread_local SgExt t_ext = {0, nullptr, 0, nullptr};
+int ext_window_s(int window) { return t_ext.window_s > 0 ? t_ext.window_s : window; }
+
 // Packed schedule (sg_pack_q.cuh, sg_pack_kv.cuh): windows of at most 64 keys, D = 128, at least four query
 // heads per KV head, q_begin a multiple of 8 (of every QB).  g_pack_off switches it off (schedule override).
 std::atomic<int> g_pack_off{0};
 bool pack_eligible(int Hq, int Hkv, int D, int window, int q_begin) {
-    return !g_pack_off.load() && D == 128 && window >= 1 && window <= 64 && Hq / Hkv >= 4 && q_begin % 8 == 0;
+    return !g_pack_off.load() && D == 128 && window >= 1 && window <= 64 && Hq / Hkv >= 4 && q_begin % 8 == 0 &&
+           ext_window_s(window) == window;          // equal windows on both key axes
 }
 int pack_slots(int window) { return window <= 16 ? 16 : window <= 32 ? 32 : 64; }
 int round_up8(int v) { return (v + 7) / 8 * 8; }
@@ -151,21 +159,21 @@ extern "C" int att3_wait_selftest(unsigned limit, void* stream) {
     return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "att3_wait_selftest: launch");
 }
 
-template <int D>
+template <int D, bool EXT>
 static int launch_ring_fwd(const sgring::FwdParams& p, int nblk, cudaStream_t stream) {
     using L = sgring::FwdSmem<D>;
     static thread_local int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(sgring::sg_ring_fwd_kernel<D>,
+        cudaError_t e = cudaFuncSetAttribute(sgring::sg_ring_fwd_kernel<D, EXT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, L::ALLOC);
         if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_forward: shared-memory opt-in");
         configured_dev = dev;
     }
     dim3 grid(nblk, p.Hkv, p.B);
     att3::TimedLaunch timed(att3::K_SG_FWD, stream);
-    sgring::sg_ring_fwd_kernel<D><<<grid, sgring::PIPE_THREADS, L::ALLOC, stream>>>(p);
+    sgring::sg_ring_fwd_kernel<D, EXT><<<grid, sgring::PIPE_THREADS, L::ALLOC, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_forward: launch");
     att3::count_launch(0);
@@ -206,6 +214,7 @@ static int run_pack_q(int mode, const void* Q, const void* R, const void* S, con
     p.Vr = static_cast<const __nv_bfloat16*>(Vr);
     p.Vs = static_cast<const __nv_bfloat16*>(Vs);
     p.mask = mask;
+    p.mask_words = t_ext.mask_words;
     if (mode == sgpack::PQ_FWD) {
         p.Y = static_cast<__nv_bfloat16*>(Y); p.m = m; p.l = l;
     } else {
@@ -214,14 +223,15 @@ static int run_pack_q(int mode, const void* Q, const void* R, const void* S, con
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status;
-    const size_t qrows = static_cast<size_t>(B) * Hq * N, krows = static_cast<size_t>(B) * Hkv * N;
+    p.bnhd = t_ext.layout;
+    p.Y_act = mode == sgpack::PQ_FWD ? static_cast<__nv_bfloat16*>(t_ext.Y_act) : nullptr;
     int rc;
-    if ((rc = att3::make_row_tensor_map(&p.tmQ, Q, qrows, D, who, QB))) return rc;
-    if (mode == sgpack::PQ_DQ && (rc = att3::make_row_tensor_map(&p.tmdY, dY, qrows, D, who, QB))) return rc;
-    if ((rc = att3::make_row_tensor_map(&p.tmR, R, krows, D, who, QB))) return rc;
-    if ((rc = att3::make_row_tensor_map(&p.tmVr, Vr, krows, D, who, QB))) return rc;
-    if ((rc = att3::make_row_tensor_map(&p.tmS, S, krows, D, who, QB))) return rc;
-    if ((rc = att3::make_row_tensor_map(&p.tmVs, Vs, krows, D, who, QB))) return rc;
+    if ((rc = att3::make_head_tensor_map(&p.tmQ, Q, B, Hq, N, D, p.bnhd, QB, who))) return rc;
+    if (mode == sgpack::PQ_DQ && (rc = att3::make_head_tensor_map(&p.tmdY, dY, B, Hq, N, D, p.bnhd, QB, who))) return rc;
+    if ((rc = att3::make_head_tensor_map(&p.tmR, R, B, Hkv, N, D, p.bnhd, QB, who))) return rc;
+    if ((rc = att3::make_head_tensor_map(&p.tmVr, Vr, B, Hkv, N, D, p.bnhd, QB, who))) return rc;
+    if ((rc = att3::make_head_tensor_map(&p.tmS, S, B, Hkv, N, D, p.bnhd, QB, who))) return rc;
+    if ((rc = att3::make_head_tensor_map(&p.tmVs, Vs, B, Hkv, N, D, p.bnhd, QB, who))) return rc;
     int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, 16, &p.block_len);
     if (const int forced = g_fwd_block.load()) p.block_len = forced;
     p.block_len = round_up8(p.block_len);
@@ -263,21 +273,24 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
     p.Vr = static_cast<const __nv_bfloat16*>(Vr);
     p.Vs = static_cast<const __nv_bfloat16*>(Vs);
     p.mask = mask;
+    p.mask_words = t_ext.mask_words;
     p.Y = static_cast<__nv_bfloat16*>(Y);
     p.m = m;
     p.l = l;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
+    p.window_s = ext_window_s(window);
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status_ptr();
     if (!p.status) return att3::set_error(ATT3_ERR_CUDA, "att3_sg_forward: status word not resolvable");
+    p.bnhd = t_ext.layout;
+    p.Y_act = static_cast<__nv_bfloat16*>(t_ext.Y_act);
     {   // TMA descriptors for the kernel's row staging (one row per copy)
-        const size_t qrows = static_cast<size_t>(B) * Hq * N, krows = static_cast<size_t>(B) * Hkv * N;
         int rc;
-        if ((rc = att3::make_row_tensor_map(&p.tmQ, Q, qrows, D, "att3_sg_forward"))) return rc;
-        if ((rc = att3::make_row_tensor_map(&p.tmR, R, krows, D, "att3_sg_forward"))) return rc;
-        if ((rc = att3::make_row_tensor_map(&p.tmVr, Vr, krows, D, "att3_sg_forward"))) return rc;
-        if ((rc = att3::make_row_tensor_map(&p.tmS, S, krows, D, "att3_sg_forward"))) return rc;
-        if ((rc = att3::make_row_tensor_map(&p.tmVs, Vs, krows, D, "att3_sg_forward"))) return rc;
+        if ((rc = att3::make_head_tensor_map(&p.tmQ, Q, B, Hq, N, D, p.bnhd, 1, "att3_sg_forward"))) return rc;
+        if ((rc = att3::make_head_tensor_map(&p.tmR, R, B, Hkv, N, D, p.bnhd, 1, "att3_sg_forward"))) return rc;
+        if ((rc = att3::make_head_tensor_map(&p.tmVr, Vr, B, Hkv, N, D, p.bnhd, 1, "att3_sg_forward"))) return rc;
+        if ((rc = att3::make_head_tensor_map(&p.tmS, S, B, Hkv, N, D, p.bnhd, 1, "att3_sg_forward"))) return rc;
+        if ((rc = att3::make_head_tensor_map(&p.tmVs, Vs, B, Hkv, N, D, p.bnhd, 1, "att3_sg_forward"))) return rc;
     }
     int nblk = plan_blocks(B, Hkv, N, q_begin, att3::sm_count(), 1, 16, &p.block_len);
     if (const int forced = g_fwd_block.load()) {
@@ -285,7 +298,10 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
         nblk = (N - q_begin + forced - 1) / forced;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return D == 64 ? launch_ring_fwd<64>(p, nblk, st) : launch_ring_fwd<128>(p, nblk, st);
+    // the lean instantiation unless an extension is in use
+    const bool ext = p.bnhd || p.Y_act || p.mask_words || p.window_s != p.window;
+    if (ext) return D == 64 ? launch_ring_fwd<64, true>(p, nblk, st) : launch_ring_fwd<128, true>(p, nblk, st);
+    return D == 64 ? launch_ring_fwd<64, false>(p, nblk, st) : launch_ring_fwd<128, false>(p, nblk, st);
 }
 
 // ---------------------------------------------------------------------------
@@ -303,31 +319,40 @@ extern "C" size_t att3_sg_backward_workspace_bytes(int B, int Hq, int Hkv, int N
            static_cast<size_t>(B) * Hq * N * sizeof(float);
 }
 
-template <int D, bool WITH_DQ>
-static int launch_ring_bwd(const sgring::BwdParams& p, int nblk, cudaStream_t stream) {
+template <int D, bool WITH_DQ, bool EXT>
+static int launch_ring_bwd_x(const sgring::BwdParams& p, int nblk, cudaStream_t stream) {
     using L = sgring::PipeSmem<D, WITH_DQ>;
     static thread_local int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (configured_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(sgring::sg_ring_bwd_kernel<D, WITH_DQ>,
+        cudaError_t e = cudaFuncSetAttribute(sgring::sg_ring_bwd_kernel<D, WITH_DQ, EXT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, L::ALLOC);
         if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: shared-memory opt-in");
         configured_dev = dev;
     }
     dim3 grid(nblk, p.Hkv, p.B);
     att3::TimedLaunch timed(att3::K_SG_BWD, stream);
-    sgring::sg_ring_bwd_kernel<D, WITH_DQ><<<grid, sgring::PIPE_THREADS, L::ALLOC, stream>>>(p);
+    sgring::sg_ring_bwd_kernel<D, WITH_DQ, EXT><<<grid, sgring::PIPE_THREADS, L::ALLOC, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: launch");
     att3::count_launch(1);
     return ATT3_OK;
 }
 
+template <int D, bool WITH_DQ>
+static int launch_ring_bwd(const sgring::BwdParams& p, int nblk, cudaStream_t stream) {
+    // the lean instantiation unless an extension is in use
+    const bool ext = p.bnhd || p.mask_words || p.window_oth != p.window;
+    return ext ? launch_ring_bwd_x<D, WITH_DQ, true>(p, nblk, stream) : launch_ring_bwd_x<D, WITH_DQ, false>(p, nblk, stream);
+}
+
 static int launch_reduce(const sgring::BwdParams& p, int nblk, int D, void* dK, void* dV, cudaStream_t stream,
                          bool f32 = false, int lead = 0) {
     sgring::ReduceParams r;
     r.lead = lead;
+    r.bnhd = t_ext.layout;
+    r.Hkv = p.Hkv;
     r.part_K = p.part_K;
     r.part_V = p.part_V;
     r.dK = f32 ? nullptr : static_cast<__nv_bfloat16*>(dK);
@@ -391,7 +416,8 @@ static int pack_backward(int passes, bool kv_f32, const void* dY, const void* Q,
         const unsigned blocks = static_cast<unsigned>((rows * 32 + threads - 1) / threads);
         att3::TimedLaunch timed(att3::K_SG_REDUCE, st);
         sgpack::sg_delta_kernel<D><<<blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(dY),
-                                                               static_cast<const __nv_bfloat16*>(Y), delta, rows);
+                                                               static_cast<const __nv_bfloat16*>(Y), delta, rows,
+                                                               t_ext.layout, Hq, N);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: delta launch");
         att3::count_launch(1);
@@ -402,6 +428,8 @@ static int pack_backward(int passes, bool kv_f32, const void* dY, const void* Q,
     p.dY = static_cast<const __nv_bfloat16*>(dY);
     p.m = m; p.l = l; p.delta = delta;
     p.mask = mask;
+    p.mask_words = t_ext.mask_words;
+    p.bnhd = t_ext.layout;
     p.part_K = part_K; p.part_V = part_V;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
     p.block_len = block_len; p.planes = planes;
@@ -482,6 +510,8 @@ static int sg_backward_impl(int passes, bool kv_f32, const void* dY, const void*
     p.Y = static_cast<const __nv_bfloat16*>(Y);
     p.m = m; p.l = l;
     p.mask = mask;
+    p.mask_words = t_ext.mask_words;
+    p.bnhd = t_ext.layout;
     p.dQ = static_cast<__nv_bfloat16*>(dQ);
     p.part_K = static_cast<float*>(workspace);
     p.block_len = bwd_block_len(B, Hkv, N);
@@ -497,6 +527,8 @@ static int sg_backward_impl(int passes, bool kv_f32, const void* dY, const void*
     int rc = ATT3_OK;
     if (passes & 1) {
         // Pass 1: own side (S, Vs) -> dS, dVs, and dQ.
+        p.window = ext_window_s(window);
+        p.window_oth = window;
         p.Ka = static_cast<const __nv_bfloat16*>(R);
         p.Va = static_cast<const __nv_bfloat16*>(Vr);
         p.Kb = static_cast<const __nv_bfloat16*>(S);
@@ -507,6 +539,8 @@ static int sg_backward_impl(int passes, bool kv_f32, const void* dY, const void*
     }
     if (!(passes & 2)) return ATT3_OK;
     // Pass 2: sides exchanged -> dR, dVr.
+    p.window = window;
+    p.window_oth = ext_window_s(window);
     p.Ka = static_cast<const __nv_bfloat16*>(S);
     p.Va = static_cast<const __nv_bfloat16*>(Vs);
     p.Kb = static_cast<const __nv_bfloat16*>(R);
@@ -547,6 +581,85 @@ extern "C" int att3_sg_backward_kv32_side(int side, const void* dY, const void* 
         return att3::set_error(ATT3_ERR_INVALID, "att3_sg_backward_kv32_side: side must be 0 (S, Vs, dQ) or 1 (R, Vr)");
     return sg_backward_impl(side == 0 ? 1 : 2, true, dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv,
                             N, D, window, q_begin, workspace, workspace_bytes, stream);
+}
+
+
+// ---------------------------------------------------------------------------
+// Extended calls: asymmetric windows, packed masks
+// ---------------------------------------------------------------------------
+
+static int check_ext(const char* who, const att3_sg_ext* ext, int window, const uint8_t* mask) {
+    if (!ext) return ATT3_OK;
+    if (ext->window_s < 0 || ext->window_s > sgring::RING)
+        return att3::set_error(ATT3_ERR_INVALID, "%s: window_s must be in [0,128], got %d", who, ext->window_s);
+    if ((ext->window_s > 0 || ext->mask_words) && window == 0)
+        return att3::set_error(ATT3_ERR_UNSUPPORTED, "%s: window_s and packed masks need the windowed path (window 1..128)", who);
+    if (ext->mask_words && mask)
+        return att3::set_error(ATT3_ERR_INVALID, "%s: pass the mask either as bytes or as packed words, not both", who);
+    if (ext->mask_words && reinterpret_cast<uintptr_t>(ext->mask_words) % 4 != 0)
+        return att3::set_error(ATT3_ERR_INVALID, "%s: mask_words must be 4-byte aligned", who);
+    if (ext->layout != 0 && ext->layout != 1)
+        return att3::set_error(ATT3_ERR_INVALID, "%s: layout must be 0 ([B,H,N,D]) or 1 ([B,N,H,D]), got %d", who, ext->layout);
+    if ((ext->layout || ext->Y_act) && window == 0)
+        return att3::set_error(ATT3_ERR_UNSUPPORTED, "%s: the [B,N,H,D] layout and the activated output need the windowed path (window 1..128)", who);
+    return ATT3_OK;
+}
+
+struct ExtScope {       // sets the calling thread's extension state for the duration of one call
+    explicit ExtScope(const att3_sg_ext* ext) { if (ext) t_ext = SgExt{ext->window_s, ext->mask_words, ext->layout, ext->Y_act}; }
+    ~ExtScope() { t_ext = SgExt{0, nullptr, 0, nullptr}; }
+};
+
+extern "C" int att3_sg_forward_ext(const void* Q, const void* R, const void* S, const void* Vr, const void* Vs,
+                                   const uint8_t* mask, void* Y, float* m, float* l, int B, int Hq, int Hkv, int N,
+                                   int D, int window, int q_begin, void* stream, const att3_sg_ext* ext) {
+    if (int rc = check_ext("att3_sg_forward_ext", ext, window, mask)) return rc;
+    ExtScope scope(ext);
+    return att3_sg_forward(Q, R, S, Vr, Vs, mask, Y, m, l, B, Hq, Hkv, N, D, window, q_begin, stream);
+}
+
+extern "C" int att3_sg_backward_ext(const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+                                    const void* Vs, const void* Y, const float* m, const float* l,
+                                    const uint8_t* mask, void* dQ, void* dR, void* dS, void* dVr, void* dVs, int B,
+                                    int Hq, int Hkv, int N, int D, int window, int q_begin, void* workspace,
+                                    size_t workspace_bytes, void* stream, const att3_sg_ext* ext) {
+    if (int rc = check_ext("att3_sg_backward_ext", ext, window, mask)) return rc;
+    ExtScope scope(ext);
+    return att3_sg_backward(dY, Q, R, S, Vr, Vs, Y, m, l, mask, dQ, dR, dS, dVr, dVs, B, Hq, Hkv, N, D, window, q_begin,
+                            workspace, workspace_bytes, stream);
+}
+
+// Packs a byte mask into words and counts each query's visible keys inside its causal window, saturated at 2
+// (0 dead, 1 a single key: exact-zero score gradients, 2 anything more): the metadata pass of the reference
+// (att3_mask_metadata::prepare, cuda/shared_kv/shared_mask_metadata.cuh:8-31).  One warp per query row.
+__global__ void pack_mask_kernel(const uint8_t* mask, uint32_t* words, uint8_t* support, int B, int N, int window) {
+    const size_t row = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= static_cast<size_t>(B) * N) return;
+    const int i = static_cast<int>(row % N), NW = (N + 31) / 32;
+    const uint8_t* src = mask + row * N;
+    int count = 0;
+    for (int c = 0; c < NW; ++c) {
+        const int key = c * 32 + lane;
+        bool v = key < N && src[key] != 0;
+        if (window > 0) v = v && key <= i && key > i - window;
+        const uint32_t w = __ballot_sync(0xFFFFFFFFu, v);
+        if (lane == 0) words[row * NW + c] = w;
+        count += __popc(w);
+    }
+    if (support && lane == 0) support[row] = static_cast<uint8_t>(count > 2 ? 2 : count);
+}
+
+extern "C" int att3_sg_pack_mask(const uint8_t* mask, uint32_t* words, uint8_t* support, int B, int N, int window,
+                                 void* stream) {
+    if (!mask || !words || B <= 0 || N <= 0 || window < 0)
+        return att3::set_error(ATT3_ERR_INVALID, "att3_sg_pack_mask: bad argument");
+    const size_t rows = static_cast<size_t>(B) * N;
+    const int threads = 256;
+    pack_mask_kernel<<<static_cast<unsigned>((rows * 32 + threads - 1) / threads), threads, 0,
+                       static_cast<cudaStream_t>(stream)>>>(mask, words, support, B, N, window);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? ATT3_OK : att3::set_cuda_error(e, "att3_sg_pack_mask: launch");
 }
 
 // ---------------------------------------------------------------------------

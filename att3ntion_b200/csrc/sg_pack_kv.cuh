@@ -40,9 +40,11 @@ struct KvParams {
     const __nv_bfloat16* Kb;         // own key side: gradients are produced for these
     const __nv_bfloat16* Vb;
     const uint8_t* mask;             // [B,N,N] or null
+    const uint32_t* mask_words;    // the same mask as packed words [B,N,ceil(N/32)], or null (takes precedence)
     float* part_K;                   // [planes][B,Hkv,N,D] FP32 partials of dKb (plane-major)
     float* part_V;
     int B, Hq, Hkv, N, window, q_begin, block_len, planes;
+    int bnhd;                        // memory layout of Q, dY and the key tensors: 0 [B,H,N,D], 1 [B,N,H,D] (RowAddr)
     float scale;
     int* status;
 };
@@ -73,10 +75,12 @@ struct KvSmem {
 // delta[row] = sum_d dY[row][d] * Y[row][d] in FP32, one warp per row (the reference's delta128,
 // cuda/shared_kv/shared_delta.cuh:9-29).
 template <int D>
-__global__ void sg_delta_kernel(const __nv_bfloat16* dY, const __nv_bfloat16* Y, float* delta, size_t rows) {
-    const size_t row = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+__global__ void sg_delta_kernel(const __nv_bfloat16* dY, const __nv_bfloat16* Y, float* delta, size_t rows, int bnhd,
+                                int H, int N) {
+    const size_t srow = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;    // [B,H,N] index
     const int lane = threadIdx.x & 31;
-    if (row >= rows) return;
+    if (srow >= rows) return;
+    const size_t row = RowAddr{bnhd, H, N, D}.elem(srow) / D;
     float acc = 0.f;
     constexpr int PER_LANE = D / 32;        // 4 (D = 128) or 2 (D = 64) elements
     if (PER_LANE == 4) {
@@ -92,7 +96,7 @@ __global__ void sg_delta_kernel(const __nv_bfloat16* dY, const __nv_bfloat16* Y,
     }
 #pragma unroll
     for (int o = 16; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-    if (lane == 0) delta[row] = acc;
+    if (lane == 0) delta[srow] = acc;
 }
 
 // Copies the accumulator lanes [lane_lo, lane_lo + count) of a warp's quarter (count < 0: all 32) to the FP32
@@ -186,27 +190,44 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
         *sFail = 0;
     }
 
-    const size_t kv_base = (static_cast<size_t>(b) * p.Hkv + g) * p.N;
-    const __nv_bfloat16* gKa = p.Ka + kv_base * D;
-    const __nv_bfloat16* gVa = p.Va + kv_base * D;
-    const __nv_bfloat16* gKb = p.Kb + kv_base * D;
-    const __nv_bfloat16* gVb = p.Vb + kv_base * D;
+    const size_t kv_base = (static_cast<size_t>(b) * p.Hkv + g) * p.N;       // statistics-style row index of key 0
+    const RowAddr kaddr{p.bnhd, p.Hkv, p.N, D};
+    const size_t kstep = kaddr.step();                                       // elements from one key's row to the next
+    const __nv_bfloat16* gKa = p.Ka + kaddr.elem(kv_base);
+    const __nv_bfloat16* gVa = p.Va + kaddr.elem(kv_base);
+    const __nv_bfloat16* gKb = p.Kb + kaddr.elem(kv_base);
+    const __nv_bfloat16* gVb = p.Vb + kaddr.elem(kv_base);
     float* gPartK = p.part_K + (static_cast<size_t>(plane_idx) * p.B * p.Hkv * p.N + kv_base) * D;
     float* gPartV = p.part_V + (static_cast<size_t>(plane_idx) * p.B * p.Hkv * p.N + kv_base) * D;
-    const uint8_t* mask_b = p.mask ? p.mask + static_cast<size_t>(b) * p.N * p.N : nullptr;
+    const MaskView mask_b = mask_view(p.mask, p.mask_words, b, p.N);
     const int n_iter = n_tiles * G;
     auto row_at = [&](int i, int hh) {
         return (static_cast<size_t>(b) * p.Hq + (g * G + hh)) * p.N + i;
     };
+    // Element offset of the row of (position i, head hh of this KV group) in Q, dY, Y, dQ, its tensor-map coordinates,
+    // and the coordinates of a key's row (RowAddr describes the two layouts; here without its divisions).
+    auto qoff_at = [&](int i, int hh) -> size_t {
+        return p.bnhd ? ((static_cast<size_t>(b) * p.N + i) * p.Hq + (g * G + hh)) * D
+                      : ((static_cast<size_t>(b) * p.Hq + (g * G + hh)) * p.N + i) * D;
+    };
+    auto q_tma = [&](int i, int hh, int& x, int& y) {
+        if (p.bnhd) { x = (g * G + hh) * D; y = b * p.N + i; }
+        else { x = 0; y = (b * p.Hq + (g * G + hh)) * p.N + i; }
+    };
+    auto k_tma = [&](int key, int& x, int& y) {
+        if (p.bnhd) { x = g * D; y = b * p.N + key; }
+        else { x = 0; y = static_cast<int>(kv_base) + key; }
+    };
+    const size_t qstep = p.bnhd ? static_cast<size_t>(p.Hq) * D : D;      // elements between consecutive positions of one head
     const float c2 = p.scale * LOG2E;
 
     auto tile_has_work = [&](int i0) {
-        if (!mask_b) return true;
+        if (!mask_b.any()) return true;
         uint32_t any = 0;
 #pragma unroll 1
         for (int gg = 0; gg < QBN; ++gg) {
             uint32_t vw[4];
-            column_visibility(mask_b + static_cast<size_t>(i0 + gg) * p.N, i0 + gg, i0 + QBN - 1, p.window, lane, vw);
+            column_visibility(mask_b.row(i0 + gg), i0 + gg, i0 + QBN - 1, p.window, lane, vw);
             any |= vw[0] | vw[1] | vw[2] | vw[3];
         }
         return any != 0;
@@ -242,12 +263,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
             for (int c = 0; c < CH; ++c) {
                 uint4 kb = z, vb = z, a = z, v = z;
                 if (okey >= 0) {
-                    kb = __ldg(reinterpret_cast<const uint4*>(gKb + static_cast<size_t>(okey) * D) + c);
-                    vb = __ldg(reinterpret_cast<const uint4*>(gVb + static_cast<size_t>(okey) * D) + c);
+                    kb = __ldg(reinterpret_cast<const uint4*>(gKb + static_cast<size_t>(okey) * kstep) + c);
+                    vb = __ldg(reinterpret_cast<const uint4*>(gVb + static_cast<size_t>(okey) * kstep) + c);
                 }
                 if (kcur >= 0) {
-                    a = __ldg(reinterpret_cast<const uint4*>(gKa + static_cast<size_t>(kcur) * D) + c);
-                    v = __ldg(reinterpret_cast<const uint4*>(gVa + static_cast<size_t>(kcur) * D) + c);
+                    a = __ldg(reinterpret_cast<const uint4*>(gKa + static_cast<size_t>(kcur) * kstep) + c);
+                    v = __ldg(reinterpret_cast<const uint4*>(gVa + static_cast<size_t>(kcur) * kstep) + c);
                 }
                 *reinterpret_cast<uint4*>(sKb + sw128_offset<RING>(hslot, c)) = kb;
                 *reinterpret_cast<uint4*>(sVb + sw128_offset<RING>(hslot, c)) = vb;
@@ -258,19 +279,20 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
                 const int plane = x / (QBN * CH), rem = x % (QBN * CH), kr = rem / CH, c = rem % CH;
                 const __nv_bfloat16* base = plane == 0 ? gKa : gVa;
                 *reinterpret_cast<uint4*>(next_row(plane, q0 + kr) + c * 16) =
-                    __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + kr) * D) + c);
+                    __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(q0 + kr) * kstep) + c);
             }
         }
         // Asynchronous staging, one commit group per call: the QBN Q and dY rows of iteration `it` and, when
         // next_tile > 0, the four rows of each key that enters with that tile; both are waited for at the next H_sync.
-        auto h_stage = [&](int it, size_t row, int next_tile) {
+        auto h_stage = [&](int it, size_t qoff, int next_tile) {
             if (it >= 0) {
                 for (int x = hslot; x < 2 * QBN * CH; x += PIPE_H_THREADS) {
                     const int which = x / (QBN * CH), rem = x % (QBN * CH);
-                    const __nv_bfloat16* src = (which == 0 ? p.Q : p.dY) + row * D;      // QBN consecutive rows
+                    // the rows of QBN consecutive queries of one head: qstep elements apart
+                    const __nv_bfloat16* src = (which == 0 ? p.Q : p.dY) + qoff + (rem / CH) * qstep;
                     const uint32_t dst = smem_u32(sStage + (it & 1) * L::STAGE_BYTES + which * (QBN * D * 2)) + rem * 16;
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
-                                 "l"(reinterpret_cast<const uint4*>(src) + rem)
+                                 "l"(reinterpret_cast<const uint4*>(src) + rem % CH)
                                  : "memory");
                 }
             }
@@ -281,13 +303,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
                     const __nv_bfloat16* base = plane == 0 ? gKa : plane == 1 ? gVa : plane == 2 ? gKb : gVb;
                     const uint32_t dst = smem_u32(sNext + (next_tile & 1) * L::NEXT_BYTES + plane * (QBN * D * 2)) + rem * 16;
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
-                                 "l"(reinterpret_cast<const uint4*>(base + static_cast<size_t>(key0) * D) + rem)
+                                 "l"(reinterpret_cast<const uint4*>(base + static_cast<size_t>(key0 + rem / CH) * kstep) + rem % CH)
                                  : "memory");
                 }
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        h_stage(0, row_at(q0, 0), -1);
+        h_stage(0, qoff_at(q0, 0), -1);
         fence_async_smem();
         cta_start_sync();
         constexpr int HB = 8;
@@ -323,7 +345,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
                 // The keys of tile t+1 go to the buffer tile t-1 used, which the other H warps may still be reading
                 // at this tile's first head: they are requested at its second head (behind another H_sync).
                 if (it + 1 < n_iter)
-                    h_stage(it + 1, hh + 1 == G ? row_at(i0 + QBN, 0) : row_at(i0, hh + 1),
+                    h_stage(it + 1, hh + 1 == G ? qoff_at(i0 + QBN, 0) : qoff_at(i0, hh + 1),
                             (hh == 1 && t + 1 < n_tiles) ? t + 1 : -1);
                 const int qb = n & 1, gb = n & 1;
                 uint8_t* dQp = sQp + qb * L::TILE;
@@ -604,7 +626,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
             for (int q = 0; q < NG; ++q) {
                 const int i = i0 + ch * NG + q;
                 uint32_t vw[4];
-                column_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, i_last, p.window, lane, vw);
+                column_visibility(mask_b.row(i), i, i_last, p.window, lane, vw);
                 const int nv = __popc(vw[0]) + __popc(vw[1]) + __popc(vw[2]) + __popc(vw[3]);
                 if (nv > 0) live_vis |= 1u << q;
                 if (nv == 1) single |= 1u << q;
@@ -621,7 +643,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
                     colw[cc] |= __ballot_sync(0xFFFFFFFFu, v);
                 }
             }
-            if (mask_b) {
+            if (mask_b.any()) {
                 any_work = tile_has_work(i0);
             } else {
                 any_work = true;

@@ -54,6 +54,7 @@ struct QParams {
     const __nv_bfloat16* Vr;
     const __nv_bfloat16* Vs;
     const uint8_t* mask;           // [B,N,N] or null
+    const uint32_t* mask_words;    // the same mask as packed words [B,N,ceil(N/32)], or null (takes precedence)
     // PQ_FWD outputs
     __nv_bfloat16* Y;              // [B,Hq,N,D]
     float* m;                      // [B,Hq,N]
@@ -64,6 +65,8 @@ struct QParams {
     const float* delta;            // [B,Hq,N]  rowsum(dY o Y)
     __nv_bfloat16* dQ;             // [B,Hq,N,D]
     int B, Hq, Hkv, N, window, q_begin, block_len;
+    int bnhd;                      // memory layout of the [B,H,N,D] operands: 0 as written, 1 [B,N,H,D] (RowAddr)
+    __nv_bfloat16* Y_act;          // PQ_FWD: optional second output QuickGELU(Y), laid out like Y; or null
     float scale;
     int* status;
     // TMA descriptors with boxes of QB rows: Q (and dY) viewed as [B*Hq*N, D], R, Vr, S, Vs as [B*Hkv*N, D]
@@ -121,13 +124,13 @@ __device__ __forceinline__ void halfwarp_transpose_sum_2x16(float (&va)[16], flo
 
 // Visibility of the 128 column slots for query i (window and optional mask row), as four ballot words;
 // every lane of the calling warp gets the same words.  i_last names the ring position (the tile's last query).
-__device__ __forceinline__ void column_visibility(const uint8_t* mask_row, int i, int i_last, int window, int lane,
+__device__ __forceinline__ void column_visibility(const MaskRow mask_row, int i, int i_last, int window, int lane,
                                                   uint32_t (&vw)[4]) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         const int key = ring_key(i_last, q * 32 + lane);
         bool v = key >= 0 && key <= i && key > i - window;
-        if (v && mask_row) v = mask_row[key] != 0;
+        if (v && mask_row.any()) v = mask_row.at(key);
         vw[q] = __ballot_sync(0xFFFFFFFFu, v);
     }
 }
@@ -195,27 +198,44 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
         *sFail = 0;
     }
 
-    const size_t kv_base = (static_cast<size_t>(b) * p.Hkv + g) * p.N;
-    const __nv_bfloat16* gR = p.R + kv_base * D;
-    const __nv_bfloat16* gS = p.S + kv_base * D;
-    const __nv_bfloat16* gVr = p.Vr + kv_base * D;
-    const __nv_bfloat16* gVs = p.Vs + kv_base * D;
-    const uint8_t* mask_b = p.mask ? p.mask + static_cast<size_t>(b) * p.N * p.N : nullptr;
+    const size_t kv_base = (static_cast<size_t>(b) * p.Hkv + g) * p.N;       // statistics-style row index of key 0
+    const RowAddr kaddr{p.bnhd, p.Hkv, p.N, D};
+    const size_t kstep = kaddr.step();                                       // elements from one key's row to the next
+    const __nv_bfloat16* gR = p.R + kaddr.elem(kv_base);
+    const __nv_bfloat16* gS = p.S + kaddr.elem(kv_base);
+    const __nv_bfloat16* gVr = p.Vr + kaddr.elem(kv_base);
+    const __nv_bfloat16* gVs = p.Vs + kaddr.elem(kv_base);
+    const MaskView mask_b = mask_view(p.mask, p.mask_words, b, p.N);
     const int n_iter = n_tiles * G;
     auto row_at = [&](int i, int hh) {
         return (static_cast<size_t>(b) * p.Hq + (g * G + hh)) * p.N + i;
     };
+    // Element offset of the row of (position i, head hh of this KV group) in Q, dY, Y, dQ, its tensor-map coordinates,
+    // and the coordinates of a key's row (RowAddr describes the two layouts; here without its divisions).
+    auto qoff_at = [&](int i, int hh) -> size_t {
+        return p.bnhd ? ((static_cast<size_t>(b) * p.N + i) * p.Hq + (g * G + hh)) * D
+                      : ((static_cast<size_t>(b) * p.Hq + (g * G + hh)) * p.N + i) * D;
+    };
+    auto q_tma = [&](int i, int hh, int& x, int& y) {
+        if (p.bnhd) { x = (g * G + hh) * D; y = b * p.N + i; }
+        else { x = 0; y = (b * p.Hq + (g * G + hh)) * p.N + i; }
+    };
+    auto k_tma = [&](int key, int& x, int& y) {
+        if (p.bnhd) { x = g * D; y = b * p.N + key; }
+        else { x = 0; y = static_cast<int>(kv_base) + key; }
+    };
+    const size_t qstep = p.bnhd ? static_cast<size_t>(p.Hq) * D : D;      // elements between consecutive positions of one head
     const float c2 = p.scale * LOG2E;
 
     // True when any query of the tile that starts at i0 has a visible pair.  Without a caller mask every
     // query sees at least itself.
     auto tile_has_work = [&](int i0) {
-        if (!mask_b) return true;
+        if (!mask_b.any()) return true;
         uint32_t any = 0;
 #pragma unroll 1
         for (int gg = 0; gg < QBN; ++gg) {
             uint32_t vw[4];
-            column_visibility(mask_b + static_cast<size_t>(i0 + gg) * p.N, i0 + gg, i0 + QBN - 1, p.window, lane, vw);
+            column_visibility(mask_b.row(i0 + gg), i0 + gg, i0 + QBN - 1, p.window, lane, vw);
             any |= vw[0] | vw[1] | vw[2] | vw[3];
         }
         return any != 0;
@@ -246,12 +266,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
             for (int c = 0; c < CH; ++c) {
                 uint4 s = z, vs = z, r = z, vr = z;
                 if (ckey >= 0) {
-                    s = __ldg(reinterpret_cast<const uint4*>(gS + static_cast<size_t>(ckey) * D) + c);
-                    vs = __ldg(reinterpret_cast<const uint4*>(gVs + static_cast<size_t>(ckey) * D) + c);
+                    s = __ldg(reinterpret_cast<const uint4*>(gS + static_cast<size_t>(ckey) * kstep) + c);
+                    vs = __ldg(reinterpret_cast<const uint4*>(gVs + static_cast<size_t>(ckey) * kstep) + c);
                 }
                 if (kcur >= 0) {
-                    r = __ldg(reinterpret_cast<const uint4*>(gR + static_cast<size_t>(kcur) * D) + c);
-                    if (DQ) vr = __ldg(reinterpret_cast<const uint4*>(gVr + static_cast<size_t>(kcur) * D) + c);
+                    r = __ldg(reinterpret_cast<const uint4*>(gR + static_cast<size_t>(kcur) * kstep) + c);
+                    if (DQ) vr = __ldg(reinterpret_cast<const uint4*>(gVr + static_cast<size_t>(kcur) * kstep) + c);
                 }
                 *reinterpret_cast<uint4*>(sS + sw128_offset<RING>(hslot, c)) = s;
                 *reinterpret_cast<uint4*>(sVs + sw128_offset<RING>(hslot, c)) = vs;
@@ -263,34 +283,37 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                 const __nv_bfloat16* base = plane == 0 ? gR : plane == 1 ? gVr : plane == 2 ? gS : gVs;
                 const int key = q0 + kr;
                 *reinterpret_cast<uint4*>(key_row(plane, key) + c * 16) =
-                    __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(key) * D) + c);
+                    __ldg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(key) * kstep) + c);
             }
         }
         // Row staging by TMA, issued by one thread: the QB query rows (Q, and dY in the dQ mode) of iteration
         // `it`, and, when next_tile > 0, the rows of the QB keys that enter with that tile.
-        auto h_stage = [&](int it, size_t row, int next_tile) {
+        auto h_stage = [&](int it, int qi, int qh, int next_tile) {
             if (hslot != 0) return;
             if (it >= 0) {
                 uint64_t* bar = &bars[QB_STAGE0 + (it & 1)];
                 uint8_t* dst = sStage + (it & 1) * L::STAGE_BYTES;
                 mbar_arrive_expect_tx(bar, L::STAGE_BYTES);
-                tma_load_2d(dst, &p.tmQ, 0, static_cast<int>(row), bar);
-                if (DQ) tma_load_2d(dst + QBN * D * 2, &p.tmdY, 0, static_cast<int>(row), bar);
+                int x, y;
+                q_tma(qi, qh, x, y);
+                tma_load_2d(dst, &p.tmQ, x, y, bar);
+                if (DQ) tma_load_2d(dst + QBN * D * 2, &p.tmdY, x, y, bar);
             }
             if (next_tile > 0) {
                 uint64_t* bar = &bars[QB_NEXT_READY0 + ((next_tile - 1) & (KEY_TILES - 1))];     // tile 0 has no staged keys
                 const int key = q0 + next_tile * QBN;
-                const int krow = static_cast<int>(kv_base) + key;
+                int kx, krow;
+                k_tma(key, kx, krow);
                 mbar_arrive_expect_tx(bar, 4 * QBN * D * 2);
-                tma_load_2d(key_row(0, key), &p.tmR, 0, krow, bar);
-                tma_load_2d(key_row(1, key), &p.tmVr, 0, krow, bar);
-                tma_load_2d(key_row(2, key), &p.tmS, 0, krow, bar);
-                tma_load_2d(key_row(3, key), &p.tmVs, 0, krow, bar);
+                tma_load_2d(key_row(0, key), &p.tmR, kx, krow, bar);
+                tma_load_2d(key_row(1, key), &p.tmVr, kx, krow, bar);
+                tma_load_2d(key_row(2, key), &p.tmS, kx, krow, bar);
+                tma_load_2d(key_row(3, key), &p.tmVs, kx, krow, bar);
             }
         };
         fence_async_smem();
         cta_start_sync();
-        h_stage(0, row_at(q0, 0), -1);
+        h_stage(0, q0, 0, -1);
         constexpr int HB = 8;                 // staged chunks in flight per thread
         int n = 0, it = 0;
         bool ok = true;
@@ -328,7 +351,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                 }
                 if (it + 1 < n_iter) {
                     const bool last_head = hh + 1 == G;
-                    h_stage(it + 1, last_head ? row_at(i0 + QBN, 0) : row_at(i0, hh + 1),
+                    h_stage(it + 1, last_head ? i0 + QBN : i0, last_head ? 0 : hh + 1,
                             (hh == 0 && t + 1 < n_tiles) ? t + 1 : -1);
                 }
                 const int qb = n & 1;
@@ -504,7 +527,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
         int kcur = ring_key_w<W>(q0 + eg, ejs);
         {
             if (kcur >= 0) {
-                const uint4* v4 = reinterpret_cast<const uint4*>(gRow + static_cast<size_t>(kcur) * D + ch * HD);
+                const uint4* v4 = reinterpret_cast<const uint4*>(gRow + static_cast<size_t>(kcur) * kstep + ch * HD);
 #pragma unroll
                 for (int c = 0; c < VW / 4; ++c) {
                     const uint4 v = __ldg(v4 + c);
@@ -519,7 +542,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
         // row group and write the QB output rows (and statistics) of head fin_m.
         bool fin_pending = false;
         int fin_m = 0;
-        size_t fin_row = 0;          // output row of the tile's first query
+        size_t fin_row = 0, fin_off = 0;   // statistics row and element offset of the tile's first query
         auto finish = [&]() {
             if (!fin_pending) return true;
             fin_pending = false;
@@ -540,11 +563,14 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                 const float* r0 = red + (gg * UPG) * (D + 4);
                 const bool live = r0[D + 3] != 0.f && (DQ || Lsum > 0.f);
                 const size_t row = fin_row + gg;
+                const size_t at = fin_off + gg * qstep + d;
                 if (DQ) {
-                    p.dQ[row * D + d] = __float2bfloat16(live ? p.scale * y : 0.f);
+                    p.dQ[at] = __float2bfloat16(live ? p.scale * y : 0.f);
                 } else {
                     // a query without a visible pair: Y = 0, m = NEG_INF, l = 0 (cuda/common.cuh:24)
-                    p.Y[row * D + d] = __float2bfloat16(live ? y / Lsum : 0.f);
+                    const float yv = live ? y / Lsum : 0.f;
+                    p.Y[at] = __float2bfloat16(yv);
+                    if (p.Y_act) p.Y_act[at] = __float2bfloat16(yv / (1.f + __expf(-1.702f * yv)));
                     if (d == 0) {
                         p.m[row] = live ? r0[D + 2] * p.scale : NEG_INF_F;
                         p.l[row] = live ? Lsum : 0.f;
@@ -554,7 +580,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
             return true;
         };
         // Epilogue of head m, one head late:  out[g][d] = sum_{rows of group g} rowop[d] * U[row][d].
-        auto epilogue = [&](int m, size_t row0, bool live, float M, float l_half) {
+        auto epilogue = [&](int m, size_t row0, size_t off0, bool live, float M, float l_half) {
             const int ub = m & 1;
             if (!finish()) return false;
             bool r = pipe_wait<true>(&bars[QB_U_DONE0 + ub], (m >> 1) & 1, sFail, 32);
@@ -616,7 +642,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                 }
             }
             warp_arrive(&bars[QB_E_SYNC], lane);
-            fin_pending = true; fin_m = m; fin_row = row0;
+            fin_pending = true; fin_m = m; fin_row = row0; fin_off = off0;
             return true;
         };
         // Tile t takes over: QB keys enter the column ring (forward: the Vs ring rows are this role's to
@@ -646,7 +672,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
         int n = 0;
         bool ok = true, pend = false, pend_live = false;
         int pend_n = 0;
-        size_t pend_row = 0;
+        size_t pend_row = 0, pend_off = 0;
         float pend_M = 0.f, pend_l = 0.f;
         // dQ mode: the forward statistics and delta of this thread's query for the next head, fetched a head ahead
         float pre_m = 0.f, pre_l = 0.f, pre_d = 0.f;
@@ -663,7 +689,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
 #pragma unroll 1
             for (int gg = 0; gg < QBN; ++gg) {
                 uint32_t w4[4];
-                column_visibility(mask_b ? mask_b + static_cast<size_t>(i0 + gg) * p.N : nullptr, i0 + gg, i_last,
+                column_visibility(mask_b.row(i0 + gg), i0 + gg, i_last,
                                   p.window, lane, w4);
                 if ((w4[0] | w4[1] | w4[2] | w4[3]) != 0) live_vis |= 1u << gg;
                 if (gg == eg) { vw[0] = w4[0]; vw[1] = w4[1]; vw[2] = w4[2]; vw[3] = w4[3]; }
@@ -683,15 +709,17 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                     else if (t + 1 < n_tiles) prefetch(row_at(i0 + QBN + eg, 0));
                 }
                 if (!work) {
-                    if (pend) { ok = epilogue(pend_n, pend_row, pend_live, pend_M, pend_l); pend = false; }
+                    if (pend) { ok = epilogue(pend_n, pend_row, pend_off, pend_live, pend_M, pend_l); pend = false; }
                     if (!ok) break;
                     if (boundary) ok = ring_update(t);
                     if (!ok) break;
                     for (int idx = tid; idx < QBN * D; idx += PIPE_E_THREADS) {
                         const size_t row = row0 + idx / D;
-                        if (DQ) p.dQ[row * D + idx % D] = __float2bfloat16(0.f);
+                        const size_t at = qoff_at(i0 + idx / D, hh) + idx % D;
+                        if (DQ) p.dQ[at] = __float2bfloat16(0.f);
                         else {
-                            p.Y[row * D + idx % D] = __float2bfloat16(0.f);
+                            p.Y[at] = __float2bfloat16(0.f);
+                            if (p.Y_act) p.Y_act[at] = __float2bfloat16(0.f);
                             if (idx % D == 0) { p.m[row] = NEG_INF_F; p.l[row] = 0.f; }
                         }
                     }
@@ -734,7 +762,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                     }
                     warp_arrive(&bars[QB_M_SYNC], lane);
                     // ---- epilogue of the previous head, behind its U product; then the rows of the entering keys
-                    if (pend) { ok = epilogue(pend_n, pend_row, pend_live, pend_M, pend_l); pend = false; }
+                    if (pend) { ok = epilogue(pend_n, pend_row, pend_off, pend_live, pend_M, pend_l); pend = false; }
                     if (ok && boundary) ok = ring_update(t);
                     if (!ok) break;
                     ok = pipe_wait<true>(&bars[QB_M_SYNC], n & 1, sFail, 31);
@@ -775,7 +803,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                     tc_fence_before();
                     // P_full also tells the MMA warp that the Vs ring rows are current (ring_update above)
                     warp_arrive(&bars[QB_P_FULL0 + xb], lane);
-                    pend = true; pend_n = n; pend_row = row0; pend_live = live_g; pend_M = M;
+                    pend = true; pend_n = n; pend_row = row0; pend_off = qoff_at(i0, hh); pend_live = live_g; pend_M = M;
                     pend_l = (ls[0] + ls[1]) + (ls[2] + ls[3]);
                 } else {
                     // ---- gA = P o (dP - delta), P = exp2(x c2 - lse) from the forward's statistics; BF16 over the
@@ -813,15 +841,15 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                     tc_fence_before();
                     warp_arrive(&bars[QB_P_FULL0 + xb], lane);
                     // ---- collapse of the previous head's Ug, then this tile's row registers
-                    if (pend) { ok = epilogue(pend_n, pend_row, pend_live, pend_M, pend_l); pend = false; }
+                    if (pend) { ok = epilogue(pend_n, pend_row, pend_off, pend_live, pend_M, pend_l); pend = false; }
                     if (ok && boundary) ok = ring_update(t);
                     if (!ok) break;
-                    pend = true; pend_n = n; pend_row = row0; pend_live = live_q; pend_M = 0.f; pend_l = 0.f;
+                    pend = true; pend_n = n; pend_row = row0; pend_off = qoff_at(i0, hh); pend_live = live_q; pend_M = 0.f; pend_l = 0.f;
                 }
                 ++n;
             }
         }
-        if (ok && pend) ok = epilogue(pend_n, pend_row, pend_live, pend_M, pend_l);
+        if (ok && pend) ok = epilogue(pend_n, pend_row, pend_off, pend_live, pend_M, pend_l);
         if (ok) ok = finish();
     }
     tc_fence_before();

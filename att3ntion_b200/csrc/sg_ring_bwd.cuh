@@ -85,10 +85,13 @@ struct BwdParams {
     const __nv_bfloat16* Kb;         // own key side: gradients are produced for these
     const __nv_bfloat16* Vb;
     const uint8_t* mask;             // [B,N,N] or null
+    const uint32_t* mask_words;    // the same mask as packed words [B,N,ceil(N/32)], or null (takes precedence)
     __nv_bfloat16* dQ;               // [B,Hq,N,D], written only by the WITH_DQ instantiation
     float* part_K;                   // [planes][B,Hkv,N,D] FP32 partials of dKb (plane-major)
     float* part_V;                   // [planes][B,Hkv,N,D] FP32 partials of dVb
     int B, Hq, Hkv, N, window, q_begin, block_len, planes;
+    int bnhd;                        // memory layout of Q, dY, Y, dQ and the key tensors: 0 [B,H,N,D], 1 [B,N,H,D] (RowAddr)
+    int window_oth;                  // window on the other side's key axis (`window` is the own side's); equal unless asymmetric
     float scale;
     int* status;
 };
@@ -160,8 +163,13 @@ __device__ __noinline__ void flush_acc_lanes(uint32_t tl, int lane, int only_lan
     }
 }
 
-template <int D, bool WITH_DQ>
+// EXT = false compiles the plain call (layout [B,H,N,D], one window, byte mask) with the extension fields folded
+// to constants: the role loops are sensitive to every live register, and the plain call is the common one.
+template <int D, bool WITH_DQ, bool EXT = false>
 __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdParams p) {
+    const int x_bnhd = EXT ? p.bnhd : 0;
+    const int x_window_oth = EXT ? p.window_oth : p.window;
+    const uint32_t* const x_mask_words = EXT ? p.mask_words : nullptr;
     using L = PipeSmem<D, WITH_DQ>;
     constexpr int CH = D / 8;            // 16-byte chunks per row
     constexpr int DW = D / 2;            // packed words per row
@@ -213,14 +221,16 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         *sFail = 0;
     }
 
-    const size_t kv_base = (static_cast<size_t>(b) * p.Hkv + g) * p.N;
-    const __nv_bfloat16* gKa = p.Ka + kv_base * D;
-    const __nv_bfloat16* gVa = p.Va + kv_base * D;
-    const __nv_bfloat16* gKb = p.Kb + kv_base * D;
-    const __nv_bfloat16* gVb = p.Vb + kv_base * D;
+    const size_t kv_base = (static_cast<size_t>(b) * p.Hkv + g) * p.N;       // statistics-style row index of key 0
+    const RowAddr kaddr{x_bnhd, p.Hkv, p.N, D};
+    const size_t kstep = kaddr.step();                                       // elements from one key's row to the next
+    const __nv_bfloat16* gKa = p.Ka + kaddr.elem(kv_base);
+    const __nv_bfloat16* gVa = p.Va + kaddr.elem(kv_base);
+    const __nv_bfloat16* gKb = p.Kb + kaddr.elem(kv_base);
+    const __nv_bfloat16* gVb = p.Vb + kaddr.elem(kv_base);
     float* gPartK = p.part_K + (static_cast<size_t>(parity_buf) * p.B * p.Hkv * p.N + kv_base) * D;
     float* gPartV = p.part_V + (static_cast<size_t>(parity_buf) * p.B * p.Hkv * p.N + kv_base) * D;
-    const uint8_t* mask_b = p.mask ? p.mask + static_cast<size_t>(b) * p.N * p.N : nullptr;
+    const MaskView mask_b = mask_view(p.mask, x_mask_words, b, p.N);
 
     const int n_iter = (q1 - q0) * G;
     // Row of (query i, head hh of this KV group) in the [B,Hq,N] arrays; the successor of (i, hh) in
@@ -229,6 +239,22 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         return (static_cast<size_t>(b) * p.Hq + (g * G + hh)) * p.N + i;
     };
     auto next_row = [&](int i, int hh) { return hh + 1 < G ? row_at(i, hh + 1) : row_at(i + 1, 0); };
+    // Element offset of the row of (position i, head hh of this KV group) in Q, dY, Y, dQ, its tensor-map coordinates,
+    // and the coordinates of a key's row (RowAddr describes the two layouts; here without its divisions).
+    auto qoff_at = [&](int i, int hh) -> size_t {
+        return x_bnhd ? ((static_cast<size_t>(b) * p.N + i) * p.Hq + (g * G + hh)) * D
+                      : ((static_cast<size_t>(b) * p.Hq + (g * G + hh)) * p.N + i) * D;
+    };
+    auto q_tma = [&](int i, int hh, int& x, int& y) {
+        if (x_bnhd) { x = (g * G + hh) * D; y = b * p.N + i; }
+        else { x = 0; y = (b * p.Hq + (g * G + hh)) * p.N + i; }
+    };
+    auto k_tma = [&](int key, int& x, int& y) {
+        if (x_bnhd) { x = g * D; y = b * p.N + key; }
+        else { x = 0; y = static_cast<int>(kv_base) + key; }
+    };
+    const size_t qstep = x_bnhd ? static_cast<size_t>(p.Hq) * D : D;      // elements between consecutive positions of one head
+    auto next_qoff = [&](int i, int hh) { return hh + 1 < G ? qoff_at(i, hh + 1) : qoff_at(i + 1, 0); };
     const float c2 = p.scale * LOG2E;
 
     // Each role first sets its register budget (the CTA starts at 128 per thread: the E warps work in
@@ -254,10 +280,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         {   // initial fill of this thread's ring slot: registers (other side) and operand tiles (own side)
             const int key = ring_key(q0, hslot);
             if (key >= 0) {
-                const uint4* ka4 = reinterpret_cast<const uint4*>(gKa + static_cast<size_t>(key) * D);
-                const uint4* va4 = reinterpret_cast<const uint4*>(gVa + static_cast<size_t>(key) * D);
-                const uint4* kb4 = reinterpret_cast<const uint4*>(gKb + static_cast<size_t>(key) * D);
-                const uint4* vb4 = reinterpret_cast<const uint4*>(gVb + static_cast<size_t>(key) * D);
+                const uint4* ka4 = reinterpret_cast<const uint4*>(gKa + static_cast<size_t>(key) * kstep);
+                const uint4* va4 = reinterpret_cast<const uint4*>(gVa + static_cast<size_t>(key) * kstep);
+                const uint4* kb4 = reinterpret_cast<const uint4*>(gKb + static_cast<size_t>(key) * kstep);
+                const uint4* vb4 = reinterpret_cast<const uint4*>(gVb + static_cast<size_t>(key) * kstep);
 #pragma unroll
                 for (int c = 0; c < CH; ++c) {
                     const uint4 a = __ldg(ka4 + c), v = __ldg(va4 + c);
@@ -282,10 +308,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         // Asynchronous staging, one commit group per call: the Q and dY rows of iteration `it`
         // (threads [0, 2*CH)) and, when next_key >= 0, the four rows of the key that enters the
         // ring with query next_key (threads [0, 4*CH)); both are waited for at the next H_sync.
-        auto h_stage = [&](int it, size_t row, int next_key) {
+        auto h_stage = [&](int it, size_t qoff, int next_key) {
             if (it >= 0 && hslot < 2 * CH) {
                 const int which = hslot / CH, c = hslot % CH;
-                const __nv_bfloat16* src = (which == 0 ? p.Q : p.dY) + row * D;
+                const __nv_bfloat16* src = (which == 0 ? p.Q : p.dY) + qoff;
                 const uint32_t dst = smem_u32(sStage + ((it & 1) * 2 + which) * D) + c * 16;
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
                              "l"(reinterpret_cast<const uint4*>(src) + c)
@@ -296,12 +322,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 const __nv_bfloat16* base = which == 0 ? gKa : which == 1 ? gVa : which == 2 ? gKb : gVb;
                 const uint32_t dst = smem_u32(sNext + (next_key & 1) * L::NEXT_BYTES + which * (D * 2)) + c * 16;
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
-                             "l"(reinterpret_cast<const uint4*>(base + static_cast<size_t>(next_key) * D) + c)
+                             "l"(reinterpret_cast<const uint4*>(base + static_cast<size_t>(next_key) * kstep) + c)
                              : "memory");
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        h_stage(0, row_at(q0, 0), -1);
+        h_stage(0, qoff_at(q0, 0), -1);
         fence_async_smem();
         cta_start_sync();
         constexpr int GB = L::G_BUFS;
@@ -315,7 +341,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             n_query = n;
             const int s = i & (RING - 1);
             uint32_t vw[4];
-            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
+            ring_visibility(mask_b.row(i), i, min(p.window, x_window_oth), lane, vw);    // a pair needs a key on both axes
             const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
 #pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
@@ -338,7 +364,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                         rVa[4 * c] = v.x; rVa[4 * c + 1] = v.y; rVa[4 * c + 2] = v.z; rVa[4 * c + 3] = v.w;
                     }
                 }
-                if (it + 1 < n_iter) h_stage(it + 1, next_row(i, hh), (hh == 0 && i + 1 < q1) ? i + 1 : -1);
+                if (it + 1 < n_iter) h_stage(it + 1, next_qoff(i, hh), (hh == 0 && i + 1 < q1) ? i + 1 : -1);
                 const bool work = any_vis && l_i > 0.f;
                 const int qb = n & 1, gb = n % GB;
                 uint8_t* dQp = sQp + qb * L::TILE;
@@ -552,7 +578,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 else commit_acc();
             }
             uint32_t vw[4];
-            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
+            ring_visibility(mask_b.row(i), i, min(p.window, x_window_oth), lane, vw);    // a pair needs a key on both axes
             const bool any_vis = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
             bool ring_committed = false;
 #pragma unroll 1
@@ -656,31 +682,36 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         uint2 pre_dy = make_uint2(0, 0), pre_y = make_uint2(0, 0);
         uint32_t pre_dy2[2] = {0, 0}, pre_y2[2] = {0, 0};
         float pre_m = 0.f, pre_l = 0.f;
-        auto prefetch = [&](size_t row) {
+        auto prefetch = [&](size_t row, size_t qoff) {
             if (D == 128) {
-                pre_dy = __ldg(reinterpret_cast<const uint2*>(p.dY + row * D) + lane);
-                pre_y = __ldg(reinterpret_cast<const uint2*>(p.Y + row * D) + lane);
+                pre_dy = __ldg(reinterpret_cast<const uint2*>(p.dY + qoff) + lane);
+                pre_y = __ldg(reinterpret_cast<const uint2*>(p.Y + qoff) + lane);
             } else {
-                pre_dy2[0] = __ldg(reinterpret_cast<const uint32_t*>(p.dY + row * D) + lane);
-                pre_y2[0] = __ldg(reinterpret_cast<const uint32_t*>(p.Y + row * D) + lane);
+                pre_dy2[0] = __ldg(reinterpret_cast<const uint32_t*>(p.dY + qoff) + lane);
+                pre_y2[0] = __ldg(reinterpret_cast<const uint32_t*>(p.Y + qoff) + lane);
             }
             pre_m = __ldg(p.m + row);
             pre_l = __ldg(p.l + row);
         };
-        prefetch(row_at(q0, 0));
+        prefetch(row_at(q0, 0), qoff_at(q0, 0));
         int n = 0, it = 0, n_query = 0;
         bool ok = true;
 #pragma unroll 1
         for (int i = q0; i < q1 && ok; ++i) {
-            uint32_t vw[4];
-            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
-            const int n_vis = __popc(vw[0]) + __popc(vw[1]) + __popc(vw[2]) + __popc(vw[3]);
-            const bool all_vis = n_vis == RING;
-            const bool single = n_vis == 1;
+            // lanes of the score tile are own-side keys (window), columns other-side keys (window_oth)
+            uint32_t vw[4], vo[4];
+            ring_visibility(mask_b.row(i), i, p.window, lane, vw);
+            if (x_window_oth != p.window) ring_visibility(mask_b.row(i), i, x_window_oth, lane, vo);
+            else { vo[0] = vw[0]; vo[1] = vw[1]; vo[2] = vw[2]; vo[3] = vw[3]; }
+            const int n_own = __popc(vw[0]) + __popc(vw[1]) + __popc(vw[2]) + __popc(vw[3]);
+            const int n_oth = __popc(vo[0]) + __popc(vo[1]) + __popc(vo[2]) + __popc(vo[3]);
+            const int n_vis = min(n_own, n_oth);                 // 0: no visible pair
+            const bool all_vis = n_own == RING && n_oth == RING;
+            const bool single = n_own * n_oth == 1;              // one visible pair: exact zero score gradients
             const bool my_vis = (vw[warp & 3] >> lane) & 1u;
             // visibility words of this thread's two 32-column chunks
-            const uint32_t cw0 = my_vis ? (ch ? vw[2] : vw[0]) : 0u;
-            const uint32_t cw1 = my_vis ? (ch ? vw[3] : vw[1]) : 0u;
+            const uint32_t cw0 = my_vis ? (ch ? vo[2] : vo[0]) : 0u;
+            const uint32_t cw1 = my_vis ? (ch ? vo[3] : vo[1]) : 0u;
             bool ring_arrived = false;
 #pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
@@ -698,9 +729,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
 #pragma unroll
                 for (int o = 16; o >= 1; o >>= 1) delta += __shfl_xor_sync(0xFFFFFFFFu, delta, o);
                 const float m_i = pre_m, l_i = pre_l;
-                if (it + 1 < n_iter) prefetch(next_row(i, hh));
+                if (it + 1 < n_iter) prefetch(next_row(i, hh), next_qoff(i, hh));
                 if (n_vis == 0 || !(l_i > 0.f)) {
-                    if (WITH_DQ && tid < D) p.dQ[row * D + tid] = __float2bfloat16(0.f);
+                    if (WITH_DQ && tid < D) p.dQ[qoff_at(i, hh) + tid] = __float2bfloat16(0.f);
                     continue;
                 }
                 const float lse2 = m_i * LOG2E + __log2f(l_i);
@@ -824,7 +855,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     ok = pipe_wait(&bars[PB_E_SYNC2], ph, sFail);
                     if (!ok) break;
                     if (tid < D)
-                        p.dQ[row * D + tid] =
+                        p.dQ[qoff_at(i, hh) + tid] =
                             __float2bfloat16(p.scale * (red[tid] + red[D + tid] + red[2 * D + tid] + red[3 * D + tid]));
                 }
                 ++n;
@@ -853,6 +884,7 @@ struct ReduceParams {
     float* dV32;         // query heads are only a part of the KV head's: summed across ranks before rounding)
     int rows;            // B * Hkv
     int N, D, q_begin, block_len, nblk, planes;
+    int bnhd, Hkv;       // layout of dK, dV (RowAddr) and KV heads per batch
     int lead;            // the writer's ring is positioned `lead` queries ahead of its first query (packed schedule: QB - 1)
 };
 
@@ -879,16 +911,17 @@ __global__ void sg_bwd_reduce_kernel(const ReduceParams p) {
                 sv.x += v.x; sv.y += v.y; sv.z += v.z; sv.w += v.w;
             }
         }
+        const size_t at = RowAddr{p.bnhd, p.Hkv, p.N, p.D}.elem(rk) + c * 4;      // the planes are [B,Hkv,N,D]; the outputs follow the layout
         if (p.dK32) {
-            *reinterpret_cast<float4*>(p.dK32 + rk * p.D + c * 4) = sk;
-            *reinterpret_cast<float4*>(p.dV32 + rk * p.D + c * 4) = sv;
+            *reinterpret_cast<float4*>(p.dK32 + at) = sk;
+            *reinterpret_cast<float4*>(p.dV32 + at) = sv;
             continue;
         }
         uint2 ok, ov;
         ok.x = pack_bf16x2(sk.x, sk.y); ok.y = pack_bf16x2(sk.z, sk.w);
         ov.x = pack_bf16x2(sv.x, sv.y); ov.y = pack_bf16x2(sv.z, sv.w);
-        *reinterpret_cast<uint2*>(p.dK + rk * p.D + c * 4) = ok;
-        *reinterpret_cast<uint2*>(p.dV + rk * p.D + c * 4) = ov;
+        *reinterpret_cast<uint2*>(p.dK + at) = ok;
+        *reinterpret_cast<uint2*>(p.dV + at) = ov;
     }
 }
 

@@ -101,14 +101,66 @@ __device__ __forceinline__ bool pipe_wait(uint64_t* bar, uint32_t parity, volati
     return false;
 }
 
+// A caller's visibility mask comes as bytes ([B,N,N], non-zero = visible) or as packed words ([B,N,ceil(N/32)],
+// bit t of word c = key 32 c + t: the form of the reference's mask metadata, cuda/shared_kv/shared_mask_metadata.cuh:8-31,
+// 32 times less to read); MaskRow is one query's row of either, MaskView the batch's.
+struct MaskRow {
+    const uint8_t* bytes;
+    const uint32_t* words;
+    __device__ __forceinline__ bool any() const { return bytes != nullptr || words != nullptr; }
+    __device__ __forceinline__ bool at(int key) const {
+        return words ? ((__ldg(words + (key >> 5)) >> (key & 31)) & 1u) != 0 : bytes[key] != 0;
+    }
+};
+struct MaskView {
+    const uint8_t* bytes;
+    const uint32_t* words;
+    int N, NW;
+    __device__ __forceinline__ bool any() const { return bytes != nullptr || words != nullptr; }
+    __device__ __forceinline__ MaskRow row(int i) const {
+        return MaskRow{bytes ? bytes + static_cast<size_t>(i) * N : nullptr,
+                       words ? words + static_cast<size_t>(i) * NW : nullptr};
+    }
+};
+__device__ __forceinline__ MaskView mask_view(const uint8_t* bytes, const uint32_t* words, int b, int N) {
+    const int NW = (N + 31) / 32;
+    return MaskView{bytes ? bytes + static_cast<size_t>(b) * N * N : nullptr,
+                    words ? words + static_cast<size_t>(b) * N * NW : nullptr, N, NW};
+}
+
+// Memory layout of the [B,H,N,D] operands.  0: B,H,N,D contiguous (the reference's, cuda/forward.cu:1609-1631).
+// 1: B,N,H,D contiguous -- what a projection x W gives before the head split is permuted and copied
+// (att3ntion/_autograd.py:349-363 does that copy for every operand of every call).  Statistics are [B,H,N] in
+// both.  A row is named by its index in the statistics, r = (b*H + head)*N + i; RowAddr turns that into the
+// element offset of the row and into the (x, y) coordinates of a 2-D tensor map over the same memory
+// (layout 0: [B*H*N, D]; layout 1: [B*N, H*D] with the head as a column offset).
+struct RowAddr {
+    int bnhd, H, N, D;
+    __device__ __forceinline__ size_t elem(size_t r) const {
+        if (!bnhd) return r * D;
+        const size_t bh = r / N;
+        const int i = static_cast<int>(r - bh * N), head = static_cast<int>(bh % H);
+        return ((bh / H * N + i) * H + head) * static_cast<size_t>(D);
+    }
+    __device__ __forceinline__ void tma(size_t r, int& x, int& y) const {
+        if (!bnhd) { x = 0; y = static_cast<int>(r); return; }
+        const size_t bh = r / N;
+        const int i = static_cast<int>(r - bh * N), head = static_cast<int>(bh % H);
+        x = head * D;
+        y = static_cast<int>(bh / H * N + i);
+    }
+    // elements between the rows of consecutive positions of one (batch, head)
+    __device__ __forceinline__ size_t step() const { return bnhd ? static_cast<size_t>(H) * D : D; }
+};
+
 // Visibility of the 128 ring slots for query i as four ballot words; every warp
 // computes the same words (lane L looks at slots L, 32+L, 64+L, 96+L).
-__device__ __forceinline__ void ring_visibility(const uint8_t* mask_row, int i, int window, int lane, uint32_t (&vw)[4]) {
+__device__ __forceinline__ void ring_visibility(const MaskRow mask_row, int i, int window, int lane, uint32_t (&vw)[4]) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         const int key = ring_key(i, q * 32 + lane);
         bool v = key >= 0 && key > i - window;
-        if (v && mask_row) v = mask_row[key] != 0;
+        if (v && mask_row.any()) v = mask_row.at(key);
         vw[q] = __ballot_sync(0xFFFFFFFFu, v);
     }
 }

@@ -61,10 +61,14 @@ struct FwdParams {
     const __nv_bfloat16* Vr;
     const __nv_bfloat16* Vs;
     const uint8_t* mask;           // [B,N,N] or null
+    const uint32_t* mask_words;    // the same mask as packed words [B,N,ceil(N/32)], or null (takes precedence)
     __nv_bfloat16* Y;              // [B,Hq,N,D]
     float* m;                      // [B,Hq,N]
     float* l;
     int B, Hq, Hkv, N, window, q_begin, block_len;
+    int bnhd;                      // memory layout of Q, R, S, Vr, Vs, Y: 0 [B,H,N,D], 1 [B,N,H,D] (RowAddr)
+    __nv_bfloat16* Y_act;          // optional second output QuickGELU(Y) = Y * sigmoid(1.702 Y), laid out like Y; or null
+    int window_s;                  // window on the S / Vs key axis (`window` is the R / Vr axis's); equal unless asymmetric
     float scale;
     int* status;                   // device status word (bounded-wait failures)
     // TMA descriptors (box = one row) over Q viewed as [B*Hq*N, D] and R, Vr, S, Vs viewed as [B*Hkv*N, D]
@@ -99,8 +103,15 @@ struct FwdSmem {
     static constexpr int ALLOC = BYTES + 1024;          // slack for manual 1024-byte alignment
 };
 
-template <int D>
+// EXT = false compiles the plain call (layout [B,H,N,D], one window, byte mask, no activated output) with the
+// extension fields folded to constants: the role loops are sensitive to every live register, and the plain
+// call is the common one.
+template <int D, bool EXT = false>
 __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __grid_constant__ FwdParams p) {
+    const int x_bnhd = EXT ? p.bnhd : 0;
+    const int x_window_s = EXT ? p.window_s : p.window;
+    __nv_bfloat16* const x_Y_act = EXT ? p.Y_act : nullptr;
+    const uint32_t* const x_mask_words = EXT ? p.mask_words : nullptr;
     using L = FwdSmem<D>;
     constexpr int CH = D / 8;            // 16-byte chunks per row
     constexpr int DW = D / 2;            // packed bf16x2 words per row
@@ -154,17 +165,34 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         *sFail = 0;
     }
 
-    const size_t kv_base = (static_cast<size_t>(b) * p.Hkv + g) * p.N;
-    const __nv_bfloat16* gR = p.R + kv_base * D;
-    const __nv_bfloat16* gS = p.S + kv_base * D;
-    const __nv_bfloat16* gVr = p.Vr + kv_base * D;
-    const __nv_bfloat16* gVs = p.Vs + kv_base * D;
-    const uint8_t* mask_b = p.mask ? p.mask + static_cast<size_t>(b) * p.N * p.N : nullptr;
+    const size_t kv_base = (static_cast<size_t>(b) * p.Hkv + g) * p.N;       // statistics-style row index of key 0
+    const RowAddr kaddr{x_bnhd, p.Hkv, p.N, D};
+    const size_t kstep = kaddr.step();                                       // elements from one key's row to the next
+    const __nv_bfloat16* gR = p.R + kaddr.elem(kv_base);
+    const __nv_bfloat16* gS = p.S + kaddr.elem(kv_base);
+    const __nv_bfloat16* gVr = p.Vr + kaddr.elem(kv_base);
+    const __nv_bfloat16* gVs = p.Vs + kaddr.elem(kv_base);
+    const MaskView mask_b = mask_view(p.mask, x_mask_words, b, p.N);
     const int n_iter = (q1 - q0) * G;
     auto row_at = [&](int i, int hh) {
         return (static_cast<size_t>(b) * p.Hq + (g * G + hh)) * p.N + i;
     };
     auto next_row = [&](int i, int hh) { return hh + 1 < G ? row_at(i, hh + 1) : row_at(i + 1, 0); };
+    // Element offset of the row of (position i, head hh of this KV group) in Q, dY, Y, dQ, its tensor-map coordinates,
+    // and the coordinates of a key's row (RowAddr describes the two layouts; here without its divisions).
+    auto qoff_at = [&](int i, int hh) -> size_t {
+        return x_bnhd ? ((static_cast<size_t>(b) * p.N + i) * p.Hq + (g * G + hh)) * D
+                      : ((static_cast<size_t>(b) * p.Hq + (g * G + hh)) * p.N + i) * D;
+    };
+    auto q_tma = [&](int i, int hh, int& x, int& y) {
+        if (x_bnhd) { x = (g * G + hh) * D; y = b * p.N + i; }
+        else { x = 0; y = (b * p.Hq + (g * G + hh)) * p.N + i; }
+    };
+    auto k_tma = [&](int key, int& x, int& y) {
+        if (x_bnhd) { x = g * D; y = b * p.N + key; }
+        else { x = 0; y = static_cast<int>(kv_base) + key; }
+    };
+    const size_t qstep = x_bnhd ? static_cast<size_t>(p.Hq) * D : D;      // elements between consecutive positions of one head
     const float c2 = p.scale * LOG2E;
 
     uint32_t tmem_base = 0;
@@ -183,9 +211,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         {   // initial fill: R row in registers, S and Vs rows in the operand tiles
             const int key = ring_key(q0, hslot);
             if (key >= 0) {
-                const uint4* r4 = reinterpret_cast<const uint4*>(gR + static_cast<size_t>(key) * D);
-                const uint4* s4 = reinterpret_cast<const uint4*>(gS + static_cast<size_t>(key) * D);
-                const uint4* vs4 = reinterpret_cast<const uint4*>(gVs + static_cast<size_t>(key) * D);
+                const uint4* r4 = reinterpret_cast<const uint4*>(gR + static_cast<size_t>(key) * kstep);
+                const uint4* s4 = reinterpret_cast<const uint4*>(gS + static_cast<size_t>(key) * kstep);
+                const uint4* vs4 = reinterpret_cast<const uint4*>(gVs + static_cast<size_t>(key) * kstep);
 #pragma unroll
                 for (int c = 0; c < CH; ++c) {
                     const uint4 a = __ldg(r4 + c);
@@ -206,27 +234,30 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         // Row staging by TMA, issued by one thread: the Q row of iteration `it` into its stage buffer and, when
         // next_key >= 0, the four rows (R, Vr, S, Vs) of the key that enters the ring with query next_key.
         // Each copy names an mbarrier that counts its bytes; the consumers wait on that barrier.
-        auto h_stage = [&](int it, size_t row, int next_key) {
+        auto h_stage = [&](int it, int qi, int qh, int next_key) {
             if (hslot != 0) return;
             if (it >= 0) {
                 uint64_t* bar = &bars[FB_STAGE0 + (it & 1)];
                 mbar_arrive_expect_tx(bar, D * 2);
-                tma_load_2d(sQst + (it & 1) * D, &p.tmQ, 0, static_cast<int>(row), bar);
+                int x, y;
+                q_tma(qi, qh, x, y);
+                tma_load_2d(sQst + (it & 1) * D, &p.tmQ, x, y, bar);
             }
             if (next_key >= 0) {
                 uint64_t* bar = &bars[FB_NEXT_READY0 + ((next_key - q0 - 1) & (NEXT_BUFS - 1))];
                 uint8_t* dst = sNext + (next_key & (NEXT_BUFS - 1)) * L::NEXT_BYTES;
-                const int krow = static_cast<int>(kv_base) + next_key;
+                int kx, krow;
+                k_tma(next_key, kx, krow);
                 mbar_arrive_expect_tx(bar, 4 * D * 2);
-                tma_load_2d(dst, &p.tmR, 0, krow, bar);
-                tma_load_2d(dst + D * 2, &p.tmVr, 0, krow, bar);
-                tma_load_2d(dst + 2 * D * 2, &p.tmS, 0, krow, bar);
-                tma_load_2d(dst + 3 * D * 2, &p.tmVs, 0, krow, bar);
+                tma_load_2d(dst, &p.tmR, kx, krow, bar);
+                tma_load_2d(dst + D * 2, &p.tmVr, kx, krow, bar);
+                tma_load_2d(dst + 2 * D * 2, &p.tmS, kx, krow, bar);
+                tma_load_2d(dst + 3 * D * 2, &p.tmVs, kx, krow, bar);
             }
         };
         fence_async_smem();
         cta_start_sync();
-        h_stage(0, row_at(q0, 0), -1);
+        h_stage(0, q0, 0, -1);
         constexpr int HB = 8;                 // staged chunks in flight per thread
         int n = 0, it = 0;
         bool ok = true;
@@ -234,7 +265,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         for (int i = q0; i < q1 && ok; ++i) {
             const int s = i & (RING - 1);
             uint32_t vw[4];
-            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
+            ring_visibility(mask_b.row(i), i, min(p.window, x_window_s), lane, vw);      // a pair needs a key on both axes
             const bool work = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
 #pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
@@ -261,7 +292,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                         rR[4 * c] = a.x; rR[4 * c + 1] = a.y; rR[4 * c + 2] = a.z; rR[4 * c + 3] = a.w;
                     }
                 }
-                if (it + 1 < n_iter) h_stage(it + 1, next_row(i, hh), (hh == 0 && i + 1 < q1) ? i + 1 : -1);
+                if (it + 1 < n_iter)
+                    h_stage(it + 1, hh + 1 < G ? i : i + 1, hh + 1 < G ? hh + 1 : 0, (hh == 0 && i + 1 < q1) ? i + 1 : -1);
                 const int qb = n & 1;
                 if (work) {
                     // Qp[n&1] was last read by the score MMAs of head n-2
@@ -338,7 +370,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
 #pragma unroll 1
         for (int i = q0; i < q1 && ok; ++i) {
             uint32_t vw[4];
-            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
+            ring_visibility(mask_b.row(i), i, min(p.window, x_window_s), lane, vw);      // a pair needs a key on both axes
             const bool work = (vw[0] | vw[1] | vw[2] | vw[3]) != 0;
 #pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh) {
@@ -388,7 +420,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         {
             const int key = ring_key(q0, slot);
             if (key >= 0) {
-                const uint4* v4 = reinterpret_cast<const uint4*>(gVr + static_cast<size_t>(key) * D + ch * HD);
+                const uint4* v4 = reinterpret_cast<const uint4*>(gVr + static_cast<size_t>(key) * kstep + ch * HD);
 #pragma unroll
                 for (int c = 0; c < VW / 4; ++c) {
                     const uint4 v = __ldg(v4 + c);
@@ -406,7 +438,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         // quarters' partials and write Y, m, l of head fin_m.
         bool fin_pending = false;
         int fin_m = 0;
-        size_t fin_row = 0;
+        size_t fin_row = 0, fin_off = 0;
         float fin_M = 0.f;
         auto finish = [&]() {
             if (!fin_pending) return true;
@@ -417,13 +449,15 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
 #pragma unroll
             for (int q = 0; q < 4; ++q) Lsum += red[q * (D + 4) + D] + red[q * (D + 4) + D + 1];
             if (tid < D) {
-                const float y = red[tid] + red[(D + 4) + tid] + red[2 * (D + 4) + tid] + red[3 * (D + 4) + tid];
-                p.Y[fin_row * D + tid] = __float2bfloat16(y / Lsum);
+                const float y = (red[tid] + red[(D + 4) + tid] + red[2 * (D + 4) + tid] + red[3 * (D + 4) + tid]) / Lsum;
+                const size_t at = fin_off + tid;
+                p.Y[at] = __float2bfloat16(y);
+                if (x_Y_act) x_Y_act[at] = __float2bfloat16(y / (1.f + __expf(-1.702f * y)));
             }
             if (tid == 0) { p.m[fin_row] = fin_M * p.scale; p.l[fin_row] = Lsum; }
             return true;
         };
-        auto epilogue = [&](int m, size_t row, float M, float l_half) {
+        auto epilogue = [&](int m, size_t row, size_t off, float M, float l_half) {
             const int ub = m & 1;
             if (!finish()) return false;
             bool r = pipe_wait<true>(&bars[FB_U_DONE0 + ub], (m >> 1) & 1, sFail, 32);
@@ -473,7 +507,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
             for (int o = 16; o >= 1; o >>= 1) wl += __shfl_xor_sync(0xFFFFFFFFu, wl, o);
             if (lane == 0) red[quarter * (D + 4) + D + ch] = wl;
             warp_arrive(&bars[FB_E_SYNC], lane);
-            fin_pending = true; fin_m = m; fin_row = row; fin_M = M;
+            fin_pending = true; fin_m = m; fin_row = row; fin_off = off; fin_M = M;
             return true;
         };
         // Key i takes over slot s: the Vs ring row (every U product that read the old row is complete,
@@ -499,29 +533,37 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
         int n = 0;
         bool ok = true, pend = false;
         int pend_n = 0;
-        size_t pend_row = 0;
+        size_t pend_row = 0, pend_off = 0;
         float pend_m = 0.f, pend_l = 0.f;
 #pragma unroll 1
         for (int i = q0; i < q1 && ok; ++i) {
-            uint32_t vw[4];
-            ring_visibility(mask_b ? mask_b + static_cast<size_t>(i) * p.N : nullptr, i, p.window, lane, vw);
-            const int n_vis = __popc(vw[0]) + __popc(vw[1]) + __popc(vw[2]) + __popc(vw[3]);
-            const bool all_vis = n_vis == RING;
+            // rows of the score tile are R keys (window), columns S keys (window_s)
+            uint32_t vw[4], vs[4];
+            ring_visibility(mask_b.row(i), i, p.window, lane, vw);
+            if (x_window_s != p.window) ring_visibility(mask_b.row(i), i, x_window_s, lane, vs);
+            else { vs[0] = vw[0]; vs[1] = vw[1]; vs[2] = vw[2]; vs[3] = vw[3]; }
+            const int n_rows = __popc(vw[0]) + __popc(vw[1]) + __popc(vw[2]) + __popc(vw[3]);
+            const int n_cols = __popc(vs[0]) + __popc(vs[1]) + __popc(vs[2]) + __popc(vs[3]);
+            const int n_vis = min(n_rows, n_cols);               // 0: no visible pair
+            const bool all_vis = n_rows == RING && n_cols == RING;
             const bool my_vis = (vw[quarter] >> lane) & 1u;
             // visibility words of this thread's two 32-column chunks
-            const uint32_t cw0 = my_vis ? (ch ? vw[2] : vw[0]) : 0u;
-            const uint32_t cw1 = my_vis ? (ch ? vw[3] : vw[1]) : 0u;
+            const uint32_t cw0 = my_vis ? (ch ? vs[2] : vs[0]) : 0u;
+            const uint32_t cw1 = my_vis ? (ch ? vs[3] : vs[1]) : 0u;
 #pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh) {
                 const size_t row = row_at(i, hh);
                 const bool boundary = hh == 0 && i > q0;
                 if (n_vis == 0) {
                     // No visible pair: Y = 0, m = NEG_INF, l = 0 (cuda/common.cuh:24).
-                    if (pend) { ok = epilogue(pend_n, pend_row, pend_m, pend_l); pend = false; }
+                    if (pend) { ok = epilogue(pend_n, pend_row, pend_off, pend_m, pend_l); pend = false; }
                     if (!ok) break;
                     if (boundary) ok = ring_update(i);
                     if (!ok) break;
-                    if (tid < D) p.Y[row * D + tid] = __float2bfloat16(0.f);
+                    if (tid < D) {
+                        p.Y[qoff_at(i, hh) + tid] = __float2bfloat16(0.f);
+                        if (x_Y_act) x_Y_act[qoff_at(i, hh) + tid] = __float2bfloat16(0.f);
+                    }
                     if (tid == 0) { p.m[row] = NEG_INF_F; p.l[row] = 0.f; }
                     continue;
                 }
@@ -568,7 +610,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 }
                 warp_arrive(&bars[FB_M_SYNC], lane);
                 // ---- epilogue of the previous head, behind its U product; then the ring rows of a new key
-                if (pend) { ok = epilogue(pend_n, pend_row, pend_m, pend_l); pend = false; }
+                if (pend) { ok = epilogue(pend_n, pend_row, pend_off, pend_m, pend_l); pend = false; }
                 if (ok && boundary) ok = ring_update(i);
                 if (!ok) break;
                 ok = pipe_wait<true>(&bars[FB_M_SYNC], n & 1, sFail, 31);
@@ -603,11 +645,11 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 tc_fence_before();
                 // P_full also tells the MMA warp that the Vs ring row is current (ring_update above)
                 warp_arrive(&bars[FB_P_FULL0 + xb], lane);
-                pend = true; pend_n = n; pend_row = row; pend_m = M; pend_l = l_half;
+                pend = true; pend_n = n; pend_row = row; pend_off = qoff_at(i, hh); pend_m = M; pend_l = l_half;
                 ++n;
             }
         }
-        if (ok && pend) ok = epilogue(pend_n, pend_row, pend_m, pend_l);
+        if (ok && pend) ok = epilogue(pend_n, pend_row, pend_off, pend_m, pend_l);
         if (ok) ok = finish();
     }
     tc_fence_before();

@@ -113,6 +113,40 @@ int att3_sg_backward_kv32(const void* dY, const void* Q, const void* R, const vo
                           int B, int Hq, int Hkv, int N, int D, int window, int q_begin,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* Extended calls for the windowed path.  Options beyond the reference's call surface travel in one
+ * struct so that the plain entry points keep their signatures; a NULL ext or an all-zero struct is the plain call.
+ *   window_s    window on the S / Vs key axis, with `window` then the R / Vr axis's: query i sees the pairs
+ *               (j, k) with j in (i - window, i] and k in (i - window_s, i].  0 = equal windows.  The reference
+ *               lists independent (W1, W2) windows as an open item (docs/KERNEL_HISTORY.md:180).
+ *   mask_words  the caller's mask as packed words [B, N, ceil(N/32)], bit t of word c = key 32 c + t, in place of
+ *               the byte mask (pass mask = NULL): the representation of the reference's mask metadata
+ *               (cuda/shared_kv/shared_mask_metadata.cuh:8-31), 1/32 of the bytes per query row.
+ *   layout      memory layout of Q, R, S, Vr, Vs, Y, dY and all gradients: 0 = [B,H,N,D] contiguous (the
+ *               reference's contract, cuda/forward.cu:1609-1631); 1 = [B,N,H,D] contiguous, i.e. the projections'
+ *               own output viewed as heads -- the reference's module permutes and copies every operand into
+ *               layout 0 on every call (att3ntion/_autograd.py:349-363), which this removes.  m, l stay [B,H,N].
+ *   Y_act       forward only: a second output QuickGELU(Y) = Y * sigmoid(1.702 Y), laid out like Y (the module's
+ *               activation, att3ntion/_autograd.py:254-256, written from the forward's epilogue), or NULL.
+ * All need window >= 1.  att3_sg_pack_mask produces the words (and, optionally, the per-query count of
+ * visible keys inside the causal window saturated at 2, [B, N] bytes; window = 0: the mask alone). */
+typedef struct att3_sg_ext {
+    int window_s;
+    const uint32_t* mask_words;
+    int layout;
+    void* Y_act;
+} att3_sg_ext;
+
+int att3_sg_forward_ext(const void* Q, const void* R, const void* S, const void* Vr, const void* Vs,
+                        const uint8_t* mask, void* Y, float* m, float* l,
+                        int B, int Hq, int Hkv, int N, int D, int window, int q_begin, void* stream,
+                        const att3_sg_ext* ext);
+int att3_sg_backward_ext(const void* dY, const void* Q, const void* R, const void* S, const void* Vr,
+                         const void* Vs, const void* Y, const float* m, const float* l, const uint8_t* mask,
+                         void* dQ, void* dR, void* dS, void* dVr, void* dVs,
+                         int B, int Hq, int Hkv, int N, int D, int window, int q_begin,
+                         void* workspace, size_t workspace_bytes, void* stream, const att3_sg_ext* ext);
+int att3_sg_pack_mask(const uint8_t* mask, uint32_t* words, uint8_t* support, int B, int N, int window, void* stream);
+
 /* One key side of att3_sg_backward_kv32 per call: side 0 writes dQ, dS, dVs
  * (the other gradient pointers may be NULL), side 1 writes dR, dVr.  Two calls,
  * side 0 then side 1, equal one att3_sg_backward_kv32 bit for bit; in between a

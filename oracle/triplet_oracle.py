@@ -61,10 +61,12 @@ def reduce_kv(g: torch.Tensor, hkv: int) -> torch.Tensor:
     return g if hkv == hq else g.reshape(b, hkv, hq // hkv, n, d).sum(2)
 
 
-def single_gather_dense(Q, R, S, Vr, Vs, mask=None, dY=None):
+def single_gather_dense(Q, R, S, Vr, Vs, mask=None, dY=None, mask_s=None):
     """One joint softmax over (j,k) per query i.
 
-    Q [B,Hq,N,D]; R,S,Vr,Vs [B,Hkv,N,D]; mask [B,N,N] bool or None.
+    Q [B,Hq,N,D]; R,S,Vr,Vs [B,Hkv,N,D]; mask [B,N,N] bool or None.  mask_s, if given, is the
+    visibility of the S / Vs key axis and `mask` that of the R / Vr axis only (independent windows per
+    axis; the reference's operator has one mask for both, tests/test_single_gather.py:52-66).
     Returns dict with Y, lse (-inf on dead rows), m, l and, if dY is given, the five
     gradients (KV gradients reduced to Hkv heads).  FP64 throughout.
     """
@@ -75,7 +77,7 @@ def single_gather_dense(Q, R, S, Vr, Vs, mask=None, dY=None):
     scale = 1.0 / math.sqrt(D)
     x = torch.einsum("bhid,bhjd,bhkd->bhijk", Q, Re, Se) * scale
     if mask is not None:
-        vis = (mask[:, :, :, None] & mask[:, :, None, :])[:, None]
+        vis = (mask[:, :, :, None] & (mask if mask_s is None else mask_s)[:, :, None, :])[:, None]
         x = x.masked_fill(~vis, float("-inf"))
     flat = x.flatten(3)
     m = flat.max(-1).values

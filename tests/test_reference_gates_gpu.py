@@ -251,3 +251,108 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_survives(ck):
     ck.device_status()
     assert torch.isfinite(Y.float()).all()
     assert lib.att3_wait_selftest(0, None) == _cabi.ERR_INVALID
+
+
+# --------------------------------------------------------------------------- extended calls: packed masks, window pairs
+
+def test_packed_mask_words_equal_the_byte_mask(ck):
+    """The same mask as bytes and as packed words gives bit-identical results on both windowed schedules
+    (ring: w = 128; packed tiles: w = 32), and the packer's words / support counts match a torch restatement."""
+    B, Hq, N, D = 2, 4, 208, 128
+    xs, dY = draw(B, Hq, N, D, seed=41, hkv=1)
+    g = torch.Generator().manual_seed(2)
+    mask = torch.rand(B, N, N, generator=g) < 0.7
+    mask[:, 9, :] = False
+    mask[:, 77, :] = False
+    mask[:, 77, 77] = True
+    q = [xs[n].cuda() for n in NAMES]
+    mk = mask.cuda().contiguous()
+    for w in (128, 32):
+        words, support = ck.pack_mask(mk, window=w, with_support=True)
+        i = torch.arange(N)
+        vis = mask & (i[None, :] <= i[:, None]) & (i[None, :] > i[:, None] - w)
+        assert torch.equal(support.cpu(), vis.sum(-1).clamp(max=2).to(torch.uint8))
+        bits = torch.nn.functional.pad(vis, (0, (-N) % 32)).reshape(B, N, -1, 32).long()
+        want = (bits << torch.arange(32)).sum(-1)
+        assert torch.equal(words.cpu().long() & 0xFFFFFFFF, want)
+        plain = ck.pack_mask(mk)                                          # the mask alone; the kernels apply the window
+        Y0, m0, l0 = ck.sg_forward_raw(*q, mk, w)
+        g0 = ck.sg_backward_raw(dY.cuda(), *q, Y0, m0, l0, mk, w)
+        Y1, m1, l1 = ck.sg_forward_raw(*q, None, w, mask_words=plain)
+        g1 = ck.sg_backward_raw(dY.cuda(), *q, Y1, m1, l1, None, w, mask_words=plain)
+        ck.device_status()
+        assert torch.equal(Y0, Y1) and torch.equal(m0, m1) and torch.equal(l0, l1)
+        assert all(torch.equal(a, b) for a, b in zip(g0, g1))
+        ref = O.single_gather_banded(*[xs[n] for n in NAMES], window=w, dY=dY, mask=mask, chunk=40)
+        O.check_gate("Y", Y1.float().cpu(), ref["Y"])
+        O.check_lse(m1, l1, ref["lse"])
+        for name, t in zip(GRADS, g1):
+            O.check_gate(name, t.float().cpu(), ref[name])
+    with pytest.raises(RuntimeError, match="either as bytes or as packed words"):
+        ck.sg_forward_raw(*q, mk, 32, mask_words=ck.pack_mask(mk))
+    with pytest.raises(RuntimeError, match="windowed path"):
+        ck.sg_forward_raw(*[xs[n][:, :1].expand(-1, 4, -1, -1).contiguous().cuda() if n != "Q" else q[0] for n in NAMES],
+                          None, 0, mask_words=ck.pack_mask(mk))
+
+
+@pytest.mark.parametrize("wr,ws", [(128, 32), (16, 96), (48, 48), (1, 128)])
+def test_one_window_per_key_axis(wr, ws):
+    """window = (w_r, w_s): query i sees the pairs (j, k) with j in (i - w_r, i] and k in (i - w_s, i]."""
+    from att3ntion_b200 import single_gather_attention
+    B, H, N, D = 1, 2, 200, 128
+    xs, dY = draw(B, H, N, D, seed=wr + ws)
+    mr = O.window_mask(N, wr)[None].expand(B, -1, -1)
+    ms = O.window_mask(N, ws)[None].expand(B, -1, -1)
+    ref = O.single_gather_dense(*[xs[n] for n in NAMES], mask=mr, dY=dY, mask_s=ms)
+    leaves = {n: xs[n].cuda().requires_grad_(True) for n in NAMES}
+    Y = single_gather_attention(*[leaves[n] for n in NAMES], None, window=(wr, ws))
+    Y.backward(dY.cuda())
+    check(Y.detach(), {g: leaves[n].grad for g, n in zip(GRADS, NAMES)}, ref)
+    if wr == ws:        # a pair of equal windows is the plain windowed call
+        Yb, gb = bridge(xs, dY, None, wr)
+        assert torch.equal(Y.detach(), Yb)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,w", [(8, 1, 128, 128), (8, 1, 128, 32), (4, 4, 64, 64), (2, 2, 128, 48)])
+def test_heads_last_layout_and_activated_output(ck, Hq, Hkv, D, w):
+    """Operands laid out [B,N,H,D] give, element for element, what the [B,H,N,D] call gives (both windowed schedules
+    and both head sizes), and the activated output equals QuickGELU of the plain one."""
+    B, N = 2, 272
+    xs, dY = draw(B, Hq, N, D, seed=Hq + w, hkv=Hkv)
+    q = [xs[n].cuda() for n in NAMES]
+    Y0, m0, l0 = ck.sg_forward_raw(*q, None, w)
+    g0 = ck.sg_backward_raw(dY.cuda(), *q, Y0, m0, l0, None, w)
+    t = lambda x: x.permute(0, 2, 1, 3).contiguous()
+    qt = [t(x) for x in q]
+    Y1, m1, l1, Ya = ck.sg_forward_raw(*qt, None, w, bnhd=True, act=True)
+    g1 = ck.sg_backward_raw(t(dY.cuda()), *qt, Y1, m1, l1, None, w, bnhd=True)
+    ck.device_status()
+    assert torch.equal(t(Y0), Y1) and torch.equal(m0, m1) and torch.equal(l0, l1)
+    for a, b in zip(g0, g1):
+        assert torch.equal(t(a), b)
+    yf = Y1.float()
+    assert torch.allclose(Ya.float(), yf * torch.sigmoid(1.702 * yf), rtol=2e-2, atol=1e-3)
+
+
+def test_module_window_path_reads_projections_in_place():
+    """HypergraphAttention(gather_mode=1, window): the path without permute-and-copy and with the fused activation
+    agrees with the path through single_gather_attention + QuickGELU (same kernels, other memory layout)."""
+    from att3ntion_b200 import HypergraphAttention
+    from att3ntion_b200 import _autograd
+    torch.manual_seed(0)
+    mod = HypergraphAttention(256, 2, gather_mode=1, window=64).cuda()
+    x = torch.randn(2, 96, 256, device="cuda", requires_grad=True)
+    y = mod(x)
+    y.sum().backward()
+    gx, gw = x.grad.clone(), mod.Wq.weight.grad.clone()
+    x.grad = None
+    mod.zero_grad()
+    tile = _autograd.TILE
+    _autograd.TILE = 10 ** 9                       # n % TILE != 0: forces the permute-and-copy path
+    try:
+        y2 = mod(x)
+        y2.sum().backward()
+    finally:
+        _autograd.TILE = tile
+    assert torch.allclose(y, y2, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(gx, x.grad, rtol=5e-2, atol=5e-2) and torch.allclose(gw, mod.Wq.weight.grad, rtol=5e-2, atol=5e-1)
