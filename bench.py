@@ -82,7 +82,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -120,8 +120,9 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def draw_shared(batch, n, seed, d=D, hq=HQ):
+def draw_shared(batch, n, seed, d=D, hq=None):
     """(Q, R, S, Vr, Vs, dY) on the CPU in the reference's draw order (tests/test_single_gather_shared.py:45-54)."""
+    hq = hq or HQ
     g = torch.Generator(device="cpu").manual_seed(seed)
     s = 1.0 / math.sqrt(d)
     Q = (torch.randn(batch, hq, n, d, generator=g) * s).to(torch.bfloat16)
@@ -426,7 +427,6 @@ def run_single(args):
     launches = ctx.launches() - l0
     ktime = kernel_times(lib)
     lib.att3_timing_enable(0)
-    sampler.__exit__()
     ck.device_status()
     value = flops_step / (ms_step * 1e-3) / 1e12
 
@@ -445,6 +445,7 @@ def run_single(args):
     e2e_steps = max(2, min(args.steps, 20))
     e2e_ms = e2e_loop(ctx, host_in, host_out, api_step, e2e_steps)
     e2e_value = flops_step / (e2e_ms * 1e-3) / 1e12
+    sampler.__exit__()                       # the samples cover the warm-up, the timed loop and the end-to-end loop
 
     burst, sustained, src = measured_peaks()
     bwd_ms, bwd_n = ktime["sg_ring_bwd"]
@@ -482,7 +483,7 @@ def run_single(args):
         out["rows"] = long_sequence_single(ctx, max(3, min(args.steps, 5)))
         torch.cuda.empty_cache()
         out["secondary"] = secondary_configs(ctx, short)
-        out["ref_gpu"] = reference_gpu_arm([128, 32])
+        out["ref_gpu"] = reference_gpu_arm([128, 64, 32, 16])
     if not args.no_cpu:
         cpu_v, cpu_dt, cores = cpu_sample(w, queries=args.cpu_queries)
         out["cpu_baseline"] = {"value": cpu_v, "unit": "TFLOP/s", "cores": cores, "kind": "port",
@@ -749,7 +750,6 @@ def run_scale(args):
     l0 = ctx.launches()
     ms_step = ctx.timed(lambda: run_step(dev_t), args.steps, 0)
     launches = ctx.launches() - l0
-    sampler.__exit__()
     ck.device_status()
     value = flops_step / (ms_step * 1e-3) / 1e12
 
@@ -759,6 +759,7 @@ def run_scale(args):
     d2h = sum(t.numel() * t.element_size() for t in host_out)
     e2e_steps = max(2, min(args.steps, 20))
     e2e_ms = e2e_loop(ctx, host_in, host_out, run_step, e2e_steps)
+    sampler.__exit__()                       # the samples cover the warm-up, the timed loop and the end-to-end loop
     del dev_t
     torch.cuda.empty_cache()
 
@@ -895,6 +896,7 @@ if __name__ == "__main__":
                     help="one GPU: only the headline problem (no window sweep, long sequence, secondary, reference kernels)")
     ap.add_argument("--seq-len", type=int, default=N, help="sequence length (profiling captures use a smaller case)")
     ap.add_argument("--batch", type=int, default=B)
+    ap.add_argument("--heads", type=int, default=HQ, help="query heads (profiling a rank's share of the (batch, head) split)")
     ap.add_argument("--workload", default="auto", choices=["auto", "single", "scale", "batch", "rows", "heads", "other"],
                     help="auto: the headline problem on one GPU, or split by (batch, head) over N > 1 GPUs together with "
                          "the row-sharded long sequence and the replica run; batch: replicas only; rows: the row-sharded "
@@ -907,7 +909,7 @@ if __name__ == "__main__":
                     help="kernel-only run for profiler captures: exact warm-up count, no gate, no e2e and no CPU leg")
     ap.add_argument("--refgpu-child", action="store_true", help=argparse.SUPPRESS)
     a = ap.parse_args()
-    N, B = a.seq_len, a.batch
+    N, B, HQ = a.seq_len, a.batch, a.heads
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if a.refgpu_child:
         refgpu_child(a)

@@ -42,8 +42,20 @@ def test_abi_version_and_error_text():
 
 
 def test_workspace_size_formula():
-    n = _cabi.lib.att3_sg_backward_workspace_bytes(4, 8, 1, 8192, 128, 128)
-    assert n == 4 * 4 * 1 * 8192 * 128 * 4
+    """Two key gradients x P partial planes of [B,Hkv,N,D] floats, plus delta [B,Hq,N] floats.  P follows from the
+    backward's query-block length: blocks of at least 127 queries need 2 planes, shorter blocks more."""
+    lib = _cabi.lib
+    n = lib.att3_sg_backward_workspace_bytes(4, 8, 1, 8192, 128, 128)
+    assert n == 2 * 2 * 4 * 1 * 8192 * 128 * 4 + 4 * 8 * 8192 * 4        # 148 SMs / 4 batches: 222 queries per block
+    # one short sequence: 148 blocks of 16 queries -> ceil(127 / 16) + 1 = 9 planes
+    n = lib.att3_sg_backward_workspace_bytes(1, 4, 1, 1024, 128, 64)
+    assert n == 2 * 9 * 1 * 1 * 1024 * 128 * 4 + 1 * 4 * 1024 * 4
+    assert lib.att3_sg_set_query_block(0, 64) == _cabi.OK                # forced block length: ceil(127 / 64) + 1 = 3
+    try:
+        assert lib.att3_sg_backward_workspace_bytes(4, 8, 1, 8192, 128, 128) == 2 * 3 * 4 * 8192 * 128 * 4 + 4 * 8 * 8192 * 4
+    finally:
+        lib.att3_sg_set_query_block(0, 0)
+    assert lib.att3_sg_set_query_block(8, 0) == _cabi.ERR_INVALID
 
 
 def test_query_block_partition():
