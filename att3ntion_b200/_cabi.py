@@ -48,7 +48,7 @@ SIGNATURES = {
 
 class SgExt(C.Structure):
     """att3_sg_ext of include/att3_b200.h."""
-    _fields_ = [("window_s", C.c_int), ("mask_words", C.c_void_p), ("layout", C.c_int), ("Y_act", C.c_void_p)]
+    _fields_ = [("window_s", C.c_int), ("mask_words", C.c_void_p), ("layout", C.c_int), ("Y_act", C.c_void_p), ("precise", C.c_int)]
 
 
 class Att3Error(RuntimeError):

@@ -150,11 +150,11 @@ def pack_mask(mask: torch.Tensor, window: int = 0, with_support: bool = False):
     return (words, support) if with_support else words
 
 
-def _ext(window_s: int, mask_words, bnhd: bool = False, y_act=None):
+def _ext(window_s: int, mask_words, bnhd: bool = False, y_act=None, precise: bool = False):
     """att3_sg_ext for a call, or None for the plain entry points."""
-    if not window_s and mask_words is None and not bnhd and y_act is None:
+    if not window_s and mask_words is None and not bnhd and y_act is None and not precise:
         return None
-    return _cabi.SgExt(int(window_s), _ptr(mask_words), 1 if bnhd else 0, _ptr(y_act))
+    return _cabi.SgExt(int(window_s), _ptr(mask_words), 1 if bnhd else 0, _ptr(y_act), 1 if precise else 0)
 
 
 def _dims(Q, R, bnhd: bool):
@@ -167,21 +167,22 @@ def _dims(Q, R, bnhd: bool):
 
 
 def sg_forward_raw(Q, R, S, Vr, Vs, mask, window: int, q_begin: int = 0, window_s: int = 0, mask_words=None,
-                   bnhd: bool = False, act: bool = False):
+                   bnhd: bool = False, act: bool = False, precise: bool = False):
     """Windowed/dense single gather on already-validated BF16 tensors.  mask may be
     None: with window > 0 the causal window is generated from indices inside the
     kernel, so no [B,N,N] tensor is ever materialised.  window_s > 0: another window on the
     S / Vs key axis (`window` is then the R / Vr axis's); mask_words: the mask as packed words
     (see pack_mask) instead of `mask`; bnhd: the operands (and Y) are [B,N,H,D] contiguous
     instead of [B,H,N,D]; act: also return QuickGELU(Y) as a fourth result, written by the
-    forward's epilogue.  m, l are [B,H,N] either way."""
+    forward's epilogue; precise: score products on the exact split of Q o R (value + residual), to be
+    used with the same setting in the backward.  m, l are [B,H,N] either way."""
     B, Hq, Hkv, N, D = _dims(Q, R, bnhd)
     with torch.cuda.device(Q.device):
         Y = torch.empty_like(Q)
         Ya = torch.empty_like(Q) if act else None
         m = torch.empty((B, Hq, N), dtype=torch.float32, device=Q.device)
         l = torch.empty_like(m)
-        ext = _ext(window_s, mask_words, bnhd, Ya)
+        ext = _ext(window_s, mask_words, bnhd, Ya, precise)
         args = (Q.data_ptr(), R.data_ptr(), S.data_ptr(), Vr.data_ptr(), Vs.data_ptr(),
                 _ptr(mask), Y.data_ptr(), m.data_ptr(), l.data_ptr(), B, Hq, Hkv, N, D, int(window), int(q_begin),
                 _stream(Q))
@@ -193,12 +194,12 @@ def sg_forward_raw(Q, R, S, Vr, Vs, mask, window: int, q_begin: int = 0, window_
 
 
 def sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, window: int, q_begin: int = 0, kv_f32: bool = False,
-                    window_s: int = 0, mask_words=None, bnhd: bool = False):
+                    window_s: int = 0, mask_words=None, bnhd: bool = False, precise: bool = False):
     """kv_f32: leave dR, dS, dVr, dVs in FP32 (partial sums of a process that holds only part of the
     query heads of a KV head; windowed path only).  window_s, mask_words, bnhd: as in sg_forward_raw
     (with bnhd the gradients come back [B,N,H,D] too)."""
     B, Hq, Hkv, N, D = _dims(Q, R, bnhd)
-    ext = _ext(window_s, mask_words, bnhd)
+    ext = _ext(window_s, mask_words, bnhd, None, precise)
     if ext is not None and kv_f32:
         raise RuntimeError("sg_backward_raw: kv_f32 and the extended options do not combine")
     with torch.cuda.device(Q.device):

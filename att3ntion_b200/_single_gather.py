@@ -62,7 +62,7 @@ def _window_pair(window, n: int):
 
 class _SingleGatherFn(Function):
     @staticmethod
-    def forward(ctx, Q, R, S, Vr, Vs, mask, window):
+    def forward(ctx, Q, R, S, Vr, Vs, mask, window, precise=False):
         n = Q.size(2)
         n_pad = (-n) % TILE
         xs = [_pad_rows(x.contiguous().to(torch.bfloat16), n_pad) for x in (Q, R, S, Vr, Vs)]
@@ -78,13 +78,16 @@ class _SingleGatherFn(Function):
         mask = _prepare_mask(mask, Q.size(0), n, n_pad, Q.device)
         win = window if ring else 0
         win_s = window_s if (ring and window_s != window) else 0
+        if precise and not ring:
+            raise ValueError("single_gather_attention: precise=True needs a causal window in 1..128")
         words = None
         if ring and mask is not None:
             words, mask = _ck.pack_mask(mask), None          # the window itself comes from indices inside the kernels
-        Y, m, l = _ck.sg_forward_raw(*xs, mask, win, 0, win_s, words)
+        Y, m, l = _ck.sg_forward_raw(*xs, mask, win, 0, win_s, words, precise=bool(precise))
         keep = words if words is not None else (mask if mask is not None else torch.empty(0))
         ctx.save_for_backward(*xs, Y, m, l, keep)
         ctx.n, ctx.dtype, ctx.win, ctx.win_s, ctx.packed = n, Q.dtype, win, win_s, words is not None
+        ctx.precise = bool(precise)
         return Y[:, :, :n].to(Q.dtype)
 
     @staticmethod
@@ -93,18 +96,23 @@ class _SingleGatherFn(Function):
         mask = keep if (keep.numel() and not ctx.packed) else None
         words = keep if ctx.packed else None
         dY = _pad_rows(dY.contiguous().to(torch.bfloat16), Q.size(2) - ctx.n)
-        grads = _ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, ctx.win, 0, False, ctx.win_s, words)
-        return tuple(g[:, :, :ctx.n].to(ctx.dtype) for g in grads) + (None, None)
+        grads = _ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, mask, ctx.win, 0, False, ctx.win_s, words,
+                                    precise=ctx.precise)
+        return tuple(g[:, :, :ctx.n].to(ctx.dtype) for g in grads) + (None, None, None)
 
 
-def single_gather_attention(Q, R, S, Vr, Vs, mask=None, window=0):
+def single_gather_attention(Q, R, S, Vr, Vs, mask=None, window=0, *, precise=False):
     """Q, R, S, Vr, Vs: [B,H,N,D] with D in {64,128}.  mask: [B,N,N] or [N,N] bool,
     True = visible; query i attends the pairs (j,k) whose members are both visible
     to it, and a fully masked query returns zeros.  window > 0 declares an equal
     causal window of that width on both key axes (>= N: causal); with no mask the
     window is the visibility, with a mask the two are intersected.  window = (w_r, w_s)
-    gives the R / Vr axis and the S / Vs axis a causal window each (both in 1..128)."""
-    return _SingleGatherFn.apply(Q, R, S, Vr, Vs, mask, window)
+    gives the R / Vr axis and the S / Vs axis a causal window each (both in 1..128).
+    precise=True (windows in 1..128 only) runs the score products on the exact split of
+    Q o R into its BF16 value and residual: scores of large magnitude, whose BF16 rounding
+    the softmax would amplify, keep FP32 accuracy at 1.8x the time (the
+    reference's unshipped "compensated" path, docs/KERNEL_HISTORY.md:22)."""
+    return _SingleGatherFn.apply(Q, R, S, Vr, Vs, mask, window, precise)
 
 
 class _SingleGatherHeadsLastFn(Function):

@@ -24,7 +24,7 @@ WINDOW = 128
 
 class _SharedFn(Function):
     @staticmethod
-    def forward(ctx, Q, R, S, Vr, Vs, mask, fwd_group, rs_group, window):
+    def forward(ctx, Q, R, S, Vr, Vs, mask, fwd_group, rs_group, window, precise=False):
         n = Q.size(2)
         n_pad = (-n) % TILE
         xs = [_pad_rows(x.contiguous().to(torch.bfloat16), n_pad) for x in (Q, R, S, Vr, Vs)]
@@ -33,9 +33,9 @@ class _SharedFn(Function):
         mask = _prepare_mask(mask, Q.size(0), n, n_pad, Q.device)
         # an extra mask is packed into words once (1/32 of the bytes) and serves the forward and the backward
         words = _ck.pack_mask(mask) if mask is not None else None
-        Y, m, l = _ck.sg_forward_raw(*xs, None, window, 0, 0, words)
+        Y, m, l = _ck.sg_forward_raw(*xs, None, window, 0, 0, words, precise=bool(precise))
         ctx.save_for_backward(*xs, Y, m, l, words if words is not None else torch.empty(0))
-        ctx.n, ctx.dtype, ctx.window = n, Q.dtype, window
+        ctx.n, ctx.dtype, ctx.window, ctx.precise = n, Q.dtype, window, bool(precise)
         return Y[:, :, :n].to(Q.dtype)
 
     @staticmethod
@@ -43,11 +43,12 @@ class _SharedFn(Function):
         Q, R, S, Vr, Vs, Y, m, l, words = ctx.saved_tensors
         words = words if words.numel() else None
         dY = _pad_rows(dY.contiguous().to(torch.bfloat16), Q.size(2) - ctx.n)
-        grads = _ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, None, ctx.window, 0, False, 0, words)
-        return tuple(g[:, :, :ctx.n].to(ctx.dtype) for g in grads) + (None, None, None, None)
+        grads = _ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, None, ctx.window, 0, False, 0, words,
+                                    precise=ctx.precise)
+        return tuple(g[:, :, :ctx.n].to(ctx.dtype) for g in grads) + (None, None, None, None, None)
 
 
-def single_gather_shared_attention(Q, R, S, Vr, Vs, mask=None, fwd_group=0, rs_group=0, window=WINDOW):
+def single_gather_shared_attention(Q, R, S, Vr, Vs, mask=None, fwd_group=0, rs_group=0, window=WINDOW, *, precise=False):
     """Q: [B,Hq,N,128]; R, S, Vr, Vs: [B,1,N,128].  Causal `window` (16, 32, 64 or
     128) on both key axes, optionally narrowed by `mask` ([B,N,N] or [N,N] bool).
 
@@ -55,5 +56,6 @@ def single_gather_shared_attention(Q, R, S, Vr, Vs, mask=None, fwd_group=0, rs_g
     divisible by a non-zero group): the sm_100a kernels always let one CTA walk
     all query heads of a KV head, so every value runs the same schedule and gives
     bit-identical results.  A query with a single visible key gets exactly zero
-    score gradients.  Inputs and dY are cast to BF16; accumulation is FP32."""
-    return _SharedFn.apply(Q, R, S, Vr, Vs, mask, fwd_group, rs_group, window)
+    score gradients.  Inputs and dY are cast to BF16; accumulation is FP32.  precise=True: score
+    products on the exact value + residual split of Q o R (see single_gather_attention)."""
+    return _SharedFn.apply(Q, R, S, Vr, Vs, mask, fwd_group, rs_group, window, precise)

@@ -68,8 +68,8 @@ std::atomic<int> g_fwd_block{0}, g_bwd_block{0};
 // Extensions of the current call (att3_sg_forward_ext / att3_sg_backward_ext set them around the regular entry
 // point on the calling thread): the window of the S / Vs key axis when it differs from the R / Vr axis's, and the
 // caller's mask as packed words.
-struct SgExt { int window_s; const uint32_t* mask_words; int layout; void* Y_act; };
-thread_local SgExt t_ext = {0, nullptr, 0, nullptr};
+struct SgExt { int window_s; const uint32_t* mask_words; int layout; void* Y_act; int precise; };
+thread_local SgExt t_ext = {0, nullptr, 0, nullptr, 0};
 int ext_window_s(int window) { return t_ext.window_s > 0 ? t_ext.window_s : window; }
 
 // Packed schedule (sg_pack_q.cuh, sg_pack_kv.cuh): windows of at most 64 keys, D = 128, at least four query
@@ -77,7 +77,7 @@ int ext_window_s(int window) { return t_ext.window_s > 0 ? t_ext.window_s : wind
 std::atomic<int> g_pack_off{0};
 bool pack_eligible(int Hq, int Hkv, int D, int window, int q_begin) {
     return !g_pack_off.load() && D == 128 && window >= 1 && window <= 64 && Hq / Hkv >= 4 && q_begin % 8 == 0 &&
-           ext_window_s(window) == window;          // equal windows on both key axes
+           ext_window_s(window) == window && !t_ext.precise;     // equal windows on both key axes, plain products
 }
 int pack_slots(int window) { return window <= 16 ? 16 : window <= 32 ? 32 : 64; }
 int round_up8(int v) { return (v + 7) / 8 * 8; }
@@ -279,6 +279,7 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
     p.l = l;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
     p.window_s = ext_window_s(window);
+    p.precise = t_ext.precise;
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status_ptr();
     if (!p.status) return att3::set_error(ATT3_ERR_CUDA, "att3_sg_forward: status word not resolvable");
@@ -299,7 +300,7 @@ extern "C" int att3_sg_forward(const void* Q, const void* R, const void* S, cons
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // the lean instantiation unless an extension is in use
-    const bool ext = p.bnhd || p.Y_act || p.mask_words || p.window_s != p.window;
+    const bool ext = p.bnhd || p.Y_act || p.mask_words || p.window_s != p.window || p.precise;
     if (ext) return D == 64 ? launch_ring_fwd<64, true>(p, nblk, st) : launch_ring_fwd<128, true>(p, nblk, st);
     return D == 64 ? launch_ring_fwd<64, false>(p, nblk, st) : launch_ring_fwd<128, false>(p, nblk, st);
 }
@@ -343,7 +344,7 @@ static int launch_ring_bwd_x(const sgring::BwdParams& p, int nblk, cudaStream_t 
 template <int D, bool WITH_DQ>
 static int launch_ring_bwd(const sgring::BwdParams& p, int nblk, cudaStream_t stream) {
     // the lean instantiation unless an extension is in use
-    const bool ext = p.bnhd || p.mask_words || p.window_oth != p.window;
+    const bool ext = p.bnhd || p.mask_words || p.window_oth != p.window || p.precise;
     return ext ? launch_ring_bwd_x<D, WITH_DQ, true>(p, nblk, stream) : launch_ring_bwd_x<D, WITH_DQ, false>(p, nblk, stream);
 }
 
@@ -512,6 +513,7 @@ static int sg_backward_impl(int passes, bool kv_f32, const void* dY, const void*
     p.mask = mask;
     p.mask_words = t_ext.mask_words;
     p.bnhd = t_ext.layout;
+    p.precise = t_ext.precise;
     p.dQ = static_cast<__nv_bfloat16*>(dQ);
     p.part_K = static_cast<float*>(workspace);
     p.block_len = bwd_block_len(B, Hkv, N);
@@ -600,14 +602,16 @@ static int check_ext(const char* who, const att3_sg_ext* ext, int window, const 
         return att3::set_error(ATT3_ERR_INVALID, "%s: mask_words must be 4-byte aligned", who);
     if (ext->layout != 0 && ext->layout != 1)
         return att3::set_error(ATT3_ERR_INVALID, "%s: layout must be 0 ([B,H,N,D]) or 1 ([B,N,H,D]), got %d", who, ext->layout);
+    if (ext->precise && window == 0)
+        return att3::set_error(ATT3_ERR_UNSUPPORTED, "%s: the compensated products need the windowed path (window 1..128)", who);
     if ((ext->layout || ext->Y_act) && window == 0)
         return att3::set_error(ATT3_ERR_UNSUPPORTED, "%s: the [B,N,H,D] layout and the activated output need the windowed path (window 1..128)", who);
     return ATT3_OK;
 }
 
 struct ExtScope {       // sets the calling thread's extension state for the duration of one call
-    explicit ExtScope(const att3_sg_ext* ext) { if (ext) t_ext = SgExt{ext->window_s, ext->mask_words, ext->layout, ext->Y_act}; }
-    ~ExtScope() { t_ext = SgExt{0, nullptr, 0, nullptr}; }
+    explicit ExtScope(const att3_sg_ext* ext) { if (ext) t_ext = SgExt{ext->window_s, ext->mask_words, ext->layout, ext->Y_act, ext->precise}; }
+    ~ExtScope() { t_ext = SgExt{0, nullptr, 0, nullptr, 0}; }
 };
 
 extern "C" int att3_sg_forward_ext(const void* Q, const void* R, const void* S, const void* Vr, const void* Vs,

@@ -91,6 +91,7 @@ struct BwdParams {
     float* part_V;                   // [planes][B,Hkv,N,D] FP32 partials of dVb
     int B, Hq, Hkv, N, window, q_begin, block_len, planes;
     int bnhd;                        // memory layout of Q, dY, Y, dQ and the key tensors: 0 [B,H,N,D], 1 [B,N,H,D] (RowAddr)
+    int precise;                     // 1: score product on Q o Ka split into its BF16 value and the exact BF16 residual
     int window_oth;                  // window on the other side's key axis (`window` is the own side's); equal unless asymmetric
     float scale;
     int* status;
@@ -170,6 +171,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
     const int x_bnhd = EXT ? p.bnhd : 0;
     const int x_window_oth = EXT ? p.window_oth : p.window;
     const uint32_t* const x_mask_words = EXT ? p.mask_words : nullptr;
+    const bool x_precise = EXT && p.precise != 0;
     using L = PipeSmem<D, WITH_DQ>;
     constexpr int CH = D / 8;            // 16-byte chunks per row
     constexpr int DW = D / 2;            // packed words per row
@@ -367,14 +369,15 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 if (it + 1 < n_iter) h_stage(it + 1, next_qoff(i, hh), (hh == 0 && i + 1 < q1) ? i + 1 : -1);
                 const bool work = any_vis && l_i > 0.f;
                 const int qb = n & 1, gb = n % GB;
-                uint8_t* dQp = sQp + qb * L::TILE;
+                uint8_t* dQp = sQp + (x_precise ? 0 : qb) * L::TILE;      // compensated mode: buffer 0 value, buffer 1 residual
                 uint8_t* dG = sG + gb * L::TILE;
                 const uint4* q4 = reinterpret_cast<const uint4*>(sStage + (it & 1) * 2 * D);
                 const uint4* y4 = q4 + CH;
                 if (work) {
                     // Buffer reuse: Qp[n&1] was last read by the dKb MMAs of head n-2.  Each per-buffer
                     // barrier is waited on at every one of its phases.
-                    if (n >= 2) ok = pipe_wait(&bars[PB_D_DONE0 + qb], ((n >> 1) - 1) & 1, sFail);
+                    if (!x_precise) { if (n >= 2) ok = pipe_wait(&bars[PB_D_DONE0 + qb], ((n >> 1) - 1) & 1, sFail); }
+                    else if (n >= 1) ok = pipe_wait(&bars[PB_D_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail);
                     if (!ok) break;
                     // The staged row is read in batches of HB chunks ahead of the stores: the compiler
                     // cannot tell that the tile stores do not alias the staging area, and would otherwise
@@ -392,6 +395,14 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                             o.z = mul_bf16x2(q[c].z, rKa[4 * (c0 + c) + 2]);
                             o.w = mul_bf16x2(q[c].w, rKa[4 * (c0 + c) + 3]);
                             *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c0 + c)) = o;
+                            if (EXT && x_precise) {
+                                uint4 lo;
+                                lo.x = mul_residual_bf16x2(q[c].x, rKa[4 * (c0 + c)], o.x);
+                                lo.y = mul_residual_bf16x2(q[c].y, rKa[4 * (c0 + c) + 1], o.y);
+                                lo.z = mul_residual_bf16x2(q[c].z, rKa[4 * (c0 + c) + 2], o.z);
+                                lo.w = mul_residual_bf16x2(q[c].w, rKa[4 * (c0 + c) + 3], o.w);
+                                *reinterpret_cast<uint4*>(dQp + L::TILE + sw128_offset<RING>(hslot, c0 + c)) = lo;
+                            }
                         }
                     }
                 }
@@ -534,7 +545,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
             if (r) {
                 tc_fence_after();
                 const uint32_t tA = tmem_base + C_R0 + (m & 1) * 128 + 32;
-                const uint32_t qoff = (m & 1) * (L::TILE / 16);
+                const uint32_t qoff = x_precise ? 0u : (m & 1) * (L::TILE / 16);
                 run_ts(tAK, tA, dQpM + qoff, 1);
                 umma_commit_pred(&bars[PB_D_DONE0 + (m & 1)], issuer);
                 if (acc_commit_pending) commit_acc();
@@ -592,7 +603,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 }
                 const uint32_t ph = n & 1;
                 const int qb = n & 1, gb = n % GB;
-                const uint32_t qoff = qb * (L::TILE / 16), goff = gb * (L::TILE / 16);   // buffer offsets, 16-byte units
+                const uint32_t qoff = x_precise ? 0u : qb * (L::TILE / 16), goff = gb * (L::TILE / 16);   // buffer offsets, 16-byte units
                 const uint32_t tA = tmem_base + C_R0 + (n & 1) * 128;          // X^T, then P^T | gA^T
                 const uint32_t tB = tmem_base + C_R0 + ((n & 1) ^ 1) * 128;    // dP^T, then W
                 ok = pipe_wait(&bars[PB_QP_FULL0 + qb], (n >> 1) & 1, sFail);
@@ -601,6 +612,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                 if (!ok) break;
                 tc_fence_after();
                 run_ss(tA, dKb, dQpK + qoff);                  // X^T = Kb Qp^T
+                if (EXT && x_precise) {                        // + Kb (residual tile)^T
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        const uint32_t off = (kk >> 2) * (RING * 128 / 16) + (kk & 3) * 2;
+                        umma_ss_pred(tA, dKb + off, dQpK + L::TILE / 16 + off, idesc_s, 1, issuer);
+                    }
+                }
                 umma_commit_pred(&bars[PB_S_XT], issuer);
                 if (!WITH_DQ && dk_pending) {
                     ok = issue_dk(n - 1);
@@ -637,6 +655,11 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     umma_commit_pred(&bars[PB_W_FULL], issuer);
                     run_ts(tAK, tA + 32, dQpM + qoff, 1);      // dKb += gA^T Qp
                     umma_commit_pred(&bars[PB_D_DONE0 + qb], issuer);
+                } else if (EXT && x_precise) {
+                    // both Qp buffers belong to this head: its dKb MMAs cannot be kept back behind the next head's
+                    // score product, which needs the buffers rewritten first
+                    ok = issue_dk(n);
+                    if (!ok) break;
                 } else {
                     dk_pending = true;
                 }

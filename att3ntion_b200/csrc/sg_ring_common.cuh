@@ -128,6 +128,16 @@ __device__ __forceinline__ MaskView mask_view(const uint8_t* bytes, const uint32
                     words ? words + static_cast<size_t>(b) * N * NW : nullptr, N, NW};
 }
 
+// Residual of a packed BF16 product: with hi = bf16x2(a * b) (round to nearest), returns bf16x2(a * b - hi).  The
+// product of two BF16 numbers has at most 16 significant bits, so it is exact in FP32, and so is the difference,
+// which has at most 8 significant bits and is therefore exact in BF16 (barring underflow): hi + lo carries the
+// product without rounding.  This is the split the reference prototyped as its "compensated" path
+// (docs/KERNEL_HISTORY.md:22: high + residual parts of each BF16 product).
+__device__ __forceinline__ uint32_t mul_residual_bf16x2(uint32_t a, uint32_t b, uint32_t hi) {
+    const float2 fa = unpack_bf16x2(a), fb = unpack_bf16x2(b), fh = unpack_bf16x2(hi);
+    return pack_bf16x2(fa.x * fb.x - fh.x, fa.y * fb.y - fh.y);
+}
+
 // Memory layout of the [B,H,N,D] operands.  0: B,H,N,D contiguous (the reference's, cuda/forward.cu:1609-1631).
 // 1: B,N,H,D contiguous -- what a projection x W gives before the head split is permuted and copied
 // (att3ntion/_autograd.py:349-363 does that copy for every operand of every call).  Statistics are [B,H,N] in

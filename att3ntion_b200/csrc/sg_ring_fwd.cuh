@@ -68,6 +68,7 @@ struct FwdParams {
     int B, Hq, Hkv, N, window, q_begin, block_len;
     int bnhd;                      // memory layout of Q, R, S, Vr, Vs, Y: 0 [B,H,N,D], 1 [B,N,H,D] (RowAddr)
     __nv_bfloat16* Y_act;          // optional second output QuickGELU(Y) = Y * sigmoid(1.702 Y), laid out like Y; or null
+    int precise;                   // 1: the score product runs on Q o R split into its BF16 value and the exact BF16 residual
     int window_s;                  // window on the S / Vs key axis (`window` is the R / Vr axis's); equal unless asymmetric
     float scale;
     int* status;                   // device status word (bounded-wait failures)
@@ -112,6 +113,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
     const int x_window_s = EXT ? p.window_s : p.window;
     __nv_bfloat16* const x_Y_act = EXT ? p.Y_act : nullptr;
     const uint32_t* const x_mask_words = EXT ? p.mask_words : nullptr;
+    const bool x_precise = EXT && p.precise != 0;
     using L = FwdSmem<D>;
     constexpr int CH = D / 8;            // 16-byte chunks per row
     constexpr int DW = D / 2;            // packed bf16x2 words per row
@@ -296,10 +298,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                     h_stage(it + 1, hh + 1 < G ? i : i + 1, hh + 1 < G ? hh + 1 : 0, (hh == 0 && i + 1 < q1) ? i + 1 : -1);
                 const int qb = n & 1;
                 if (work) {
-                    // Qp[n&1] was last read by the score MMAs of head n-2
-                    if (n >= 2) ok = pipe_wait<true>(&bars[FB_X_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, 11);
+                    // Qp[n&1] was last read by the score MMAs of head n-2.  In the compensated mode a head fills both
+                    // buffers (value, residual), which the score MMAs of head n-1 were the last to read.
+                    if (!x_precise) { if (n >= 2) ok = pipe_wait<true>(&bars[FB_X_DONE0 + qb], ((n >> 1) - 1) & 1, sFail, 11); }
+                    else if (n >= 1) ok = pipe_wait<true>(&bars[FB_X_DONE0 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, sFail, 11);
                     if (!ok) break;
-                    uint8_t* dQp = sQp + qb * L::TILE;
+                    uint8_t* dQp = sQp + (x_precise ? 0 : qb) * L::TILE;
                     const uint4* q4 = reinterpret_cast<const uint4*>(sQst + (it & 1) * D);
                     // The staged row is read in batches ahead of the stores: the compiler cannot tell that the
                     // tile stores do not alias the staging area and would otherwise serialise per chunk.
@@ -316,6 +320,14 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                             o.z = mul_bf16x2(q[c].z, rR[4 * (c0 + c) + 2]);
                             o.w = mul_bf16x2(q[c].w, rR[4 * (c0 + c) + 3]);
                             *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c0 + c)) = o;
+                            if (EXT && x_precise) {
+                                uint4 lo;
+                                lo.x = mul_residual_bf16x2(q[c].x, rR[4 * (c0 + c)], o.x);
+                                lo.y = mul_residual_bf16x2(q[c].y, rR[4 * (c0 + c) + 1], o.y);
+                                lo.z = mul_residual_bf16x2(q[c].z, rR[4 * (c0 + c) + 2], o.z);
+                                lo.w = mul_residual_bf16x2(q[c].w, rR[4 * (c0 + c) + 3], o.w);
+                                *reinterpret_cast<uint4*>(dQp + L::TILE + sw128_offset<RING>(hslot, c0 + c)) = lo;
+                            }
                         }
                     }
                 }
@@ -387,11 +399,18 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                 tc_fence_after();
                 {
                     const uint32_t tX = tmem_base + qb * 256;
-                    const uint64_t dA = dQp + qb * (L::TILE / 16);
+                    const uint64_t dA = dQp + (x_precise ? 0 : qb) * (L::TILE / 16);
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         const uint32_t off = (kk >> 2) * (RING * 128 / 16) + (kk & 3) * 2;
                         umma_ss_pred(tX, dA + off, dS + off, idesc_x, kk > 0, issuer);
+                    }
+                    if (EXT && x_precise) {          // + residual tile: X = (value + residual) S^T
+#pragma unroll
+                        for (int kk = 0; kk < D / 16; ++kk) {
+                            const uint32_t off = (kk >> 2) * (RING * 128 / 16) + (kk & 3) * 2;
+                            umma_ss_pred(tX, dA + L::TILE / 16 + off, dS + off, idesc_x, 1, issuer);
+                        }
                     }
                     umma_commit_pred(&bars[FB_X_DONE0 + qb], issuer);
                 }

@@ -392,8 +392,8 @@ def run_single(args):
     flops_step = 16 * D * triplets(B, HQ, N, w)
 
     def step():
-        Y, m, l = ck.sg_forward_raw(Q, R, S, Vr, Vs, None, w)
-        return Y, ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, None, w)
+        Y, m, l = ck.sg_forward_raw(Q, R, S, Vr, Vs, None, w, precise=args.precise)
+        return Y, ck.sg_backward_raw(dY, Q, R, S, Vr, Vs, Y, m, l, None, w, precise=args.precise)
 
     if args.profile:
         # kernel-only run for profiler captures: exact warm-up count, no gate, no e2e, no CPU leg
@@ -905,6 +905,8 @@ if __name__ == "__main__":
                     help="(batch, head) partition: ranks per batch shard (default: batches first)")
     ap.add_argument("--fwd-block", type=int, default=0, help="queries per forward CTA (0: built-in choice)")
     ap.add_argument("--bwd-block", type=int, default=0, help="queries per backward CTA (0: built-in choice)")
+    ap.add_argument("--precise", action="store_true",
+                    help="with --profile: time the compensated score products (value + residual split of Q o R)")
     ap.add_argument("--profile", action="store_true",
                     help="kernel-only run for profiler captures: exact warm-up count, no gate, no e2e and no CPU leg")
     ap.add_argument("--refgpu-child", action="store_true", help=argparse.SUPPRESS)

@@ -127,6 +127,11 @@ int att3_sg_backward_kv32(const void* dY, const void* Q, const void* R, const vo
  *               layout 0 on every call (att3ntion/_autograd.py:349-363), which this removes.  m, l stay [B,H,N].
  *   Y_act       forward only: a second output QuickGELU(Y) = Y * sigmoid(1.702 Y), laid out like Y (the module's
  *               activation, att3ntion/_autograd.py:254-256, written from the forward's epilogue), or NULL.
+ *   precise     1: the score product runs on the Hadamard operand split into its BF16 value and the exact BF16
+ *               residual (two tensor-core products instead of one), so the scores carry no rounding of Q o R; the
+ *               reference prototyped this "compensated" path for its stress gates and did not ship it
+ *               (docs/KERNEL_HISTORY.md:22, 185).  Forward and backward must use the same setting.  Always the
+ *               128-slot ring schedule; 1.8x the time of the plain call at the headline shape (27.0 against 14.9 ms).
  * All need window >= 1.  att3_sg_pack_mask produces the words (and, optionally, the per-query count of
  * visible keys inside the causal window saturated at 2, [B, N] bytes; window = 0: the mask alone). */
 typedef struct att3_sg_ext {
@@ -134,6 +139,7 @@ typedef struct att3_sg_ext {
     const uint32_t* mask_words;
     int layout;
     void* Y_act;
+    int precise;
 } att3_sg_ext;
 
 int att3_sg_forward_ext(const void* Q, const void* R, const void* S, const void* Vr, const void* Vs,

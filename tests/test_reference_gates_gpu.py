@@ -356,3 +356,31 @@ def test_module_window_path_reads_projections_in_place():
         _autograd.TILE = tile
     assert torch.allclose(y, y2, rtol=2e-2, atol=2e-2)
     assert torch.allclose(gx, x.grad, rtol=5e-2, atol=5e-2) and torch.allclose(gw, mod.Wq.weight.grad, rtol=5e-2, atol=5e-1)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("dist", ["scale4", "concentrated"])
+@pytest.mark.parametrize("seed", [0, 1])
+def test_compensated_products_pass_the_stress_gates(D, dist, seed):
+    """precise=True: the score product on the exact split of Q o R.  The two stress distributions whose scores are
+    large enough for the BF16 rounding of that operand to matter (and which fail without it, above) pass the
+    reference's gates."""
+    from att3ntion_b200 import single_gather_attention
+    B, H, N = 1, 2, 65
+    xs, dY = draw_dist(B, H, N, D, seed, dist)
+    mask = make_mask("causal", B, N)
+    ref = O.single_gather_dense(*[xs[n] for n in NAMES], mask=mask, dY=dY)
+    leaves = {n: xs[n].cuda().requires_grad_(True) for n in NAMES}
+    Y = single_gather_attention(*[leaves[n] for n in NAMES], mask.cuda(), window=N, precise=True)
+    Y.backward(dY.cuda())
+    check(Y.detach(), {g: leaves[n].grad for g, n in zip(GRADS, NAMES)}, ref)
+
+
+def test_compensated_products_on_the_shared_kv_operator():
+    from att3ntion_b200 import single_gather_shared_attention
+    xs, dY = draw(2, 8, 400, 128, seed=77, hkv=1, scale=1.5)
+    ref = O.single_gather_banded(*[xs[n] for n in NAMES], window=128, dY=dY, chunk=40)
+    leaves = {n: xs[n].cuda().requires_grad_(True) for n in NAMES}
+    Y = single_gather_shared_attention(*[leaves[n] for n in NAMES], None, window=128, precise=True)
+    Y.backward(dY.cuda())
+    check(Y.detach(), {g: leaves[n].grad for g, n in zip(GRADS, NAMES)}, ref)
