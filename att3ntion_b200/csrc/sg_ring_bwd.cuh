@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                             o.y = mul_bf16x2(q[c].y, rKa[4 * (c0 + c) + 1]);
                             o.z = mul_bf16x2(q[c].z, rKa[4 * (c0 + c) + 2]);
                             o.w = mul_bf16x2(q[c].w, rKa[4 * (c0 + c) + 3]);
-                            *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c0 + c)) = o;
+                            st_shared_v4(dQp + sw128_offset<RING>(hslot, c0 + c), o.x, o.y, o.z, o.w);
                             if (EXT && x_precise) {
                                 uint4 lo;
                                 lo.x = mul_residual_bf16x2(q[c].x, rKa[4 * (c0 + c)], o.x);
@@ -442,7 +442,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                             gq.y = mul_bf16x2(y[c].y, rVa[4 * (c0 + c) + 1]);
                             gq.z = mul_bf16x2(y[c].z, rVa[4 * (c0 + c) + 2]);
                             gq.w = mul_bf16x2(y[c].w, rVa[4 * (c0 + c) + 3]);
-                            *reinterpret_cast<uint4*>(dG + sw128_offset<RING>(hslot, c0 + c)) = gq;
+                            st_shared_v4(dG + sw128_offset<RING>(hslot, c0 + c), gq.x, gq.y, gq.z, gq.w);
                         }
                     }
                     fence_async_smem();
@@ -758,6 +758,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     continue;
                 }
                 const float lse2 = m_i * LOG2E + __log2f(l_i);
+                // packed FP32 arithmetic: one instruction for two columns
+                const uint64_t c2p = pair_f32(c2, c2), lsep = pair_f32(-lse2, -lse2), dltp = pair_f32(-delta, -delta);
                 const uint32_t ph = n & 1;
                 const uint32_t tA = tl + C_R0 + (n & 1) * 128 + ch * 64;          // this thread's 64 score columns
                 const uint32_t tB = tl + C_R0 + ((n & 1) ^ 1) * 128;
@@ -776,8 +778,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     const uint32_t cw = cc ? cw1 : cw0;
 #pragma unroll
                     for (int t = 0; t < 32; t += 2) {
-                        float p0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2, -lse2));
-                        float p1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2, -lse2));
+                        float a0, a1;
+                        unpair_f32(fma_f32x2(pair_b32(x[t], x[t + 1]), c2p, lsep), a0, a1);
+                        float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
                         if (!all_vis) {
                             if (!((cw >> t) & 1u)) p0 = 0.f;
                             if (!((cw >> (t + 1)) & 1u)) p1 = 0.f;
@@ -805,11 +808,12 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                         warp_arrive(&bars[PB_B_FREE], lane);
                     }
                     // packed BF16 product: (dP - delta) is rounded to BF16 like P before them (both are MMA
-                    // operands in BF16 anyway); four instructions a pair instead of seven
+                    // operands in BF16 anyway); three instructions a pair
 #pragma unroll
                     for (int t = 0; t < 32; t += 2) {
-                        const uint32_t d2 = pack_bf16x2(__uint_as_float(dp[t]) - delta, __uint_as_float(dp[t + 1]) - delta);
-                        pk[t >> 1] = single ? 0u : mul_bf16x2(pk[t >> 1], d2);
+                        float d0, d1;
+                        unpair_f32(add_f32x2(pair_b32(dp[t], dp[t + 1]), dltp), d0, d1);
+                        pk[t >> 1] = single ? 0u : mul_bf16x2(pk[t >> 1], pack_bf16x2(d0, d1));
                     }
                     tmem_st16(tA + 32 + cc * 16, pk);
                 }
@@ -825,8 +829,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     float* red = sRed + (n & 1) * 4 * D;
 #pragma unroll 1
                     for (int c = 0; c < NC; ++c) {
-                        // two rounds of 16 columns keep the live set small (this role runs on 80 registers)
-                        float va[16], vb[16];
+                        // two rounds of 16 columns keep the live set small (this role runs on 80 registers).  W is
+                        // rounded to BF16 pairs and multiplied by the packed Kb words as they are: two instructions a pair
+                        uint32_t w[16];
                         {
                             uint32_t u[16];
                             tmem_ld16(tB + ch * HD + c * 32, u);
@@ -837,11 +842,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                                     sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + q));
                                 const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float2 kf = unpack_bf16x2(w4[e]);
-                                    va[q * 8 + 2 * e] = kf.x * __uint_as_float(u[q * 8 + 2 * e]);
-                                    va[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[q * 8 + 2 * e + 1]);
-                                }
+                                for (int e = 0; e < 4; ++e)
+                                    w[q * 4 + e] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[q * 8 + 2 * e]),
+                                                                          __uint_as_float(u[q * 8 + 2 * e + 1])), w4[e]);
                             }
                         }
                         {
@@ -859,11 +862,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                                     sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + 2 + q));
                                 const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float2 kf = unpack_bf16x2(w4[e]);
-                                    vb[q * 8 + 2 * e] = kf.x * __uint_as_float(u[q * 8 + 2 * e]);
-                                    vb[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[q * 8 + 2 * e + 1]);
-                                }
+                                for (int e = 0; e < 4; ++e)
+                                    w[8 + q * 4 + e] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[q * 8 + 2 * e]),
+                                                                              __uint_as_float(u[q * 8 + 2 * e + 1])), w4[e]);
                             }
                         }
                         // the query's last head: this warp is done with the Kb rows of the ring
@@ -871,7 +872,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                             warp_arrive(&bars[PB_RING_FREE], lane);
                             ring_arrived = true;
                         }
-                        const float s = warp_transpose_sum_2x16_packed(va, vb, lane);
+                        const float s = warp_transpose_sum_words(w, lane);
                         red[(warp & 3) * D + ch * HD + c * 32 + lane] = s;
                     }
                     warp_arrive(&bars[PB_E_SYNC2], lane);

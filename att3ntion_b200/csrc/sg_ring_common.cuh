@@ -205,13 +205,8 @@ __device__ __forceinline__ float warp_transpose_sum_2x16(float (&va)[16], float 
 // lane share a register), the last one and the result in FP32: 80 instead of ~125 instructions.  The
 // partial sums are rounded to BF16 at each of the four packed stages (relative 2^-9 each), which is the
 // precision of the MMA operands these sums are built from; the gates leave an order of magnitude of room.
-__device__ __forceinline__ float warp_transpose_sum_2x16_packed(const float (&va)[16], const float (&vb)[16], int lane) {
-    uint32_t w[16];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        w[k] = pack_bf16x2(va[2 * k], va[2 * k + 1]);           // values 2k, 2k+1
-        w[8 + k] = pack_bf16x2(vb[2 * k], vb[2 * k + 1]);       // values 16+2k, 16+2k+1
-    }
+// w[k] holds this lane's values 2k and 2k+1 as a BF16 pair.
+__device__ __forceinline__ float warp_transpose_sum_words(uint32_t (&w)[16], int lane) {
     // stage o (in values) exchanges value v with v ^ o across lanes l and l ^ o; in packed registers that is
     // register r with r ^ (o/2) for o >= 2
 #pragma unroll
@@ -235,6 +230,17 @@ __device__ __forceinline__ float warp_transpose_sum_2x16_packed(const float (&va
     const float send = odd ? mine.x : mine.y;
     const float keep = odd ? mine.y : mine.x;
     return keep + __shfl_xor_sync(0xFFFFFFFFu, send, 1);
+}
+
+// The same from FP32 values: one rounding to BF16 first.
+__device__ __forceinline__ float warp_transpose_sum_2x16_packed(const float (&va)[16], const float (&vb)[16], int lane) {
+    uint32_t w[16];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        w[k] = pack_bf16x2(va[2 * k], va[2 * k + 1]);           // values 2k, 2k+1
+        w[8 + k] = pack_bf16x2(vb[2 * k], vb[2 * k + 1]);       // values 16+2k, 16+2k+1
+    }
+    return warp_transpose_sum_words(w, lane);
 }
 
 }  // namespace sgring

@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                             o.y = mul_bf16x2(q[c].y, rR[4 * (c0 + c) + 1]);
                             o.z = mul_bf16x2(q[c].z, rR[4 * (c0 + c) + 2]);
                             o.w = mul_bf16x2(q[c].w, rR[4 * (c0 + c) + 3]);
-                            *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c0 + c)) = o;
+                            st_shared_v4(dQp + sw128_offset<RING>(hslot, c0 + c), o.x, o.y, o.z, o.w);
                             if (EXT && x_precise) {
                                 uint4 lo;
                                 lo.x = mul_residual_bf16x2(q[c].x, rR[4 * (c0 + c)], o.x);
@@ -487,18 +487,17 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
             constexpr int NC = HD / 32;
 #pragma unroll
             for (int c = 0; c < NC; ++c) {      // unrolled: rVr must be indexed with constants to stay in registers
-                // two rounds of 16 columns keep the live set small
-                float va[16], vb[16];
+                // two rounds of 16 columns keep the live set small.  U is rounded to BF16 pairs and multiplied by the
+                // packed Vr words as they are: two instructions a pair, and the lane sum below wants BF16 pairs anyway
+                uint32_t w[16];
                 {
                     uint32_t u[16];
                     tmem_ld16(tU + c * 32, u);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int t = 0; t < 16; t += 2) {
-                        const float2 vr = unpack_bf16x2(rVr[c * 16 + (t >> 1)]);
-                        va[t] = vr.x * __uint_as_float(u[t]);
-                        va[t + 1] = vr.y * __uint_as_float(u[t + 1]);
-                    }
+                    for (int t = 0; t < 16; t += 2)
+                        w[t >> 1] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
+                                               rVr[c * 16 + (t >> 1)]);
                 }
                 {
                     uint32_t u[16];
@@ -510,15 +509,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                         warp_arrive(&bars[FB_U_FREE0 + ub], lane);
                     }
 #pragma unroll
-                    for (int t = 0; t < 16; t += 2) {
-                        const float2 vr = unpack_bf16x2(rVr[c * 16 + 8 + (t >> 1)]);
-                        vb[t] = vr.x * __uint_as_float(u[t]);
-                        vb[t + 1] = vr.y * __uint_as_float(u[t + 1]);
-                    }
+                    for (int t = 0; t < 16; t += 2)
+                        w[8 + (t >> 1)] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
+                                                     rVr[c * 16 + 8 + (t >> 1)]);
                 }
                 // (a shared-memory transpose for this lane sum was measured slower: it competes with the
                 //  MMA operand reads for shared-memory bandwidth)
-                const float s = warp_transpose_sum_2x16_packed(va, vb, lane);
+                const float s = warp_transpose_sum_words(w, lane);
                 red[quarter * (D + 4) + ch * HD + c * 32 + lane] = s;
             }
             float wl = l_half;
@@ -563,7 +560,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
             else { vs[0] = vw[0]; vs[1] = vw[1]; vs[2] = vw[2]; vs[3] = vw[3]; }
             const int n_rows = __popc(vw[0]) + __popc(vw[1]) + __popc(vw[2]) + __popc(vw[3]);
             const int n_cols = __popc(vs[0]) + __popc(vs[1]) + __popc(vs[2]) + __popc(vs[3]);
-            const int n_vis = min(n_rows, n_cols);               // 0: no visible pair
+            const bool live = min(n_rows, n_cols) != 0;          // false: no visible pair
             const bool all_vis = n_rows == RING && n_cols == RING;
             const bool my_vis = (vw[quarter] >> lane) & 1u;
             // visibility words of this thread's two 32-column chunks
@@ -573,12 +570,56 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
             for (int hh = 0; hh < G && ok; ++hh) {
                 const size_t row = row_at(i, hh);
                 const bool boundary = hh == 0 && i > q0;
-                if (n_vis == 0) {
+                const int xb = n & 1;
+                const uint32_t tX = tl + xb * 256 + ch * 64;          // this thread's 64 score columns
+                if (live) {
+                    ok = pipe_wait<true>(&bars[FB_X_DONE0 + xb], (n >> 1) & 1, sFail, 30);
+                    if (!ok) break;
+                    tc_fence_after();
+                    // ---- maximum of this thread's half row; the other half belongs to the thread with the same
+                    //      lane in the partner warp, and the exchange completes behind the epilogue below
+                    // four independent running maxima: one chain of 64 dependent max operations would cost
+                    // more than the loads
+                    float mh0 = -INFINITY, mh1 = -INFINITY, mh2 = -INFINITY, mh3 = -INFINITY;
+#pragma unroll 1
+                    for (int cc = 0; cc < 2; ++cc) {
+                        uint32_t x[32];
+                        tmem_ld32(tX + cc * 32, x);
+                        tmem_wait_ld();
+                        const uint32_t cw = cc ? cw1 : cw0;
+                        if (all_vis) {
+#pragma unroll
+                            for (int t = 0; t < 32; t += 8) {
+                                mh0 = fmaxf(mh0, fmaxf(__uint_as_float(x[t]), __uint_as_float(x[t + 1])));
+                                mh1 = fmaxf(mh1, fmaxf(__uint_as_float(x[t + 2]), __uint_as_float(x[t + 3])));
+                                mh2 = fmaxf(mh2, fmaxf(__uint_as_float(x[t + 4]), __uint_as_float(x[t + 5])));
+                                mh3 = fmaxf(mh3, fmaxf(__uint_as_float(x[t + 6]), __uint_as_float(x[t + 7])));
+                            }
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < 32; t += 4) {
+                                if ((cw >> t) & 1u) mh0 = fmaxf(mh0, __uint_as_float(x[t]));
+                                if ((cw >> (t + 1)) & 1u) mh1 = fmaxf(mh1, __uint_as_float(x[t + 1]));
+                                if ((cw >> (t + 2)) & 1u) mh2 = fmaxf(mh2, __uint_as_float(x[t + 2]));
+                                if ((cw >> (t + 3)) & 1u) mh3 = fmaxf(mh3, __uint_as_float(x[t + 3]));
+                            }
+                        }
+                    }
+                    const float mh = fmaxf(fmaxf(mh0, mh1), fmaxf(mh2, mh3));
+                    {
+                        float m_w = mh;
+#pragma unroll
+                        for (int o = 16; o >= 1; o >>= 1) m_w = fmaxf(m_w, __shfl_xor_sync(0xFFFFFFFFu, m_w, o));
+                        if (lane == 0) sMpart[xb * 8 + warp] = m_w;
+                    }
+                    warp_arrive(&bars[FB_M_SYNC], lane);
+                }
+                // ---- epilogue of the previous head, behind its U product; then the ring rows of a new key
+                if (pend) { ok = epilogue(pend_n, pend_row, pend_off, pend_m, pend_l); pend = false; }
+                if (ok && boundary) ok = ring_update(i);
+                if (!ok) break;
+                if (!live) {
                     // No visible pair: Y = 0, m = NEG_INF, l = 0 (cuda/common.cuh:24).
-                    if (pend) { ok = epilogue(pend_n, pend_row, pend_off, pend_m, pend_l); pend = false; }
-                    if (!ok) break;
-                    if (boundary) ok = ring_update(i);
-                    if (!ok) break;
                     if (tid < D) {
                         p.Y[qoff_at(i, hh) + tid] = __float2bfloat16(0.f);
                         if (x_Y_act) x_Y_act[qoff_at(i, hh) + tid] = __float2bfloat16(0.f);
@@ -586,52 +627,6 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                     if (tid == 0) { p.m[row] = NEG_INF_F; p.l[row] = 0.f; }
                     continue;
                 }
-                const int xb = n & 1;
-                const uint32_t tX = tl + xb * 256 + ch * 64;          // this thread's 64 score columns
-                ok = pipe_wait<true>(&bars[FB_X_DONE0 + xb], (n >> 1) & 1, sFail, 30);
-                if (!ok) break;
-                tc_fence_after();
-                // ---- maximum of this thread's half row; the other half belongs to the thread with the same
-                //      lane in the partner warp, and the exchange completes behind the epilogue below
-                // four independent running maxima: one chain of 64 dependent max operations would cost
-                // more than the loads
-                float mh0 = -INFINITY, mh1 = -INFINITY, mh2 = -INFINITY, mh3 = -INFINITY;
-#pragma unroll 1
-                for (int cc = 0; cc < 2; ++cc) {
-                    uint32_t x[32];
-                    tmem_ld32(tX + cc * 32, x);
-                    tmem_wait_ld();
-                    const uint32_t cw = cc ? cw1 : cw0;
-                    if (all_vis) {
-#pragma unroll
-                        for (int t = 0; t < 32; t += 8) {
-                            mh0 = fmaxf(mh0, fmaxf(__uint_as_float(x[t]), __uint_as_float(x[t + 1])));
-                            mh1 = fmaxf(mh1, fmaxf(__uint_as_float(x[t + 2]), __uint_as_float(x[t + 3])));
-                            mh2 = fmaxf(mh2, fmaxf(__uint_as_float(x[t + 4]), __uint_as_float(x[t + 5])));
-                            mh3 = fmaxf(mh3, fmaxf(__uint_as_float(x[t + 6]), __uint_as_float(x[t + 7])));
-                        }
-                    } else {
-#pragma unroll
-                        for (int t = 0; t < 32; t += 4) {
-                            if ((cw >> t) & 1u) mh0 = fmaxf(mh0, __uint_as_float(x[t]));
-                            if ((cw >> (t + 1)) & 1u) mh1 = fmaxf(mh1, __uint_as_float(x[t + 1]));
-                            if ((cw >> (t + 2)) & 1u) mh2 = fmaxf(mh2, __uint_as_float(x[t + 2]));
-                            if ((cw >> (t + 3)) & 1u) mh3 = fmaxf(mh3, __uint_as_float(x[t + 3]));
-                        }
-                    }
-                }
-                const float mh = fmaxf(fmaxf(mh0, mh1), fmaxf(mh2, mh3));
-                {
-                    float m_w = mh;
-#pragma unroll
-                    for (int o = 16; o >= 1; o >>= 1) m_w = fmaxf(m_w, __shfl_xor_sync(0xFFFFFFFFu, m_w, o));
-                    if (lane == 0) sMpart[xb * 8 + warp] = m_w;
-                }
-                warp_arrive(&bars[FB_M_SYNC], lane);
-                // ---- epilogue of the previous head, behind its U product; then the ring rows of a new key
-                if (pend) { ok = epilogue(pend_n, pend_row, pend_off, pend_m, pend_l); pend = false; }
-                if (ok && boundary) ok = ring_update(i);
-                if (!ok) break;
                 ok = pipe_wait<true>(&bars[FB_M_SYNC], n & 1, sFail, 31);
                 if (!ok) break;
                 const float* mp = sMpart + xb * 8;
@@ -639,7 +634,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                                       fmaxf(fmaxf(mp[4], mp[5]), fmaxf(mp[6], mp[7])));
                 const float mc = M * c2;
                 // ---- P = exp2((x - M) c2), BF16 over the first 32 of this thread's columns; half-row sum
-                float ls[4] = {0.f, 0.f, 0.f, 0.f};          // independent partial sums (no 32-long add chain)
+                // packed FP32 arithmetic: one instruction for the exponents of two columns, one for their sums
+                const uint64_t c2p = pair_f32(c2, c2), mcp = pair_f32(-mc, -mc);
+                uint64_t ls0 = pair_f32(0.f, 0.f), ls1 = ls0;          // two independent chains of partial sums
 #pragma unroll 1
                 for (int cc = 0; cc < 2; ++cc) {
                     uint32_t x[32], pk[16];
@@ -648,18 +645,25 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
                     const uint32_t cw = cc ? cw1 : cw0;
 #pragma unroll
                     for (int t = 0; t < 32; t += 2) {
-                        float e0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2, -mc));
-                        float e1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2, -mc));
+                        float a0, a1;
+                        unpair_f32(fma_f32x2(pair_b32(x[t], x[t + 1]), c2p, mcp), a0, a1);
+                        float e0 = fast_exp2(a0), e1 = fast_exp2(a1);
                         if (!all_vis) {
                             if (!((cw >> t) & 1u)) e0 = 0.f;
                             if (!((cw >> (t + 1)) & 1u)) e1 = 0.f;
                         }
-                        ls[(t >> 1) & 3] += e0 + e1;
+                        if (t & 2) ls1 = add_f32x2(ls1, pair_f32(e0, e1));
+                        else ls0 = add_f32x2(ls0, pair_f32(e0, e1));
                         pk[t >> 1] = pack_bf16x2(e0, e1);
                     }
                     tmem_st16(tX + cc * 16, pk);
                 }
-                const float l_half = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                float l_half;
+                {
+                    float s0, s1;
+                    unpair_f32(add_f32x2(ls0, ls1), s0, s1);
+                    l_half = s0 + s1;
+                }
                 tmem_wait_st();
                 tc_fence_before();
                 // P_full also tells the MMA warp that the Vs ring row is current (ring_update above)
