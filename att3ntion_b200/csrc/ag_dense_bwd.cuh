@@ -290,8 +290,8 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
                 o.y = mul_bf16x2(q.y, rKa[4 * c + 1]);  gq.y = mul_bf16x2(y.y, rVa[4 * c + 1]);
                 o.z = mul_bf16x2(q.z, rKa[4 * c + 2]);  gq.z = mul_bf16x2(y.z, rVa[4 * c + 2]);
                 o.w = mul_bf16x2(q.w, rKa[4 * c + 3]);  gq.w = mul_bf16x2(y.w, rVa[4 * c + 3]);
-                *reinterpret_cast<uint4*>(sQp + sw128_offset<TILE>(slot, cc)) = o;
-                *reinterpret_cast<uint4*>(sG + sw128_offset<TILE>(slot, cc)) = gq;
+                st_shared_v4(sQp + sw128_offset<TILE>(slot, cc), o.x, o.y, o.z, o.w);
+                st_shared_v4(sG + sw128_offset<TILE>(slot, cc), gq.x, gq.y, gq.z, gq.w);
             }
             fence_async_smem();
             tc_fence_before();

@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                         o.y = mul_bf16x2(q[4 * c + 1], rRw[4 * c + 1]);
                         o.z = mul_bf16x2(q[4 * c + 2], rRw[4 * c + 2]);
                         o.w = mul_bf16x2(q[4 * c + 3], rRw[4 * c + 3]);
-                        *reinterpret_cast<uint4*>(sQp + sw128_offset<TILE>(tid, c)) = o;
+                        st_shared_v4(sQp + sw128_offset<TILE>(tid, c), o.x, o.y, o.z, o.w);
                     }
                 }
                 fence_async_smem();

@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
                             o.y = mul_bf16x2(q[c].y, rKa[4 * (c0 + c) + 1]);
                             o.z = mul_bf16x2(q[c].z, rKa[4 * (c0 + c) + 2]);
                             o.w = mul_bf16x2(q[c].w, rKa[4 * (c0 + c) + 3]);
-                            *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c0 + c)) = o;
+                            st_shared_v4(dQp + sw128_offset<RING>(hslot, c0 + c), o.x, o.y, o.z, o.w);
                         }
                     }
                 }
@@ -408,7 +408,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
                             gq.y = mul_bf16x2(y[c].y, rVa[4 * (c0 + c) + 1]);
                             gq.z = mul_bf16x2(y[c].z, rVa[4 * (c0 + c) + 2]);
                             gq.w = mul_bf16x2(y[c].w, rVa[4 * (c0 + c) + 3]);
-                            *reinterpret_cast<uint4*>(dG + sw128_offset<RING>(hslot, c0 + c)) = gq;
+                            st_shared_v4(dG + sw128_offset<RING>(hslot, c0 + c), gq.x, gq.y, gq.z, gq.w);
                         }
                     }
                     fence_async_smem();
@@ -687,6 +687,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
                 ok = pipe_wait(&bars[KB_S_XT], ph, sFail);
                 if (!ok) break;
                 tc_fence_after();
+                const uint64_t c2p = pair_f32(c2, c2);
                 const bool warp0 = __ballot_sync(0xFFFFFFFFu, cw[0] != 0) != 0, warp1 = __ballot_sync(0xFFFFFFFFu, cw[1] != 0) != 0;
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
@@ -702,8 +703,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
 #pragma unroll
                         for (int t4 = 0; t4 < 32; t4 += 2) {
                             const float ls = lse2[(cc * 32 + t4) / W];
-                            float p0 = fast_exp2(fmaf(__uint_as_float(x[t4]), c2, -ls));
-                            float p1 = fast_exp2(fmaf(__uint_as_float(x[t4 + 1]), c2, -ls));
+                            float a0, a1;                     // packed FP32: two columns an instruction
+                            unpair_f32(fma_f32x2(pair_b32(x[t4], x[t4 + 1]), c2p, pair_f32(-ls, -ls)), a0, a1);
+                            float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
                             if (!((w >> t4) & 1u)) p0 = 0.f;
                             if (!((w >> (t4 + 1)) & 1u)) p1 = 0.f;
                             pk[t4 >> 1] = pack_bf16x2(p0, p1);
@@ -730,7 +732,9 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_kv_kernel(const KvPar
 #pragma unroll
                         for (int t4 = 0; t4 < 32; t4 += 2) {
                             const int q = (cc * 32 + t4) / W;
-                            const uint32_t d2 = pack_bf16x2(__uint_as_float(dp[t4]) - dlt[q], __uint_as_float(dp[t4 + 1]) - dlt[q]);
+                            float d0, d1;
+                            unpair_f32(add_f32x2(pair_b32(dp[t4], dp[t4 + 1]), pair_f32(-dlt[q], -dlt[q])), d0, d1);
+                            const uint32_t d2 = pack_bf16x2(d0, d1);
                             pk[t4 >> 1] = ((single >> q) & 1u) ? 0u : mul_bf16x2(pk[t4 >> 1], d2);
                         }
                     } else {

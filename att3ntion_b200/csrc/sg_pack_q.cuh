@@ -374,7 +374,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                             o.y = mul_bf16x2(q[c].y, rR[4 * (c0 + c) + 1]);
                             o.z = mul_bf16x2(q[c].z, rR[4 * (c0 + c) + 2]);
                             o.w = mul_bf16x2(q[c].w, rR[4 * (c0 + c) + 3]);
-                            *reinterpret_cast<uint4*>(dQp + sw128_offset<RING>(hslot, c0 + c)) = o;
+                            st_shared_v4(dQp + sw128_offset<RING>(hslot, c0 + c), o.x, o.y, o.z, o.w);
                         }
                     }
                 }
@@ -416,7 +416,7 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                                 o.y = mul_bf16x2(y[c].y, rVr[DQ ? 4 * (c0 + c) + 1 : 0]);
                                 o.z = mul_bf16x2(y[c].z, rVr[DQ ? 4 * (c0 + c) + 2 : 0]);
                                 o.w = mul_bf16x2(y[c].w, rVr[DQ ? 4 * (c0 + c) + 3 : 0]);
-                                *reinterpret_cast<uint4*>(sGt + sw128_offset<RING>(hslot, c0 + c)) = o;
+                                st_shared_v4(sGt + sw128_offset<RING>(hslot, c0 + c), o.x, o.y, o.z, o.w);
                             }
                         }
                         fence_async_smem();
@@ -591,41 +591,67 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
             constexpr int NC = HD / 32;
 #pragma unroll
             for (int c = 0; c < NC; ++c) {      // unrolled: rVr must be indexed with constants to stay in registers
-                float va[16], vb[16];
-                {
-                    uint32_t u[16];
-                    tmem_ld16(tU + c * 32, u);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int t = 0; t < 16; t += 2) {
-                        const float2 vr = unpack_bf16x2(rVr[c * 16 + (t >> 1)]);
-                        va[t] = vr.x * __uint_as_float(u[t]);
-                        va[t + 1] = vr.y * __uint_as_float(u[t + 1]);
-                    }
-                }
-                {
-                    uint32_t u[16];
-                    tmem_ld16(tU + c * 32 + 16, u);
-                    tmem_wait_ld();
-                    if (c == NC - 1) {
-                        // U is in registers: a later product may overwrite it
-                        tc_fence_before();
-                        warp_arrive(&bars[QB_U_FREE0 + ub], lane);
-                    }
-#pragma unroll
-                    for (int t = 0; t < 16; t += 2) {
-                        const float2 vr = unpack_bf16x2(rVr[c * 16 + 8 + (t >> 1)]);
-                        vb[t] = vr.x * __uint_as_float(u[t]);
-                        vb[t + 1] = vr.y * __uint_as_float(u[t + 1]);
-                    }
-                }
                 if (W == 16) {
+                    float va[16], vb[16];
+                    {
+                        uint32_t u[16];
+                        tmem_ld16(tU + c * 32, u);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int t = 0; t < 16; t += 2) {
+                            const float2 vr = unpack_bf16x2(rVr[c * 16 + (t >> 1)]);
+                            va[t] = vr.x * __uint_as_float(u[t]);
+                            va[t + 1] = vr.y * __uint_as_float(u[t + 1]);
+                        }
+                    }
+                    {
+                        uint32_t u[16];
+                        tmem_ld16(tU + c * 32 + 16, u);
+                        tmem_wait_ld();
+                        if (c == NC - 1) {
+                            // U is in registers: a later product may overwrite it
+                            tc_fence_before();
+                            warp_arrive(&bars[QB_U_FREE0 + ub], lane);
+                        }
+#pragma unroll
+                        for (int t = 0; t < 16; t += 2) {
+                            const float2 vr = unpack_bf16x2(rVr[c * 16 + 8 + (t >> 1)]);
+                            vb[t] = vr.x * __uint_as_float(u[t]);
+                            vb[t + 1] = vr.y * __uint_as_float(u[t + 1]);
+                        }
+                    }
                     float r0, r1;
                     halfwarp_transpose_sum_2x16(va, vb, lane, r0, r1);
                     red[unit * (D + 4) + ch * HD + c * 32 + (lane & 15)] = r0;
                     red[unit * (D + 4) + ch * HD + c * 32 + 16 + (lane & 15)] = r1;
                 } else {
-                    const float s = warp_transpose_sum_2x16(va, vb, lane);
+                    // U is rounded to BF16 pairs and multiplied by the packed Vr words as they are: two instructions
+                    // a pair, and the lane sum works on BF16 pairs anyway
+                    uint32_t w[16];
+                    {
+                        uint32_t u[16];
+                        tmem_ld16(tU + c * 32, u);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int t = 0; t < 16; t += 2)
+                            w[t >> 1] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
+                                                   rVr[c * 16 + (t >> 1)]);
+                    }
+                    {
+                        uint32_t u[16];
+                        tmem_ld16(tU + c * 32 + 16, u);
+                        tmem_wait_ld();
+                        if (c == NC - 1) {
+                            // U is in registers: a later product may overwrite it
+                            tc_fence_before();
+                            warp_arrive(&bars[QB_U_FREE0 + ub], lane);
+                        }
+#pragma unroll
+                        for (int t = 0; t < 16; t += 2)
+                            w[8 + (t >> 1)] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
+                                                         rVr[c * 16 + 8 + (t >> 1)]);
+                    }
+                    const float s = warp_transpose_sum_words(w, lane);
                     red[unit * (D + 4) + ch * HD + c * 32 + lane] = s;
                 }
             }
@@ -775,7 +801,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                     if (!live_g) M = 0.f;
                     const float mc = M * c2;
                     // ---- P = exp2((x - M) c2), BF16 over the first 32 of this thread's columns; half-row sum
-                    float ls[4] = {0.f, 0.f, 0.f, 0.f};
+                    const uint64_t c2p = pair_f32(c2, c2), mcp = pair_f32(-mc, -mc);     // packed FP32: two columns an instruction
+                    uint64_t ls0 = pair_f32(0.f, 0.f), ls1 = ls0;
 #pragma unroll 1
                     for (int cc = 0; cc < 2; ++cc) {
                         uint32_t pk[16];
@@ -789,11 +816,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                             const uint32_t cw = my_vis ? vw[ch * 2 + cc] : 0u;
 #pragma unroll
                             for (int t4 = 0; t4 < 32; t4 += 2) {
-                                float e0 = fast_exp2(fmaf(__uint_as_float(x[t4]), c2, -mc));
-                                float e1 = fast_exp2(fmaf(__uint_as_float(x[t4 + 1]), c2, -mc));
+                                float a0, a1;
+                                unpair_f32(fma_f32x2(pair_b32(x[t4], x[t4 + 1]), c2p, mcp), a0, a1);
+                                float e0 = fast_exp2(a0), e1 = fast_exp2(a1);
                                 if (!((cw >> t4) & 1u)) e0 = 0.f;
                                 if (!((cw >> (t4 + 1)) & 1u)) e1 = 0.f;
-                                ls[(t4 >> 1) & 3] += e0 + e1;
+                                if (t4 & 2) ls1 = add_f32x2(ls1, pair_f32(e0, e1));
+                                else ls0 = add_f32x2(ls0, pair_f32(e0, e1));
                                 pk[t4 >> 1] = pack_bf16x2(e0, e1);
                             }
                         }
@@ -804,13 +833,18 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                     // P_full also tells the MMA warp that the Vs ring rows are current (ring_update above)
                     warp_arrive(&bars[QB_P_FULL0 + xb], lane);
                     pend = true; pend_n = n; pend_row = row0; pend_off = qoff_at(i0, hh); pend_live = live_g; pend_M = M;
-                    pend_l = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                    {
+                        float s0, s1;
+                        unpair_f32(add_f32x2(ls0, ls1), s0, s1);
+                        pend_l = s0 + s1;
+                    }
                 } else {
                     // ---- gA = P o (dP - delta), P = exp2(x c2 - lse) from the forward's statistics; BF16 over the
                     //      first 32 of this thread's score columns.  A query with one visible key gets exact zeros.
                     const bool live_q = live_g && l_i > 0.f;
                     const float lse2 = live_q ? m_i * LOG2E + __log2f(l_i) : 0.f;
                     const bool zero_all = !live_q || n_vis == 1 || !my_vis;
+                    const uint64_t c2p = pair_f32(c2, c2), lsep = pair_f32(-lse2, -lse2), dltp = pair_f32(-dlt, -dlt);
 #pragma unroll 1
                     for (int cc = 0; cc < 2; ++cc) {
                         uint32_t pk[16];
@@ -827,8 +861,10 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
                                 tmem_wait_ld();
 #pragma unroll
                                 for (int t4 = 0; t4 < 16; t4 += 2) {
-                                    float g0 = fast_exp2(fmaf(__uint_as_float(x[t4]), c2, -lse2)) * (__uint_as_float(dp[t4]) - dlt);
-                                    float g1 = fast_exp2(fmaf(__uint_as_float(x[t4 + 1]), c2, -lse2)) * (__uint_as_float(dp[t4 + 1]) - dlt);
+                                    float a0, a1, d0, d1;
+                                    unpair_f32(fma_f32x2(pair_b32(x[t4], x[t4 + 1]), c2p, lsep), a0, a1);
+                                    unpair_f32(add_f32x2(pair_b32(dp[t4], dp[t4 + 1]), dltp), d0, d1);
+                                    float g0 = fast_exp2(a0) * d0, g1 = fast_exp2(a1) * d1;
                                     if (!((cw >> (r16 * 16 + t4)) & 1u)) g0 = 0.f;
                                     if (!((cw >> (r16 * 16 + t4 + 1)) & 1u)) g1 = 0.f;
                                     pk[r16 * 8 + (t4 >> 1)] = pack_bf16x2(g0, g1);
