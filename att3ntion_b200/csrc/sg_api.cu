@@ -394,6 +394,22 @@ static int launch_pack_kv(const sgpack::KvParams& p, int nblk, cudaStream_t stre
     return ATT3_OK;
 }
 
+// delta[b,h,i] = sum_d dY o Y, the pre-pass of every windowed backward.
+template <int D>
+static int launch_delta(const void* dY, const void* Y, float* delta, int B, int Hq, int N, cudaStream_t st) {
+    const size_t rows = static_cast<size_t>(B) * Hq * N;
+    const int threads = 256;
+    const unsigned blocks = static_cast<unsigned>((rows * 32 + threads - 1) / threads);
+    att3::TimedLaunch timed(att3::K_SG_REDUCE, st);
+    sgpack::sg_delta_kernel<D><<<blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(dY),
+                                                           static_cast<const __nv_bfloat16*>(Y), delta, rows, t_ext.layout,
+                                                           Hq, N);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: delta launch");
+    att3::count_launch(1);
+    return ATT3_OK;
+}
+
 // The backward on the packed schedule: delta, dQ from the query-anchored kernel, then one key-side kernel per side.
 static int pack_backward(int passes, bool kv_f32, const void* dY, const void* Q, const void* R, const void* S,
                          const void* Vr, const void* Vs, const void* Y, const float* m, const float* l,
@@ -411,18 +427,7 @@ static int pack_backward(int passes, bool kv_f32, const void* dY, const void* Q,
     float* part_V = part_K + static_cast<size_t>(planes) * plane;
     // delta sits behind the planes the workspace was sized for (which may be more than this launch uses)
     float* delta = part_K + static_cast<size_t>(2 * sgring::bwd_planes(bwd_block_len(B, Hkv, N))) * plane;
-    {
-        const size_t rows = static_cast<size_t>(B) * Hq * N;
-        const int threads = 256;
-        const unsigned blocks = static_cast<unsigned>((rows * 32 + threads - 1) / threads);
-        att3::TimedLaunch timed(att3::K_SG_REDUCE, st);
-        sgpack::sg_delta_kernel<D><<<blocks, threads, 0, st>>>(static_cast<const __nv_bfloat16*>(dY),
-                                                               static_cast<const __nv_bfloat16*>(Y), delta, rows,
-                                                               t_ext.layout, Hq, N);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return att3::set_cuda_error(e, "att3_sg_backward: delta launch");
-        att3::count_launch(1);
-    }
+    if (int rc = launch_delta<D>(dY, Y, delta, B, Hq, N, st)) return rc;
     int rc = ATT3_OK;
     sgpack::KvParams p{};
     p.Q = static_cast<const __nv_bfloat16*>(Q);
@@ -520,13 +525,17 @@ static int sg_backward_impl(int passes, bool kv_f32, const void* dY, const void*
     const int nblk = (N - q_begin + p.block_len - 1) / p.block_len;
     p.planes = sgring::bwd_planes(p.block_len);
     p.part_V = p.part_K + static_cast<size_t>(p.planes) * B * Hkv * N * D;
+    // delta sits behind the partial planes; each call computes it (a call may be one key side of two)
+    float* delta = p.part_K + static_cast<size_t>(2 * p.planes) * B * Hkv * N * D;
+    p.delta = delta;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.N = N; p.window = window; p.q_begin = q_begin;
     p.scale = 1.0f / sqrtf(static_cast<float>(D));
     p.status = status_ptr();
     if (!p.status) return att3::set_error(ATT3_ERR_CUDA, "att3_sg_backward: status word not resolvable");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-    int rc = ATT3_OK;
+    int rc = D == 64 ? launch_delta<64>(dY, Y, delta, B, Hq, N, st) : launch_delta<128>(dY, Y, delta, B, Hq, N, st);
+    if (rc) return rc;
     if (passes & 1) {
         // Pass 1: own side (S, Vs) -> dS, dVs, and dQ.
         p.window = ext_window_s(window);

@@ -86,6 +86,7 @@ struct BwdParams {
     const __nv_bfloat16* Vb;
     const uint8_t* mask;             // [B,N,N] or null
     const uint32_t* mask_words;    // the same mask as packed words [B,N,ceil(N/32)], or null (takes precedence)
+    const float* delta;              // [B,Hq,N]: rowsum(dY o Y), from the pre-pass (sg_delta_kernel)
     __nv_bfloat16* dQ;               // [B,Hq,N,D], written only by the WITH_DQ instantiation
     float* part_K;                   // [planes][B,Hkv,N,D] FP32 partials of dKb (plane-major)
     float* part_V;                   // [planes][B,Hkv,N,D] FP32 partials of dVb
@@ -701,22 +702,14 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
         }
         // The accumulators must be zero before the first accumulating MMA; that MMA waits for
         // P_full of the first head, which every E warp arrives on after this point.
-        // per-head scalars, fetched one iteration ahead: this lane's slice of dY and Y, and m, l
-        uint2 pre_dy = make_uint2(0, 0), pre_y = make_uint2(0, 0);
-        uint32_t pre_dy2[2] = {0, 0}, pre_y2[2] = {0, 0};
-        float pre_m = 0.f, pre_l = 0.f;
-        auto prefetch = [&](size_t row, size_t qoff) {
-            if (D == 128) {
-                pre_dy = __ldg(reinterpret_cast<const uint2*>(p.dY + qoff) + lane);
-                pre_y = __ldg(reinterpret_cast<const uint2*>(p.Y + qoff) + lane);
-            } else {
-                pre_dy2[0] = __ldg(reinterpret_cast<const uint32_t*>(p.dY + qoff) + lane);
-                pre_y2[0] = __ldg(reinterpret_cast<const uint32_t*>(p.Y + qoff) + lane);
-            }
+        // per-head scalars, fetched one iteration ahead: delta = dY . Y (from the pre-pass), m, l
+        float pre_d = 0.f, pre_m = 0.f, pre_l = 0.f;
+        auto prefetch = [&](size_t row) {
+            pre_d = __ldg(p.delta + row);
             pre_m = __ldg(p.m + row);
             pre_l = __ldg(p.l + row);
         };
-        prefetch(row_at(q0, 0), qoff_at(q0, 0));
+        prefetch(row_at(q0, 0));
         int n = 0, it = 0, n_query = 0;
         bool ok = true;
 #pragma unroll 1
@@ -739,20 +732,8 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
 #pragma unroll 1
             for (int hh = 0; hh < G && ok; ++hh, ++it) {
                 const size_t row = row_at(i, hh);
-                // delta = dY . Y and lse (log2 units) of this head from the prefetched slices
-                float delta;
-                if (D == 128) {
-                    const float2 a0 = unpack_bf16x2(pre_dy.x), a1 = unpack_bf16x2(pre_dy.y);
-                    const float2 b0 = unpack_bf16x2(pre_y.x), b1 = unpack_bf16x2(pre_y.y);
-                    delta = a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y;
-                } else {
-                    const float2 a0 = unpack_bf16x2(pre_dy2[0]), b0 = unpack_bf16x2(pre_y2[0]);
-                    delta = a0.x * b0.x + a0.y * b0.y;
-                }
-#pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) delta += __shfl_xor_sync(0xFFFFFFFFu, delta, o);
-                const float m_i = pre_m, l_i = pre_l;
-                if (it + 1 < n_iter) prefetch(next_row(i, hh), next_qoff(i, hh));
+                const float delta = pre_d, m_i = pre_m, l_i = pre_l;
+                if (it + 1 < n_iter) prefetch(next_row(i, hh));
                 if (n_vis == 0 || !(l_i > 0.f)) {
                     if (WITH_DQ && tid < D) p.dQ[qoff_at(i, hh) + tid] = __float2bfloat16(0.f);
                     continue;
