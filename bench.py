@@ -327,13 +327,13 @@ def kernel_times(lib):
 
 
 # DRAM bytes (read + write) of one sg_ring_bwd_kernel launch, from an ncu capture of the kernels at
-# B4 Hq8 Hkv1 N4096 D128 w128: 162.5 MB (key side S + dQ) and 140.0 MB (key side R), i.e. 9232 bytes
+# B4 Hq8 Hkv1 N4096 D128 w128: 123.1 MB (key side S + dQ) and 95.8 MB (key side R), i.e. 6683 bytes
 # per (batch, query) on average over the two launches of a step.  The traffic is per-row streaming
 # (Q, dY, Y rows, key rows, FP32 partial rows), so it scales with B*N; other head counts, head sizes
 # or windows have not been captured (None).
 def traffic_bytes_per_launch(batch, hq, hkv, n, d, w):
     if (hq, hkv, d, w) == (8, 1, 128, 128):
-        return 9232 * batch * n
+        return 6683 * batch * n
     return None
 
 
