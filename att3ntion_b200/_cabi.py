@@ -33,6 +33,9 @@ SIGNATURES = {
     "att3_hg_forward": (_i, [_vp] * 22 + [_i] * 7 + [_vp]),
     "att3_hg_backward_workspace_bytes": (_sz, [_i] * 4),
     "att3_hg_backward": (_i, [_vp] * 34 + [_i] * 7 + [_vp, _sz, _vp]),
+    "att3_hg_forward_axes": (_i, [_vp] * 22 + [_i] * 11 + [_vp]),
+    "att3_hg_backward_axes_workspace_bytes": (_sz, [_i] * 6),
+    "att3_hg_backward_axes": (_i, [_vp] * 34 + [_i] * 11 + [_vp, _sz, _vp]),
     "att3_sg_tile_ranges": (_i, [_i] * 6 + [C.POINTER(_i), _i]),
     "att3_pack_mask32": (C.c_uint32, [_vp, _i]),
     "att3_sg_query_blocks": (_i, [_i] * 6 + [C.POINTER(_i)]),

@@ -353,25 +353,33 @@ _HG_NAMES = ("Q", "R", "S", "Vq_1", "Vq_2", "Vr_1", "Vr_2", "Vs_1", "Vs_2")
 
 
 def _check_hg(tensors, mask, who):
-    Q = tensors[0]
+    """Shape contract of the three-gather operator (cuda/forward.cu:1281-1296): Q, Vq_* are [B,H,I,D], R, Vr_*
+    [B,H,J,D], S, Vs_* [B,H,K,D]; a mask needs I == J == K.  Returns (mask or None, (I, J, K))."""
+    Q, R, S = tensors[0], tensors[1], tensors[2]
     if not (isinstance(Q, torch.Tensor) and Q.is_cuda and Q.dim() == 4):
         raise RuntimeError(f"{who}: inputs must be CUDA [B,H,N,D] tensors")
-    B, H, N, D = Q.shape
+    B, H, I, D = Q.shape
     if D not in (16, 32, 64, 128):
         raise RuntimeError(f"{who}: head dim must be 16, 32, 64 or 128, got {D}")
-    if N % 16:
-        raise RuntimeError(f"{who}: N must be a multiple of 16, got {N}")
+    lead = {"Q": Q, "Vq_1": Q, "Vq_2": Q, "R": R, "Vr_1": R, "Vr_2": R, "S": S, "Vs_1": S, "Vs_2": S}
     for name, t in zip(_HG_NAMES, tensors):
         if not (t.is_cuda and t.device == Q.device and t.dtype == _BF16 and t.is_contiguous()):
             raise RuntimeError(f"{who}: {name} must be contiguous bf16 on Q's device")
-        if t.shape != Q.shape:
-            raise RuntimeError(f"{who}: masked/tensor-core path requires equal shapes, {name} is {tuple(t.shape)}")
+        if t.dim() != 4 or t.shape != lead[name].shape or t.shape[0] != B or t.shape[1] != H or t.shape[3] != D:
+            raise RuntimeError(f"{who}: {name} is {tuple(t.shape)}, expected {tuple(lead[name].shape)} "
+                               f"(batch, heads and head dim of Q; the length of its own axis)")
+    J, K = R.shape[2], S.shape[2]
+    for n in (I, J, K):
+        if n % 16:
+            raise RuntimeError(f"{who}: N must be a multiple of 16, got {n}")
     if mask is not None and mask.numel():
+        if not (I == J == K):
+            raise RuntimeError(f"{who}: masked/tensor-core path requires equal shapes (I == J == K), got {(I, J, K)}")
         if not (mask.is_cuda and mask.device == Q.device and mask.dtype == torch.bool and mask.is_contiguous()
-                and tuple(mask.shape) == (B, N, N)):
+                and tuple(mask.shape) == (B, I, I)):
             raise RuntimeError(f"{who}: mask must be a contiguous bool [B,N,N] on Q's device")
-        return mask
-    return None
+        return mask, (I, J, K)
+    return None, (I, J, K)
 
 
 def _scatter_in_use(*tensors) -> bool:
@@ -387,22 +395,18 @@ def forward(Q, R, S, Vq_1, Vq_2, Vr_1, Vr_2, Vs_1, Vs_2, dropout_rate=0.0, I_val
     `forward` (cpp/cuda_bindings.cpp:143-177).  dropout_rate is accepted and unused,
     as in the reference (cuda/forward.cu:1259)."""
     ts = [Q, R, S, Vq_1, Vq_2, Vr_1, Vr_2, Vs_1, Vs_2]
-    mask = _check_hg(ts, mask, "forward")
-    B, H, N, D = Q.shape
-    # The reference takes one valid length per role (cuda/forward.cu:1300-1302) and defaults each to the
-    # padded length.  These kernels take one length for all three roles; a call that asks for different
-    # ones would silently see other keys than it asked for, so it is rejected.
-    valid = [int(v) if 0 < int(v) <= N else N for v in (I_valid, J_valid, K_valid)]
-    if not (valid[0] == valid[1] == valid[2]):
-        raise RuntimeError(f"forward: I_valid, J_valid and K_valid must agree (one valid length for all three "
-                           f"roles), got {tuple(valid)}")
-    n_valid = valid[0] if valid[0] < N else 0
+    mask, (I, J, K) = _check_hg(ts, mask, "forward")
+    B, H, _, D = Q.shape
+    # one valid length per axis, each defaulting to the padded length (cuda/forward.cu:1300-1302)
+    valid = [int(v) if 0 < int(v) <= n else n for v, n in zip((I_valid, J_valid, K_valid), (I, J, K))]
     scatter = 1 if (gather_mode == 0 and _scatter_in_use(Vq_2, Vr_2, Vs_2)) else 0
+    if scatter and not (I == J == K):
+        raise RuntimeError(f"forward: Scatter requires I == J == K, got {(I, J, K)}")
     with torch.cuda.device(Q.device):
-        outs = [torch.empty_like(Q) for _ in range(6)]
-        stats = [torch.empty((B, H, N), dtype=torch.float32, device=Q.device) for _ in range(6)]
-        _call(lib.att3_hg_forward, *[t.data_ptr() for t in ts], _ptr(mask), *[o.data_ptr() for o in outs],
-              *[s.data_ptr() for s in stats], B, H, N, D, n_valid, int(gather_mode), scatter, _stream(Q))
+        outs = [torch.empty_like(t) for t in (Q, R, S, Q, R, S)]
+        stats = [torch.empty((B, H, n), dtype=torch.float32, device=Q.device) for n in (I, I, J, J, K, K)]
+        _call(lib.att3_hg_forward_axes, *[t.data_ptr() for t in ts], _ptr(mask), *[o.data_ptr() for o in outs],
+              *[s.data_ptr() for s in stats], B, H, I, J, K, D, *valid, int(gather_mode), scatter, _stream(Q))
     return (*outs, *stats)
 
 
@@ -411,24 +415,28 @@ def backward(grad_Y_q, grad_Y_r, grad_Y_s, grad_Y_q_, grad_Y_r_, grad_Y_s_, Q, R
     """Nine gradients from the forward's statistics (cpp/cuda_bindings.cpp:179-233).  The
     gather outputs Y_q, Y_r, Y_s are required: the Jacobian correction is rowsum(dY o Y)."""
     ts = [Q, R, S, Vq_1, Vq_2, Vr_1, Vr_2, Vs_1, Vs_2]
-    mask = _check_hg(ts, mask, "backward")
+    mask, (I, J, K) = _check_hg(ts, mask, "backward")
     if Y_q is None or Y_r is None or Y_s is None:
         raise RuntimeError("backward: tensor-core path unavailable without the forward outputs Y_q, Y_r, Y_s")
-    B, H, N, D = Q.shape
+    B, H, _, D = Q.shape
     gs = [grad_Y_q, grad_Y_r, grad_Y_s, grad_Y_q_, grad_Y_r_, grad_Y_s_]
-    for g in gs + [Y_q, Y_r, Y_s]:
-        if not (g.is_cuda and g.device == Q.device and g.dtype == _BF16 and g.is_contiguous() and g.shape == Q.shape):
-            raise RuntimeError("backward: cotangents and outputs must be contiguous bf16 [B,H,N,D] on Q's device")
+    for g, like in zip(gs + [Y_q, Y_r, Y_s], (Q, R, S, Q, R, S, Q, R, S)):
+        if not (g.is_cuda and g.device == Q.device and g.dtype == _BF16 and g.is_contiguous() and g.shape == like.shape):
+            raise RuntimeError("backward: cotangents and outputs must be contiguous bf16 on Q's device, shaped like "
+                               "the tensor of their axis ([B,H,I,D], [B,H,J,D], [B,H,K,D])")
     # gather_mode 1 leaves (m = +1e30, l = 1) in the R/S statistics (cuda/forward.cu:1455-1459)
     gather_mode = 1 if bool((m_j[0, 0, 0] > 1e29).item()) else 0
     scatter = 1 if (gather_mode == 0 and _scatter_in_use(grad_Y_q_, grad_Y_r_, grad_Y_s_)) else 0
+    if scatter and not (I == J == K):
+        raise RuntimeError(f"backward: Scatter requires I == J == K, got {(I, J, K)}")
     with torch.cuda.device(Q.device):
-        grads = [torch.empty_like(Q) for _ in range(9)]
-        nbytes = lib.att3_hg_backward_workspace_bytes(B, H, N, D)
+        grads = [torch.empty_like(t) for t in ts]
+        nbytes = lib.att3_hg_backward_axes_workspace_bytes(B, H, I, J, K, D)
         ws = _workspace(Q.device, nbytes)
-        _call(lib.att3_hg_backward, *[g.data_ptr() for g in gs], *[t.data_ptr() for t in ts],
+        # the reference's backward takes no valid lengths: padded slots take part (cpp/cuda_bindings.cpp:179-205)
+        _call(lib.att3_hg_backward_axes, *[g.data_ptr() for g in gs], *[t.data_ptr() for t in ts],
               Y_q.data_ptr(), Y_r.data_ptr(), Y_s.data_ptr(),
               m_i.data_ptr(), l_i.data_ptr(), m_j.data_ptr(), l_j.data_ptr(), m_k.data_ptr(), l_k.data_ptr(),
-              _ptr(mask), *[g.data_ptr() for g in grads], B, H, N, D, 0, gather_mode, scatter,
+              _ptr(mask), *[g.data_ptr() for g in grads], B, H, I, J, K, D, 0, 0, 0, gather_mode, scatter,
               ws.data_ptr(), nbytes, _stream(Q))
     return tuple(grads)

@@ -33,26 +33,28 @@ namespace agdense {
 constexpr int BWD_THREADS = 256;
 
 struct BwdParams {
-    const __nv_bfloat16* A;          // anchor rows         [B,H,N,D]
+    const __nv_bfloat16* A;          // anchor rows         [B,H,NA,D]  (dY, Y, m, l likewise)
     const __nv_bfloat16* dY;         // cotangent of the gather's output
     const __nv_bfloat16* Y;          // the gather's output
     const float* m;                  // [B,H,N] statistics of the gather (per anchor)
     const float* l;
-    const __nv_bfloat16* Ka;         // other side
+    const __nv_bfloat16* Ka;         // other side          [B,H,N_oth,D]
     const __nv_bfloat16* Va;
-    const __nv_bfloat16* Kb;         // own side
+    const __nv_bfloat16* Kb;         // own side            [B,H,N_own,D]
     const __nv_bfloat16* Vb;
-    const uint8_t* mask;             // [B,N,N] or null
-    float* dKb;                      // [B,H,N,D] FP32, this kernel adds into it
+    const uint8_t* mask;             // [B,N,N] or null (then NA = N_own = N_oth = N)
+    float* dKb;                      // [B,H,N_own,D] FP32, this kernel adds into it
     float* dVb;
-    float* dA_part;                  // [n_tiles][B,H,N,D] FP32 partial planes, zero-filled by the caller
+    float* dA_part;                  // [own tiles][B,H,NA,D] FP32 partial planes, zero-filled by the caller
     // Anchor chunks: with few (tile, batch, head) triples the anchors are split over a_chunks CTAs per
     // triple (grid.x = n_tiles * a_chunks).  Chunk 0 adds into dKb / dVb; chunk 1 adds into its own
     // zero-filled planes, which the caller adds afterwards, so the order of the sums stays fixed.
     int a_chunks;                    // 1 or 2
     float* dKb1;
     float* dVb1;
-    int B, H, N, D, n_valid;
+    // Lengths of the anchor, own-side and other-side axes and how many leading entries of each are real (0 or > length:
+    // all); a_valid only matters to the scatter forms.
+    int B, H, NA, N_own, N_oth, D, a_valid, own_valid, oth_valid;
     float scale;
     int* status;
     // Scatter forms (SC = 1, 2): statistics of the softmaxes anchored at the own and at the other index, and
@@ -114,11 +116,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
     const int slot = tid & (TILE - 1);
     const int half = tid >> 7;
     const int b = blockIdx.z, h = blockIdx.y;
-    const int N = p.N, D = p.D;
-    const int n_keys = (p.n_valid > 0 && p.n_valid < N) ? p.n_valid : N;
-    const int n_tiles = (n_keys + TILE - 1) / TILE;
-    const int kb = blockIdx.x % n_tiles, chunk = blockIdx.x / n_tiles;
-    const int n_anchors = SC ? n_keys : N;            // padded anchors take no part in a scatter sum
+    const int N = p.NA, D = p.D;                 // N: the mask's side (a mask needs equal lengths)
+    const int n_own = (p.own_valid > 0 && p.own_valid < p.N_own) ? p.own_valid : p.N_own;
+    const int n_oth = (p.oth_valid > 0 && p.oth_valid < p.N_oth) ? p.oth_valid : p.N_oth;
+    const int n_anch = (p.a_valid > 0 && p.a_valid < p.NA) ? p.a_valid : p.NA;
+    const int own_tiles = (n_own + TILE - 1) / TILE, oth_tiles = (n_oth + TILE - 1) / TILE;
+    const int kb = blockIdx.x % own_tiles, chunk = blockIdx.x / own_tiles;
+    const int n_anchors = SC ? n_anch : p.NA;         // padded anchors take no part in a scatter sum
     const int a_begin = static_cast<int>((static_cast<long long>(n_anchors) * chunk) / p.a_chunks);
     const int a_end = static_cast<int>((static_cast<long long>(n_anchors) * (chunk + 1)) / p.a_chunks);
 
@@ -131,14 +135,15 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
         fence_mbar_init();
         *sFail = 0;
     }
-    const size_t bh = (static_cast<size_t>(b) * p.H + h) * N;
+    const size_t bh = (static_cast<size_t>(b) * p.H + h) * p.NA;                   // anchor-indexed arrays
+    const size_t bh_own = (static_cast<size_t>(b) * p.H + h) * p.N_own, bh_oth = (static_cast<size_t>(b) * p.H + h) * p.N_oth;
     const __nv_bfloat16* gA = p.A + bh * D;
     const __nv_bfloat16* gdY = p.dY + bh * D;
     const __nv_bfloat16* gY = p.Y + bh * D;
-    const __nv_bfloat16* gKa = p.Ka + bh * D;
-    const __nv_bfloat16* gVa = p.Va + bh * D;
-    const __nv_bfloat16* gKb = p.Kb + bh * D;
-    const __nv_bfloat16* gVb = p.Vb + bh * D;
+    const __nv_bfloat16* gKa = p.Ka + bh_oth * D;
+    const __nv_bfloat16* gVa = p.Va + bh_oth * D;
+    const __nv_bfloat16* gKb = p.Kb + bh_own * D;
+    const __nv_bfloat16* gVb = p.Vb + bh_own * D;
     const uint8_t* mask_b = p.mask ? p.mask + static_cast<size_t>(b) * N * N : nullptr;
     const int own_key = kb * TILE + slot;
 
@@ -148,7 +153,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
         for (int c = 0; c < HCH; ++c) {
             const int cc = half * HCH + c;
             uint4 v = make_uint4(0, 0, 0, 0);
-            if (idx < n_keys && cc * 8 < D) v = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(idx) * D) + cc);
+            if (idx < n_own && cc * 8 < D) v = __ldg(reinterpret_cast<const uint4*>(src + static_cast<size_t>(idx) * D) + cc);
             *reinterpret_cast<uint4*>(dst + sw128_offset<TILE>(slot, cc)) = v;
         }
     };
@@ -181,17 +186,17 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
     const float c2 = p.scale * LOG2E;
     uint32_t phase = 0;
     bool failed = false;
-    float* gPart = WITH_DA ? p.dA_part + (static_cast<size_t>(kb) * p.B * p.H * N + bh) * D : nullptr;
+    float* gPart = WITH_DA ? p.dA_part + (static_cast<size_t>(kb) * p.B * p.H * p.NA + bh) * D : nullptr;
     // scatter forms: constants of this thread's own key; a dead or padded anchor gets an LSE that makes its
     // softmax vanish
     float lse_own = 1e30f, c_own = 0.f;
-    if (SC && own_key < n_keys) {
-        const float lo = __ldg(p.l_own + bh + own_key);
-        if (lo > 0.f) lse_own = __ldg(p.m_own + bh + own_key) * LOG2E + __log2f(lo);
-        if (SC == 2) c_own = __ldg(p.C_own + bh + own_key);
+    if (SC && own_key < n_own) {
+        const float lo = __ldg(p.l_own + bh_own + own_key);
+        if (lo > 0.f) lse_own = __ldg(p.m_own + bh_own + own_key) * LOG2E + __log2f(lo);
+        if (SC == 2) c_own = __ldg(p.C_own + bh_own + own_key);
     }
 
-    for (int jb = 0; jb < n_tiles && !failed; ++jb) {
+    for (int jb = 0; jb < oth_tiles && !failed; ++jb) {
         // other-side tile: this thread's half row of Ka and Va in registers (Ka also in smem for W)
         uint32_t rKa[HW], rVa[HW];
         const int oth_key = jb * TILE + slot;
@@ -199,7 +204,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
         for (int c = 0; c < HCH; ++c) {
             const int cc = half * HCH + c;
             uint4 a = make_uint4(0, 0, 0, 0), v = a;
-            if (oth_key < n_keys && cc * 8 < D) {
+            if (oth_key < n_oth && cc * 8 < D) {
                 a = __ldg(reinterpret_cast<const uint4*>(gKa + static_cast<size_t>(oth_key) * D) + cc);
                 v = __ldg(reinterpret_cast<const uint4*>(gVa + static_cast<size_t>(oth_key) * D) + cc);
             }
@@ -213,21 +218,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
         if (SC) {
             if (half == 0) {
                 float lt = 1e30f, ct = 0.f;
-                if (oth_key < n_keys) {
-                    const float l = __ldg(p.l_oth + bh + oth_key);
-                    if (l > 0.f) lt = __ldg(p.m_oth + bh + oth_key) * LOG2E + __log2f(l);
-                    if (SC == 2) ct = __ldg(p.C_oth + bh + oth_key);
+                if (oth_key < n_oth) {
+                    const float l = __ldg(p.l_oth + bh_oth + oth_key);
+                    if (l > 0.f) lt = __ldg(p.m_oth + bh_oth + oth_key) * LOG2E + __log2f(l);
+                    if (SC == 2) ct = __ldg(p.C_oth + bh_oth + oth_key);
                 }
                 sColL[slot] = lt;
                 sColC[slot] = ct;
             }
-            if (own_key < n_keys) {
+            if (own_key < n_own) {
 #pragma unroll 1
                 for (int rd = 0; rd < 2; ++rd) {
                     uint32_t wo = 0, wt = 0;
                     for (int t = 0; t < 32; ++t) {
                         const int j = jb * TILE + (2 * rd + half) * 32 + t;
-                        if (j >= n_keys) break;
+                        if (j >= n_oth) break;
                         const bool so = !mask_b || mask_b[static_cast<size_t>(own_key) * N + j] != 0;
                         const bool st = !mask_b || mask_b[static_cast<size_t>(j) * N + own_key] != 0;
                         wo |= static_cast<uint32_t>(so) << t;
@@ -242,7 +247,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
         for (int a = a_begin; a < a_end && !failed; ++a) {
             // visibility from anchor a: own-side keys of this tile, other-side keys of tile jb
             {
-                bool vo = own_key < n_keys, vt = oth_key < n_keys;
+                bool vo = own_key < n_own, vt = oth_key < n_oth;
                 if (mask_b && SC) {
                     // the anchors of the two softmaxes are the own and the other key: each must see a
                     if (vo) vo = mask_b[static_cast<size_t>(own_key) * N + a] != 0;
@@ -444,11 +449,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
         for (int c = 0; c < DP / 32; ++c) {
             tmem_ld32(tl + (half ? C_AV : C_AK) + c * 32, acc);
             tmem_wait_ld();
-            if (own_key < n_keys) {
+            if (own_key < n_own) {
 #pragma unroll
                 for (int t = 0; t < 32; ++t) {
                     const int d = c * 32 + t;
-                    if (d < D) dst_base[(bh + own_key) * D + d] += mul * __uint_as_float(acc[t]);
+                    if (d < D) dst_base[(bh_own + own_key) * D + d] += mul * __uint_as_float(acc[t]);
                 }
             }
         }

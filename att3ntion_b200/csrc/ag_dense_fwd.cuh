@@ -36,16 +36,19 @@ constexpr int NTHREADS = 128;
 constexpr int MAX_GROUP = 16;       // anchors per CTA
 
 struct FwdParams {
-    const __nv_bfloat16* A;         // anchor   [B,H,N,D]
-    const __nv_bfloat16* Rw;        // rows     [B,H,N,D]
-    const __nv_bfloat16* C;         // cols     [B,H,N,D]
-    const __nv_bfloat16* Vrow;
-    const __nv_bfloat16* Vcol;
-    const uint8_t* mask;            // [B,N,N] or null; row index = anchor
-    __nv_bfloat16* Y;               // [B,H,N,D]
-    float* m;                       // [B,H,N]
+    const __nv_bfloat16* A;         // anchor   [B,H,NA,D]
+    const __nv_bfloat16* Rw;        // rows     [B,H,NR,D]
+    const __nv_bfloat16* C;         // cols     [B,H,NC,D]
+    const __nv_bfloat16* Vrow;      // [B,H,NR,D]
+    const __nv_bfloat16* Vcol;      // [B,H,NC,D]
+    const uint8_t* mask;            // [B,N,N] or null (then NA = NR = NC = N); row index = anchor
+    __nv_bfloat16* Y;               // [B,H,NA,D]
+    float* m;                       // [B,H,NA]
     float* l;
-    int B, H, N, D, n_valid, group;
+    // Lengths of the three index axes and how many leading entries of each are real (the rest is padding that stays
+    // out of every softmax; 0 or > length: all).  The reference's gather takes the same five numbers
+    // (cuda/forward.cu:1436-1452: n_anchor, n_rows, rows_valid, n_cols, cols_valid); a_valid only matters to the scatter form.
+    int B, H, NA, NR, NC, D, a_valid, r_valid, c_valid, group;
     float scale;
     int* status;
     // Scatter form (SC kernels only): statistics of the softmaxes anchored at the row index and at the col index
@@ -112,10 +115,12 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t issuer = elect_one();     // one lane per warp; warp 0 predicates its MMAs on it
     const int b = blockIdx.z, h = blockIdx.y;
-    const int N = p.N, D = p.D;
-    const int n_keys = (p.n_valid > 0 && p.n_valid < N) ? p.n_valid : N;   // keys at or past this index are padding
+    const int N = p.NA, D = p.D;                 // N: the mask's side (a mask needs equal lengths)
+    const int n_rows = (p.r_valid > 0 && p.r_valid < p.NR) ? p.r_valid : p.NR;   // rows at or past this index are padding
+    const int n_cols = (p.c_valid > 0 && p.c_valid < p.NC) ? p.c_valid : p.NC;
+    const int n_anch = (p.a_valid > 0 && p.a_valid < p.NA) ? p.a_valid : p.NA;
     const int a0 = blockIdx.x * p.group;
-    const int a1 = min(a0 + p.group, SC ? n_keys : p.N);     // padded anchors take no part in a scatter sum
+    const int a1 = min(a0 + p.group, SC ? n_anch : p.NA);    // padded anchors take no part in a scatter sum
     if (a0 >= a1) return;
 
     if (warp == 0) {
@@ -131,12 +136,13 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
     for (int t = tid; t < MAX_GROUP * (DP + 4); t += NTHREADS) sState[t] = 0.f;
     if (tid < MAX_GROUP) sState[tid * (DP + 4) + DP] = -INFINITY;
 
-    const size_t bh = (static_cast<size_t>(b) * p.H + h) * N;
+    const size_t bh = (static_cast<size_t>(b) * p.H + h) * p.NA;        // anchor-indexed arrays
+    const size_t bh_r = (static_cast<size_t>(b) * p.H + h) * p.NR, bh_c = (static_cast<size_t>(b) * p.H + h) * p.NC;
     const __nv_bfloat16* gA = p.A + bh * D;
-    const __nv_bfloat16* gRw = p.Rw + bh * D;
-    const __nv_bfloat16* gC = p.C + bh * D;
-    const __nv_bfloat16* gVrow = p.Vrow + bh * D;
-    const __nv_bfloat16* gVcol = p.Vcol + bh * D;
+    const __nv_bfloat16* gRw = p.Rw + bh_r * D;
+    const __nv_bfloat16* gC = p.C + bh_c * D;
+    const __nv_bfloat16* gVrow = p.Vrow + bh_r * D;
+    const __nv_bfloat16* gVcol = p.Vcol + bh_c * D;
     const uint8_t* mask_b = p.mask ? p.mask + static_cast<size_t>(b) * N * N : nullptr;
 
     tc_fence_before();
@@ -154,30 +160,30 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
     uint32_t phase = 0;
     bool failed = false;
 
-    const int n_tiles = (n_keys + TILE - 1) / TILE;
-    for (int jb = 0; jb < n_tiles && !failed; ++jb) {
+    const int row_tiles = (n_rows + TILE - 1) / TILE, col_tiles = (n_cols + TILE - 1) / TILE;
+    for (int jb = 0; jb < row_tiles && !failed; ++jb) {
         uint32_t rRw[DW], rVr[DW];
         const int jrow = jb * TILE + tid;
-        load_row_padded<DP>(gRw, jrow, n_keys, D, rRw);
-        load_row_padded<DP>(gVrow, jrow, n_keys, D, rVr);
+        load_row_padded<DP>(gRw, jrow, n_rows, D, rRw);
+        load_row_padded<DP>(gVrow, jrow, n_rows, D, rVr);
         // scatter form: LSE (log2 units) of the softmax anchored at this thread's row; an anchor without any
         // visible cell (l = 0) or a padded one gets a value that makes every weight vanish
         float lse_row = 1e30f;
-        if (SC && jrow < n_keys) {
-            const float lu = __ldg(p.l_row + bh + jrow);
-            if (lu > 0.f) lse_row = __ldg(p.m_row + bh + jrow) * LOG2E + __log2f(lu);
+        if (SC && jrow < n_rows) {
+            const float lu = __ldg(p.l_row + bh_r + jrow);
+            if (lu > 0.f) lse_row = __ldg(p.m_row + bh_r + jrow) * LOG2E + __log2f(lu);
         }
-        for (int kb = 0; kb < n_tiles && !failed; ++kb) {
+        for (int kb = 0; kb < col_tiles && !failed; ++kb) {
             // stage the col tile; every MMA that read the previous one has been waited for
             {
                 uint32_t t[DW];
                 const int krow = kb * TILE + tid;
-                load_row_padded<DP>(gC, krow, n_keys, D, t);
+                load_row_padded<DP>(gC, krow, n_cols, D, t);
 #pragma unroll
                 for (int c = 0; c < CH; ++c)
                     *reinterpret_cast<uint4*>(sC + sw128_offset<TILE>(tid, c)) =
                         make_uint4(t[4 * c], t[4 * c + 1], t[4 * c + 2], t[4 * c + 3]);
-                load_row_padded<DP>(gVcol, krow, n_keys, D, t);
+                load_row_padded<DP>(gVcol, krow, n_cols, D, t);
 #pragma unroll
                 for (int c = 0; c < CH; ++c)
                     *reinterpret_cast<uint4*>(sVc + sw128_offset<TILE>(tid, c)) =
@@ -188,17 +194,17 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
             if (SC) {
                 const int krow = kb * TILE + tid;
                 float lc = 1e30f;
-                if (krow < n_keys) {
-                    const float lv = __ldg(p.l_col + bh + krow);
-                    if (lv > 0.f) lc = __ldg(p.m_col + bh + krow) * LOG2E + __log2f(lv);
+                if (krow < n_cols) {
+                    const float lv = __ldg(p.l_col + bh_c + krow);
+                    if (lv > 0.f) lc = __ldg(p.m_col + bh_c + krow) * LOG2E + __log2f(lv);
                 }
                 sColL[tid] = lc;
                 if (mask_b) {
                     uint32_t w[4] = {0, 0, 0, 0};
-                    if (jrow < n_keys) {
+                    if (jrow < n_rows) {
                         for (int t = 0; t < TILE; ++t) {
                             const int v = kb * TILE + t;
-                            if (v < n_keys && mask_b[static_cast<size_t>(jrow) * N + v] != 0 &&
+                            if (v < n_cols && mask_b[static_cast<size_t>(jrow) * N + v] != 0 &&
                                 mask_b[static_cast<size_t>(v) * N + jrow] != 0)
                                 w[t >> 5] |= 1u << (t & 31);
                         }
@@ -211,7 +217,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                 // visibility of this tile's rows and cols from anchor a
                 {
                     const int krow = kb * TILE + tid;
-                    bool vr = jrow < n_keys, vc = krow < n_keys;
+                    bool vr = jrow < n_rows, vc = krow < n_cols;
                     if (mask_b && SC) {
                         // the anchors of the two softmaxes are the row and the col: each must see a
                         if (vr) vr = mask_b[static_cast<size_t>(jrow) * N + a] != 0;
@@ -236,7 +242,7 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                 // --- Hadamard tile from the anchor row -----------------------------------------
                 {
                     uint32_t q[DW];
-                    load_row_padded<DP>(gA, a, N, D, q);
+                    load_row_padded<DP>(gA, a, p.NA, D, q);
 #pragma unroll
                     for (int c = 0; c < CH; ++c) {
                         uint4 o;

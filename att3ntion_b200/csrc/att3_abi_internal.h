@@ -52,6 +52,16 @@ int make_head_tensor_map(CUtensorMap* out, const void* base, int B, int H, int N
 int dense_gather_forward(const void* A, const void* Rw, const void* C, const void* Vrow, const void* Vcol,
                          const uint8_t* mask, void* Y, float* m, float* l, int B, int H, int N, int D, int n_valid,
                          cudaStream_t st);
+// The same with a length and a valid count per index axis (anchor, rows, cols; valid 0 = all): the three axes of the
+// reference's gather (cuda/forward.cu:1436-1452).  A mask needs equal lengths.
+struct Axis { int n; int valid; };
+int dense_gather_forward_axes(const void* A, const void* Rw, const void* C, const void* Vrow, const void* Vcol,
+                              const uint8_t* mask, void* Y, float* m, float* l, int B, int H, int D, Axis a, Axis r,
+                              Axis c, cudaStream_t st);
+int dense_gather_backward_side_axes(const void* A, const void* dY, const void* Y, const float* m, const float* l,
+                                    const void* Ka, const void* Va, const void* Kb, const void* Vb,
+                                    const uint8_t* mask, float* dKb, float* dVb, float* dA_part, int B, int H, int D,
+                                    Axis a, Axis own, Axis oth, cudaStream_t st, float* chunk_scratch = nullptr);
 // Backward for one key side: adds d(Kb), d(Vb) into FP32 planes; if dA_part is non-null also
 // accumulates the anchor gradient into one zero-filled partial plane per 128-key tile of the own side.
 // chunk_scratch: optional two planes of scratch; with it, short sequences split their anchors over two CTAs

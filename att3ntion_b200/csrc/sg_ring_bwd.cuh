@@ -794,7 +794,13 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     for (int t = 0; t < 32; t += 2) {
                         float d0, d1;
                         unpair_f32(add_f32x2(pair_b32(dp[t], dp[t + 1]), dltp), d0, d1);
-                        pk[t >> 1] = single ? 0u : mul_bf16x2(pk[t >> 1], pack_bf16x2(d0, d1));
+                        if (EXT && x_precise) {
+                            // compensated mode: the product in FP32, one rounding to BF16
+                            const float2 pf = unpack_bf16x2(pk[t >> 1]);
+                            pk[t >> 1] = single ? 0u : pack_bf16x2(pf.x * d0, pf.y * d1);
+                        } else {
+                            pk[t >> 1] = single ? 0u : mul_bf16x2(pk[t >> 1], pack_bf16x2(d0, d1));
+                        }
                     }
                     tmem_st16(tA + 32 + cc * 16, pk);
                 }
@@ -810,50 +816,101 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_bwd_kernel(const BwdP
                     float* red = sRed + (n & 1) * 4 * D;
 #pragma unroll 1
                     for (int c = 0; c < NC; ++c) {
-                        // two rounds of 16 columns keep the live set small (this role runs on 80 registers).  W is
-                        // rounded to BF16 pairs and multiplied by the packed Kb words as they are: two instructions a pair
-                        uint32_t w[16];
-                        {
-                            uint32_t u[16];
-                            tmem_ld16(tB + ch * HD + c * 32, u);
-                            tmem_wait_ld();
+                        float s;
+                        if (EXT && x_precise) {
+                            // compensated mode: FP32 products and an FP32 lane sum
+                            float va[16], vb[16];
+                            {
+                                uint32_t u[16];
+                                tmem_ld16(tB + ch * HD + c * 32, u);
+                                tmem_wait_ld();
 #pragma unroll
-                            for (int q = 0; q < 2; ++q) {
-                                const uint4 kb = *reinterpret_cast<const uint4*>(
-                                    sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + q));
-                                const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
+                                for (int q = 0; q < 2; ++q) {
+                                    const uint4 kb = *reinterpret_cast<const uint4*>(
+                                        sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + q));
+                                    const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
 #pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    w[q * 4 + e] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[q * 8 + 2 * e]),
-                                                                          __uint_as_float(u[q * 8 + 2 * e + 1])), w4[e]);
+                                    for (int e = 0; e < 4; ++e) {
+                                        const float2 kf = unpack_bf16x2(w4[e]);
+                                        va[q * 8 + 2 * e] = kf.x * __uint_as_float(u[q * 8 + 2 * e]);
+                                        va[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[q * 8 + 2 * e + 1]);
+                                    }
+                                }
                             }
-                        }
-                        {
-                            uint32_t u[16];
-                            tmem_ld16(tB + ch * HD + c * 32 + 16, u);
-                            tmem_wait_ld();
-                            if (c == NC - 1) {
-                                // W is in registers: the next head's scores may land on these columns
-                                tc_fence_before();
-                                warp_arrive(&bars[PB_B_FREE], lane);
+                            {
+                                uint32_t u[16];
+                                tmem_ld16(tB + ch * HD + c * 32 + 16, u);
+                                tmem_wait_ld();
+                                if (c == NC - 1) {
+                                    // W is in registers: the next head's scores may land on these columns
+                                    tc_fence_before();
+                                    warp_arrive(&bars[PB_B_FREE], lane);
+                                }
+#pragma unroll
+                                for (int q = 0; q < 2; ++q) {
+                                    const uint4 kb = *reinterpret_cast<const uint4*>(
+                                        sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + 2 + q));
+                                    const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) {
+                                        const float2 kf = unpack_bf16x2(w4[e]);
+                                        vb[q * 8 + 2 * e] = kf.x * __uint_as_float(u[q * 8 + 2 * e]);
+                                        vb[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[q * 8 + 2 * e + 1]);
+                                    }
+                                }
                             }
+                            // the query's last head: this warp is done with the Kb rows of the ring
+                            if (c == NC - 1 && hh == G - 1) {
+                                warp_arrive(&bars[PB_RING_FREE], lane);
+                                ring_arrived = true;
+                            }
+                            s = warp_transpose_sum_2x16(va, vb, lane);
+                        } else {
+                            // two rounds of 16 columns keep the live set small (this role runs on 80 registers).  W is
+                            // rounded to BF16 pairs and multiplied by the packed Kb words as they are: two instructions a pair
+                            uint32_t w[16];
+                            {
+                                uint32_t u[16];
+                                tmem_ld16(tB + ch * HD + c * 32, u);
+                                tmem_wait_ld();
 #pragma unroll
-                            for (int q = 0; q < 2; ++q) {
-                                const uint4 kb = *reinterpret_cast<const uint4*>(
-                                    sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + 2 + q));
-                                const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
+                                for (int q = 0; q < 2; ++q) {
+                                    const uint4 kb = *reinterpret_cast<const uint4*>(
+                                        sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + q));
+                                    const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
 #pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    w[8 + q * 4 + e] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[q * 8 + 2 * e]),
+                                    for (int e = 0; e < 4; ++e)
+                                        w[q * 4 + e] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[q * 8 + 2 * e]),
                                                                               __uint_as_float(u[q * 8 + 2 * e + 1])), w4[e]);
+                                }
                             }
+                            {
+                                uint32_t u[16];
+                                tmem_ld16(tB + ch * HD + c * 32 + 16, u);
+                                tmem_wait_ld();
+                                if (c == NC - 1) {
+                                    // W is in registers: the next head's scores may land on these columns
+                                    tc_fence_before();
+                                    warp_arrive(&bars[PB_B_FREE], lane);
+                                }
+#pragma unroll
+                                for (int q = 0; q < 2; ++q) {
+                                    const uint4 kb = *reinterpret_cast<const uint4*>(
+                                        sKb + sw128_offset<RING>(slot, ch * (HD / 8) + c * 4 + 2 + q));
+                                    const uint32_t w4[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e)
+                                        w[8 + q * 4 + e] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[q * 8 + 2 * e]),
+                                                                                  __uint_as_float(u[q * 8 + 2 * e + 1])), w4[e]);
+                                }
+                            }
+                            // the query's last head: this warp is done with the Kb rows of the ring
+                            if (c == NC - 1 && hh == G - 1) {
+                                warp_arrive(&bars[PB_RING_FREE], lane);
+                                ring_arrived = true;
+                            }
+                            s = warp_transpose_sum_words(w, lane);
                         }
-                        // the query's last head: this warp is done with the Kb rows of the ring
-                        if (c == NC - 1 && hh == G - 1) {
-                            warp_arrive(&bars[PB_RING_FREE], lane);
-                            ring_arrived = true;
-                        }
-                        const float s = warp_transpose_sum_words(w, lane);
                         red[(warp & 3) * D + ch * HD + c * 32 + lane] = s;
                     }
                     warp_arrive(&bars[PB_E_SYNC2], lane);

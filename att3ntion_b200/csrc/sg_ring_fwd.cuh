@@ -487,35 +487,68 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_ring_fwd_kernel(const __gr
             constexpr int NC = HD / 32;
 #pragma unroll
             for (int c = 0; c < NC; ++c) {      // unrolled: rVr must be indexed with constants to stay in registers
-                // two rounds of 16 columns keep the live set small.  U is rounded to BF16 pairs and multiplied by the
-                // packed Vr words as they are: two instructions a pair, and the lane sum below wants BF16 pairs anyway
-                uint32_t w[16];
-                {
-                    uint32_t u[16];
-                    tmem_ld16(tU + c * 32, u);
-                    tmem_wait_ld();
+                float s;
+                if (EXT && x_precise) {
+                    // compensated mode: FP32 products and an FP32 lane sum (no BF16 rounding between U and Y)
+                    float va[16], vb[16];
+                    {
+                        uint32_t u[16];
+                        tmem_ld16(tU + c * 32, u);
+                        tmem_wait_ld();
 #pragma unroll
-                    for (int t = 0; t < 16; t += 2)
-                        w[t >> 1] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
-                                               rVr[c * 16 + (t >> 1)]);
-                }
-                {
-                    uint32_t u[16];
-                    tmem_ld16(tU + c * 32 + 16, u);
-                    tmem_wait_ld();
-                    if (c == NC - 1) {
-                        // U is in registers: the product of head m + 2 may overwrite it
-                        tc_fence_before();
-                        warp_arrive(&bars[FB_U_FREE0 + ub], lane);
+                        for (int t = 0; t < 16; t += 2) {
+                            const float2 vr = unpack_bf16x2(rVr[c * 16 + (t >> 1)]);
+                            va[t] = vr.x * __uint_as_float(u[t]);
+                            va[t + 1] = vr.y * __uint_as_float(u[t + 1]);
+                        }
                     }
+                    {
+                        uint32_t u[16];
+                        tmem_ld16(tU + c * 32 + 16, u);
+                        tmem_wait_ld();
+                        if (c == NC - 1) {
+                            tc_fence_before();
+                            warp_arrive(&bars[FB_U_FREE0 + ub], lane);
+                        }
 #pragma unroll
-                    for (int t = 0; t < 16; t += 2)
-                        w[8 + (t >> 1)] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
-                                                     rVr[c * 16 + 8 + (t >> 1)]);
+                        for (int t = 0; t < 16; t += 2) {
+                            const float2 vr = unpack_bf16x2(rVr[c * 16 + 8 + (t >> 1)]);
+                            vb[t] = vr.x * __uint_as_float(u[t]);
+                            vb[t + 1] = vr.y * __uint_as_float(u[t + 1]);
+                        }
+                    }
+                    s = warp_transpose_sum_2x16(va, vb, lane);
+                } else {
+                    // two rounds of 16 columns keep the live set small.  U is rounded to BF16 pairs and multiplied by the
+                    // packed Vr words as they are: two instructions a pair, and the lane sum below wants BF16 pairs anyway
+                    uint32_t w[16];
+                    {
+                        uint32_t u[16];
+                        tmem_ld16(tU + c * 32, u);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int t = 0; t < 16; t += 2)
+                            w[t >> 1] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
+                                                   rVr[c * 16 + (t >> 1)]);
+                    }
+                    {
+                        uint32_t u[16];
+                        tmem_ld16(tU + c * 32 + 16, u);
+                        tmem_wait_ld();
+                        if (c == NC - 1) {
+                            // U is in registers: the product of head m + 2 may overwrite it
+                            tc_fence_before();
+                            warp_arrive(&bars[FB_U_FREE0 + ub], lane);
+                        }
+#pragma unroll
+                        for (int t = 0; t < 16; t += 2)
+                            w[8 + (t >> 1)] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
+                                                         rVr[c * 16 + 8 + (t >> 1)]);
+                    }
+                    // (a shared-memory transpose for this lane sum was measured slower: it competes with the
+                    //  MMA operand reads for shared-memory bandwidth)
+                    s = warp_transpose_sum_words(w, lane);
                 }
-                // (a shared-memory transpose for this lane sum was measured slower: it competes with the
-                //  MMA operand reads for shared-memory bandwidth)
-                const float s = warp_transpose_sum_words(w, lane);
                 red[quarter * (D + 4) + ch * HD + c * 32 + lane] = s;
             }
             float wl = l_half;

@@ -236,6 +236,37 @@ int att3_hg_backward(const void* gYq, const void* gYr, const void* gYs,
                      int B, int H, int N, int D, int n_valid, int gather_mode, int scatter,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same operator with a length per axis: Q, Vq*, Yq*, dQ ... are [B,H,I,D], the R tensors [B,H,J,D], the S
+ * tensors [B,H,K,D], the statistics [B,H,I], [B,H,J], [B,H,K] (cuda/forward.cu:1281-1285), and I_valid, J_valid,
+ * K_valid mark trailing padding per axis (cuda/forward.cu:1300-1302, cpp/cuda_bindings.cpp:143-177: each defaults
+ * to its length when <= 0 or larger).  As in the reference, a mask and the scatter outputs need I == J == K
+ * (cuda/forward.cu:1292, 1545); the scatter outputs also take one valid length for all three axes.  The reference's
+ * backward has no valid lengths (cpp/cuda_bindings.cpp:179-205: padded slots take part); the ones given here are
+ * applied like the forward's, pass zeros for the reference's behaviour.
+ * att3_hg_forward / att3_hg_backward are these with I = J = K = N and one valid length. */
+int att3_hg_forward_axes(const void* Q, const void* R, const void* S,
+                         const void* Vq1, const void* Vq2, const void* Vr1, const void* Vr2,
+                         const void* Vs1, const void* Vs2, const uint8_t* mask,
+                         void* Yq, void* Yr, void* Ys, void* Yq_, void* Yr_, void* Ys_,
+                         float* m_i, float* l_i, float* m_j, float* l_j, float* m_k, float* l_k,
+                         int B, int H, int I, int J, int K, int D, int I_valid, int J_valid, int K_valid,
+                         int gather_mode, int scatter, void* stream);
+
+size_t att3_hg_backward_axes_workspace_bytes(int B, int H, int I, int J, int K, int D);
+
+int att3_hg_backward_axes(const void* gYq, const void* gYr, const void* gYs,
+                          const void* gYq_, const void* gYr_, const void* gYs_,
+                          const void* Q, const void* R, const void* S,
+                          const void* Vq1, const void* Vq2, const void* Vr1, const void* Vr2,
+                          const void* Vs1, const void* Vs2,
+                          const void* Yq, const void* Yr, const void* Ys,
+                          const float* m_i, const float* l_i, const float* m_j, const float* l_j,
+                          const float* m_k, const float* l_k, const uint8_t* mask,
+                          void* dQ, void* dR, void* dS, void* dVq1, void* dVq2, void* dVr1, void* dVr2,
+                          void* dVs1, void* dVs2,
+                          int B, int H, int I, int J, int K, int D, int I_valid, int J_valid, int K_valid,
+                          int gather_mode, int scatter, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------- *
  * Host-side helpers (no GPU needed).
  * ------------------------------------------------------------------------- */

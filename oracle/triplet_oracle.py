@@ -183,35 +183,46 @@ def _chunk_dense(Q, R, S, Vr, Vs, vis, dY):
 
 
 def hypergraph_dense(Q, R, S, Vq1, Vq2, Vr1, Vr2, Vs1, Vs2, mask=None, gather_mode=0, scatter=True,
-                     dtype=torch.float64):
+                     dtype=torch.float64, valid=None):
     """Three anchored softmaxes of the same score cube (cpp/torch_reference.cpp:31-54).
 
     mask [B,N,N] bool: a cell of anchor a is live iff both non-anchor indices are
     visible from a (tests/test_tc_paths.py:218-238).  A fully masked anchor yields
     zeros.  Returns (Y_q, Y_r, Y_s, Y_q_, Y_r_, Y_s_) and the three LSE tensors.
     Differentiable: callers obtain the nine gradients with torch.autograd.
+
+    The three axes may have different lengths I, J, K (no mask then, cuda/forward.cu:1281-1296).
+    valid = (I_valid, J_valid, K_valid): entries of an axis at or past its valid length are padding
+    that stays out of every softmax in which the axis is a key axis (cuda/forward.cu:1300-1302, 1446-1452).
     """
     Q, R, S, Vq1, Vq2, Vr1, Vr2, Vs1, Vs2 = (t.to(dtype) for t in (Q, R, S, Vq1, Vq2, Vr1, Vr2, Vs1, Vs2))
     D = Q.shape[-1]
     x = torch.einsum("bhid,bhjd,bhkd->bhijk", Q, R, S) / math.sqrt(D)
 
-    def anchored(xp):
-        # xp: [b,h,anchor,u,v]; mask[b,anchor,u] & mask[b,anchor,v]
+    lens = (Q.shape[2], R.shape[2], S.shape[2])
+    live = [torch.arange(n, device=Q.device) < (n if valid is None or not (0 < valid[a] <= n) else valid[a])
+            for a, n in enumerate(lens)]
+
+    def anchored(xp, u_axis, v_axis):
+        # xp: [b,h,anchor,u,v]; mask[b,anchor,u] & mask[b,anchor,v]; u, v below their axes' valid lengths
         if mask is not None:
             vp = (mask[:, :, :, None] & mask[:, :, None, :]).unsqueeze(1)
+            xp = xp.masked_fill(~vp, float("-inf"))
+        if valid is not None:
+            vp = live[u_axis][:, None] & live[v_axis][None, :]
             xp = xp.masked_fill(~vp, float("-inf"))
         flat = xp.flatten(3)
         lse = torch.logsumexp(flat, -1)
         p = torch.nan_to_num(torch.softmax(flat, -1), nan=0.0).reshape(xp.shape)
         return p, lse
 
-    Aq, lse_q = anchored(x)                                    # [i,j,k]
+    Aq, lse_q = anchored(x, 1, 2)                              # [i,j,k]
     Y_q = torch.einsum("bhijk,bhjd,bhkd->bhid", Aq, Vr1, Vs1)
-    zeros = torch.zeros_like(Y_q)
+    zq, zr, zs = torch.zeros_like(Q), torch.zeros_like(R), torch.zeros_like(S)
     if gather_mode == 1:
-        return (Y_q, zeros, zeros, zeros, zeros, zeros), (lse_q, None, None)
-    Ar_p, lse_r = anchored(x.permute(0, 1, 3, 2, 4))           # [j,i,k]
-    As_p, lse_s = anchored(x.permute(0, 1, 4, 2, 3))           # [k,i,j]
+        return (Y_q, zr, zs, zq, zr, zs), (lse_q, None, None)
+    Ar_p, lse_r = anchored(x.permute(0, 1, 3, 2, 4), 0, 2)     # [j,i,k]
+    As_p, lse_s = anchored(x.permute(0, 1, 4, 2, 3), 0, 1)     # [k,i,j]
     Ar = Ar_p.permute(0, 1, 3, 2, 4)
     As = As_p.permute(0, 1, 3, 4, 2)
     Y_r = torch.einsum("bhijk,bhid,bhkd->bhjd", Ar, Vq1, Vs1)
@@ -221,14 +232,14 @@ def hypergraph_dense(Q, R, S, Vq1, Vq2, Vr1, Vr2, Vs1, Vs2, mask=None, gather_mo
         Y_r_ = torch.einsum("bhijk,bhid,bhkd->bhjd", Aq * As, Vq2, Vs2)
         Y_s_ = torch.einsum("bhijk,bhid,bhjd->bhkd", Aq * Ar, Vq2, Vr2)
     else:
-        Y_q_ = Y_r_ = Y_s_ = zeros
+        Y_q_, Y_r_, Y_s_ = zq, zr, zs
     return (Y_q, Y_r, Y_s, Y_q_, Y_r_, Y_s_), (lse_q, lse_r, lse_s)
 
 
-def hypergraph_grads(inputs, cotangents, mask=None, gather_mode=0, scatter=True):
+def hypergraph_grads(inputs, cotangents, mask=None, gather_mode=0, scatter=True, valid=None):
     """Nine input gradients of hypergraph_dense under the six cotangents, by FP64 autograd."""
     leaves = [t.detach().double().requires_grad_(True) for t in inputs]
-    outs, _ = hypergraph_dense(*leaves, mask=mask, gather_mode=gather_mode, scatter=scatter)
+    outs, _ = hypergraph_dense(*leaves, mask=mask, gather_mode=gather_mode, scatter=scatter, valid=valid)
     total = None
     for o, g in zip(outs, cotangents):
         if g is None or not o.requires_grad:

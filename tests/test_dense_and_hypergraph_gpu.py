@@ -193,6 +193,89 @@ def test_three_gather_scatter_two_key_tiles(ck, masked):
     assert all(torch.equal(a, b) for a, b in zip(grads, grads2))
 
 
+def _axes_inputs(B, H, lens, D, seed, scatter_values=False):
+    """Nine inputs with one length per axis (Q-like [I], R-like [J], S-like [K]) and six cotangents; the second value
+    tensors are zero unless asked for, so that the scatter outputs vanish."""
+    gen = torch.Generator().manual_seed(seed)
+    I, J, K = lens
+    axis = {"Q": I, "Vq_1": I, "Vq_2": I, "R": J, "Vr_1": J, "Vr_2": J, "S": K, "Vs_1": K, "Vs_2": K}
+    ins = []
+    for k, n in enumerate(HG_NAMES):
+        t = (torch.randn(B, H, axis[n], D, generator=gen) * (0.5 if k < 3 else 1.0)).bfloat16()
+        if n.endswith("_2") and not scatter_values:
+            t = torch.zeros_like(t)
+        ins.append(t)
+    cot = [torch.randn(B, H, n, D, generator=gen).bfloat16() for n in (I, J, K)]
+    cot += [torch.zeros(B, H, n, D).bfloat16() for n in (I, J, K)]
+    return ins, cot
+
+
+@pytest.mark.parametrize("lens,D", [((48, 160, 32), 64), ((144, 16, 272), 128), ((32, 48, 16), 16)])
+def test_three_gather_unequal_axes_vs_oracle(ck, lens, D):
+    """I != J != K without a mask (cuda/forward.cu:1281-1296; every output has the length of its own axis): the three
+    gathers, their statistics and the nine gradients against the FP64 oracle, key axes spanning one, two and three
+    128-key tiles; bit-identical on a second call."""
+    B, H = 2, 2
+    ins, cot = _axes_inputs(B, H, lens, D, seed=31)
+    dins, dcot = [t.cuda() for t in ins], [c.cuda() for c in cot]
+    out = ck.forward(*dins, 0.0, -1, -1, -1, None, 0)
+    ref, lse = O.hypergraph_dense(*ins, scatter=False)
+    for k, what in enumerate(("Y_q", "Y_r", "Y_s")):
+        assert out[k].shape == ref[k].shape
+        hg_close(out[k], ref[k], 5e-2, 5e-2, what)
+        assert not out[3 + k].any()
+        O.check_lse(out[6 + 2 * k].cpu(), out[7 + 2 * k].cpu(), lse[k])
+    grads = ck.backward(*dcot, *dins, *out[6:12], 0.0, None, out[0], out[1], out[2])
+    ck.device_status()
+    gref = O.hypergraph_grads(ins, cot, scatter=False)
+    for k, n in enumerate(HG_NAMES):
+        assert grads[k].shape == ins[k].shape
+        hg_close(grads[k], gref[k], 5e-2, 1e-1 if k < 3 else 2e-2, f"d{n}")
+    out2 = ck.forward(*dins, 0.0, -1, -1, -1, None, 0)
+    grads2 = ck.backward(*dcot, *dins, *out2[6:12], 0.0, None, out2[0], out2[1], out2[2])
+    assert all(torch.equal(a, b) for a, b in zip(out[:3], out2[:3]))
+    assert all(torch.equal(a, b) for a, b in zip(grads, grads2))
+
+
+@pytest.mark.parametrize("lens,valid", [((160, 160, 160), (100, 140, 37)), ((48, 160, 32), (48, 129, 5))])
+def test_three_gather_axis_valid_lengths(ck, lens, valid):
+    """I_valid, J_valid, K_valid (cuda/forward.cu:1300-1302, 1446-1452): entries of an axis past its valid length stay
+    out of every softmax in which that axis is a key axis; all anchors are still computed.  Forward against the
+    oracle, and unchanged when the padded entries are overwritten."""
+    B, H, D = 1, 2, 64
+    ins, _ = _axes_inputs(B, H, lens, D, seed=37)
+    dins = [t.cuda() for t in ins]
+    out = ck.forward(*dins, 0.0, *valid, None, 0)
+    ck.device_status()
+    ref, lse = O.hypergraph_dense(*ins, scatter=False, valid=valid)
+    for k, what in enumerate(("Y_q", "Y_r", "Y_s")):
+        hg_close(out[k], ref[k], 5e-2, 5e-2, what)
+        O.check_lse(out[6 + 2 * k].cpu(), out[7 + 2 * k].cpu(), lse[k])
+    # the padded key rows are never read as keys: Y_q depends on R, Vr_1 below J_valid and S, Vs_1 below K_valid only
+    poked = [t.clone() for t in dins]
+    for idx, axis in ((1, 1), (5, 1), (2, 2), (7, 2)):
+        poked[idx][:, :, valid[axis]:] = 3.0
+    out_p = ck.forward(*poked, 0.0, *valid, None, 0)
+    assert torch.equal(out[0], out_p[0]) and torch.equal(out[6], out_p[6]) and torch.equal(out[7], out_p[7])
+
+
+def test_three_gather_axes_rejections(ck):
+    """A mask and the scatter outputs need I == J == K, as in the reference (cuda/forward.cu:1292, 1545)."""
+    B, H, D = 1, 1, 64
+    ins, _ = _axes_inputs(B, H, (32, 48, 32), D, seed=41)
+    dins = [t.cuda() for t in ins]
+    mask = torch.ones(B, 32, 32, dtype=torch.bool, device="cuda")
+    with pytest.raises(RuntimeError, match="equal shapes"):
+        ck.forward(*dins, 0.0, -1, -1, -1, mask, 0)
+    ins2, _ = _axes_inputs(B, H, (32, 48, 32), D, seed=41, scatter_values=True)
+    with pytest.raises(RuntimeError, match="Scatter requires I == J == K"):
+        ck.forward(*[t.cuda() for t in ins2], 0.0, -1, -1, -1, None, 0)
+    bad = list(dins)
+    bad[3] = bad[3][:, :, :16].contiguous()          # Vq_1 shorter than Q
+    with pytest.raises(RuntimeError, match="Vq_1"):
+        ck.forward(*bad, 0.0, -1, -1, -1, None, 0)
+
+
 @pytest.mark.parametrize("name", golden_files("hg_masked_"))
 def test_three_gather_masked(ck, name):
     g = load_golden(name)
