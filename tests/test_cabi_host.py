@@ -116,3 +116,25 @@ def test_shim_rejections_need_no_gpu():
     ck.sg_set_config({"fwd_warps": 0})
     assert ck.tc_set_enabled(True, True) == (True, True)
     assert set(ck.tc_launches()) >= {"forward", "backward", "sg_forward", "sg_backward"}
+
+
+def test_three_gather_axes_are_checked_before_any_device_work():
+    """Per-axis lengths of the three-gather operator: every axis a multiple of 16, a mask and the scatter outputs
+    only with I == J == K (the reference's checks, cuda/forward.cu:1292, 1545)."""
+    lib = _cabi.lib
+    nul = [None] * 22
+    one = C.c_void_p(16)          # a non-null mask pointer; the call is rejected before anything reads it
+
+    def fwd(mask, I, J, K, scatter=0, D=64):
+        args = list(nul)
+        args[9] = mask
+        return lib.att3_hg_forward_axes(*args, 1, 1, I, J, K, D, 0, 0, 0, 0, scatter, None)
+
+    assert fwd(None, 32, 40, 32) == _cabi.ERR_INVALID and "multiple of 16" in _cabi.last_error()
+    assert fwd(one, 32, 48, 32) == _cabi.ERR_INVALID and "mask requires I == J == K" in _cabi.last_error()
+    assert fwd(None, 32, 48, 32, scatter=1) == _cabi.ERR_INVALID and "scatter requires I == J == K" in _cabi.last_error()
+    assert fwd(None, 32, 48, 64, D=48) == _cabi.ERR_INVALID and "head dim" in _cabi.last_error()
+    assert fwd(None, 32, 48, 64) == _cabi.ERR_INVALID and "null" in _cabi.last_error()
+    # workspace: planes sized for the longest axis
+    n = lib.att3_hg_backward_axes_workspace_bytes(2, 2, 32, 160, 48, 64)
+    assert n == lib.att3_hg_backward_workspace_bytes(2, 2, 160, 64) > 0
