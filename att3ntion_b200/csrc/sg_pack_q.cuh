@@ -102,24 +102,27 @@ struct QSmem {
     static constexpr int ALLOC = BYTES + 1024;
 };
 
-// Sum over the 16 lanes of each half-warp of 32 per-lane values given as two halves (va: values 0-15,
-// vb: values 16-31).  Lane L ends up with the half-warp totals of value (L & 15) in r0 and of value
-// 16 + (L & 15) in r1.  30 shuffles.
-__device__ __forceinline__ void halfwarp_transpose_sum_2x16(float (&va)[16], float (&vb)[16], int lane, float& r0,
-                                                            float& r1) {
+// Sum over the 16 lanes of each half-warp of 32 per-lane values given as 16 BF16 pairs (w[k] = values 2k, 2k + 1).
+// Four exchange stages on the packed pairs (the partial sums are rounded to BF16 at each, like the first four stages
+// of warp_transpose_sum_words); lane L ends up with the half-warp totals of values 2 (L & 15) and 2 (L & 15) + 1.
+__device__ __forceinline__ void halfwarp_transpose_sum_words(uint32_t (&w)[16], int lane, float& r0, float& r1) {
 #pragma unroll
     for (int o = 8; o >= 1; o >>= 1) {
         const bool up = (lane & o) != 0;
 #pragma unroll
         for (int k = 0; k < o; ++k) {
-            const float sa = up ? va[k] : va[k + o], ka = up ? va[k + o] : va[k];
-            const float sb = up ? vb[k] : vb[k + o], kb = up ? vb[k + o] : vb[k];
-            va[k] = ka + __shfl_xor_sync(0xFFFFFFFFu, sa, o);
-            vb[k] = kb + __shfl_xor_sync(0xFFFFFFFFu, sb, o);
+            const uint32_t send = up ? w[k] : w[k + o];
+            const uint32_t keep = up ? w[k + o] : w[k];
+            const uint32_t got = __shfl_xor_sync(0xFFFFFFFFu, send, o);
+            __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&keep);
+            __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&got);
+            __nv_bfloat162 c = __hadd2(a, b);
+            w[k] = *reinterpret_cast<uint32_t*>(&c);
         }
     }
-    r0 = va[0];
-    r1 = vb[0];
+    const float2 v = unpack_bf16x2(w[0]);
+    r0 = v.x;
+    r1 = v.y;
 }
 
 // Visibility of the 128 column slots for query i (window and optional mask row), as four ballot words;
@@ -591,66 +594,38 @@ __global__ void __launch_bounds__(PIPE_THREADS, 1) sg_pack_q_kernel(const __grid
             constexpr int NC = HD / 32;
 #pragma unroll
             for (int c = 0; c < NC; ++c) {      // unrolled: rVr must be indexed with constants to stay in registers
+                // U is rounded to BF16 pairs and multiplied by the packed Vr words as they are: two instructions a pair,
+                // and the lane sums work on BF16 pairs anyway
+                uint32_t w[16];
+                {
+                    uint32_t u[16];
+                    tmem_ld16(tU + c * 32, u);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int t = 0; t < 16; t += 2)
+                        w[t >> 1] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
+                                               rVr[c * 16 + (t >> 1)]);
+                }
+                {
+                    uint32_t u[16];
+                    tmem_ld16(tU + c * 32 + 16, u);
+                    tmem_wait_ld();
+                    if (c == NC - 1) {
+                        // U is in registers: a later product may overwrite it
+                        tc_fence_before();
+                        warp_arrive(&bars[QB_U_FREE0 + ub], lane);
+                    }
+#pragma unroll
+                    for (int t = 0; t < 16; t += 2)
+                        w[8 + (t >> 1)] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
+                                                     rVr[c * 16 + 8 + (t >> 1)]);
+                }
                 if (W == 16) {
-                    float va[16], vb[16];
-                    {
-                        uint32_t u[16];
-                        tmem_ld16(tU + c * 32, u);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int t = 0; t < 16; t += 2) {
-                            const float2 vr = unpack_bf16x2(rVr[c * 16 + (t >> 1)]);
-                            va[t] = vr.x * __uint_as_float(u[t]);
-                            va[t + 1] = vr.y * __uint_as_float(u[t + 1]);
-                        }
-                    }
-                    {
-                        uint32_t u[16];
-                        tmem_ld16(tU + c * 32 + 16, u);
-                        tmem_wait_ld();
-                        if (c == NC - 1) {
-                            // U is in registers: a later product may overwrite it
-                            tc_fence_before();
-                            warp_arrive(&bars[QB_U_FREE0 + ub], lane);
-                        }
-#pragma unroll
-                        for (int t = 0; t < 16; t += 2) {
-                            const float2 vr = unpack_bf16x2(rVr[c * 16 + 8 + (t >> 1)]);
-                            vb[t] = vr.x * __uint_as_float(u[t]);
-                            vb[t + 1] = vr.y * __uint_as_float(u[t + 1]);
-                        }
-                    }
                     float r0, r1;
-                    halfwarp_transpose_sum_2x16(va, vb, lane, r0, r1);
-                    red[unit * (D + 4) + ch * HD + c * 32 + (lane & 15)] = r0;
-                    red[unit * (D + 4) + ch * HD + c * 32 + 16 + (lane & 15)] = r1;
+                    halfwarp_transpose_sum_words(w, lane, r0, r1);
+                    red[unit * (D + 4) + ch * HD + c * 32 + 2 * (lane & 15)] = r0;
+                    red[unit * (D + 4) + ch * HD + c * 32 + 2 * (lane & 15) + 1] = r1;
                 } else {
-                    // U is rounded to BF16 pairs and multiplied by the packed Vr words as they are: two instructions
-                    // a pair, and the lane sum works on BF16 pairs anyway
-                    uint32_t w[16];
-                    {
-                        uint32_t u[16];
-                        tmem_ld16(tU + c * 32, u);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int t = 0; t < 16; t += 2)
-                            w[t >> 1] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
-                                                   rVr[c * 16 + (t >> 1)]);
-                    }
-                    {
-                        uint32_t u[16];
-                        tmem_ld16(tU + c * 32 + 16, u);
-                        tmem_wait_ld();
-                        if (c == NC - 1) {
-                            // U is in registers: a later product may overwrite it
-                            tc_fence_before();
-                            warp_arrive(&bars[QB_U_FREE0 + ub], lane);
-                        }
-#pragma unroll
-                        for (int t = 0; t < 16; t += 2)
-                            w[8 + (t >> 1)] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[t]), __uint_as_float(u[t + 1])),
-                                                         rVr[c * 16 + 8 + (t >> 1)]);
-                    }
                     const float s = warp_transpose_sum_words(w, lane);
                     red[unit * (D + 4) + ch * HD + c * 32 + lane] = s;
                 }
