@@ -280,6 +280,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
                 for (int o = 16; o >= 1; o >>= 1) delta += __shfl_xor_sync(0xFFFFFFFFu, delta, o);
             }
             const float lse2 = m_a * LOG2E + __log2f(l_a);
+            const uint64_t c2p = pair_f32(c2, c2), lsep = pair_f32(-lse2, -lse2), dltp = pair_f32(-delta, -delta);
 
             // --- Hadamard tiles (this thread: half a row) -----------------------------------------
 #pragma unroll
@@ -361,12 +362,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
                 } else {
 #pragma unroll
                     for (int t = 0; t < 32; t += 2) {
-                        float p0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2, -lse2));
-                        float p1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2, -lse2));
+                        // packed FP32 arithmetic: two columns an instruction
+                        float a0, a1;
+                        unpair_f32(fma_f32x2(pair_b32(x[t], x[t + 1]), c2p, lsep), a0, a1);
+                        float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
                         if (!((cw >> t) & 1u)) p0 = 0.f;
                         if (!((cw >> (t + 1)) & 1u)) p1 = 0.f;
-                        const float g0 = p0 * (__uint_as_float(dp[t]) - delta);
-                        const float g1 = p1 * (__uint_as_float(dp[t + 1]) - delta);
+                        float g0, g1;
+                        unpair_f32(mul_f32x2(pair_f32(p0, p1), add_f32x2(pair_b32(dp[t], dp[t + 1]), dltp)), g0, g1);
                         pk[t >> 1] = pack_bf16x2(p0, p1);
                         gk[t >> 1] = pack_bf16x2(g0, g1);
                     }
@@ -410,23 +413,22 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) ag_dense_bwd_kernel(const BwdP
                 const uint32_t wcol = (DP == 128) ? (half ? C_W1 : C_W0) : (C_W0 + half * 32);
 #pragma unroll
                 for (int c = 0; c < HD / 32; ++c) {
-                    uint32_t u[32];
-                    float v[32];
+                    uint32_t u[32], w[16];
                     tmem_ld32(tl + wcol + c * 32, u);
                     tmem_wait_ld();
+                    // W rounded to BF16 pairs and multiplied by the packed Kb words as they are; the lane sum works on
+                    // pairs (as in the windowed kernels)
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const uint4 kbv =
                             *reinterpret_cast<const uint4*>(sKb + sw128_offset<TILE>(slot, half * HCH + c * 4 + q));
                         const uint32_t w4[4] = {kbv.x, kbv.y, kbv.z, kbv.w};
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 kf = unpack_bf16x2(w4[e]);
-                            v[q * 8 + 2 * e] = kf.x * __uint_as_float(u[q * 8 + 2 * e]);
-                            v[q * 8 + 2 * e + 1] = kf.y * __uint_as_float(u[q * 8 + 2 * e + 1]);
-                        }
+                        for (int e = 0; e < 4; ++e)
+                            w[q * 4 + e] = mul_bf16x2(pack_bf16x2(__uint_as_float(u[q * 8 + 2 * e]),
+                                                                  __uint_as_float(u[q * 8 + 2 * e + 1])), w4[e]);
                     }
-                    const float s = warp_transpose_sum(v, lane);
+                    const float s = sgring::warp_transpose_sum_words(w, lane);
                     sRed[(warp & 3) * DP + half * HD + c * 32 + lane] = s;
                 }
                 tc_fence_before();

@@ -303,12 +303,32 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                         tmem_ld32(tX + c * 32, x);
                         tmem_wait_ld();
                         const uint32_t vw = my_vis ? (c == 0 ? vc0 : c == 1 ? vc1 : c == 2 ? vc2 : vc3) : 0u;
+                        // four independent running maxima instead of one chain of 32 dependent operations
+                        float m0 = m_row, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+                        if (vw == 0xFFFFFFFFu) {
 #pragma unroll
-                        for (int t = 0; t < 32; ++t)
-                            if ((vw >> t) & 1u) m_row = fmaxf(m_row, __uint_as_float(x[t]));
+                            for (int t = 0; t < 32; t += 8) {
+                                m0 = fmaxf(m0, fmaxf(__uint_as_float(x[t]), __uint_as_float(x[t + 1])));
+                                m1 = fmaxf(m1, fmaxf(__uint_as_float(x[t + 2]), __uint_as_float(x[t + 3])));
+                                m2 = fmaxf(m2, fmaxf(__uint_as_float(x[t + 4]), __uint_as_float(x[t + 5])));
+                                m3 = fmaxf(m3, fmaxf(__uint_as_float(x[t + 6]), __uint_as_float(x[t + 7])));
+                            }
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < 32; t += 4) {
+                                if ((vw >> t) & 1u) m0 = fmaxf(m0, __uint_as_float(x[t]));
+                                if ((vw >> (t + 1)) & 1u) m1 = fmaxf(m1, __uint_as_float(x[t + 1]));
+                                if ((vw >> (t + 2)) & 1u) m2 = fmaxf(m2, __uint_as_float(x[t + 2]));
+                                if ((vw >> (t + 3)) & 1u) m3 = fmaxf(m3, __uint_as_float(x[t + 3]));
+                            }
+                        }
+                        m_row = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
                     }
                     const bool live = m_row > -INFINITY;
                     const float mc = (live ? m_row : 0.f) * c2;
+                    // packed FP32 arithmetic: one instruction for the exponents of two columns, one for their sums
+                    const uint64_t c2p = pair_f32(c2, c2), mcp = pair_f32(-mc, -mc);
+                    uint64_t ls0 = pair_f32(0.f, 0.f), ls1 = ls0;
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
                         tmem_ld32(tX + c * 32, x);
@@ -317,16 +337,23 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
                         uint32_t pk[16];
 #pragma unroll
                         for (int t = 0; t < 32; t += 2) {
-                            float e0 = fast_exp2(fmaf(__uint_as_float(x[t]), c2, -mc));
-                            float e1 = fast_exp2(fmaf(__uint_as_float(x[t + 1]), c2, -mc));
+                            float a0, a1;
+                            unpair_f32(fma_f32x2(pair_b32(x[t], x[t + 1]), c2p, mcp), a0, a1);
+                            float e0 = fast_exp2(a0), e1 = fast_exp2(a1);
                             if (!all_cols || !live) {
                                 if (!((vw >> t) & 1u)) e0 = 0.f;
                                 if (!((vw >> (t + 1)) & 1u)) e1 = 0.f;
                             }
-                            l_row += e0 + e1;
+                            if (t & 2) ls1 = add_f32x2(ls1, pair_f32(e0, e1));
+                            else ls0 = add_f32x2(ls0, pair_f32(e0, e1));
                             pk[t >> 1] = pack_bf16x2(e0, e1);
                         }
                         tmem_st16(tX + c * 16, pk);
+                    }
+                    {
+                        float s0, s1;
+                        unpair_f32(add_f32x2(ls0, ls1), s0, s1);
+                        l_row = s0 + s1;
                     }
                 }
                 tmem_wait_st();
@@ -353,19 +380,21 @@ __global__ void __launch_bounds__(NTHREADS, 2) ag_dense_fwd_kernel(const FwdPara
 
                 // --- collapse and merge into the anchor's running state ---------------------------
                 {
-                    uint32_t u[32];
-                    float v[32];
+                    uint32_t u[32], w[16];
+                    const uint64_t wp = pair_f32(w_row, w_row);
 #pragma unroll
                     for (int c = 0; c < DP / 32; ++c) {
                         tmem_ld32(tU + c * 32, u);
                         tmem_wait_ld();
+                        // the row's weight in FP32, then BF16 pairs: the product with the packed Vr words and the lane
+                        // sum work on pairs (as in the windowed kernels)
 #pragma unroll
                         for (int t = 0; t < 32; t += 2) {
-                            const float2 vr = unpack_bf16x2(rVr[c * 16 + (t >> 1)]);
-                            v[t] = w_row * vr.x * __uint_as_float(u[t]);
-                            v[t + 1] = w_row * vr.y * __uint_as_float(u[t + 1]);
+                            float a0, a1;
+                            unpair_f32(mul_f32x2(pair_b32(u[t], u[t + 1]), wp), a0, a1);
+                            w[t >> 1] = mul_bf16x2(pack_bf16x2(a0, a1), rVr[c * 16 + (t >> 1)]);
                         }
-                        const float s = warp_transpose_sum(v, lane);
+                        const float s = sgring::warp_transpose_sum_words(w, lane);
                         sRed[warp * (DP + 4) + c * 32 + lane] = s;
                     }
                     float wl = w_row * l_row;
